@@ -1,0 +1,132 @@
+/*
+ * laplace_cuda.h - C ABI of the B200 (sm_100a) back-end for Laplace's
+ * block-quantized weight matmul.
+ *
+ * The library replaces the box that Laplace calls its "SIMD back-end": the
+ * three function pointers of src/kernels.h:92-119 and the weight-registration
+ * hook of src/matmul.h:26. Every entry point below names the reference
+ * interface it stands in for. Signatures carry plain pointers and sizes only.
+ *
+ * Conventions (all taken from the reference, src/matmul_simd.cpp:432-544):
+ *   - a weight matrix is N contiguous rows of K elements in GGUF block format;
+ *     one row is rb = K / elems_per_block * bytes_per_block bytes;
+ *   - stacked experts are contiguous, N * rb bytes apart;
+ *   - x is fp32 row-major, y is fp32 row-major and is OVERWRITTEN;
+ *   - activations are quantized per 32 values to int8 with an fp32 scale
+ *     (amax / 127) before the dot products; block sums are exact integers.
+ *
+ * Return values: 0 = done; 1 = this weight type is not handled here (the
+ * reference's contract for "return false, caller falls back", kernels.h:94-96);
+ * negative = error (see enum). No entry point ever computes on the CPU.
+ *
+ * Threading: one caller at a time per process, like the reference
+ * (src/threadpool.h:236-257 has a single dispatch slot). Host-pointer entry
+ * points are synchronous. *_dev entry points only enqueue work on the given
+ * stream.
+ */
+#ifndef LAPLACE_CUDA_H
+#define LAPLACE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* GGML type ids, src/tensor.h:11-34 */
+#define LAPLACE_TYPE_Q4_0 2u
+#define LAPLACE_TYPE_Q8_0 8u
+#define LAPLACE_TYPE_Q4_K 12u
+#define LAPLACE_TYPE_Q6_K 14u
+
+enum {
+    LAPLACE_OK            = 0,
+    LAPLACE_UNSUPPORTED   = 1,   /* type not handled: caller may fall back */
+    LAPLACE_ERR_ARG       = -1,  /* null pointer, bad size, K not a block multiple */
+    LAPLACE_ERR_CUDA      = -2,  /* a CUDA call failed; text in laplace_cuda_last_error() */
+    LAPLACE_ERR_STATE     = -3,  /* not initialised / no CUDA device */
+    LAPLACE_ERR_TIMEOUT   = -4,  /* a bounded device-side wait gave up */
+    LAPLACE_ERR_LIMIT     = -5   /* request exceeds a documented size limit */
+};
+
+/* ---- lifetime ---------------------------------------------------------- */
+
+/* Binds the calling process to one GPU and creates the library's stream and
+ * scratch. Safe to call again with the same device. No reference counterpart
+ * (the reference has no device); called from the shim's static initialiser. */
+int  laplace_cuda_init(int device);
+void laplace_cuda_shutdown(void);
+int  laplace_cuda_sync(void);
+const char* laplace_cuda_last_error(void);
+int  laplace_cuda_sm_count(void);
+
+/* ---- weights ----------------------------------------------------------- */
+
+/* Replaces matmul_register_weights(base, size) (src/matmul.h:26, called once
+ * per model at src/main.cpp:705; Metal version src/metal.mm:552-584). Copies
+ * the whole mapped file region into HBM. Later calls that pass a weight
+ * pointer inside [base, base+size) resolve it by offset, as
+ * src/metal.mm:590-599 does. Weight pointers outside every registered region
+ * are uploaded for that call only. */
+int laplace_cuda_register_weights(const void* base, size_t size);
+int laplace_cuda_unregister_weights(const void* base);
+
+/* Row range [row_begin, row_end) of an N-row matrix as seen by rank `rank`
+ * of `world` when the matrix is split along N (no reference counterpart; the
+ * reference is single-device). */
+void laplace_cuda_nsplit(int N, int rank, int world, int* row_begin, int* row_end);
+
+/* ---- the three back-end entry points (host pointers) -------------------- */
+
+/* Replaces kernels::gemm_fn (src/kernels.h:97), implemented in the reference
+ * by gemm_simd (src/matmul_simd.cpp:480-496): y[m*N+j] = dot(x[m], row j). */
+int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type,
+                      float* y, int M, int K, int N);
+
+/* Replaces kernels::moe_gemv_fn (src/kernels.h:103; src/matmul_simd.cpp:506-522):
+ * y[k*N+j] = dot(x, row j of expert expert_idx[k]); one shared x of length K. */
+int laplace_cuda_moe_gemv(const float* x, const uint8_t* w, uint32_t type,
+                          const int* expert_idx, int n_experts,
+                          float* y, int K, int N);
+
+/* Replaces kernels::moe_gemv_multi_fn (src/kernels.h:110;
+ * src/matmul_simd.cpp:527-544): as above with x[k*K..] per selected expert. */
+int laplace_cuda_moe_gemv_multi(const float* x, const uint8_t* w, uint32_t type,
+                                const int* expert_idx, int n_experts,
+                                float* y, int K, int N);
+
+/* ---- device-pointer twins (all pointers are device memory) -------------- */
+
+/* `stream` is a cudaStream_t passed as void* (NULL = the library's stream). */
+int laplace_cuda_gemm_dev(const float* x, const uint8_t* w, uint32_t type,
+                          float* y, int M, int K, int N, void* stream);
+int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type,
+                              const int* expert_idx, int n_experts,
+                              float* y, int K, int N, int per_expert_x, void* stream);
+
+/* The activation quantizer on its own (src/matmul_simd.cpp:348-427).
+ * Outputs, all device memory, M rows: q int8 [M][K]; d fp32 [M][K/32];
+ * sum fp32 [M][K/32] (= d * (sum_lo + sum_hi)); isum int16 [M][K/32][2]
+ * (sum_lo, sum_hi). Any output pointer may be NULL. */
+int laplace_cuda_quantize_act_dev(const float* x, int M, int K,
+                                  int8_t* q, float* d, float* sum, int16_t* isum,
+                                  void* stream);
+
+/* Exact integer block sums, for parity tests on small shapes:
+ * out[(m*N+j)*per_row + b], per_row = K/32 (Q8_0, Q4_0, Q4_K) or K/16 (Q6_K);
+ * same definition as the per-block accumulations of
+ * src/matmul_simd.cpp:143-342. Device pointers. */
+int laplace_cuda_debug_blocksums_dev(const float* x, const uint8_t* w, uint32_t type,
+                                     int32_t* out, int M, int K, int N, void* stream);
+
+/* Which kernel family the last *_dev gemm call used: 1 = streaming dp4a GEMV,
+ * 2 = tensor-core GEMM. For tests and the benchmark's launch count. */
+int laplace_cuda_last_path(void);
+/* Kernel launches issued by this library since the counter was last reset. */
+long long laplace_cuda_launch_count(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,51 @@
+"""ctypes binding of liblaplace_cuda.so (declarations: include/laplace_cuda.h)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "liblaplace_cuda.so"
+
+# every symbol include/laplace_cuda.h declares: name -> (restype, argtypes)
+_vp, _i, _u32, _sz = C.c_void_p, C.c_int, C.c_uint32, C.c_size_t
+SYMBOLS = {
+    "laplace_cuda_init": (_i, [_i]),
+    "laplace_cuda_shutdown": (None, []),
+    "laplace_cuda_sync": (_i, []),
+    "laplace_cuda_last_error": (C.c_char_p, []),
+    "laplace_cuda_sm_count": (_i, []),
+    "laplace_cuda_register_weights": (_i, [_vp, _sz]),
+    "laplace_cuda_unregister_weights": (_i, [_vp]),
+    "laplace_cuda_nsplit": (None, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "laplace_cuda_gemm": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i]),
+    "laplace_cuda_moe_gemv": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i]),
+    "laplace_cuda_moe_gemv_multi": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i]),
+    "laplace_cuda_gemm_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
+    "laplace_cuda_moe_gemv_dev": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "laplace_cuda_quantize_act_dev": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "laplace_cuda_debug_blocksums_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
+    "laplace_cuda_last_path": (_i, []),
+    "laplace_cuda_launch_count": (C.c_longlong, [_i]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library and types every entry point. No CUDA call is made."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m laplace_b200.build` "
+            "(there is no CPU fallback for this path)"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,357 @@
+// lp_api.cu - the C ABI (include/laplace_cuda.h): process state, the weight
+// registry, host-pointer entry points that mirror Laplace's back-end function
+// pointers (src/kernels.h:92-119), and their device-pointer twins.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "lp_common.cuh"
+
+namespace lp {
+
+namespace {
+
+std::mutex g_mu;
+char g_err[512] = "";
+
+// A registered host region and its HBM copy (Laplace's Metal path keeps the
+// same kind of table, src/metal.mm:552-621).
+struct Region {
+    const uint8_t* host;
+    size_t         size;
+    uint8_t*       dev;
+};
+std::vector<Region> g_regions;
+
+// Growable device / pinned-host staging for the host-pointer entry points.
+struct Buf {
+    void*  p = nullptr;
+    size_t cap = 0;
+    bool   pinned = false;
+    int ensure(size_t n) {
+        if (n <= cap) return LAPLACE_OK;
+        release();
+        size_t want = n + n / 4 + 256;
+        cudaError_t e = pinned ? cudaMallocHost(&p, want) : cudaMalloc(&p, want);
+        if (e != cudaSuccess) { p = nullptr; return cuda_check(e, pinned ? "cudaMallocHost" : "cudaMalloc"); }
+        cap = want;
+        return LAPLACE_OK;
+    }
+    void release() {
+        if (p) { if (pinned) cudaFreeHost(p); else cudaFree(p); }
+        p = nullptr; cap = 0;
+    }
+};
+Buf g_dx, g_dy, g_dw, g_didx, g_dq;          // device
+Buf g_hx{nullptr, 0, true}, g_hy{nullptr, 0, true};   // pinned host
+
+Context g_ctx;
+
+}  // namespace
+
+Context& ctx() { return g_ctx; }
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_check(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return LAPLACE_OK;
+    return fail(LAPLACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+namespace {
+
+int require_ready() {
+    if (!g_ctx.ready) return fail(LAPLACE_ERR_STATE, "laplace_cuda_init has not been called (or found no GPU)");
+    return LAPLACE_OK;
+}
+
+// Reads and clears the device status word after the stream has drained.
+int check_device_status(cudaStream_t st) {
+    int h = 0;
+    cudaError_t e = cudaMemcpyAsync(&h, g_ctx.d_err, sizeof h, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_check(e, "reading device status");
+    if (h != DEV_OK) {
+        cudaMemsetAsync(g_ctx.d_err, 0, sizeof(int), st);
+        cudaStreamSynchronize(st);
+        return fail(LAPLACE_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", h);
+    }
+    return LAPLACE_OK;
+}
+
+const uint8_t* resolve_registered(const uint8_t* w, size_t bytes) {
+    for (const Region& r : g_regions)
+        if (w >= r.host && w + bytes <= r.host + r.size) return r.dev + (w - r.host);
+    return nullptr;
+}
+
+// Device address of `bytes` of weights at host pointer w: inside a registered
+// region by offset, otherwise uploaded for this call. Q4_K rows are read with
+// 16-byte vector loads, so a registered Q4_K tensor at an odd offset is
+// re-staged as well.
+int weights_on_device(const uint8_t* w, size_t bytes, uint32_t type, const uint8_t** out) {
+    const uint8_t* d = resolve_registered(w, bytes);
+    if (d && !(type == LAPLACE_TYPE_Q4_K && (reinterpret_cast<uintptr_t>(d) & 15))) { *out = d; return LAPLACE_OK; }
+    int rc = g_dw.ensure(bytes + 64);
+    if (rc) return rc;
+    rc = cuda_check(cudaMemcpyAsync(g_dw.p, w, bytes, cudaMemcpyHostToDevice, g_ctx.stream), "weight upload");
+    *out = static_cast<const uint8_t*>(g_dw.p);
+    return rc;
+}
+
+int dispatch_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N,
+                      cudaStream_t st) {
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm: null pointer");
+    if (M <= 0 || N <= 0 || K <= 0) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
+    // Small M: one streaming pass per group of up to 8 activation rows.
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        GemvArgs a{};
+        a.x = x + static_cast<size_t>(m0) * K;
+        a.w = w;
+        a.y = y + static_cast<size_t>(m0) * N;
+        a.type = type;
+        a.M = (M - m0) < 8 ? (M - m0) : 8;
+        a.K = K; a.N = N; a.n_seg = 1; a.per_seg_x = 0; a.expert_idx = nullptr;
+        int rc = launch_gemv_stream(a, st);
+        if (rc) return rc;
+    }
+    return LAPLACE_OK;
+}
+
+int dispatch_moe_dev(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx, int n_experts,
+                     float* y, int K, int N, int per_expert_x, cudaStream_t st) {
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w || !y || !expert_idx) return fail(LAPLACE_ERR_ARG, "moe_gemv: null pointer");
+    if (n_experts <= 0 || N <= 0 || K <= 0) return fail(LAPLACE_ERR_ARG, "moe_gemv: n_experts=%d K=%d N=%d", n_experts, K, N);
+    GemvArgs a{};
+    a.x = x; a.w = w; a.y = y; a.type = type; a.M = 1; a.K = K; a.N = N;
+    a.n_seg = n_experts; a.per_seg_x = per_expert_x ? 1 : 0; a.expert_idx = expert_idx;
+    return launch_gemv_stream(a, st);
+}
+
+int moe_host(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx, int n_experts,
+             float* y, int K, int N, int per_expert_x) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w || !y || !expert_idx) return fail(LAPLACE_ERR_ARG, "moe_gemv: null pointer");
+    if (n_experts <= 0 || N <= 0 || K <= 0 || K % block_elems(type))
+        return fail(LAPLACE_ERR_ARG, "moe_gemv: n_experts=%d K=%d N=%d", n_experts, K, N);
+    int max_e = 0;
+    for (int k = 0; k < n_experts; ++k) {
+        if (expert_idx[k] < 0) return fail(LAPLACE_ERR_ARG, "moe_gemv: negative expert index");
+        if (expert_idx[k] > max_e) max_e = expert_idx[k];
+    }
+    cudaStream_t st = g_ctx.stream;
+    const size_t per_expert = static_cast<size_t>(N) * row_bytes(type, K);
+    const uint8_t* dw = nullptr;
+    if ((rc = weights_on_device(w, per_expert * (static_cast<size_t>(max_e) + 1), type, &dw))) return rc;
+    const size_t xb = sizeof(float) * static_cast<size_t>(per_expert_x ? n_experts : 1) * K;
+    const size_t yb = sizeof(float) * static_cast<size_t>(n_experts) * N;
+    if ((rc = g_hx.ensure(xb + sizeof(int) * n_experts)) || (rc = g_hy.ensure(yb)) || (rc = g_dx.ensure(xb)) ||
+        (rc = g_dy.ensure(yb)) || (rc = g_didx.ensure(sizeof(int) * n_experts)))
+        return rc;
+    std::memcpy(g_hx.p, x, xb);
+    std::memcpy(static_cast<uint8_t*>(g_hx.p) + xb, expert_idx, sizeof(int) * n_experts);
+    cudaMemcpyAsync(g_dx.p, g_hx.p, xb, cudaMemcpyHostToDevice, st);
+    cudaMemcpyAsync(g_didx.p, static_cast<uint8_t*>(g_hx.p) + xb, sizeof(int) * n_experts, cudaMemcpyHostToDevice, st);
+    rc = dispatch_moe_dev(static_cast<const float*>(g_dx.p), dw, type, static_cast<const int*>(g_didx.p), n_experts,
+                          static_cast<float*>(g_dy.p), K, N, per_expert_x, st);
+    if (rc) return rc;
+    cudaMemcpyAsync(g_hy.p, g_dy.p, yb, cudaMemcpyDeviceToHost, st);
+    if ((rc = check_device_status(st))) return rc;
+    std::memcpy(y, g_hy.p, yb);
+    return LAPLACE_OK;
+}
+
+}  // namespace
+}  // namespace lp
+
+using namespace lp;
+
+extern "C" {
+
+int laplace_cuda_init(int device) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_ctx.ready && g_ctx.device == device) return LAPLACE_OK;
+    if (g_ctx.ready) return fail(LAPLACE_ERR_STATE, "already bound to device %d", g_ctx.device);
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0)
+        return fail(LAPLACE_ERR_STATE, "no CUDA device: %s", e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+    if (device < 0 || device >= n) return fail(LAPLACE_ERR_ARG, "device %d out of range (have %d)", device, n);
+    int rc;
+    if ((rc = cuda_check(cudaSetDevice(device), "cudaSetDevice"))) return rc;
+    cudaDeviceProp prop;
+    if ((rc = cuda_check(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties"))) return rc;
+    if (prop.major != 10)
+        return fail(LAPLACE_ERR_STATE, "device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+    g_ctx.device = device;
+    g_ctx.sm_count = prop.multiProcessorCount;
+    g_ctx.smem_optin = prop.sharedMemPerBlockOptin;
+    if ((rc = cuda_check(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking), "cudaStreamCreate"))) return rc;
+    if ((rc = cuda_check(cudaMalloc(&g_ctx.d_err, sizeof(int)), "cudaMalloc status"))) return rc;
+    if ((rc = cuda_check(cudaMemset(g_ctx.d_err, 0, sizeof(int)), "cudaMemset status"))) return rc;
+    g_ctx.ready = true;
+    return LAPLACE_OK;
+}
+
+void laplace_cuda_shutdown(void) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_ctx.ready) return;
+    cudaSetDevice(g_ctx.device);
+    cudaStreamSynchronize(g_ctx.stream);
+    for (Region& r : g_regions) cudaFree(r.dev);
+    g_regions.clear();
+    g_dx.release(); g_dy.release(); g_dw.release(); g_didx.release(); g_dq.release();
+    g_hx.release(); g_hy.release();
+    cudaFree(g_ctx.d_err);
+    cudaStreamDestroy(g_ctx.stream);
+    g_ctx = Context{};
+}
+
+int laplace_cuda_sync(void) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = require_ready();
+    if (rc) return rc;
+    return check_device_status(g_ctx.stream);
+}
+
+const char* laplace_cuda_last_error(void) { return g_err; }
+
+int laplace_cuda_sm_count(void) { return g_ctx.ready ? g_ctx.sm_count : 0; }
+
+int laplace_cuda_last_path(void) { return g_ctx.last_path; }
+
+long long laplace_cuda_launch_count(int reset) {
+    long long v = g_ctx.launches;
+    if (reset) g_ctx.launches = 0;
+    return v;
+}
+
+int laplace_cuda_register_weights(const void* base, size_t size) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!base || !size) return fail(LAPLACE_ERR_ARG, "register_weights: empty region");
+    const uint8_t* h = static_cast<const uint8_t*>(base);
+    for (Region& r : g_regions)
+        if (r.host == h) {                      // same base registered again: refresh the copy
+            if (r.size != size) return fail(LAPLACE_ERR_ARG, "register_weights: region re-registered with another size");
+            return cuda_check(cudaMemcpy(r.dev, h, size, cudaMemcpyHostToDevice), "weight upload");
+        }
+    uint8_t* d = nullptr;
+    if ((rc = cuda_check(cudaMalloc(&d, size + 64), "cudaMalloc weights"))) return rc;   // slack: 16-byte read-ahead
+    if ((rc = cuda_check(cudaMemcpy(d, h, size, cudaMemcpyHostToDevice), "weight upload"))) { cudaFree(d); return rc; }
+    cudaMemset(d + size, 0, 64);
+    g_regions.push_back(Region{h, size, d});
+    return LAPLACE_OK;
+}
+
+int laplace_cuda_unregister_weights(const void* base) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = require_ready();
+    if (rc) return rc;
+    for (size_t i = 0; i < g_regions.size(); ++i)
+        if (g_regions[i].host == base) {
+            cudaStreamSynchronize(g_ctx.stream);
+            cudaFree(g_regions[i].dev);
+            g_regions.erase(g_regions.begin() + i);
+            return LAPLACE_OK;
+        }
+    return fail(LAPLACE_ERR_ARG, "unregister_weights: region not registered");
+}
+
+void laplace_cuda_nsplit(int N, int rank, int world, int* row_begin, int* row_end) {
+    if (world < 1) world = 1;
+    if (rank < 0) rank = 0;
+    if (rank >= world) rank = world - 1;
+    // contiguous ranges, sizes differ by at most one 16-row group
+    const long long groups = (static_cast<long long>(N) + 15) / 16;
+    long long b = groups * rank / world * 16, e = groups * (rank + 1) / world * 16;
+    if (b > N) b = N;
+    if (e > N) e = N;
+    if (row_begin) *row_begin = static_cast<int>(b);
+    if (row_end) *row_end = static_cast<int>(e);
+}
+
+int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm: null pointer");
+    if (M <= 0 || N <= 0 || K <= 0 || K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
+    cudaStream_t st = g_ctx.stream;
+    const uint8_t* dw = nullptr;
+    if ((rc = weights_on_device(w, static_cast<size_t>(N) * row_bytes(type, K), type, &dw))) return rc;
+    const size_t xb = sizeof(float) * static_cast<size_t>(M) * K, yb = sizeof(float) * static_cast<size_t>(M) * N;
+    if ((rc = g_hx.ensure(xb)) || (rc = g_hy.ensure(yb)) || (rc = g_dx.ensure(xb)) || (rc = g_dy.ensure(yb))) return rc;
+    std::memcpy(g_hx.p, x, xb);
+    cudaMemcpyAsync(g_dx.p, g_hx.p, xb, cudaMemcpyHostToDevice, st);
+    rc = dispatch_gemm_dev(static_cast<const float*>(g_dx.p), dw, type, static_cast<float*>(g_dy.p), M, K, N, st);
+    if (rc) return rc;
+    cudaMemcpyAsync(g_hy.p, g_dy.p, yb, cudaMemcpyDeviceToHost, st);
+    if ((rc = check_device_status(st))) return rc;
+    std::memcpy(y, g_hy.p, yb);
+    return LAPLACE_OK;
+}
+
+int laplace_cuda_moe_gemv(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx, int n_experts,
+                          float* y, int K, int N) {
+    return moe_host(x, w, type, expert_idx, n_experts, y, K, N, 0);
+}
+
+int laplace_cuda_moe_gemv_multi(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx,
+                                int n_experts, float* y, int K, int N) {
+    return moe_host(x, w, type, expert_idx, n_experts, y, K, N, 1);
+}
+
+int laplace_cuda_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N,
+                          void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    return dispatch_gemm_dev(x, w, type, y, M, K, N, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx,
+                              int n_experts, float* y, int K, int N, int per_expert_x, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    return dispatch_moe_dev(x, w, type, expert_idx, n_experts, y, K, N, per_expert_x,
+                            stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_quantize_act_dev(const float* x, int M, int K, int8_t* q, float* d, float* sum, int16_t* isum,
+                                  void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!x) return fail(LAPLACE_ERR_ARG, "quantize: null input");
+    return launch_quantize_act(x, M, K, q, d, sum, isum, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_debug_blocksums_dev(const float* x, const uint8_t* w, uint32_t type, int32_t* out, int M, int K,
+                                     int N, void* stream) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w || !out) return fail(LAPLACE_ERR_ARG, "blocksums: null pointer");
+    if (M <= 0 || N <= 0 || K <= 0 || K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "blocksums: M=%d K=%d N=%d", M, K, N);
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream;
+    if ((rc = g_dq.ensure(static_cast<size_t>(M) * K))) return rc;
+    if ((rc = launch_quantize_act(x, M, K, static_cast<int8_t*>(g_dq.p), nullptr, nullptr, nullptr, st))) return rc;
+    return launch_blocksums_q(static_cast<const int8_t*>(g_dq.p), w, type, out, M, K, N, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,93 @@
+"""Device-pointer calls into the C ABI with torch tensors as the memory owners.
+
+torch is plumbing here: it allocates HBM, owns streams and (for multi-GPU runs)
+the NCCL process group. Every function passes raw device pointers and the
+current CUDA stream to the ``*_dev`` entry points of include/laplace_cuda.h.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _lib
+from .ggml import blocksums_per_row, row_bytes
+from .matmul import LaplaceCudaError, _check
+
+_ready_on = None
+
+
+def lib(device: int | None = None):
+    """Loads the library and binds it to ``device`` (default: torch's current device)."""
+    global _ready_on
+    L = _lib.load()
+    if not torch.cuda.is_available():
+        raise LaplaceCudaError(-3, "no CUDA device visible to this process; the library has no CPU path")
+    dev = torch.cuda.current_device() if device is None else device
+    if _ready_on is None:
+        _check(L, L.laplace_cuda_init(dev))
+        _ready_on = dev
+        from . import matmul as _m
+        _m._initialised = True
+    elif _ready_on != dev:
+        raise LaplaceCudaError(-3, f"library already bound to device {_ready_on}")
+    return L
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def upload_weights(w: np.ndarray) -> torch.Tensor:
+    """Copies GGUF bytes to HBM with the 16-byte read-ahead slack the kernels may touch."""
+    flat = np.ascontiguousarray(w, dtype=np.uint8).reshape(-1)
+    t = torch.zeros(flat.size + 64, dtype=torch.uint8, device="cuda")
+    t[: flat.size].copy_(torch.from_numpy(flat))
+    return t
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, t: int, M: int, K: int, N: int, y: torch.Tensor | None = None) -> torch.Tensor:
+    L = lib()
+    assert x.dtype == torch.float32 and x.is_cuda and x.is_contiguous() and x.numel() >= M * K
+    assert w.dtype == torch.uint8 and w.is_cuda and w.numel() >= N * row_bytes(t, K)
+    if y is None:
+        y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _check(L, L.laplace_cuda_gemm_dev(x.data_ptr(), w.data_ptr(), int(t), y.data_ptr(), M, K, N, _stream()))
+    return y
+
+
+def moe_gemv(x: torch.Tensor, w: torch.Tensor, t: int, expert_idx: torch.Tensor, K: int, N: int,
+             per_expert_x: bool, y: torch.Tensor | None = None) -> torch.Tensor:
+    L = lib()
+    n = expert_idx.numel()
+    assert expert_idx.dtype == torch.int32 and expert_idx.is_cuda
+    if y is None:
+        y = torch.empty((n, N), dtype=torch.float32, device=x.device)
+    _check(L, L.laplace_cuda_moe_gemv_dev(x.data_ptr(), w.data_ptr(), int(t), expert_idx.data_ptr(), n,
+                                          y.data_ptr(), K, N, 1 if per_expert_x else 0, _stream()))
+    return y
+
+
+def quantize_act(x: torch.Tensor, M: int, K: int):
+    """Returns (q int8 [M,K], d f32 [M,K/32], sum f32 [M,K/32], isum int16 [M,K/32,2])."""
+    L = lib()
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    d = torch.empty((M, K // 32), dtype=torch.float32, device=x.device)
+    s = torch.empty((M, K // 32), dtype=torch.float32, device=x.device)
+    i = torch.empty((M, K // 32, 2), dtype=torch.int16, device=x.device)
+    _check(L, L.laplace_cuda_quantize_act_dev(x.data_ptr(), M, K, q.data_ptr(), d.data_ptr(), s.data_ptr(),
+                                              i.data_ptr(), _stream()))
+    return q, d, s, i
+
+
+def debug_blocksums(x: torch.Tensor, w: torch.Tensor, t: int, M: int, K: int, N: int) -> torch.Tensor:
+    L = lib()
+    out = torch.empty((M, N, blocksums_per_row(t, K)), dtype=torch.int32, device=x.device)
+    _check(L, L.laplace_cuda_debug_blocksums_dev(x.data_ptr(), w.data_ptr(), int(t), out.data_ptr(), M, K, N, _stream()))
+    return out
+
+
+def sync() -> None:
+    """Drains torch's stream and the library's, then surfaces any device-side timeout."""
+    torch.cuda.synchronize()
+    L = lib()
+    _check(L, L.laplace_cuda_sync())

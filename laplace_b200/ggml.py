@@ -1,0 +1,50 @@
+"""GGML type ids and block geometry of the four weight formats on this path.
+
+Values follow Laplace ``src/tensor.h:11-34`` (ids) and ``src/tensor.h:41-100`` /
+``src/kernels.h:21-54`` (bytes and elements per block).
+"""
+from __future__ import annotations
+
+import enum
+
+
+class GGMLType(enum.IntEnum):
+    F32 = 0
+    F16 = 1
+    Q4_0 = 2
+    Q5_0 = 6
+    Q8_0 = 8
+    Q4_K = 12
+    Q6_K = 14
+    BF16 = 30
+
+
+_GEOM = {
+    GGMLType.Q4_0: (32, 18),
+    GGMLType.Q8_0: (32, 34),
+    GGMLType.Q4_K: (256, 144),
+    GGMLType.Q6_K: (256, 210),
+}
+
+SUPPORTED = tuple(_GEOM)
+
+
+def block_elems(t: int) -> int:
+    return _GEOM[GGMLType(t)][0]
+
+
+def block_bytes(t: int) -> int:
+    return _GEOM[GGMLType(t)][1]
+
+
+def row_bytes(t: int, K: int) -> int:
+    """Bytes of one weight row of K elements (``rb`` in src/matmul_simd.cpp:482)."""
+    e, b = _GEOM[GGMLType(t)]
+    if K % e:
+        raise ValueError(f"K={K} is not a multiple of the {e}-element block of {GGMLType(t).name}")
+    return K // e * b
+
+
+def blocksums_per_row(t: int, K: int) -> int:
+    """Integer block sums per (activation row, weight row): per 16 values for Q6_K, per 32 otherwise."""
+    return K // 16 if GGMLType(t) == GGMLType.Q6_K else K // 32
