@@ -1,0 +1,336 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized weight-matmul hot path on B200.
+
+Headline workload (BASELINE.json configs[1], the shape its metric is quoted on):
+Q4_K x Q8 decode GEMV, M=1, K=4096, N=14336 (33,030,144 bytes of packed weights).
+A "step" is one pass of the hot path over one activation row: quantize x,
+stream one weight matrix, write y. `value` is effective packed-weight GB/s =
+original GGUF weight bytes / time, inputs resident in HBM. `e2e` is the same
+metric through the reference-facing host-pointer C ABI (x copied host->device,
+y device->host inside the timed region, weights registered once as the
+reference does at load time).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): the weight matrix
+is split along N (rows) across ranks; each step runs the local GEMV and
+all-gathers the fp32 output slices with NCCL. Total work is fixed: "strong".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+TYPE_Q4_K = 12
+K_DIM, N_DIM, M_ROWS = 4096, 14336, 1
+WEIGHT_BYTES = N_DIM * (K_DIM // 256) * 144          # 33,030,144
+N_COPIES = 16                                        # 528 MB of rotating weights, > 4x the 126 MB L2
+WORKLOAD = "Q4_K x Q8 decode GEMV M=1 K=4096 N=14336 (Llama-3-8B gate/up projection)"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed regions run."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------- reference CPU arm
+def cpu_gemv_runner():
+    """The reference's own CPU implementation of the path when its build is present
+    (oracle/_ref: scalar fp32-activation matmul_rows), else the int8 oracle port."""
+    from laplace_b200 import synth
+    from tests import oracle_lib
+    cores = os.cpu_count() or 1
+    w = synth.weights(TYPE_Q4_K, K_DIM, N_DIM, seed=1012, how="ref")
+    x = synth.normal_f32(2001, (M_ROWS, K_DIM))
+    if oracle_lib.Reference.available():
+        ref = oracle_lib.Reference()
+        cores = ref.set_threads(cores)
+        return "reference", cores, (lambda: ref.matmul_rows(x, w, TYPE_Q4_K, M_ROWS, K_DIM, N_DIM))
+    orc = oracle_lib.Oracle()
+    return "port", cores, (lambda: orc.gemm(x, w, TYPE_Q4_K, M_ROWS, K_DIM, N_DIM, mode=0, threads=cores))
+
+
+def time_cpu(run, steps: int, warmup: int):
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    return (time.perf_counter() - t0) / steps
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind, cores, run = cpu_gemv_runner()
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    if steps > 400:
+        steps = 400                                   # a step is a whole GEMV (ms on CPU): keep the run to minutes
+    dt = time_cpu(run, steps, warmup)
+    gbs = WEIGHT_BYTES / dt / 1e9
+    sample = f"{steps} full GEMVs of the workload, all host threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "Q4_K GEMV effective packed-weight GB/s (M=1)", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x u4 -> int32, fp32 scales"
+        if kind == "port" else "fp32 activations x dequantized weights",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "weights": "seeded N(0,0.02^2), reference test packer"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------ GPU arm
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from laplace_b200 import _lib, device, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = device.lib(local)
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+
+    # ---- inputs: seeded weights (reference test packer), rows split across ranks
+    w_full = synth.weights(TYPE_Q4_K, K_DIM, N_DIM, seed=1012, how="ref")
+    b, e = C.c_int(), C.c_int()
+    L.laplace_cuda_nsplit(N_DIM, rank, world, C.byref(b), C.byref(e))
+    r0, r1 = b.value, e.value
+    n_loc = r1 - r0
+    w_loc = np.ascontiguousarray(w_full[r0:r1])
+    copies = []
+    for i in range(N_COPIES):                       # distinct HBM copies, rows rotated so outputs differ
+        copies.append(device.upload_weights(np.roll(w_loc, i * 16, axis=0)))
+    x_host = synth.normal_f32(2001, (M_ROWS, K_DIM))
+    x = torch.from_numpy(x_host).cuda()
+    y_loc = torch.empty((N_COPIES, M_ROWS, n_loc), dtype=torch.float32, device="cuda")
+    y_all = torch.empty((world, M_ROWS * (N_DIM // world + 16)), dtype=torch.float32, device="cuda") if world > 1 else None
+    uneven = world > 1 and any(
+        (lambda bb, ee: ee - bb)(*_split(L, N_DIM, r, world)) != n_loc for r in range(world))
+
+    def step(i):
+        c = i % N_COPIES
+        device.gemm(x, copies[c], TYPE_Q4_K, M_ROWS, K_DIM, n_loc, y=y_loc[c])
+        if world > 1:
+            if uneven:
+                pad = torch.zeros(y_all.shape[1], dtype=torch.float32, device="cuda")
+                pad[: M_ROWS * n_loc] = y_loc[c].reshape(-1)
+                dist.all_gather_into_tensor(y_all, pad)
+            else:
+                dist.all_gather_into_tensor(y_all[:, : M_ROWS * n_loc], y_loc[c].reshape(-1))
+
+    for i in range(warmup):
+        step(i)
+    device.sync()
+    # self-check: copy c holds copy 0's rows rotated by 16c, so its output is copy 0's output rotated
+    y0 = y_loc[0].cpu().numpy()
+    for c in range(1, min(N_COPIES, warmup)):
+        assert np.array_equal(np.roll(y0, c * 16, axis=-1), y_loc[c].cpu().numpy()), "rotated weight copies disagree"
+
+    # ---- device-timed region: exactly `steps` steps, replayed as one CUDA graph when single-GPU
+    use_graph = world == 1
+    graph = None
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(graph, stream=s):
+                for i in range(steps):
+                    step(i)
+        torch.cuda.current_stream().wait_stream(s)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    L.laplace_cuda_launch_count(1)
+    times = []
+    t_begin = time.perf_counter()
+    repeats = 0
+    while (repeats < args.repeats) if args.repeats else (repeats < 3 or (time.perf_counter() - t_begin < 1.5 and repeats < 2000)):
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        if use_graph:
+            graph.replay()
+        else:
+            for i in range(steps):
+                step(i)
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        times.append(ms)
+        repeats += 1
+    launches_eager = L.laplace_cuda_launch_count(0)
+    device.sync()
+    ms_total = statistics.median(times)
+    ms_step = ms_total / steps
+    value = WEIGHT_BYTES / (ms_step * 1e-3) / 1e9
+
+    # ---- e2e: the reference-facing host-pointer call (kernels::gemm_fn shape), weights registered once
+    import laplace_b200 as lb
+    e2e_val, h2d, d2h = None, M_ROWS * K_DIM * 4, M_ROWS * n_loc * 4
+    if not args.no_e2e:
+        region = np.ascontiguousarray(np.concatenate([np.roll(w_loc, i * 16, axis=0) for i in range(4)]))
+        lb.matmul_register_weights(region)
+        yh = np.empty((M_ROWS, n_loc), dtype=np.float32)
+        per = n_loc * (K_DIM // 256) * 144
+        views = [lb.Tensor(TYPE_Q4_K, region.reshape(-1)[i * per:(i + 1) * per]) for i in range(4)]
+        fn, xp, yp = L.laplace_cuda_gemm, x_host.ctypes.data, yh.ctypes.data
+        wps = [v.data.ctypes.data for v in views]
+        n_e2e = max(steps, 200)
+        for i in range(20):
+            fn(xp, wps[i % 4], TYPE_Q4_K, yp, M_ROWS, K_DIM, n_loc)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            rc = fn(xp, wps[i % 4], TYPE_Q4_K, yp, M_ROWS, K_DIM, n_loc)
+        dt = (time.perf_counter() - t0) / n_e2e
+        assert rc == 0, L.laplace_cuda_last_error()
+        if world > 1:
+            t = torch.tensor([dt], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        e2e_val = WEIGHT_BYTES / dt / 1e9
+        last = (n_e2e - 1) % 4
+        assert np.array_equal(yh, y_loc[last].cpu().numpy()), "host-pointer result differs from the device-pointer result"
+        lb.matmul_unregister_weights(region)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        achieved = (WEIGHT_BYTES / world) / (ms_step * 1e-3) / 1e9 if world == 1 else None
+        line = {
+            "metric": "Q4_K GEMV effective packed-weight GB/s (M=1)", "value": value, "unit": "GB/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "u4 x s8 -> s32 block sums, fp32 scales", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "weights": "seeded N(0,0.02^2), reference test packer (Q4_K, 144 B / 256)",
+                       "activations": "seeded N(0,1), quantized per 32 inside the kernel",
+                       "l2": f"{N_COPIES} rotating weight copies ({N_COPIES * WEIGHT_BYTES // world >> 20} MiB per GPU) exceed the 126 MB L2",
+                       "parallelism": "single GPU" if world == 1 else f"N-split over {world} GPUs + NCCL all-gather of y",
+                       "timing": f"CUDA events around {'one CUDA graph of ' if use_graph else ''}{steps} steps; median of {repeats} repeats; max over ranks"},
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "how": "laplace_cuda_gemm with host x and y, synchronous, weights registered (resident) as at model load"},
+            "gpu_launches": steps if use_graph else int(launches_eager // max(repeats, 1)),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved if achieved else value / world, "peak": peak, "unit": "GB/s",
+                         "frac": (achieved if achieved else value / world) / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "gemv_stream_kernel<Q4_K, M=1>", "algorithmic_bytes_per_launch": WEIGHT_BYTES // world},
+        }
+        if world == 1 and not args.no_cpu:
+            kind, cores, run = cpu_gemv_runner()
+            t1 = time_cpu(run, 1, 1)
+            n = max(3, min(5000, int(12.0 / max(t1, 1e-4))))
+            dt = time_cpu(run, n, 1)
+            line["cpu_baseline"] = {"value": WEIGHT_BYTES / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+                                    "sample": f"{n} full GEMVs of the same workload (~{n * dt:.0f} s), all host threads"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _split(L, N, r, world):
+    b, e = C.c_int(), C.c_int()
+    L.laplace_cuda_nsplit(N, r, world, C.byref(b), C.byref(e))
+    return b.value, e.value
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1024)
+    ap.add_argument("--warmup", type=int, default=32)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=0, help="timed repeats of the K-step region (0: until ~1.5 s have passed)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer leg (for short profiler runs)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for short profiler runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

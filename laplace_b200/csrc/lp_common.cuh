@@ -158,10 +158,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) /* suspend-time hint, ns */ : "memory");
     return ok != 0;
 }
-// Returns false when the wait gave up (about a second of polling).
+// Returns false when the wait gave up (a second or so of polling). After the
+// first miss the warp backs off between polls so that it does not take issue
+// slots from warps that have data.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < (1u << 21); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        __nanosleep(40);
         if (mbar_try_wait(bar, parity)) return true;
+    }
     return false;
 }
 __device__ __forceinline__ void fence_barrier_init() {

@@ -3,30 +3,31 @@
 // prologue. Replaces the row loop + dot kernels of Laplace's NEON back-end
 // (src/matmul_simd.cpp:143-342, 348-455, 506-544) for small M.
 //
-// Shape of the kernel (one persistent CTA per SM):
-//   * warp 16 is the producer: it issues 1-D bulk copies (TMA engine,
-//     cp.async.bulk, no multicast) that bring 16 consecutive weight rows - one
-//     contiguous byte range of the GGUF tensor, or one K-slice per row when
-//     rows are long - into a ring of shared-memory stages, each guarded by a
-//     full/empty mbarrier pair;
-//   * while the first stages are in flight, the 16 consumer warps quantize the
-//     fp32 activations into shared memory (per 32 values: d = amax/127, int8,
+// Shape of the kernel (one persistent CTA per SM, 24+1 warps for M <= 2):
+//   * every consumer warp owns a private ring of shared-memory slots that a
+//     producer warp fills with its weight rows by 1-D bulk copies (TMA engine,
+//     cp.async.bulk, no multicast), a full/empty mbarrier pair per slot. A row
+//     is one contiguous byte range of the GGUF tensor; long rows are cut into
+//     K-slices on 16-byte boundaries. Consumers never wait for each other
+//     after the prologue, and a CTA keeps ~220 KB of weight bytes in flight;
+//   * while the first copies are in flight, all warps quantize the fp32
+//     activations into shared memory (per 32 values: d = amax/127, int8,
 //     d*sum), so the quantized activations never touch HBM;
-//   * consumers unpack nibbles / 6-bit fields in registers, take exact int32
-//     block sums with dp4a, apply the fp16 block scales in fp32, reduce across
-//     the warp with shuffles and write y.
+//   * lanes unpack nibbles / 6-bit fields in registers, take exact int32 block
+//     sums with dp4a, apply the fp16 block scales in fp32, reduce across the
+//     warp with shuffles and write y.
 // HBM traffic is the packed weights once, plus x and y. Every wait is bounded:
-// a wait that gives up raises a status word and the CTA drains and returns.
+// a wait that gives up raises a status word, the warp drains its own copies
+// and leaves.
 #include "lp_common.cuh"
 
 namespace lp {
 
 namespace {
 
-constexpr int CONSUMER_WARPS = 16;
-constexpr int THREADS        = (CONSUMER_WARPS + 1) * 32;
-constexpr int MAX_STAGES     = 8;
-constexpr int REC_BYTES      = 80;   // activation record: 64 int8 + d0,d1,sum0,sum1 (fp32)
+constexpr int MAX_SLOTS = 4;
+constexpr int REC_BYTES = 176;   // activation record per 128 values: 128 int8, d[4], sum[4], 16 pad
+                                 // (44 words: consecutive lanes fall in distinct bank groups)
 
 struct KParams {
     const float*   x;
@@ -39,124 +40,133 @@ struct KParams {
     int            act_rows;        // rows of x quantized into shared memory
     int            per_seg_x;
     uint32_t       rb;              // bytes per weight row
-    int            n_slices;        // K-slices per row (1: a tile is 16 whole rows, one copy)
-    uint32_t       slice_bytes;     // bytes of a full slice of one row (16-byte multiple when n_slices > 1)
+    int            rows_per_unit;   // whole rows per bulk copy (when n_slices == 1)
+    int            n_slices;        // K-slices per row
+    uint32_t       slice_bytes;     // bytes of a full slice (16-byte multiple when n_slices > 1)
     int            slice_items;     // items of a full slice
-    uint32_t       slot_bytes;      // per-row slot in a stage when n_slices > 1
-    int            n_stages;
-    uint32_t       stage_bytes;     // multiple of 16, includes alignment slack
+    uint32_t       slot_bytes;      // one slot of a warp's ring
+    int            n_slots;
     uint32_t       act_row_stride;  // bytes between quantized activation rows
-    uint32_t       isum_row_stride; // bytes between rows of the int16 half-sums
-    uint32_t       off_isum, off_stages;
+    uint32_t       isum_row_stride; // bytes between rows of the int16 half-sums (Q6_K only, else 0)
+    uint32_t       off_isum, off_ring;
+    int            rows_q, rows_r;  // CTA b owns rows_q (+1 if b < rows_r) rows
 };
 
-// Shared-memory map: [0,64) full barriers, [64,128) empty barriers, [128,132)
-// abort flag, then activations, half-sums, stages.
-constexpr uint32_t OFF_FULL = 0, OFF_EMPTY = 64, OFF_ABORT = 128;
-constexpr uint32_t OFF_ACT = 256;
-
-// ------------------------------------------------------------------ tiles
-// A tile is up to 16 consecutive weight rows of one segment (one per consumer
-// warp), restricted to one K-slice. Slices of a row group come back to back so
-// a warp keeps its row's accumulators in registers across them.
-struct Tile {
-    long long src_off;   // byte offset of the first row (start of the row, not of the slice) from p.w
-    int seg, j0, nrows, slice;
-};
-
-struct TileWalker {
-    long long g, g_end;
-    int N, n_slices, slice;
-    uint32_t rb;
-    const int* expert_idx;
-    __device__ bool next(Tile& t) {
-        if (g >= g_end) return false;
-        int seg = static_cast<int>(g / N);
-        int j0 = static_cast<int>(g - static_cast<long long>(seg) * N);
-        long long left = g_end - g;
-        int nrows = CONSUMER_WARPS;
-        if (nrows > N - j0) nrows = N - j0;
-        if (nrows > left) nrows = static_cast<int>(left);
-        long long e = expert_idx ? expert_idx[seg] : 0;
-        t.src_off = (e * N + j0) * static_cast<long long>(rb);
-        t.seg = seg; t.j0 = j0; t.nrows = nrows; t.slice = slice;
-        if (++slice == n_slices) { slice = 0; g += nrows; }
-        return true;
-    }
-};
+// Shared-memory map: [0, 64 * warps) slot barriers (per consumer warp: 4 "full"
+// then 4 "empty"), then activations, half-sums, the rings.
+constexpr uint32_t OFF_ACT = 2048;
 
 // ------------------------------------------------------ per-type item code
 // An "item" is the unit one lane processes at a time; items of a row are
-// numbered along K. Each traits struct gives items per row and the dot.
+// numbered along K. `row` is the shared address where byte 0 of the weight row
+// would sit; `act` the address of the activation row's first record.
+
+__device__ __forceinline__ uint32_t act_q(uint32_t act, int blk) {        // 32 int8 of activation block blk
+    return act + (blk >> 2) * REC_BYTES + (blk & 3) * 32;
+}
+__device__ __forceinline__ uint32_t act_d(uint32_t act, int blk) {        // its fp32 scale; +16 is d*sum
+    return act + (blk >> 2) * REC_BYTES + 128 + (blk & 3) * 4;
+}
 
 template <uint32_t TYPE> struct Traits;
 
-// Q4_K: item = one 64-value chunk (32 bytes of nibbles) of a super-block.
-// Activation record i holds exactly the two 32-value blocks of item i.
+// Q4_K: item = half a super-block: 128 values, 64 bytes of nibbles, the four
+// sub-blocks 4h..4h+3, which are exactly activation record i.
+struct Q4KAct {            // one activation record in registers
+    uint32_t q[32];        // 128 int8
+    float    d[4], s[4];   // per 32 values: scale, scale * integer sum
+};
+__device__ __forceinline__ void q4k_load_act(uint32_t rec, Q4KAct& a) {
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+        const uint4 v = lds128(rec + 16 * t);
+        a.q[4 * t] = v.x; a.q[4 * t + 1] = v.y; a.q[4 * t + 2] = v.z; a.q[4 * t + 3] = v.w;
+    }
+    const uint4 dx = lds128(rec + 128), sx = lds128(rec + 144);
+    a.d[0] = __uint_as_float(dx.x); a.d[1] = __uint_as_float(dx.y); a.d[2] = __uint_as_float(dx.z); a.d[3] = __uint_as_float(dx.w);
+    a.s[0] = __uint_as_float(sx.x); a.s[1] = __uint_as_float(sx.y); a.s[2] = __uint_as_float(sx.z); a.s[3] = __uint_as_float(sx.w);
+}
+struct Q4KWts {            // half a super-block of weights in registers
+    uint32_t q[16];        // 64 bytes of nibbles
+    uint32_t sc4, mn4;     // 6-bit scales / mins of sub-blocks 4h..4h+3, one per byte
+    float    d, dmin;
+};
+__device__ __forceinline__ void q4k_load_wts(uint32_t row, int i, Q4KWts& w) {
+    const uint32_t blk = row + (i >> 1) * Q4_K_BYTES;
+    const int h = i & 1;
+    const uint4 hdr = lds128(blk);
+    const uint32_t qaddr = blk + 16 + 64 * h;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const uint4 v = lds128(qaddr + 16 * t);
+        w.q[4 * t] = v.x; w.q[4 * t + 1] = v.y; w.q[4 * t + 2] = v.z; w.q[4 * t + 3] = v.w;
+    }
+    // Laplace src/kernels.h:82-90, four sub-blocks at a time
+    if (h == 0) {
+        w.sc4 = hdr.y & 0x3f3f3f3fu;
+        w.mn4 = hdr.z & 0x3f3f3f3fu;
+    } else {
+        w.sc4 = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+        w.mn4 = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+    }
+    w.d = half_bits_to_float(hdr.x);
+    w.dmin = half_bits_to_float(hdr.x >> 16);
+}
+__device__ __forceinline__ float q4k_dot(const Q4KWts& w, const Q4KAct& x) {
+    float a = 0.f, am = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {                      // 64-value chunk: low nibbles, then high
+        int u1a = 0, u1b = 0, u2a = 0, u2b = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            u1a = dp4a_us(w.q[8 * c + t] & 0x0f0f0f0fu, x.q[16 * c + t], u1a);
+            u1b = dp4a_us(w.q[8 * c + 4 + t] & 0x0f0f0f0fu, x.q[16 * c + 4 + t], u1b);
+            u2a = dp4a_us(w.q[8 * c + t] & 0xf0f0f0f0u, x.q[16 * c + 8 + t], u2a);      // 16 x the high-nibble sum
+            u2b = dp4a_us(w.q[8 * c + 4 + t] & 0xf0f0f0f0u, x.q[16 * c + 12 + t], u2b);
+        }
+        const int u1 = u1a + u1b, u2 = (u2a + u2b) >> 4;                                // exact: a multiple of 16
+        const float d1 = w.d * static_cast<float>((w.sc4 >> (16 * c)) & 0xff);
+        const float d2 = w.d * static_cast<float>((w.sc4 >> (16 * c + 8)) & 0xff);
+        const float m1 = w.dmin * static_cast<float>((w.mn4 >> (16 * c)) & 0xff);
+        const float m2 = w.dmin * static_cast<float>((w.mn4 >> (16 * c + 8)) & 0xff);
+        a = fmaf(d1 * x.d[2 * c], static_cast<float>(u1), a);
+        a = fmaf(d2 * x.d[2 * c + 1], static_cast<float>(u2), a);
+        am = fmaf(m1, x.s[2 * c], am);
+        am = fmaf(m2, x.s[2 * c + 1], am);
+    }
+    return a - am;
+}
 template <> struct Traits<LAPLACE_TYPE_Q4_K> {
-    __device__ static int items(int K) { return K / 64; }
+    static constexpr int ITEMS_PER_BLOCK = 2;
     template <int M>
     __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
-                                float (&acc)[M], float (&acc2)[M]) {
-        const uint32_t blk = row + (i >> 2) * Q4_K_BYTES;
-        const int c = i & 3;
-        const uint4 hdr = lds128(blk);
-        const uint4 qa = lds128(blk + 16 + 32 * c);
-        const uint4 qb = lds128(blk + 32 + 32 * c);
-        // 6-bit scale/min pairs of sub-blocks 2c and 2c+1 (Laplace src/kernels.h:82-90)
-        uint32_t scp, mnp;
-        if (c < 2) {
-            scp = (hdr.y >> (16 * c)) & 0x3f3fu;
-            mnp = (hdr.z >> (16 * c)) & 0x3f3fu;
-        } else {
-            const int s = 16 * (c - 2);
-            const uint32_t a = (hdr.w >> s) & 0xffffu, b = (hdr.y >> s) & 0xffffu, cc = (hdr.z >> s) & 0xffffu;
-            scp = (a & 0x0f0fu) | ((b >> 2) & 0x3030u);
-            mnp = ((a >> 4) & 0x0f0fu) | ((cc >> 2) & 0x3030u);
-        }
-        const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
-        const float d1 = d * static_cast<float>(scp & 0xff), d2 = d * static_cast<float>(scp >> 8);
-        const float m1 = dmin * static_cast<float>(mnp & 0xff), m2 = dmin * static_cast<float>(mnp >> 8);
-        const uint32_t wq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                                float (&acc)[M]) {
+        Q4KWts w;
+        q4k_load_wts(row, i, w);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const uint32_t rec = act + m * astride + i * REC_BYTES;
-            const uint4 x0 = lds128(rec), x1 = lds128(rec + 16), x2 = lds128(rec + 32), x3 = lds128(rec + 48);
-            const uint4 sc = lds128(rec + 64);
-            const uint32_t xa[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-            const uint32_t xb[8] = {x2.x, x2.y, x2.z, x2.w, x3.x, x3.y, x3.z, x3.w};
-            int u1 = 0, u2 = 0;
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                u1 = dp4a_us(wq[t] & 0x0f0f0f0fu, xa[t], u1);
-                u2 = dp4a_us(wq[t] & 0xf0f0f0f0u, xb[t], u2);   // 16 x the high-nibble sum
-            }
-            u2 >>= 4;                                            // exact: a multiple of 16
-            acc[m] = fmaf(d1 * __uint_as_float(sc.x), static_cast<float>(u1), acc[m]);
-            acc[m] = fmaf(d2 * __uint_as_float(sc.y), static_cast<float>(u2), acc[m]);
-            acc2[m] = fmaf(m1, __uint_as_float(sc.z), acc2[m]);
-            acc2[m] = fmaf(m2, __uint_as_float(sc.w), acc2[m]);
+            Q4KAct x;
+            q4k_load_act(act + m * astride + i * REC_BYTES, x);
+            acc[m] += q4k_dot(w, x);
         }
     }
 };
 
-// Q4_0: item = one 18-byte block. acc2 collects d_w * 8 * sum_x.
+// Q4_0: item = one 18-byte block. The second term is d_w * 8 * sum_x.
 template <> struct Traits<LAPLACE_TYPE_Q4_0> {
-    __device__ static int items(int K) { return K / 32; }
+    static constexpr int ITEMS_PER_BLOCK = 1;
     template <int M>
     __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
-                                float (&acc)[M], float (&acc2)[M]) {
+                                float (&acc)[M]) {
         const uint32_t blk = row + i * Q4_0_BYTES;
         const float d = half_bits_to_float(lds16(blk));
         uint32_t wq[4];
         lds16B_align2(blk + 2, wq);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const uint32_t rec = act + m * astride + (i >> 1) * REC_BYTES;
-            const uint32_t q = rec + 32 * (i & 1);
+            const uint32_t q = act_q(act + m * astride, i), ds = act_d(act + m * astride, i);
             const uint4 x0 = lds128(q), x1 = lds128(q + 16);
-            const float dx = __uint_as_float(lds32(rec + 64 + 4 * (i & 1)));
-            const float sx = __uint_as_float(lds32(rec + 72 + 4 * (i & 1)));
+            const float dx = __uint_as_float(lds32(ds)), sx = __uint_as_float(lds32(ds + 16));
             const uint32_t xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
             int ul = 0, uh = 0;
 #pragma unroll
@@ -165,18 +175,17 @@ template <> struct Traits<LAPLACE_TYPE_Q4_0> {
                 uh = dp4a_us(wq[t] & 0xf0f0f0f0u, xh[t], uh);
             }
             const int u = ul + (uh >> 4);
-            acc[m] = fmaf(d * dx, static_cast<float>(u), acc[m]);
-            acc2[m] = fmaf(d * 8.0f, sx, acc2[m]);
+            acc[m] = fmaf(d * dx, static_cast<float>(u), acc[m]) - d * 8.0f * sx;
         }
     }
 };
 
 // Q8_0: item = one 34-byte block.
 template <> struct Traits<LAPLACE_TYPE_Q8_0> {
-    __device__ static int items(int K) { return K / 32; }
+    static constexpr int ITEMS_PER_BLOCK = 1;
     template <int M>
     __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
-                                float (&acc)[M], float (&)[M]) {
+                                float (&acc)[M]) {
         const uint32_t blk = row + i * Q8_0_BYTES;
         const float d = half_bits_to_float(lds16(blk));
         uint32_t w0[4], w1[4];
@@ -184,16 +193,15 @@ template <> struct Traits<LAPLACE_TYPE_Q8_0> {
         lds16B_align2(blk + 18, w1);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const uint32_t rec = act + m * astride + (i >> 1) * REC_BYTES;
-            const uint32_t q = rec + 32 * (i & 1);
+            const uint32_t q = act_q(act + m * astride, i);
             const uint4 x0 = lds128(q), x1 = lds128(q + 16);
-            const float dx = __uint_as_float(lds32(rec + 64 + 4 * (i & 1)));
-            int u = 0;
-            u = dp4a_ss(w0[0], x0.x, u); u = dp4a_ss(w0[1], x0.y, u);
-            u = dp4a_ss(w0[2], x0.z, u); u = dp4a_ss(w0[3], x0.w, u);
-            u = dp4a_ss(w1[0], x1.x, u); u = dp4a_ss(w1[1], x1.y, u);
-            u = dp4a_ss(w1[2], x1.z, u); u = dp4a_ss(w1[3], x1.w, u);
-            acc[m] = fmaf(d * dx, static_cast<float>(u), acc[m]);
+            const float dx = __uint_as_float(lds32(act_d(act + m * astride, i)));
+            int ua = 0, ub = 0;
+            ua = dp4a_ss(w0[0], x0.x, ua); ub = dp4a_ss(w0[1], x0.y, ub);
+            ua = dp4a_ss(w0[2], x0.z, ua); ub = dp4a_ss(w0[3], x0.w, ub);
+            ua = dp4a_ss(w1[0], x1.x, ua); ub = dp4a_ss(w1[1], x1.y, ub);
+            ua = dp4a_ss(w1[2], x1.z, ua); ub = dp4a_ss(w1[3], x1.w, ub);
+            acc[m] = fmaf(d * dx, static_cast<float>(ua + ub), acc[m]);
         }
     }
 };
@@ -205,10 +213,10 @@ template <> struct Traits<LAPLACE_TYPE_Q8_0> {
 // subtracts 32 * (sum of the 16 activations): the same integer as summing
 // (q6 - 32) * x (Laplace src/matmul_simd.cpp:300-335).
 template <> struct Traits<LAPLACE_TYPE_Q6_K> {
-    __device__ static int items(int K) { return K / 64; }
+    static constexpr int ITEMS_PER_BLOCK = 4;
     template <int M>
     __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t isum,
-                                uint32_t isum_stride, float (&acc)[M], float (&)[M]) {
+                                uint32_t isum_stride, float (&acc)[M]) {
         const int s = i & 1, half = (i >> 1) & 1, sb = i >> 2;
         const uint32_t blk = row + sb * Q6_K_BYTES;
         uint32_t qa[4], qb[4], qh[4];
@@ -229,210 +237,308 @@ template <> struct Traits<LAPLACE_TYPE_Q6_K> {
         for (int g = 0; g < 4; ++g) scf[g] = static_cast<float>(lds_s8(blk + 192 + 8 * half + 2 * g + s));
 #pragma unroll
         for (int m = 0; m < M; ++m) {
+            // the four activation blocks half*4+g share record sb*2+half
+            const uint32_t rec = act + m * astride + (sb * 2 + half) * REC_BYTES;
+            const uint4 dx = lds128(rec + 128);
+            const float dxs[4] = {__uint_as_float(dx.x), __uint_as_float(dx.y), __uint_as_float(dx.z), __uint_as_float(dx.w)};
+            const uint32_t hs_base = isum + m * isum_stride + (sb * 8 + half * 4) * 4 + 2 * s;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-                const int ab = sb * 8 + half * 4 + g;   // activation block
-                const uint32_t rec = act + m * astride + (ab >> 1) * REC_BYTES;
-                const uint4 xq = lds128(rec + 32 * (ab & 1) + 16 * s);
-                const float dx = __uint_as_float(lds32(rec + 64 + 4 * (ab & 1)));
-                const int hs = static_cast<short>(lds16(isum + m * isum_stride + ab * 4 + 2 * s));
-                int u = 0;
-                u = dp4a_us(v[g][0], xq.x, u); u = dp4a_us(v[g][1], xq.y, u);
-                u = dp4a_us(v[g][2], xq.z, u); u = dp4a_us(v[g][3], xq.w, u);
-                u -= 32 * hs;
-                acc[m] = fmaf(d * dx * scf[g], static_cast<float>(u), acc[m]);
+                const uint4 xq = lds128(rec + 32 * g + 16 * s);
+                const int hs = static_cast<short>(lds16(hs_base + 4 * g));
+                int ua = 0, ub = 0;
+                ua = dp4a_us(v[g][0], xq.x, ua); ub = dp4a_us(v[g][1], xq.y, ub);
+                ua = dp4a_us(v[g][2], xq.z, ua); ub = dp4a_us(v[g][3], xq.w, ub);
+                const int u = ua + ub - 32 * hs;
+                acc[m] = fmaf(d * dxs[g] * scf[g], static_cast<float>(u), acc[m]);
             }
         }
     }
 };
 
 // ------------------------------------------------------------------ kernel
-template <uint32_t TYPE, int M>
-__global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const KParams p) {
+// A unit is what one bulk copy brings: up to rows_per_unit consecutive whole
+// rows of one segment, or one K-slice of one row. Producer lane w and consumer
+// warp w walk the same sequence of units over w's contiguous range of rows.
+struct Unit {
+    long long src_off;   // byte offset from p.w of the first byte to copy
+    uint32_t  len;       // bytes the unit needs
+    int       seg, j, nrows, slice;
+};
+struct Walker {
+    int g, g_end, slice;
+    __device__ bool next(const KParams& p, Unit& u) {
+        if (g >= g_end) return false;
+        int seg = 0, j = g;
+        long long rowidx = g;
+        if (p.expert_idx) {
+            seg = g / p.N;
+            j = g - seg * p.N;
+            rowidx = static_cast<long long>(p.expert_idx[seg]) * p.N + j;
+        }
+        u.seg = seg; u.j = j; u.slice = slice;
+        if (p.n_slices > 1) {
+            const uint32_t off = static_cast<uint32_t>(slice) * p.slice_bytes;
+            u.nrows = 1;
+            u.len = (p.rb - off) < p.slice_bytes ? (p.rb - off) : p.slice_bytes;
+            u.src_off = rowidx * p.rb + off;
+            if (++slice == p.n_slices) { slice = 0; ++g; }
+        } else {
+            int n = p.rows_per_unit;
+            if (n > g_end - g) n = g_end - g;
+            if (n > p.N - j) n = p.N - j;              // a copy never crosses into another expert
+            u.nrows = n;
+            u.len = static_cast<uint32_t>(n) * p.rb;
+            u.src_off = rowidx * p.rb;
+            g += n;
+        }
+        return true;
+    }
+};
+
+// WARPS consumer warps plus one producer warp. Lane w of the producer serves
+// consumer w: it waits for a slot of w's ring to be released and issues the
+// next bulk copy into it. Issuing a bulk copy holds the issuing lane for ~100
+// cycles and the SM's copy engine takes roughly one copy per 55 cycles, so
+// consumers never issue copies themselves, and copies are made as large as the
+// ring allows (two 2.3 KB rows per copy move ~1.5x faster than one).
+//
+// RESIDENT: M == 1, Q4_K, one item per lane and row (K <= 4096): the lane's
+// activation record never changes, so it lives in registers for the whole
+// kernel and the row loop reads only weights from shared memory.
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT>
+__global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const KParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_ABORT);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.n_stages; ++s) {
-            mbar_init(sbase + OFF_FULL + 8 * s, 1);
-            mbar_init(sbase + OFF_EMPTY + 8 * s, CONSUMER_WARPS);
+    // This CTA's contiguous share of the n_seg * N weight rows (fewer than 2^31),
+    // cut again into one contiguous range per consumer warp.
+    const int bx = static_cast<int>(blockIdx.x);
+    const int g0 = bx * p.rows_q + (bx < p.rows_r ? bx : p.rows_r);
+    const int cta_rows = p.rows_q + (bx < p.rows_r ? 1 : 0);
+    auto walker_of = [&](int w) {
+        const int q = cta_rows / WARPS, r = cta_rows - q * WARPS;
+        Walker wk;
+        wk.g = g0 + w * q + (w < r ? w : r);
+        wk.g_end = wk.g + q + (w < r ? 1 : 0);
+        wk.slice = 0;
+        return wk;
+    };
+    auto bar_full = [&](int w, int slot) { return sbase + w * 64 + 8 * slot; };
+    auto bar_empty = [&](int w, int slot) { return sbase + w * 64 + 32 + 8 * slot; };
+    auto ring_of = [&](int w) { return sbase + p.off_ring + w * (p.n_slots * p.slot_bytes); };
+
+    if (warp == WARPS) {
+        // ------------------------------ producer warp ------------------------------
+        const int w = lane;
+        const bool serving = w < WARPS;
+        if (serving) {
+            for (int s = 0; s < p.n_slots; ++s) { mbar_init(bar_full(w, s), 1); mbar_init(bar_empty(w, s), 1); }
         }
-        *abort_flag = 0;
         fence_barrier_init();
-    }
-    __syncthreads();
-
-    // This CTA's contiguous share of the n_seg * N weight rows.
-    const long long total = static_cast<long long>(p.n_seg) * p.N;
-    TileWalker walk;
-    walk.g = total * blockIdx.x / gridDim.x;
-    walk.g_end = total * (blockIdx.x + 1) / gridDim.x;
-    walk.N = p.N; walk.n_slices = p.n_slices; walk.slice = 0; walk.rb = p.rb; walk.expert_idx = p.expert_idx;
-
-    const uint32_t stages = sbase + p.off_stages;
-
-    if (warp == CONSUMER_WARPS) {
-        // ---------------- producer warp ----------------
-        Tile t;
-        int issued = 0;
-        bool ok = true;
-        while (ok && walk.next(t)) {
-            const int s = issued % p.n_stages;
-            const uint32_t ph = (issued / p.n_stages) & 1;
-            const uint32_t full = sbase + OFF_FULL + 8 * s;
-            if (lane == 0) {
-                if (!mbar_wait_bounded(sbase + OFF_EMPTY + 8 * s, ph ^ 1) || *abort_flag) {
-                    if (!*abort_flag) { atomicExch(p.err, DEV_TIMEOUT_EMPTY); *abort_flag = 1; }
-                    ok = false;
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) break;
-            const uint32_t stage = stages + s * p.stage_bytes;
-            if (p.n_slices == 1) {
-                // 16 whole rows are one contiguous byte range: a single copy
-                if (lane == 0) {
-                    const uint8_t* src = p.w + t.src_off;
+        __syncwarp();
+        asm volatile("bar.arrive 1, %0;" :: "r"((WARPS + 1) * 32) : "memory");   // barriers exist; do not wait
+        const uint32_t ring = ring_of(w);
+        Walker wk = walker_of(serving ? w : 0);
+        if (!serving) wk.g_end = wk.g;
+        Unit un;
+        bool have = wk.next(p, un);
+        int ui = 0;
+        uint32_t idle = 0;
+        bool gave_up = false;
+        while (__any_sync(0xffffffffu, have)) {
+            bool issued = false;
+            if (have) {
+                const int slot = ui % p.n_slots, round = ui / p.n_slots;
+                if (round == 0 || mbar_try_wait(bar_empty(w, slot), (round - 1) & 1)) {
+                    const uint8_t* src = p.w + un.src_off;
                     const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15u);
-                    const uint32_t bytes = (mis + static_cast<uint32_t>(t.nrows) * p.rb + 15u) & ~15u;
-                    mbar_expect_tx(full, bytes);
-                    bulk_g2s(stage, src - mis, bytes, full);
+                    const uint32_t bytes = (mis + un.len + 15u) & ~15u;
+                    mbar_expect_tx(bar_full(w, slot), bytes);
+                    bulk_g2s(ring + slot * p.slot_bytes, src - mis, bytes, bar_full(w, slot));
+                    ++ui;
+                    issued = true;
+                    have = wk.next(p, un);
                 }
+            }
+            if (__any_sync(0xffffffffu, issued)) {
+                idle = 0;
             } else {
-                // one copy per row: the slice of that row, into the row's slot
-                const uint32_t off = static_cast<uint32_t>(t.slice) * p.slice_bytes;
-                const uint32_t len = (p.rb - off) < p.slice_bytes ? (p.rb - off) : p.slice_bytes;
-                const uint8_t* src = p.w + t.src_off + static_cast<long long>(lane) * p.rb + off;
-                const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15u);
-                uint32_t bytes = lane < t.nrows ? ((mis + len + 15u) & ~15u) : 0u;
-                uint32_t sum = bytes;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                if (lane == 0) mbar_expect_tx(full, sum);
-                __syncwarp();
-                if (lane < t.nrows) bulk_g2s(stage + lane * p.slot_bytes, src - mis, bytes, full);
+                __nanosleep(64);
+                if (++idle > (1u << 22)) { gave_up = true; break; }      // a consumer never released its slot
             }
-            ++issued;
         }
+        if (gave_up && lane == 0) atomicExch(p.err, DEV_TIMEOUT_EMPTY);
         // Copies still in flight must land before the CTA gives its shared memory back.
-        if (lane == 0) {
-            const int pending = issued < p.n_stages ? issued : p.n_stages;
+        if (serving) {
+            const int pending = ui < p.n_slots ? ui : p.n_slots;
             for (int k = 0; k < pending; ++k) {
-                const int tix = issued - 1 - k;
-                if (!mbar_wait_bounded(sbase + OFF_FULL + 8 * (tix % p.n_stages), (tix / p.n_stages) & 1))
-                    atomicExch(p.err, DEV_TIMEOUT_DRAIN);
+                const int v = ui - 1 - k;
+                if (!mbar_wait_bounded(bar_full(w, v % p.n_slots), (v / p.n_slots) & 1)) atomicExch(p.err, DEV_TIMEOUT_DRAIN);
             }
         }
-    } else {
-        // ---------------- consumer warps ----------------
-        // (1) quantize the activations into shared memory while the ring fills
-        {
-            const int bpr = p.K >> 5;
-            const int groups = (CONSUMER_WARPS * 32) / 8;
-            const int grp = threadIdx.x >> 3, t8 = threadIdx.x & 7;
-            const int nblk = p.act_rows * bpr;
-            // whole warps iterate together so the 8-lane shuffles stay converged
-            for (int base = 0; base < nblk; base += groups) {
-                const int b = base + grp;
-                const bool live = b < nblk;
-                const int m = live ? b / bpr : 0, kb = live ? b - m * bpr : 0;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (live) v = __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8);
-                uint32_t packed; int hs;
-                const float d = quantize_block_8lanes(v, packed, hs);
-                const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
-                if (live) {
-                    uint8_t* rec = smem + OFF_ACT + m * p.act_row_stride + (kb >> 1) * REC_BYTES;
-                    reinterpret_cast<uint32_t*>(rec + 32 * (kb & 1))[t8] = packed;
-                    if (t8 == 0) {
-                        const short lo = static_cast<short>(hs), hi = static_cast<short>(hs_hi);
-                        reinterpret_cast<float*>(rec + 64)[kb & 1] = d;
-                        reinterpret_cast<float*>(rec + 72)[kb & 1] =
-                            d * static_cast<float>(static_cast<int>(lo) + static_cast<int>(hi));
-                        if (p.isum_row_stride) {
-                            short* is = reinterpret_cast<short*>(smem + p.off_isum + m * p.isum_row_stride + kb * 4);
-                            is[0] = lo; is[1] = hi;
-                        }
+        return;
+    }
+
+    // -------------------------------- consumer warps --------------------------------
+    // (1) quantize the activations into shared memory while the rings fill. Each
+    // group of 8 lanes owns 32-value blocks grp, grp + GROUPS, ...
+    {
+        const int bpr = p.K >> 5;
+        constexpr int GROUPS = WARPS * 4;
+        const int grp = threadIdx.x >> 3, t8 = threadIdx.x & 7;
+        const int nblk = p.act_rows * bpr;
+        auto load_x = [&](int b) -> float4 {
+            if (b >= nblk) return make_float4(0.f, 0.f, 0.f, 0.f);
+            const int m = b / bpr, kb = b - m * bpr;
+            return __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8);
+        };
+        float4 nxt = load_x(grp);
+        // whole warps iterate together so the 8-lane shuffles stay converged
+        for (int base = 0; base < nblk; base += GROUPS) {
+            const int b = base + grp;
+            const bool live = b < nblk;
+            const int m = live ? b / bpr : 0, kb = live ? b - m * bpr : 0;
+            const float4 v = nxt;
+            nxt = load_x(b + GROUPS);
+            uint32_t packed; int hs;
+            const float d = quantize_block_8lanes(v, packed, hs);
+            const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
+            if (live) {
+                uint8_t* rec = smem + OFF_ACT + m * p.act_row_stride + (kb >> 2) * REC_BYTES;
+                reinterpret_cast<uint32_t*>(rec + 32 * (kb & 3))[t8] = packed;
+                if (t8 == 0) {
+                    const short lo = static_cast<short>(hs), hi = static_cast<short>(hs_hi);
+                    reinterpret_cast<float*>(rec + 128)[kb & 3] = d;
+                    reinterpret_cast<float*>(rec + 144)[kb & 3] =
+                        d * static_cast<float>(static_cast<int>(lo) + static_cast<int>(hi));
+                    if (p.isum_row_stride) {
+                        short* is = reinterpret_cast<short*>(smem + p.off_isum + m * p.isum_row_stride + kb * 4);
+                        is[0] = lo; is[1] = hi;
                     }
                 }
             }
-            named_bar_sync(1, CONSUMER_WARPS * 32);
         }
+        named_bar_sync(1, (WARPS + 1) * 32);      // all consumers + the producer's arrive
+    }
 
-        // (2) stream tiles: warp r owns row r of every tile
-        const int n_items = Traits<TYPE>::items(p.K);
-        const uint32_t act0 = sbase + OFF_ACT, isum0 = sbase + p.off_isum;
-        float acc[M], acc2[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) { acc[m] = 0.f; acc2[m] = 0.f; }
-        Tile t;
-        int tix = 0;
-        while (walk.next(t)) {
-            const int s = tix % p.n_stages;
-            const uint32_t ph = (tix / p.n_stages) & 1;
-            if (!mbar_wait_bounded(sbase + OFF_FULL + 8 * s, ph) || *abort_flag) {
-                if (!*abort_flag) { atomicExch(p.err, DEV_TIMEOUT_FULL); *abort_flag = 1; }
-                break;
-            }
-            if (warp < t.nrows) {
-                const uint32_t stage = stages + s * p.stage_bytes;
-                uint32_t row;      // shared address where byte 0 of this warp's weight row would sit
-                if (p.n_slices == 1) {
-                    const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.w + t.src_off) & 15u);
-                    row = stage + mis + warp * p.rb;
-                } else {
-                    const uint32_t off = static_cast<uint32_t>(t.slice) * p.slice_bytes;
-                    const uint32_t mis = static_cast<uint32_t>(
-                        reinterpret_cast<uintptr_t>(p.w + t.src_off + static_cast<long long>(warp) * p.rb + off) & 15u);
-                    row = stage + warp * p.slot_bytes + mis - off;
+    // (2) stream this warp's units
+    Walker wk = walker_of(warp);
+    Unit un;
+    const uint32_t ring = ring_of(warp);
+    const int n_items = (p.K / block_elems(TYPE)) * Traits<TYPE>::ITEMS_PER_BLOCK;
+    const uint32_t act0 = sbase + OFF_ACT, isum0 = sbase + p.off_isum;
+    int u = 0;
+    bool ok = true;
+
+    if constexpr (RESIDENT) {
+        Q4KAct xr;
+        const bool has_item = lane < n_items;
+        if (has_item) q4k_load_act(act0 + lane * REC_BYTES, xr);
+        for (; wk.next(p, un); ++u) {
+            const int slot = u % p.n_slots;
+            if (!mbar_wait_bounded(bar_full(warp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
+            int r = 0;
+            for (; r + 2 <= un.nrows; r += 2) {                   // two rows at a time: independent chains
+                float a0 = 0.f, a1 = 0.f;
+                if (has_item) {
+                    Q4KWts w0, w1;
+                    q4k_load_wts(base + r * p.rb, lane, w0);
+                    q4k_load_wts(base + (r + 1) * p.rb, lane, w1);
+                    a0 = q4k_dot(w0, xr);
+                    a1 = q4k_dot(w1, xr);
                 }
-                const int arow = p.per_seg_x ? t.seg : 0;
-                const uint32_t act = act0 + arow * p.act_row_stride;
-                const uint32_t isum = isum0 + arow * p.isum_row_stride;
-                const int i0 = t.slice * p.slice_items;
-                const int i1 = (i0 + p.slice_items) < n_items ? (i0 + p.slice_items) : n_items;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+                    a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+                }
+                if (lane == 0) { p.y[un.j + r] = a0; p.y[un.j + r + 1] = a1; }
+            }
+            if (r < un.nrows) {
+                float a0 = 0.f;
+                if (has_item) {
+                    Q4KWts w0;
+                    q4k_load_wts(base + r * p.rb, lane, w0);
+                    a0 = q4k_dot(w0, xr);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+                if (lane == 0) p.y[un.j + r] = a0;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty(warp, slot));                  // slot may be refilled
+        }
+    } else {
+        float acc[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m] = 0.f;
+        for (; wk.next(p, un); ++u) {
+            const int slot = u % p.n_slots;
+            if (!mbar_wait_bounded(bar_full(warp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.w + un.src_off) & 15u);
+            const int arow = p.per_seg_x ? un.seg : 0;
+            const uint32_t act = act0 + arow * p.act_row_stride, isum = isum0 + arow * p.isum_row_stride;
+            const int i0 = un.slice * p.slice_items;
+            const int i1 = (i0 + p.slice_items) < n_items ? (i0 + p.slice_items) : n_items;
+            for (int r = 0; r < un.nrows; ++r) {
+                // shared address where byte 0 of this weight row would sit
+                const uint32_t row = ring + slot * p.slot_bytes + mis + r * p.rb - static_cast<uint32_t>(un.slice) * p.slice_bytes;
                 for (int i = i0 + lane; i < i1; i += 32)
-                    Traits<TYPE>::template item<M>(row, i, act, p.act_row_stride, isum, p.isum_row_stride, acc, acc2);
-                if (t.slice == p.n_slices - 1) {
+                    Traits<TYPE>::template item<M>(row, i, act, p.act_row_stride, isum, p.isum_row_stride, acc);
+                if (un.slice == p.n_slices - 1) {
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
-                        float a = acc[m], b = acc2[m];
+                        float a = acc[m];
 #pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) {
-                            a += __shfl_xor_sync(0xffffffffu, a, o);
-                            b += __shfl_xor_sync(0xffffffffu, b, o);
-                        }
-                        if (lane == 0)
-                            p.y[(static_cast<size_t>(t.seg) * M + m) * p.N + t.j0 + warp] = a - b;
-                        acc[m] = 0.f; acc2[m] = 0.f;
+                        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                        if (lane == 0) p.y[(static_cast<size_t>(un.seg) * M + m) * p.N + un.j + r] = a;
+                        acc[m] = 0.f;
                     }
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(sbase + OFF_EMPTY + 8 * s);
-            ++tix;
+            if (lane == 0) mbar_arrive(bar_empty(warp, slot));                  // slot may be refilled
         }
     }
-    __syncthreads();
+    if (!ok && lane == 0) atomicExch(p.err, DEV_TIMEOUT_FULL);   // the producer drains the copies
+}
+
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false>
+cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+    // The opt-in shared-memory size is raised once per instantiation (not on
+    // every launch, so launches stay legal inside a stream capture).
+    static bool configured = false;
+    auto k = gemv_stream_kernel<TYPE, M, WARPS, RESIDENT>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(ctx().smem_optin));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    k<<<grid, (WARPS + 1) * 32, smem, st>>>(p);
+    return cudaGetLastError();
 }
 
 template <uint32_t TYPE>
-cudaError_t launch_typed(int M, const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
-#define LP_CASE(MM)                                                                                  \
-    case MM: {                                                                                       \
-        auto k = gemv_stream_kernel<TYPE, MM>;                                                       \
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        if (e != cudaSuccess) return e;                                                              \
-        k<<<grid, THREADS, smem, st>>>(p);                                                           \
-        return cudaGetLastError();                                                                   \
-    }
+cudaError_t launch_typed(int M, bool resident, const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     switch (M) {
-        LP_CASE(1) LP_CASE(2) LP_CASE(3) LP_CASE(4) LP_CASE(5) LP_CASE(6) LP_CASE(7) LP_CASE(8)
+        case 1:
+            if constexpr (TYPE == LAPLACE_TYPE_Q4_K) {
+                if (resident) return launch_one<TYPE, 1, 16, true>(p, grid, smem, st);
+            }
+            return launch_one<TYPE, 1, 24>(p, grid, smem, st);
+        case 2: return launch_one<TYPE, 2, 24>(p, grid, smem, st);
+        case 3: return launch_one<TYPE, 3, 16>(p, grid, smem, st);
+        case 4: return launch_one<TYPE, 4, 16>(p, grid, smem, st);
+        case 5: return launch_one<TYPE, 5, 16>(p, grid, smem, st);
+        case 6: return launch_one<TYPE, 6, 16>(p, grid, smem, st);
+        case 7: return launch_one<TYPE, 7, 16>(p, grid, smem, st);
+        case 8: return launch_one<TYPE, 8, 16>(p, grid, smem, st);
         default: return cudaErrorInvalidValue;
     }
-#undef LP_CASE
 }
 
 }  // namespace
@@ -446,75 +552,90 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     if (a.N <= 0 || a.n_seg <= 0) return fail(LAPLACE_ERR_ARG, "gemv: N=%d n_seg=%d", a.N, a.n_seg);
     if (reinterpret_cast<uintptr_t>(a.w) & 1) return fail(LAPLACE_ERR_ARG, "gemv: weight pointer not 2-byte aligned");
     if (reinterpret_cast<uintptr_t>(a.x) & 15) return fail(LAPLACE_ERR_ARG, "gemv: x not 16-byte aligned");
+    if (a.type == LAPLACE_TYPE_Q4_K && (reinterpret_cast<uintptr_t>(a.w) & 15))
+        return fail(LAPLACE_ERR_ARG, "gemv: Q4_K weights must be 16-byte aligned on the device");
 
+    // Register-resident activations (see the kernel): Q4_K, one activation row,
+    // a plain matrix whose 16-byte-aligned rows hold at most 32 items.
+    const bool resident = a.type == LAPLACE_TYPE_Q4_K && a.M == 1 && !a.expert_idx && a.K <= 4096 &&
+                          (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
+    const int warps = resident ? 16 : (a.M <= 2 ? 24 : 16);   // consumer warps; one more warp issues the copies
     KParams p{};
     p.x = a.x; p.w = a.w; p.y = a.y; p.expert_idx = a.expert_idx; p.err = c.d_err;
     p.K = a.K; p.N = a.N; p.n_seg = a.n_seg; p.per_seg_x = a.per_seg_x;
     p.act_rows = a.per_seg_x ? a.n_seg : a.M;
     p.rb = static_cast<uint32_t>(row_bytes(a.type, a.K));
-    if (a.type == LAPLACE_TYPE_Q4_K && (reinterpret_cast<uintptr_t>(a.w) & 15))
-        return fail(LAPLACE_ERR_ARG, "gemv: Q4_K weights must be 16-byte aligned on the device");
-
-    p.act_row_stride = static_cast<uint32_t>((a.K + 63) / 64) * REC_BYTES;
+    p.act_row_stride = static_cast<uint32_t>((a.K + 127) / 128) * REC_BYTES;
     p.isum_row_stride = a.type == LAPLACE_TYPE_Q6_K ? static_cast<uint32_t>(a.K / 32) * 4 : 0;   // only Q6_K reads them
     const size_t act_bytes = static_cast<size_t>(p.act_rows) * p.act_row_stride;
     const size_t isum_bytes = (static_cast<size_t>(p.act_rows) * p.isum_row_stride + 15) & ~size_t(15);
     p.off_isum = static_cast<uint32_t>(OFF_ACT + act_bytes);
-    p.off_stages = static_cast<uint32_t>((p.off_isum + isum_bytes + 127) & ~size_t(127));
+    p.off_ring = static_cast<uint32_t>((p.off_isum + isum_bytes + 127) & ~size_t(127));
 
-    // K-slicing. A stage holds one slice of 16 rows. Aim at ~2.5 KB per row
-    // (a ~40 KB stage) but shrink the slice when the quantized activations
-    // leave little room, so that at least 3 stages fit. Slice boundaries sit on
-    // multiples of 8 blocks (any super-block for Q4_K), which keeps them
-    // 16-byte aligned relative to the start of the row.
-    int unit_blocks, items_per_block;
-    switch (a.type) {
-        case LAPLACE_TYPE_Q4_K: unit_blocks = 1; items_per_block = 4; break;
-        case LAPLACE_TYPE_Q6_K: unit_blocks = 8; items_per_block = 4; break;
-        default:                unit_blocks = 8; items_per_block = 1; break;   // Q4_0, Q8_0
-    }
+    // Ring planning. Each warp gets an equal share of what the activations
+    // leave; a slot holds one K-slice of one row plus slack for a source that
+    // is not 16-byte aligned (<= 15 bytes in front) and the 4-byte read-ahead
+    // of the unaligned loads. Slice boundaries sit on multiples of 8 blocks
+    // (any super-block for Q4_K) so they are 16-byte aligned within the row.
+    const int unit_blocks = a.type == LAPLACE_TYPE_Q4_K ? 1 : 8;   // 8 x 210, 8 x 18, 8 x 34 are multiples of 16
+    const int items_per_block = a.type == LAPLACE_TYPE_Q4_K ? 2 : (a.type == LAPLACE_TYPE_Q6_K ? 4 : 1);
     const uint32_t bpb = static_cast<uint32_t>(block_bytes(a.type));
     const int n_blocks = a.K / epb;
     const size_t budget = c.smem_optin;
-    if (p.off_stages + 4096 > budget)
-        return fail(LAPLACE_ERR_LIMIT, "gemv: M=%d K=%d: activations alone fill shared memory", a.M, a.K);
-    const size_t ring = budget - p.off_stages;
-    size_t target = ring / (3 * CONSUMER_WARPS);      // per-row bytes that allow 3 stages
-    if (target > 2560) target = 2560;
-    if (p.rb + 4 <= target) {
-        p.n_slices = 1;
-        p.slice_bytes = p.rb;
-        p.slice_items = n_blocks * items_per_block;
-        p.slot_bytes = p.rb;
-        p.stage_bytes = static_cast<uint32_t>((static_cast<size_t>(CONSUMER_WARPS) * p.rb + 64 + 15) & ~size_t(15));
+    if (p.off_ring + static_cast<size_t>(warps) * 2 * 256 > budget)
+        return fail(LAPLACE_ERR_LIMIT, "gemv: M=%d K=%d: the quantized activations do not fit shared memory", a.M, a.K);
+    const size_t per_warp = ((budget - p.off_ring) / warps) & ~size_t(15);
+    const bool aligned_rows = (p.rb % 16 == 0) && ((reinterpret_cast<uintptr_t>(a.w) & 15) == 0) &&
+                              (a.type == LAPLACE_TYPE_Q4_K);          // the others read 4 bytes ahead
+    const uint32_t slack = aligned_rows ? 0u : 32u;
+    const uint32_t unit_bytes = bpb * unit_blocks;
+    const int units_total = (n_blocks + unit_blocks - 1) / unit_blocks;
+    auto slot_cap = [&](int n_slots) { return (per_warp / n_slots) & ~size_t(15); };
+    p.rows_per_unit = 1;
+    if (p.rb + slack <= slot_cap(2)) {
+        // whole rows; as many per copy as give ~4.6 KB copies and still leave two slots (three if possible)
+        int R = static_cast<int>((4608 + p.rb / 2) / p.rb);
+        if (R < 1) R = 1;
+        if (R > 8) R = 8;
+        while (R > 1 && static_cast<size_t>(R) * p.rb + slack > slot_cap(3)) --R;
+        if (static_cast<size_t>(R) * p.rb + slack > slot_cap(3)) p.n_slots = 2; else p.n_slots = 3;
+        p.rows_per_unit = R;
+        p.n_slices = 1; p.slice_bytes = p.rb; p.slice_items = n_blocks * items_per_block;
+        p.slot_bytes = (static_cast<uint32_t>(R) * p.rb + slack + 15u) & ~15u;
     } else {
-        int units = target > 48 ? static_cast<int>((target - 48) / (bpb * unit_blocks)) : 0;
-        if (units < 1) units = 1;
-        const int slice_blocks = units * unit_blocks;
+        // long rows: equal K-slices, three slots
+        const size_t cap = slot_cap(3);
+        if (cap < unit_bytes + slack)
+            return fail(LAPLACE_ERR_LIMIT, "gemv: M=%d K=%d needs more shared memory than one SM has", a.M, a.K);
+        const int max_units = static_cast<int>((cap - slack) / unit_bytes);
+        p.n_slices = (units_total + max_units - 1) / max_units;
+        const int slice_blocks = ((units_total + p.n_slices - 1) / p.n_slices) * unit_blocks;
         p.n_slices = (n_blocks + slice_blocks - 1) / slice_blocks;
         p.slice_bytes = static_cast<uint32_t>(slice_blocks) * bpb;
         p.slice_items = slice_blocks * items_per_block;
-        p.slot_bytes = (p.slice_bytes + 15 + 16 + 15) & ~15u;      // misalignment + read-ahead slack
-        p.stage_bytes = CONSUMER_WARPS * p.slot_bytes;
+        p.n_slots = 3;
+        p.slot_bytes = (p.slice_bytes + slack + 15u) & ~15u;
     }
-    int stages = static_cast<int>(ring / p.stage_bytes);
-    if (stages < 2)
-        return fail(LAPLACE_ERR_LIMIT, "gemv: M=%d K=%d needs more shared memory than one SM has", a.M, a.K);
-    if (stages > MAX_STAGES) stages = MAX_STAGES;
-    p.n_stages = stages;
-    const size_t smem = p.off_stages + static_cast<size_t>(stages) * p.stage_bytes;
+    // spare room: a deeper ring
+    while (p.n_slots < MAX_SLOTS && static_cast<size_t>(p.n_slots + 1) * p.slot_bytes <= per_warp) p.n_slots++;
+    const size_t smem = p.off_ring + static_cast<size_t>(warps) * p.n_slots * p.slot_bytes;
+    if (resident && (p.n_slices != 1 || slack != 0))
+        return fail(LAPLACE_ERR_STATE, "gemv: internal planning error (resident path needs whole aligned rows)");
 
     const long long total_rows = static_cast<long long>(a.n_seg) * a.N;
-    long long tiles = (total_rows + CONSUMER_WARPS - 1) / CONSUMER_WARPS;
+    if (total_rows >= (1LL << 31)) return fail(LAPLACE_ERR_LIMIT, "gemv: more than 2^31 weight rows");
+    const long long want = (total_rows + warps * p.rows_per_unit - 1) / (warps * p.rows_per_unit);
     int grid = c.sm_count;
-    if (tiles < grid) grid = static_cast<int>(tiles);
+    if (want < grid) grid = static_cast<int>(want);
+    p.rows_q = static_cast<int>(total_rows / grid);
+    p.rows_r = static_cast<int>(total_rows % grid);
 
     cudaError_t e;
     switch (a.type) {
-        case LAPLACE_TYPE_Q4_K: e = launch_typed<LAPLACE_TYPE_Q4_K>(a.M, p, dim3(grid), smem, st); break;
-        case LAPLACE_TYPE_Q6_K: e = launch_typed<LAPLACE_TYPE_Q6_K>(a.M, p, dim3(grid), smem, st); break;
-        case LAPLACE_TYPE_Q4_0: e = launch_typed<LAPLACE_TYPE_Q4_0>(a.M, p, dim3(grid), smem, st); break;
-        case LAPLACE_TYPE_Q8_0: e = launch_typed<LAPLACE_TYPE_Q8_0>(a.M, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q4_K: e = launch_typed<LAPLACE_TYPE_Q4_K>(a.M, resident, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q6_K: e = launch_typed<LAPLACE_TYPE_Q6_K>(a.M, false, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q4_0: e = launch_typed<LAPLACE_TYPE_Q4_0>(a.M, false, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q8_0: e = launch_typed<LAPLACE_TYPE_Q8_0>(a.M, false, p, dim3(grid), smem, st); break;
         default: return LAPLACE_UNSUPPORTED;
     }
     c.launches++;

@@ -201,7 +201,7 @@ static inline float hsum_pair(const float a[4], const float b[4]) {
 /* src/matmul_simd.cpp:143-160 */
 static double dot_q8_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode, int32_t* sums) {
     float  acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
-    double acc64 = 0.0;
+    double acc64 = 0.0, mass = 0.0;
     for (int b = 0; b < K / 32; b++) {
         const uint8_t* blk = row + (size_t)b * Q8_0_BYTES;
         const int8_t*  wq  = (const int8_t*)(blk + 2);
@@ -213,8 +213,11 @@ static double dot_q8_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
         float scale = dw * xa[b].d;
         fma_lanes(acc0, scale, p0);
         fma_lanes(acc1, scale, p1);
-        acc64 += (double)dw * (double)xa[b].d * (double)(sum4(p0) + sum4(p1));
+        double term = (double)dw * (double)xa[b].d * (double)(sum4(p0) + sum4(p1));
+        acc64 += term;
+        mass += fabs(term);
     }
+    if (mode == LPO_MODE_MASS) return mass;
     return mode == LPO_MODE_F64 ? acc64 : (double)hsum_pair(acc0, acc1);
 }
 
@@ -225,7 +228,7 @@ static double dot_q8_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
 static double dot_q4_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode, int32_t* sums) {
     float  acc[4] = {0, 0, 0, 0};
     float  acc_offset = 0.0f;
-    double acc64 = 0.0;
+    double acc64 = 0.0, mass = 0.0;
     for (int b = 0; b < K / 32; b++) {
         const uint8_t* blk = row + (size_t)b * Q4_0_BYTES;
         float dw = lpo_fp16_to_fp32(rd16(blk));
@@ -239,9 +242,12 @@ static double dot_q4_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
         fma_lanes(acc, scale, p0);
         fma_lanes(acc, scale, p1);
         acc_offset += dw * 8.0f * xa[b].sum;
-        acc64 += (double)dw * (double)xa[b].d * (double)(sum4(p0) + sum4(p1))
-               - (double)dw * 8.0 * (double)xa[b].sum;
+        double t1 = (double)dw * (double)xa[b].d * (double)(sum4(p0) + sum4(p1));
+        double t2 = (double)dw * 8.0 * (double)xa[b].sum;
+        acc64 += t1 - t2;
+        mass += fabs(t1) + fabs(t2);
     }
+    if (mode == LPO_MODE_MASS) return mass;
     return mode == LPO_MODE_F64 ? acc64 : (double)(hsum4(acc) - acc_offset);
 }
 
@@ -251,7 +257,7 @@ static double dot_q4_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
 static double dot_q4_k(const lpo_actq8* xa, const uint8_t* row, int K, int mode, int32_t* sums) {
     float  acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
     float  acc_min = 0.0f;
-    double acc64 = 0.0;
+    double acc64 = 0.0, mass = 0.0;
     for (int sb = 0; sb < K / 256; sb++) {
         const uint8_t*   blk = row + (size_t)sb * Q4_K_BYTES;
         const lpo_actq8* xs  = xa + (size_t)sb * 8;
@@ -282,10 +288,13 @@ static double dot_q4_k(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
             fma_lanes(acc0, s2, p2a);
             fma_lanes(acc1, s2, p2b);
             acc_min += m1 * a1->sum + m2 * a2->sum;
-            acc64 += (double)d * sc1 * (double)a1->d * u1 + (double)d * sc2 * (double)a2->d * u2
-                   - (double)dmin * mn1 * (double)a1->sum - (double)dmin * mn2 * (double)a2->sum;
+            double t1 = (double)d * sc1 * (double)a1->d * u1, t2 = (double)d * sc2 * (double)a2->d * u2;
+            double t3 = (double)dmin * mn1 * (double)a1->sum, t4 = (double)dmin * mn2 * (double)a2->sum;
+            acc64 += t1 + t2 - t3 - t4;
+            mass += fabs(t1) + fabs(t2) + fabs(t3) + fabs(t4);
         }
     }
+    if (mode == LPO_MODE_MASS) return mass;
     return mode == LPO_MODE_F64 ? acc64 : (double)(hsum_pair(acc0, acc1) - acc_min);
 }
 
@@ -295,7 +304,7 @@ static double dot_q4_k(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
  * dot, and each 32-weight group carries two int8 sub-scales (one per 16). */
 static double dot_q6_k(const lpo_actq8* xa, const uint8_t* row, int K, int mode, int32_t* sums) {
     float  acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
-    double acc64 = 0.0;
+    double acc64 = 0.0, mass = 0.0;
     for (int sb = 0; sb < K / 256; sb++) {
         const uint8_t* blk = row + (size_t)sb * Q6_K_BYTES;
         const int8_t*  sc  = (const int8_t*)(blk + 192);
@@ -319,10 +328,14 @@ static double dot_q6_k(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
                 float scale1 = d * a->d * (float)s1;
                 fma_lanes(acc0, scale0, p0);
                 fma_lanes(acc1, scale1, p1);
-                acc64 += (double)d * (double)a->d * ((double)s0 * sum4(p0) + (double)s1 * sum4(p1));
+                double t0 = (double)d * (double)a->d * (double)s0 * sum4(p0);
+                double t1 = (double)d * (double)a->d * (double)s1 * sum4(p1);
+                acc64 += t0 + t1;
+                mass += fabs(t0) + fabs(t1);
             }
         }
     }
+    if (mode == LPO_MODE_MASS) return mass;
     return mode == LPO_MODE_F64 ? acc64 : (double)hsum_pair(acc0, acc1);
 }
 

@@ -53,7 +53,9 @@ typedef struct {
 /* Result modes of the dot products. */
 enum {
     LPO_MODE_F32_LANES = 0, /* fp32, same accumulator lanes and fma order as the NEON code */
-    LPO_MODE_F64       = 1  /* every product and sum in double; for error measurement */
+    LPO_MODE_F64       = 1, /* every product and sum in double; for error measurement */
+    LPO_MODE_MASS      = 2  /* sum of |term| in double: the magnitude that fp32 accumulation
+                               error scales with when the terms cancel */
 };
 
 float    lpo_fp16_to_fp32(uint16_t h);

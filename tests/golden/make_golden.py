@@ -1,0 +1,76 @@
+"""Regenerates tests/golden/hotpath_golden.npz. Run where the reference checkout is present:
+
+    make -C oracle all ref && python tests/golden/make_golden.py
+
+The file pins two things for machines that have no reference checkout:
+  * outputs of the reference's OWN code (oracle/_ref/libref_matmul.so, built
+    from its sources): dequantize(), the scalar fp32-activation matmul_rows,
+    and its fp16 conversions, on small seeded inputs;
+  * outputs of the C restatement of its int8 path (liboracle_q8.so) on the same
+    inputs: quantized activation blocks, integer block sums, fp32 (lane-order)
+    and float64 results, so that a later edit of the oracle cannot drift
+    silently and GPU tests can compare against stored vectors.
+Inputs are regenerated from seeds by laplace_b200.synth and are stored too.
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+from laplace_b200 import synth  # noqa: E402
+from tests.oracle_lib import Oracle, Reference  # noqa: E402
+
+CASES = [  # (type, how, M, K, N, seed)
+    (2, "random", 2, 512, 8, 1), (2, "ref", 1, 512, 5, 2), (2, "affine", 1, 256, 4, 3),
+    (8, "random", 2, 512, 8, 4), (8, "ref", 1, 512, 5, 5), (8, "affine", 1, 256, 4, 6),
+    (12, "random", 2, 512, 8, 7), (12, "ref", 1, 768, 5, 8), (12, "affine", 1, 256, 4, 9),
+    (14, "random", 2, 512, 8, 10), (14, "ref", 1, 768, 5, 11), (14, "affine", 1, 256, 4, 12),
+]
+
+
+def main():
+    o, r = Oracle(), Reference()
+    out = {}
+    hs = np.concatenate([np.array([0x3C00, 0xC000, 0x0000, 0x7BFF, 0x0001, 0x8000, 0x7C00, 0x03FF, 0x0400], dtype=np.uint16),
+                         synth.rng(77).integers(0, 0x7C00, size=1000, dtype=np.uint16)])
+    out["fp16_bits"] = hs
+    out["fp16_ref_f32"] = np.array([r.lib.ref_fp16_to_fp32(int(h)) for h in hs], dtype=np.float32)
+    fs = np.concatenate([synth.normal_f32(78, 500, 1.0), synth.normal_f32(79, 500, 1e-5),
+                         np.array([1.0, -2.0, 65504.0, 65520.0, 1e9, 6e-8, 2.98e-8, 0.1], dtype=np.float32)])
+    out["f32_vals"] = fs
+    out["f32_ref_fp16"] = np.array([r.lib.ref_fp32_to_fp16(float(v)) for v in fs], dtype=np.uint16)
+    for i, (t, how, M, K, N, seed) in enumerate(CASES):
+        w = synth.weights(t, K, N, seed=9000 + seed, how=how)
+        x = synth.normal_f32(9100 + seed, (M, K))
+        p = f"c{i}_"
+        out[p + "meta"] = np.array([t, M, K, N], dtype=np.int64)
+        out[p + "how"] = np.array(how)
+        out[p + "w"] = w
+        out[p + "x"] = x
+        out[p + "ref_dequant"] = r.dequantize(w, t, K * N)
+        out[p + "ref_scalar_y"] = r.matmul_rows(x, w, t, M, K, N)
+        out[p + "act"] = o.quantize(x).view(np.uint8)
+        out[p + "blocksums"] = o.blocksums(x, w, t, M, K, N)
+        out[p + "y_f32"] = o.gemm(x, w, t, M, K, N, mode=0)
+        out[p + "y_f64"] = o.gemm(x, w, t, M, K, N, mode=1)
+    # expert-indexed calls (the reference's scalar fall-back path, src/matmul.cpp:469-499)
+    t, K, N, n_total = 12, 256, 6, 5
+    w = synth.weights(t, K, N * n_total, seed=9500, how="affine")
+    idx = np.array([3, 0, 4], dtype=np.int32)
+    x = synth.normal_f32(9501, (3, K))
+    out["moe_w"], out["moe_idx"], out["moe_x"] = w, idx, x
+    out["moe_meta"] = np.array([t, K, N, n_total], dtype=np.int64)
+    out["moe_ref_scalar_idx"] = r.moe(x[0], w, t, idx, n_total, K, N, multi=False)
+    out["moe_ref_scalar_multi"] = r.moe(x, w, t, idx, n_total, K, N, multi=True)
+    out["moe_y_idx_f64"] = o.moe_gemv(x[0], w, t, idx, K, N, multi=False, mode=1)
+    out["moe_y_multi_f64"] = o.moe_gemv(x, w, t, idx, K, N, multi=True, mode=1)
+    path = Path(__file__).with_name("hotpath_golden.npz")
+    np.savez_compressed(path, **out)
+    print(path, path.stat().st_size, "bytes")
+
+
+if __name__ == "__main__":
+    main()

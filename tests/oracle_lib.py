@@ -18,7 +18,7 @@ ORACLE_DIR = Path(__file__).resolve().parent.parent / "oracle"
 ACTQ8 = np.dtype([("d", "<f4"), ("sum", "<f4"), ("sum_lo", "<i2"), ("sum_hi", "<i2"), ("qs", "i1", (32,))])
 assert ACTQ8.itemsize == 44
 
-MODE_F32, MODE_F64 = 0, 1
+MODE_F32, MODE_F64, MODE_MASS = 0, 1, 2
 _vp, _i, _u32 = C.c_void_p, C.c_int, C.c_uint32
 
 
