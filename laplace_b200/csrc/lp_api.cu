@@ -73,15 +73,14 @@ int require_ready() {
     return LAPLACE_OK;
 }
 
-// Reads and clears the device status word after the stream has drained.
+// Drains the stream, then reads and clears the status word. The word lives in
+// mapped pinned host memory, so reading it costs no copy.
 int check_device_status(cudaStream_t st) {
-    int h = 0;
-    cudaError_t e = cudaMemcpyAsync(&h, g_ctx.d_err, sizeof h, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) return cuda_check(e, "reading device status");
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_check(e, "stream synchronize");
+    const int h = *static_cast<volatile int*>(g_ctx.h_err);
     if (h != DEV_OK) {
-        cudaMemsetAsync(g_ctx.d_err, 0, sizeof(int), st);
-        cudaStreamSynchronize(st);
+        *g_ctx.h_err = DEV_OK;
         return fail(LAPLACE_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", h);
     }
     return LAPLACE_OK;
@@ -199,9 +198,13 @@ int laplace_cuda_init(int device) {
     g_ctx.device = device;
     g_ctx.sm_count = prop.multiProcessorCount;
     g_ctx.smem_optin = prop.sharedMemPerBlockOptin;
+    g_ctx.smem_per_sm = prop.sharedMemPerMultiprocessor;
     if ((rc = cuda_check(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking), "cudaStreamCreate"))) return rc;
-    if ((rc = cuda_check(cudaMalloc(&g_ctx.d_err, sizeof(int)), "cudaMalloc status"))) return rc;
-    if ((rc = cuda_check(cudaMemset(g_ctx.d_err, 0, sizeof(int)), "cudaMemset status"))) return rc;
+    if ((rc = cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&g_ctx.h_err), sizeof(int), cudaHostAllocMapped),
+                         "cudaHostAlloc status"))) return rc;
+    *g_ctx.h_err = DEV_OK;
+    if ((rc = cuda_check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_ctx.d_err), g_ctx.h_err, 0),
+                         "cudaHostGetDevicePointer status"))) return rc;
     g_ctx.ready = true;
     return LAPLACE_OK;
 }
@@ -215,7 +218,7 @@ void laplace_cuda_shutdown(void) {
     g_regions.clear();
     g_dx.release(); g_dy.release(); g_dw.release(); g_didx.release(); g_dq.release();
     g_hx.release(); g_hy.release();
-    cudaFree(g_ctx.d_err);
+    cudaFreeHost(g_ctx.h_err);
     cudaStreamDestroy(g_ctx.stream);
     g_ctx = Context{};
 }

@@ -40,9 +40,11 @@ struct Context {
     bool         ready = false;
     int          device = -1;
     int          sm_count = 0;
-    size_t       smem_optin = 0;
+    size_t       smem_optin = 0;       // largest dynamic shared memory one CTA may ask for
+    size_t       smem_per_sm = 0;      // shared memory of one SM
     cudaStream_t stream = nullptr;
-    int*         d_err = nullptr;      // device-side status word, 0 = fine
+    int*         d_err = nullptr;      // device view of the status word, 0 = fine
+    int*         h_err = nullptr;      // host view of the same word (mapped pinned memory)
     int          last_path = 0;
     long long    launches = 0;
 };
@@ -75,6 +77,12 @@ int launch_blocksums_q(const int8_t* q, const uint8_t* w, uint32_t type, int32_t
 
 // ---- device helpers ---------------------------------------------------------
 #ifdef __CUDACC__
+
+// Records a device-side failure in the status word (host-mapped memory).
+__device__ __forceinline__ void report_status(int* err, int code) {
+    *reinterpret_cast<volatile int*>(err) = code;
+    __threadfence_system();
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -3,7 +3,7 @@
 // prologue. Replaces the row loop + dot kernels of Laplace's NEON back-end
 // (src/matmul_simd.cpp:143-342, 348-455, 506-544) for small M.
 //
-// Shape of the kernel (one persistent CTA per SM, 24+1 warps for M <= 2):
+// Shape of the kernel (one persistent CTA per SM):
 //   * every consumer warp owns a private ring of shared-memory slots that a
 //     producer warp fills with its weight rows by 1-D bulk copies (TMA engine,
 //     cp.async.bulk, no multicast), a full/empty mbarrier pair per slot. A row
@@ -19,6 +19,7 @@
 // HBM traffic is the packed weights once, plus x and y. Every wait is bounded:
 // a wait that gives up raises a status word, the warp drains its own copies
 // and leaves.
+#include <cstdlib>
 #include "lp_common.cuh"
 
 namespace lp {
@@ -26,6 +27,7 @@ namespace lp {
 namespace {
 
 constexpr int MAX_SLOTS = 4;
+constexpr int PRODUCER_WARPS = 4;   // a lane issues a bulk copy in ~100 cycles; four warps issue in parallel
 constexpr int REC_BYTES = 176;   // activation record per 128 values: 128 int8, d[4], sum[4], 16 pad
                                  // (44 words: consecutive lanes fall in distinct bank groups)
 
@@ -50,6 +52,7 @@ struct KParams {
     uint32_t       isum_row_stride; // bytes between rows of the int16 half-sums (Q6_K only, else 0)
     uint32_t       off_isum, off_ring;
     int            rows_q, rows_r;  // CTA b owns rows_q (+1 if b < rows_r) rows
+    int            pdl;
 };
 
 // Shared-memory map: [0, 64 * warps) slot barriers (per consumer warp: 4 "full"
@@ -296,21 +299,24 @@ struct Walker {
     }
 };
 
-// WARPS consumer warps plus one producer warp. Lane w of the producer serves
-// consumer w: it waits for a slot of w's ring to be released and issues the
-// next bulk copy into it. Issuing a bulk copy holds the issuing lane for ~100
-// cycles and the SM's copy engine takes roughly one copy per 55 cycles, so
-// consumers never issue copies themselves, and copies are made as large as the
-// ring allows (two 2.3 KB rows per copy move ~1.5x faster than one).
+// WARPS consumer warps plus PRODUCER_WARPS producer warps. One producer lane
+// serves one consumer: it waits for a slot of that consumer's ring to be
+// released and issues the next bulk copy into it. Issuing a bulk copy holds the
+// issuing lane for ~100 cycles (lanes of one warp take turns) and the SM's copy
+// engine takes roughly one copy per 50 cycles, so consumers never issue copies
+// themselves, several warps issue in parallel, and copies are made as large as
+// the ring allows (two 2.3 KB rows per copy move ~1.5x faster than one).
 //
 // RESIDENT: M == 1, Q4_K, one item per lane and row (K <= 4096): the lane's
 // activation record never changes, so it lives in registers for the whole
 // kernel and the row loop reads only weights from shared memory.
 template <uint32_t TYPE, int M, int WARPS, bool RESIDENT>
-__global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const KParams p) {
+__global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_kernel(const KParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Let the next kernel in the stream start launching as SMs free up.
+    if (p.pdl == 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // This CTA's contiguous share of the n_seg * N weight rows (fewer than 2^31),
     // cut again into one contiguous range per consumer warp.
@@ -329,16 +335,21 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const 
     auto bar_empty = [&](int w, int slot) { return sbase + w * 64 + 32 + 8 * slot; };
     auto ring_of = [&](int w) { return sbase + p.off_ring + w * (p.n_slots * p.slot_bytes); };
 
-    if (warp == WARPS) {
-        // ------------------------------ producer warp ------------------------------
-        const int w = lane;
-        const bool serving = w < WARPS;
+    if (warp >= WARPS) {
+        // ------------------------------ producer warps -----------------------------
+        constexpr int PER = (WARPS + PRODUCER_WARPS - 1) / PRODUCER_WARPS;   // consumers served per producer warp
+        const int w = (warp - WARPS) * PER + lane;
+        const bool serving = lane < PER && w < WARPS;
         if (serving) {
             for (int s = 0; s < p.n_slots; ++s) { mbar_init(bar_full(w, s), 1); mbar_init(bar_empty(w, s), 1); }
         }
         fence_barrier_init();
         __syncwarp();
-        asm volatile("bar.arrive 1, %0;" :: "r"((WARPS + 1) * 32) : "memory");   // barriers exist; do not wait
+        // Order against the activations: the consumers' loads of x must enter the
+        // memory pipeline before any bulk copy, and the bulk of the copies only
+        // once x has arrived - a load issued behind ~220 KB of queued copy
+        // traffic waits microseconds for its turn.
+        named_bar_sync(2, (WARPS + PRODUCER_WARPS) * 32);   // consumers are issuing their loads of x
         const uint32_t ring = ring_of(w);
         Walker wk = walker_of(serving ? w : 0);
         if (!serving) wk.g_end = wk.g;
@@ -347,7 +358,12 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const 
         int ui = 0;
         uint32_t idle = 0;
         bool gave_up = false;
+        bool first_round = true;
         while (__any_sync(0xffffffffu, have)) {
+            if (first_round && __all_sync(0xffffffffu, !have || ui >= 1)) {
+                first_round = false;
+                named_bar_sync(1, (WARPS + PRODUCER_WARPS) * 32);       // x is quantized in shared memory; barriers visible
+            }
             bool issued = false;
             if (have) {
                 const int slot = ui % p.n_slots, round = ui / p.n_slots;
@@ -369,19 +385,22 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const 
                 if (++idle > (1u << 22)) { gave_up = true; break; }      // a consumer never released its slot
             }
         }
-        if (gave_up && lane == 0) atomicExch(p.err, DEV_TIMEOUT_EMPTY);
+        if (first_round) named_bar_sync(1, (WARPS + PRODUCER_WARPS) * 32);   // nothing to copy at all
+        if (gave_up && lane == 0) report_status(p.err, DEV_TIMEOUT_EMPTY);
         // Copies still in flight must land before the CTA gives its shared memory back.
         if (serving) {
             const int pending = ui < p.n_slots ? ui : p.n_slots;
             for (int k = 0; k < pending; ++k) {
                 const int v = ui - 1 - k;
-                if (!mbar_wait_bounded(bar_full(w, v % p.n_slots), (v / p.n_slots) & 1)) atomicExch(p.err, DEV_TIMEOUT_DRAIN);
+                if (!mbar_wait_bounded(bar_full(w, v % p.n_slots), (v / p.n_slots) & 1)) report_status(p.err, DEV_TIMEOUT_DRAIN);
             }
         }
         return;
     }
 
     // -------------------------------- consumer warps --------------------------------
+    // x may be produced, and y read, by the kernel before this one in the stream.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // (1) quantize the activations into shared memory while the rings fill. Each
     // group of 8 lanes owns 32-value blocks grp, grp + GROUPS, ...
     {
@@ -394,14 +413,18 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const 
             const int m = b / bpr, kb = b - m * bpr;
             return __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8);
         };
-        float4 nxt = load_x(grp);
+        // Tell the producers first: they need ~100 cycles from here to their
+        // first copy, the loads below are issued within a few.
+        asm volatile("bar.arrive 2, %0;" :: "r"((WARPS + PRODUCER_WARPS) * 32) : "memory");
+        float4 nxt = load_x(grp), nxt2 = load_x(grp + GROUPS);                   // two rounds ahead
         // whole warps iterate together so the 8-lane shuffles stay converged
         for (int base = 0; base < nblk; base += GROUPS) {
             const int b = base + grp;
             const bool live = b < nblk;
             const int m = live ? b / bpr : 0, kb = live ? b - m * bpr : 0;
             const float4 v = nxt;
-            nxt = load_x(b + GROUPS);
+            nxt = nxt2;
+            nxt2 = load_x(b + 2 * GROUPS);
             uint32_t packed; int hs;
             const float d = quantize_block_8lanes(v, packed, hs);
             const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
@@ -420,7 +443,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const 
                 }
             }
         }
-        named_bar_sync(1, (WARPS + 1) * 32);      // all consumers + the producer's arrive
+        named_bar_sync(1, (WARPS + PRODUCER_WARPS) * 32);      // all consumers + the producer's arrive
     }
 
     // (2) stream this warp's units
@@ -503,7 +526,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32, 1) gemv_stream_kernel(const 
             if (lane == 0) mbar_arrive(bar_empty(warp, slot));                  // slot may be refilled
         }
     }
-    if (!ok && lane == 0) atomicExch(p.err, DEV_TIMEOUT_FULL);   // the producer drains the copies
+    if (!ok && lane == 0) report_status(p.err, DEV_TIMEOUT_FULL);   // the producer drains the copies
+    if (p.pdl == 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false>
@@ -518,8 +542,21 @@ cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    k<<<grid, (WARPS + 1) * 32, smem, st>>>(p);
-    return cudaGetLastError();
+    // Programmatic dependent launch: this grid may start (and prefetch weights,
+    // which no earlier kernel writes) while the previous kernel in the stream
+    // is still draining; griddepcontrol.wait in the kernel orders the reads of
+    // x and the writes of y after that kernel's completion.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((WARPS + PRODUCER_WARPS) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k, p);
 }
 
 template <uint32_t TYPE>
@@ -627,6 +664,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     const long long want = (total_rows + warps * p.rows_per_unit - 1) / (warps * p.rows_per_unit);
     int grid = c.sm_count;
     if (want < grid) grid = static_cast<int>(want);
+    { static int mode = -1; if (mode < 0) { const char* e = getenv("LAPLACE_PDL"); mode = e ? atoi(e) : 2; } p.pdl = mode; }
     p.rows_q = static_cast<int>(total_rows / grid);
     p.rows_r = static_cast<int>(total_rows % grid);
 
