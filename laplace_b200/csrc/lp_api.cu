@@ -111,7 +111,11 @@ int dispatch_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float* y,
     if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
     if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm: null pointer");
     if (M <= 0 || N <= 0 || K <= 0) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
-    // Small M: one streaming pass per group of up to 8 activation rows.
+    if (K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm: K=%d is not a multiple of %d", K, block_elems(type));
+    // Prefill: tensor-core GEMM where one exists for the type.
+    if (gemm_tc_supports(type, M, K, N)) return launch_gemm_tc(x, w, type, y, M, K, N, st);
+    // Small M (or a type without a tensor-core kernel yet): one streaming pass
+    // per group of up to 8 activation rows.
     for (int m0 = 0; m0 < M; m0 += 8) {
         GemvArgs a{};
         a.x = x + static_cast<size_t>(m0) * K;
@@ -218,6 +222,7 @@ void laplace_cuda_shutdown(void) {
     g_regions.clear();
     g_dx.release(); g_dy.release(); g_dw.release(); g_didx.release(); g_dq.release();
     g_hx.release(); g_hy.release();
+    release_gemm_tc_scratch();
     cudaFreeHost(g_ctx.h_err);
     cudaStreamDestroy(g_ctx.stream);
     g_ctx = Context{};

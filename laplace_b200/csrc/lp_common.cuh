@@ -70,6 +70,11 @@ struct GemvArgs {
 };
 int launch_gemv_stream(const GemvArgs& a, cudaStream_t st);
 
+// Tensor-core prefill GEMM (lp_gemm_tc.cu). Uses library-owned scratch for the quantized activations.
+bool gemm_tc_supports(uint32_t type, int M, int K, int N);
+int  launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st);
+void release_gemm_tc_scratch();
+
 int launch_quantize_act(const float* x, int M, int K, int8_t* q, float* d, float* sum,
                         int16_t* isum, cudaStream_t st);
 int launch_blocksums_q(const int8_t* q, const uint8_t* w, uint32_t type, int32_t* out,

@@ -1,0 +1,490 @@
+// lp_gemm_tc.cu - prefill GEMM (M >= 9 activation rows) on the 5th-generation
+// tensor cores: Q4_K weights x Q8 activations with exact per-block integer
+// sums. Replaces gemm_int<dot_row_q4_k_int_neon> of Laplace's NEON back-end
+// (src/matmul_simd.cpp:226-283, 432-455) for large M.
+//
+// Why fp16 operands for an "int8" dot: every 32-value block carries its own
+// fp32 activation scale d_x, so the integer sum of each block has to leave the
+// tensor core and be scaled on CUDA cores; that per-block drain, not the MMA,
+// bounds throughput. With kind::f16 the accumulator already holds the block sum
+// as an exact fp32 integer (|sum| <= 32*945*127 < 2^24), so the drain is a
+// single FFMA per element - no int->float conversion - and the 6-bit sub-block
+// scale can ride inside the weight operand (sc*nibble <= 945 is exact in fp16):
+//
+//   y[m,n] = sum_sb d[n,sb] * ( sum_{j<8} d_x[m,8sb+j] * F[m,n,8sb+j] )
+//            - sum_b sum_x[m,b] * (dmin*mn)[n,b]
+//   F[m,n,b] = sum_{k in b} q_x[m,k] * (sc*nibble)[n,k]        (tcgen05.mma, exact)
+//
+// Roles in one 512-thread CTA (one CTA per SM, persistent over 128x128 tiles):
+//   warp 0      TMA: activation tiles (fp16 q values, 128 tokens x 64 k, 128-byte swizzle)
+//   warp 1      MMA issue (one lane) + TMEM allocation
+//   warps 4-7   converters: packed Q4_K super-blocks (global) -> fp16 weight operand
+//               tile in shared memory (same swizzle) + per-column scale tables
+//   warps 8-15  epilogue: tcgen05.ld of each block's 128x128 fp32 tile (double
+//               buffered in TMEM), scaling and accumulation in registers, y stores
+// All mbarrier waits are bounded; a wait that gives up raises the status word
+// and every role leaves its loop.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "lp_common.cuh"
+
+namespace lp {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BKC = 64;        // tile; BKC = k per pipeline stage (two 32-value blocks)
+constexpr int STAGES = 5;
+constexpr int A_TILE = BM * BKC * 2;               // 16 KB, fp16
+constexpr int B_TILE = BN * BKC * 2;               // 16 KB, fp16
+constexpr int TAB_BYTES = (2 * BN + BN) * 4;       // per stage: (dmin*mn) for its two blocks, d
+constexpr int THREADS = 512;
+constexpr int TMEM_COLS = 256;                     // two 128-column fp32 tiles
+
+// shared-memory map (dynamic, 1024-byte aligned base)
+constexpr uint32_t OFF_A = 0;
+constexpr uint32_t OFF_B = OFF_A + STAGES * A_TILE;
+constexpr uint32_t OFF_TAB = OFF_B + STAGES * B_TILE;
+constexpr uint32_t OFF_BAR = OFF_TAB + STAGES * TAB_BYTES;
+// barriers: full_a[S], full_b[S], empty[S], tab_empty[S], tmem_full[2], tmem_empty[2]
+constexpr uint32_t BAR_FULL_A = OFF_BAR, BAR_FULL_B = BAR_FULL_A + 8 * STAGES, BAR_EMPTY = BAR_FULL_B + 8 * STAGES,
+                   BAR_TAB_EMPTY = BAR_EMPTY + 8 * STAGES, BAR_TMEM_FULL = BAR_TAB_EMPTY + 8 * STAGES,
+                   BAR_TMEM_EMPTY = BAR_TMEM_FULL + 16, OFF_TMEM_PTR = BAR_TMEM_EMPTY + 16, OFF_ABORT = OFF_TMEM_PTR + 8;
+constexpr uint32_t SMEM_BYTES = OFF_ABORT + 8 + 1024;   // + slack for the 1024-byte alignment
+
+struct TcParams {
+    const uint8_t* w;        // Q4_K weights, N rows of rb bytes
+    const float*   dx;       // [M][K/32] activation scales
+    const float*   sumx;     // [M][K/32] d_x * integer block sum
+    float*         y;        // [M][N]
+    int*           err;
+    int            M, N, K;
+    uint32_t       rb;
+    int            tiles_m, tiles_n;
+};
+
+// ---- tcgen05 / TMA wrappers ---------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);          // start address
+    d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused with swizzle)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;                        // descriptor version (Blackwell)
+    d |= static_cast<uint64_t>(2) << 61;                        // SWIZZLE_128B
+    return d;
+}
+// kind::f16: D fp32, A fp16, B fp16, both K-major, M = 128, N = 128.
+constexpr uint32_t IDESC_F16 = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
+                               (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+
+// Waits that also give up when another role has raised the abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        if (*abort_flag) return false;
+        __nanosleep(32);
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    *abort_flag = 1;
+    report_status(err, code);
+    return false;
+}
+
+// ---- the kernel -----------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (sbase - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_ABORT);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(sbase + BAR_FULL_A + 8 * s, 1);
+            mbar_init(sbase + BAR_FULL_B + 8 * s, 4);        // one arrive per converter warp
+            mbar_init(sbase + BAR_EMPTY + 8 * s, 1);         // tcgen05.commit
+            mbar_init(sbase + BAR_TAB_EMPTY + 8 * s, 8);     // one arrive per epilogue warp
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(sbase + BAR_TMEM_FULL + 8 * t, 1);     // tcgen05.commit
+            mbar_init(sbase + BAR_TMEM_EMPTY + 8 * t, 8);    // one arrive per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(sbase + OFF_TMEM_PTR), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
+
+    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int chunks = p.K / BKC;
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer: activation tiles ----------------
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const int m0 = (tile % p.tiles_m) * BM;
+                for (int kc = 0; kc < chunks; ++kc, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, A_TILE);
+                    tma_load_2d(sbase + OFF_A + s * A_TILE, &tmap_a, kc * BKC, m0, sbase + BAR_FULL_A + 8 * s);
+                }
+            }
+            if (!ok) {
+                // tiles in flight must land before shared memory is released
+                const int pending = it < STAGES ? it : STAGES;
+                for (int k = 0; k < pending; ++k) {
+                    const int v = it - 1 - k;
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_FULL_A + 8 * (v % STAGES), (v / STAGES) & 1);
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------- MMA issuer ----------------
+            int it = 0, bc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                for (int kc = 0; kc < chunks && ok; ++kc, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!wait_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                        !wait_or_abort(sbase + BAR_FULL_B + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
+                    const uint64_t bdesc = smem_desc_sw128(sbase + OFF_B + s * B_TILE);
+#pragma unroll
+                    for (int blk = 0; blk < 2; ++blk, ++bc) {
+                        const int t = bc & 1;
+                        if (!wait_or_abort(sbase + BAR_TMEM_EMPTY + 8 * t, ((bc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                        tc_fence_after();
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const uint64_t off = static_cast<uint64_t>((blk * 64 + k * 32) >> 4);   // bytes >> 4 inside the swizzle row
+                            tc_mma_f16(tmem_base + t * BN, adesc + off, bdesc + off, IDESC_F16, k);
+                        }
+                        tc_commit(sbase + BAR_TMEM_FULL + 8 * t);      // block sum complete -> epilogue
+                    }
+                    tc_commit(sbase + BAR_EMPTY + 8 * s);              // operands consumed -> producers
+                }
+            }
+        }
+    } else if (warp < 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        // ---------------- converters: thread r owns weight row n0 + r ----------------
+        const int r = threadIdx.x - 128;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            const int n0 = (tile / p.tiles_m) * BN;
+            const bool live = n0 + r < p.N;
+            const uint4* src = reinterpret_cast<const uint4*>(p.w + static_cast<size_t>(live ? n0 + r : 0) * p.rb);
+            uint4 nxt[9];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) nxt[i] = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+            for (int sb = 0; sb < p.K / 256 && ok; ++sb) {
+                uint4 cur[9];
+#pragma unroll
+                for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
+                if (live && sb + 1 < p.K / 256) {
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) nxt[i] = __ldg(src + (sb + 1) * 9 + i);
+                }
+                const float d = half_bits_to_float(cur[0].x), dmin = half_bits_to_float(cur[0].x >> 16);
+                // 6-bit scales / mins, eight of each (Laplace src/kernels.h:82-90), one per byte
+                const uint32_t sc_lo = cur[0].y & 0x3f3f3f3fu, mn_lo = cur[0].z & 0x3f3f3f3fu;
+                const uint32_t sc_hi = (cur[0].w & 0x0f0f0f0fu) | ((cur[0].y >> 2) & 0x30303030u);
+                const uint32_t mn_hi = ((cur[0].w >> 4) & 0x0f0f0f0fu) | ((cur[0].z >> 2) & 0x30303030u);
+#pragma unroll
+                for (int c = 0; c < 4; ++c, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = ((it / STAGES) & 1) ^ 1;
+                    if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_EMPTY) ||
+                        !wait_or_abort(sbase + BAR_TAB_EMPTY + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    const uint32_t scw = c < 2 ? sc_lo : sc_hi, mnw = c < 2 ? mn_lo : mn_hi;
+                    const uint32_t sc1 = (scw >> (16 * (c & 1))) & 0xff, sc2 = (scw >> (16 * (c & 1) + 8)) & 0xff;
+                    const uint32_t mn1 = (mnw >> (16 * (c & 1))) & 0xff, mn2 = (mnw >> (16 * (c & 1) + 8)) & 0xff;
+                    // chunk c: 32 bytes of nibbles = uint4 1+2c and 2+2c
+                    const uint32_t qw[8] = {cur[1 + 2 * c].x, cur[1 + 2 * c].y, cur[1 + 2 * c].z, cur[1 + 2 * c].w,
+                                            cur[2 + 2 * c].x, cur[2 + 2 * c].y, cur[2 + 2 * c].z, cur[2 + 2 * c].w};
+                    // fp16 operand row: 32 low-nibble values * sc1, then 32 high-nibble values * sc2.
+                    // Within every 4 values the order is (0, 2, 1, 3); the activation operand uses the same order.
+                    uint32_t h[32];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t w = qw[i];
+                        const uint32_t a0 = ((w & 0x000f000fu) * sc1) | 0x64006400u;          // fp16(1024 + v) pairs
+                        const uint32_t a1 = (((w >> 8) & 0x000f000fu) * sc1) | 0x64006400u;
+                        const uint32_t b0 = (((w >> 4) & 0x000f000fu) * sc2) | 0x64006400u;
+                        const uint32_t b1 = (((w >> 12) & 0x000f000fu) * sc2) | 0x64006400u;
+                        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+                        __half2 x;
+                        x = __hsub2(*reinterpret_cast<const __half2*>(&a0), k1024); h[2 * i] = *reinterpret_cast<uint32_t*>(&x);
+                        x = __hsub2(*reinterpret_cast<const __half2*>(&a1), k1024); h[2 * i + 1] = *reinterpret_cast<uint32_t*>(&x);
+                        x = __hsub2(*reinterpret_cast<const __half2*>(&b0), k1024); h[16 + 2 * i] = *reinterpret_cast<uint32_t*>(&x);
+                        x = __hsub2(*reinterpret_cast<const __half2*>(&b1), k1024); h[16 + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&x);
+                    }
+                    uint8_t* brow = smem + OFF_B + s * B_TILE + r * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(brow + ((j ^ (r & 7)) << 4)) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+                    float* tab = reinterpret_cast<float*>(smem + OFF_TAB + s * TAB_BYTES);
+                    tab[r] = dmin * static_cast<float>(mn1);
+                    tab[BN + r] = dmin * static_cast<float>(mn2);
+                    tab[2 * BN + r] = d;
+                    fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sbase + BAR_FULL_B + 8 * s);
+                }
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+        // ---------------- epilogue: lane = token row, 64 columns per warp ----------------
+        const int e = warp - 8;
+        const int quad = e & 3, half = e >> 2;
+        const uint32_t t_lane = static_cast<uint32_t>(quad * 32) << 16;
+        int it = 0, bc = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+            const int m = m0 + quad * 32 + lane;
+            const bool row_live = m < p.M;
+            const float* dxr = p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32);
+            const float* sxr = p.sumx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32);
+            float acc[64], acc2[64];
+#pragma unroll
+            for (int c = 0; c < 64; ++c) { acc[c] = 0.f; acc2[c] = 0.f; }
+            for (int kc = 0; kc < chunks && ok; ++kc, ++it) {
+                const int s = it % STAGES;
+                const float2 dx2 = row_live ? __ldg(reinterpret_cast<const float2*>(dxr) + kc) : make_float2(0.f, 0.f);
+                const float2 sx2 = row_live ? __ldg(reinterpret_cast<const float2*>(sxr) + kc) : make_float2(0.f, 0.f);
+                const float* tab = reinterpret_cast<const float*>(smem + OFF_TAB + s * TAB_BYTES);
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk, ++bc) {
+                    const int t = bc & 1;
+                    if (!wait_or_abort(sbase + BAR_TMEM_FULL + 8 * t, (bc >> 1) & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const float dxv = blk ? dx2.y : dx2.x, nsx = blk ? -sx2.y : -sx2.x;
+                    const uint32_t taddr = tmem_base + t_lane + t * BN + half * 64;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float f[16];
+                        tc_ld16(taddr + 16 * g, f);
+                        tc_wait_ld();
+                        if (g == 3) {
+                            // the whole tile has been read: hand the TMEM buffer back early
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * t);
+                        }
+#pragma unroll
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            const float4 mm = *reinterpret_cast<const float4*>(tab + blk * BN + half * 64 + 16 * g + 4 * c4);
+                            const int c = 16 * g + 4 * c4;
+                            acc2[c] = fmaf(dxv, f[4 * c4], acc2[c]);         acc[c] = fmaf(nsx, mm.x, acc[c]);
+                            acc2[c + 1] = fmaf(dxv, f[4 * c4 + 1], acc2[c + 1]); acc[c + 1] = fmaf(nsx, mm.y, acc[c + 1]);
+                            acc2[c + 2] = fmaf(dxv, f[4 * c4 + 2], acc2[c + 2]); acc[c + 2] = fmaf(nsx, mm.z, acc[c + 2]);
+                            acc2[c + 3] = fmaf(dxv, f[4 * c4 + 3], acc2[c + 3]); acc[c + 3] = fmaf(nsx, mm.w, acc[c + 3]);
+                        }
+                    }
+                }
+                if (!ok) break;
+                if ((kc & 3) == 3) {
+                    // end of a super-block: fold in its fp16 scale d (per weight row = per column)
+#pragma unroll
+                    for (int c4 = 0; c4 < 16; ++c4) {
+                        const float4 dd = *reinterpret_cast<const float4*>(tab + 2 * BN + half * 64 + 4 * c4);
+                        acc[4 * c4] = fmaf(dd.x, acc2[4 * c4], acc[4 * c4]);             acc2[4 * c4] = 0.f;
+                        acc[4 * c4 + 1] = fmaf(dd.y, acc2[4 * c4 + 1], acc[4 * c4 + 1]); acc2[4 * c4 + 1] = 0.f;
+                        acc[4 * c4 + 2] = fmaf(dd.z, acc2[4 * c4 + 2], acc[4 * c4 + 2]); acc2[4 * c4 + 2] = 0.f;
+                        acc[4 * c4 + 3] = fmaf(dd.w, acc2[4 * c4 + 3], acc[4 * c4 + 3]); acc2[4 * c4 + 3] = 0.f;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sbase + BAR_TAB_EMPTY + 8 * s);     // tables of this stage are free
+            }
+            if (ok && row_live) {
+                float* yr = p.y + static_cast<size_t>(m) * p.N + n0 + half * 64;
+                if (n0 + half * 64 + 64 <= p.N && (reinterpret_cast<uintptr_t>(yr) & 15) == 0) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 16; ++c4)
+                        *reinterpret_cast<float4*>(yr + 4 * c4) = make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c)
+                        if (n0 + half * 64 + c < p.N) yr[c] = acc[c];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- activation quantizer for this kernel --------------------------------------
+// Same arithmetic as quantize_act_kernel (Laplace src/matmul_simd.cpp:348-410); the int8
+// values are written as fp16 (exact) in the operand's k order: within every four
+// consecutive values, (0, 2, 1, 3). Rows M..M_pad-1 of the operand are zero.
+__global__ void __launch_bounds__(256) quantize_act_f16_kernel(const float* __restrict__ x, int M, int K, long long n_blocks,
+                                                               __half* __restrict__ aq, float* __restrict__ dx,
+                                                               float* __restrict__ sumx) {
+    const int t8 = threadIdx.x & 7;
+    const long long groups = static_cast<long long>(gridDim.x) * (blockDim.x >> 3);
+    const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x >> 3) + (threadIdx.x >> 3);
+    const long long iters = (n_blocks + groups - 1) / groups;
+    const long long live_blocks = static_cast<long long>(M) * (K / 32);
+    for (long long itn = 0; itn < iters; ++itn) {
+        const long long b = first + itn * groups;
+        const bool in_range = b < n_blocks, live = b < live_blocks;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) v = __ldg(reinterpret_cast<const float4*>(x + b * 32) + t8);
+        uint32_t packed; int hs;
+        const float d = quantize_block_8lanes(v, packed, hs);
+        const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
+        if (!in_range) continue;
+        const int q0 = static_cast<int8_t>(packed & 0xff), q1 = static_cast<int8_t>((packed >> 8) & 0xff);
+        const int q2 = static_cast<int8_t>((packed >> 16) & 0xff), q3 = static_cast<int8_t>(packed >> 24);
+        const __half2 lo = __halves2half2(__int2half_rn(q0), __int2half_rn(q2));
+        const __half2 hi = __halves2half2(__int2half_rn(q1), __int2half_rn(q3));
+        uint2 out;
+        out.x = *reinterpret_cast<const uint32_t*>(&lo);
+        out.y = *reinterpret_cast<const uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(aq + b * 32)[t8] = out;
+        if (t8 == 0 && live) {
+            const short slo = static_cast<short>(hs), shi = static_cast<short>(hs_hi);
+            dx[b] = d;
+            sumx[b] = d * static_cast<float>(static_cast<int>(slo) + static_cast<int>(shi));
+        }
+    }
+}
+
+// scratch owned by this translation unit
+struct Scratch {
+    void*  p = nullptr;
+    size_t cap = 0;
+    int ensure(size_t n) {
+        if (n <= cap) return LAPLACE_OK;
+        if (p) cudaFree(p);
+        p = nullptr; cap = 0;
+        cudaError_t e = cudaMalloc(&p, n + n / 8);
+        if (e != cudaSuccess) return cuda_check(e, "cudaMalloc prefill scratch");
+        cap = n + n / 8;
+        return LAPLACE_OK;
+    }
+};
+Scratch g_scratch;
+
+}  // namespace
+
+void release_gemm_tc_scratch() {
+    if (g_scratch.p) cudaFree(g_scratch.p);
+    g_scratch.p = nullptr;
+    g_scratch.cap = 0;
+}
+
+bool gemm_tc_supports(uint32_t type, int M, int K, int N) {
+    return type == LAPLACE_TYPE_Q4_K && M > 8 && K % 256 == 0 && N > 0;
+}
+
+int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st) {
+    Context& c = ctx();
+    if (!gemm_tc_supports(type, M, K, N)) return LAPLACE_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(LAPLACE_ERR_ARG, "gemm: Q4_K weights must be 16-byte aligned on the device");
+    if (reinterpret_cast<uintptr_t>(x) & 15) return fail(LAPLACE_ERR_ARG, "gemm: x not 16-byte aligned");
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const size_t m_pad = static_cast<size_t>(tiles_m) * BM;
+    const size_t bpr = static_cast<size_t>(K / 32);
+    const size_t aq_bytes = (m_pad * K * sizeof(__half) + 255) & ~size_t(255);
+    const size_t sc_bytes = (static_cast<size_t>(M) * bpr * sizeof(float) + 255) & ~size_t(255);
+    int rc = g_scratch.ensure(aq_bytes + 2 * sc_bytes);
+    if (rc) return rc;
+    __half* aq = static_cast<__half*>(g_scratch.p);
+    float* dx = reinterpret_cast<float*>(static_cast<uint8_t*>(g_scratch.p) + aq_bytes);
+    float* sumx = reinterpret_cast<float*>(static_cast<uint8_t*>(g_scratch.p) + aq_bytes + sc_bytes);
+
+    {
+        const long long n_blocks = static_cast<long long>(m_pad) * bpr;
+        long long want = (n_blocks + 31) / 32;
+        const long long cap = static_cast<long long>(c.sm_count) * 8;
+        const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+        quantize_act_f16_kernel<<<grid, 256, 0, st>>>(x, M, K, n_blocks, aq, dx, sumx);
+        c.launches++;
+        if ((rc = cuda_check(cudaGetLastError(), "quantize_act_f16 launch"))) return rc;
+    }
+
+    // 2-D tensor map over the fp16 operand: inner dimension K, outer dimension tokens.
+    CUtensorMap tmap;
+    {
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(m_pad)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * sizeof(__half)};
+        const cuuint32_t box[2] = {BKC, BM};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = cuTensorMapEncodeTiled(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, aq, dims, strides, box, estr,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+    }
+
+    TcParams p{};
+    p.w = w; p.dx = dx; p.sumx = sumx; p.y = y; p.err = c.d_err;
+    p.M = M; p.N = N; p.K = K; p.rb = static_cast<uint32_t>(row_bytes(type, K));
+    p.tiles_m = tiles_m; p.tiles_n = tiles_n;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+        if (e != cudaSuccess) return cuda_check(e, "cudaFuncSetAttribute gemm_tc");
+        configured = true;
+    }
+    const int n_tiles = tiles_m * tiles_n;
+    const int grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
+    gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, p);
+    c.launches++;
+    c.last_path = 2;
+    return cuda_check(cudaGetLastError(), "gemm_q4k_tc launch");
+}
+
+}  // namespace lp

@@ -1,0 +1,66 @@
+"""GPU parity of the tensor-core prefill GEMM (M > 8) against the CPU oracle, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+
+from laplace_b200 import synth
+from laplace_b200.ggml import GGMLType
+from tests.parity import check_close
+
+pytestmark = pytest.mark.gpu
+THREADS = os.cpu_count() or 1
+
+
+def run_dev(t, x, w, M, K, N):
+    import torch
+    from laplace_b200 import device
+    y = device.gemm(torch.from_numpy(x).cuda(), device.upload_weights(w), t, M, K, N)
+    device.sync()
+    return y.cpu().numpy(), device.lib().laplace_cuda_last_path()
+
+
+@pytest.mark.parametrize("how", ["random", "ref", "affine"])
+@pytest.mark.parametrize("M,K,N", [(128, 512, 128), (9, 256, 8), (64, 1024, 256), (200, 2816, 200), (512, 4096, 384), (130, 768, 129)])
+def test_q4k_prefill(oracle, how, M, K, N):
+    t = GGMLType.Q4_K
+    w = synth.weights(t, K, N, seed=40 + M, how=how)
+    x = synth.normal_f32(41 + N, (M, K))
+    y, path = run_dev(t, x, w, M, K, N)
+    assert path == 2, "the tensor-core kernel did not run"
+    ref = oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS)
+    check_close(y, ref, f"Q4_K prefill {how} M={M} K={K} N={N}")
+
+
+def test_prefill_rows_equal_decode_rows(oracle):
+    """Row m of a prefill call and a decode call on row m alone agree to fp32 rounding
+    (the reference's test_batched_rows, tests/test_matmul.cpp:217-250, allows 1e-4)."""
+    t, M, K, N = GGMLType.Q4_K, 64, 512, 64
+    w = synth.weights(t, K, N, seed=77, how="affine")
+    x = synth.normal_f32(78, (M, K))
+    yb, path = run_dev(t, x, w, M, K, N)
+    assert path == 2
+    for m in (0, 17, 63):
+        ys, p1 = run_dev(t, x[m:m + 1], w, 1, K, N)
+        assert p1 == 1
+        assert np.allclose(yb[m], ys[0], rtol=1e-4, atol=1e-4)
+
+
+def test_prefill_through_host_entry_point(oracle):
+    import laplace_b200 as lb
+    t, M, K, N = GGMLType.Q4_K, 96, 512, 160
+    w = synth.weights(t, K, N, seed=79, how="random")
+    x = synth.normal_f32(80, (M, K))
+    y = np.zeros((M, N), dtype=np.float32)
+    lb.matmul_rows(x, lb.Tensor(t, w), y, M, K, N)
+    check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), "matmul_rows prefill")
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q4_0, GGMLType.Q8_0, GGMLType.Q6_K])
+def test_other_types_large_m(oracle, t):
+    """Types without a tensor-core kernel run as repeated 8-row streaming passes: still exact."""
+    M, K, N = 20, 512, 40
+    w = synth.weights(t, K, N, seed=81, how="affine")
+    x = synth.normal_f32(82, (M, K))
+    y, _ = run_dev(t, x, w, M, K, N)
+    check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"{t.name} M=20")
