@@ -70,8 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 print(log)
     objs = [objdir / (Path(s).stem + ".o") for s in SOURCES]
     if force or jobs or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
-               "-lcuda"]
+        cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
         run(cmd)
     return LIB
 

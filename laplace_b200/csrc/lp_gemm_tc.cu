@@ -7,24 +7,32 @@
 // fp32 activation scale d_x, so the integer sum of each block has to leave the
 // tensor core and be scaled on CUDA cores; that per-block drain, not the MMA,
 // bounds throughput. With kind::f16 the accumulator already holds the block sum
-// as an exact fp32 integer (|sum| <= 32*945*127 < 2^24), so the drain is a
-// single FFMA per element - no int->float conversion - and the 6-bit sub-block
-// scale can ride inside the weight operand (sc*nibble <= 945 is exact in fp16):
+// as an exact fp32 integer (|sum| <= 32*945*127 < 2^24), so the drain is one
+// fused multiply-add per element - no int->float conversion - and the 6-bit
+// sub-block scale rides inside the weight operand (sc*nibble <= 945 is exact in
+// fp16). Per super-block sb of 8 blocks:
 //
-//   y[m,n] = sum_sb d[n,sb] * ( sum_{j<8} d_x[m,8sb+j] * F[m,n,8sb+j] )
-//            - sum_b sum_x[m,b] * (dmin*mn)[n,b]
-//   F[m,n,b] = sum_{k in b} q_x[m,k] * (sc*nibble)[n,k]        (tcgen05.mma, exact)
+//   y[m,n] += d[n,sb] * sum_{j<8} d_x[m,8sb+j] * F[m,n,8sb+j]  -  dmin[n,sb] * G[m,n,sb]
+//   F[m,n,b]  = sum_{k in b} q_x[m,k] * (sc*nibble)[n,k]          (tcgen05.mma kind::f16, fp16, exact)
+//   G[m,n,sb] = sum_{j<8} sum_x[m,8sb+j] * mn[n,8sb+j]            (tcgen05.mma kind::f16, bf16)
+//
+// G, the "min" correction of Q4_K, would cost a second multiply-add per element
+// and block on CUDA cores; instead sum_x (fp32) is split into three bf16 pieces
+// (exact to 24 bits), the 6-bit mins are exact in bf16, and one K=32 MMA per
+// super-block accumulates G in TMEM, drained once per super-block.
 //
 // Roles in one 512-thread CTA (one CTA per SM, persistent over 128x128 tiles):
 //   warp 0      TMA: activation tiles (fp16 q values, 128 tokens x 64 k, 128-byte swizzle)
 //   warp 1      MMA issue (one lane) + TMEM allocation
+//   warp 2      TMA: the bf16 pieces of sum_x, one tile per pair of super-blocks
 //   warps 4-7   converters: packed Q4_K super-blocks (global) -> fp16 weight operand
-//               tile in shared memory (same swizzle) + per-column scale tables
+//               tile, bf16 mins operand and d / dmin tables in shared memory
 //   warps 8-15  epilogue: tcgen05.ld of each block's 128x128 fp32 tile (double
 //               buffered in TMEM), scaling and accumulation in registers, y stores
 // All mbarrier waits are bounded; a wait that gives up raises the status word
 // and every role leaves its loop.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include <cstring>
 
@@ -35,28 +43,34 @@ namespace lp {
 namespace {
 
 constexpr int BM = 128, BN = 128, BKC = 64;        // tile; BKC = k per pipeline stage (two 32-value blocks)
-constexpr int STAGES = 5;
+constexpr int STAGES = 4;                          // main ring: activation + weight operand tiles
+constexpr int GST = 2;                             // ring of "pair of super-blocks" stages for the G operands
 constexpr int A_TILE = BM * BKC * 2;               // 16 KB, fp16
 constexpr int B_TILE = BN * BKC * 2;               // 16 KB, fp16
-constexpr int TAB_BYTES = (2 * BN + BN) * 4;       // per stage: (dmin*mn) for its two blocks, d
+constexpr int G_TILE = 128 * 64 * 2;               // 16 KB, bf16: 32 k per super-block, two super-blocks per row
+constexpr int GTAB_BYTES = 2 * 2 * BN * 4;         // per G stage: [super-block of the pair][d, dmin][column]
 constexpr int THREADS = 512;
-constexpr int TMEM_COLS = 256;                     // two 128-column fp32 tiles
+constexpr int TMEM_COLS = 512;                     // F0, F1 (block sums, double buffered), G even, G odd
+constexpr uint32_t TM_F = 0, TM_G = 256;
 
 // shared-memory map (dynamic, 1024-byte aligned base)
 constexpr uint32_t OFF_A = 0;
 constexpr uint32_t OFF_B = OFF_A + STAGES * A_TILE;
-constexpr uint32_t OFF_TAB = OFF_B + STAGES * B_TILE;
-constexpr uint32_t OFF_BAR = OFF_TAB + STAGES * TAB_BYTES;
-// barriers: full_a[S], full_b[S], empty[S], tab_empty[S], tmem_full[2], tmem_empty[2]
+constexpr uint32_t OFF_GA = OFF_B + STAGES * B_TILE;
+constexpr uint32_t OFF_GB = OFF_GA + GST * G_TILE;
+constexpr uint32_t OFF_GTAB = OFF_GB + GST * G_TILE;
+constexpr uint32_t OFF_BAR = OFF_GTAB + GST * GTAB_BYTES;
 constexpr uint32_t BAR_FULL_A = OFF_BAR, BAR_FULL_B = BAR_FULL_A + 8 * STAGES, BAR_EMPTY = BAR_FULL_B + 8 * STAGES,
-                   BAR_TAB_EMPTY = BAR_EMPTY + 8 * STAGES, BAR_TMEM_FULL = BAR_TAB_EMPTY + 8 * STAGES,
-                   BAR_TMEM_EMPTY = BAR_TMEM_FULL + 16, OFF_TMEM_PTR = BAR_TMEM_EMPTY + 16, OFF_ABORT = OFF_TMEM_PTR + 8;
+                   BAR_TMEM_FULL = BAR_EMPTY + 8 * STAGES, BAR_TMEM_EMPTY = BAR_TMEM_FULL + 16,
+                   BAR_G_FULL_A = BAR_TMEM_EMPTY + 16, BAR_G_FULL_B = BAR_G_FULL_A + 8 * GST,
+                   BAR_G_EMPTY = BAR_G_FULL_B + 8 * GST, BAR_G_TAB_EMPTY = BAR_G_EMPTY + 8 * GST,
+                   BAR_GT_FULL = BAR_G_TAB_EMPTY + 8 * GST, BAR_GT_EMPTY = BAR_GT_FULL + 8,
+                   OFF_TMEM_PTR = BAR_GT_EMPTY + 8, OFF_ABORT = OFF_TMEM_PTR + 8;
 constexpr uint32_t SMEM_BYTES = OFF_ABORT + 8 + 1024;   // + slack for the 1024-byte alignment
 
 struct TcParams {
     const uint8_t* w;        // Q4_K weights, N rows of rb bytes
     const float*   dx;       // [M][K/32] activation scales
-    const float*   sumx;     // [M][K/32] d_x * integer block sum
     float*         y;        // [M][N]
     int*           err;
     int            M, N, K;
@@ -107,13 +121,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 constexpr uint32_t IDESC_F16 = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
                                (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
 
+// Same shape with bf16 operands (the G product).
+constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);
+
 // Waits that also give up when another role has raised the abort flag.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
-        if (*abort_flag) return false;
-        __nanosleep(32);
+    // try_wait suspends the thread in hardware (up to its time hint) and wakes it when the phase
+    // completes; a software sleep here would add its whole quantum to every hand-off between roles.
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
     }
     *abort_flag = 1;
     report_status(err, code);
@@ -121,8 +138,15 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 }
 
 // ---- the kernel -----------------------------------------------------------------
+// Counters shared by all roles (each role advances its own copy in the same order):
+//   it   main-ring chunk counter (64 k each), stage = it % STAGES
+//   bc   block counter (32 k each), TMEM block-sum buffer = bc & 1
+//   gp   pair-of-super-blocks counter, G stage = gp % GST
+// A tile walks super-blocks 0 .. nsb_pad-1, nsb_pad = K/256 rounded up to even; a
+// padding super-block has no chunks and contributes zeros to G.
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const TcParams p) {
+gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_g,
+                   const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (sbase - smem_u32(smem_raw));
@@ -134,12 +158,19 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const TcParams p)
             mbar_init(sbase + BAR_FULL_A + 8 * s, 1);
             mbar_init(sbase + BAR_FULL_B + 8 * s, 4);        // one arrive per converter warp
             mbar_init(sbase + BAR_EMPTY + 8 * s, 1);         // tcgen05.commit
-            mbar_init(sbase + BAR_TAB_EMPTY + 8 * s, 8);     // one arrive per epilogue warp
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(sbase + BAR_TMEM_FULL + 8 * t, 1);     // tcgen05.commit
             mbar_init(sbase + BAR_TMEM_EMPTY + 8 * t, 8);    // one arrive per epilogue warp
         }
+        for (int g = 0; g < GST; ++g) {
+            mbar_init(sbase + BAR_G_FULL_A + 8 * g, 1);
+            mbar_init(sbase + BAR_G_FULL_B + 8 * g, 8);      // 4 converter warps x 2 super-blocks
+            mbar_init(sbase + BAR_G_EMPTY + 8 * g, 1);       // tcgen05.commit
+            mbar_init(sbase + BAR_G_TAB_EMPTY + 8 * g, 8);   // one arrive per epilogue warp
+        }
+        mbar_init(sbase + BAR_GT_FULL, 1);                   // tcgen05.commit
+        mbar_init(sbase + BAR_GT_EMPTY, 8);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -154,17 +185,18 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const TcParams p)
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
 
     const int n_tiles = p.tiles_m * p.tiles_n;
-    const int chunks = p.K / BKC;
+    const int nsb = p.K / 256;
+    const int n_pairs = (nsb + 1) / 2;
 
     if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp == 0 && lane == 0) {
             // ---------------- TMA producer: activation tiles ----------------
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const int m0 = (tile % p.tiles_m) * BM;
-                for (int kc = 0; kc < chunks; ++kc, ++it) {
+                for (int kc = 0; kc < nsb * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, A_TILE);
@@ -173,38 +205,79 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const TcParams p)
             }
             if (!ok) {
                 // tiles in flight must land before shared memory is released
-                const int pending = it < STAGES ? it : STAGES;
-                for (int k = 0; k < pending; ++k) {
+                for (int k = 0; k < STAGES; ++k) {
                     const int v = it - 1 - k;
                     if (v >= 0) mbar_wait_bounded(sbase + BAR_FULL_A + 8 * (v % STAGES), (v / STAGES) & 1);
                 }
             }
-        } else if (warp == 1 && lane == 0) {
-            // ---------------- MMA issuer ----------------
-            int it = 0, bc = 0;
+        } else if (warp == 2 && lane == 0) {
+            // ---------------- TMA producer: bf16 pieces of sum_x, one tile per pair ----------------
+            int gp = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                for (int kc = 0; kc < chunks && ok; ++kc, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!wait_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
-                        !wait_or_abort(sbase + BAR_FULL_B + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
-                    const uint64_t bdesc = smem_desc_sw128(sbase + OFF_B + s * B_TILE);
-#pragma unroll
-                    for (int blk = 0; blk < 2; ++blk, ++bc) {
-                        const int t = bc & 1;
-                        if (!wait_or_abort(sbase + BAR_TMEM_EMPTY + 8 * t, ((bc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                const int m0 = (tile % p.tiles_m) * BM;
+                for (int pr = 0; pr < n_pairs; ++pr, ++gp) {
+                    const int g = gp % GST;
+                    if (!wait_or_abort(sbase + BAR_G_EMPTY + 8 * g, ((gp / GST) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(sbase + BAR_G_FULL_A + 8 * g, G_TILE);
+                    tma_load_2d(sbase + OFF_GA + g * G_TILE, &tmap_g, pr * 64, m0, sbase + BAR_G_FULL_A + 8 * g);
+                }
+            }
+            if (!ok) {
+                for (int k = 0; k < GST; ++k) {
+                    const int v = gp - 1 - k;
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_G_FULL_A + 8 * (v % GST), (v / GST) & 1);
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------- MMA issuer ----------------
+            int it = 0, bc = 0, gp = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
+                    const int sb_in_pair = (2 * pr + 1 < nsb) ? 2 : 1;
+                    for (int kc = 0; kc < 4 * sb_in_pair && ok; ++kc, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!wait_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                            !wait_or_abort(sbase + BAR_FULL_B + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
                         tc_fence_after();
+                        const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
+                        const uint64_t bdesc = smem_desc_sw128(sbase + OFF_B + s * B_TILE);
+#pragma unroll
+                        for (int blk = 0; blk < 2; ++blk, ++bc) {
+                            const int t = bc & 1;
+                            if (!wait_or_abort(sbase + BAR_TMEM_EMPTY + 8 * t, ((bc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                            tc_fence_after();
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const uint64_t off = static_cast<uint64_t>((blk * 64 + k * 32) >> 4);   // bytes >> 4 inside the swizzle row
+                                tc_mma_f16(tmem_base + TM_F + t * BN, adesc + off, bdesc + off, IDESC_F16, k);
+                            }
+                            tc_commit(sbase + BAR_TMEM_FULL + 8 * t);      // block sum complete -> epilogue
+                        }
+                        tc_commit(sbase + BAR_EMPTY + 8 * s);              // operands consumed -> producers
+                    }
+                    if (!ok) break;
+                    // G of both super-blocks of the pair: K = 32 bf16 each, halves of the same 128-byte rows
+                    const int g = gp % GST;
+                    const uint32_t gph = (gp / GST) & 1;
+                    if (!wait_or_abort(sbase + BAR_G_FULL_A + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                        !wait_or_abort(sbase + BAR_G_FULL_B + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                        !wait_or_abort(sbase + BAR_GT_EMPTY, (gp & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t gadesc = smem_desc_sw128(sbase + OFF_GA + g * G_TILE);
+                    const uint64_t gbdesc = smem_desc_sw128(sbase + OFF_GB + g * G_TILE);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
 #pragma unroll
                         for (int k = 0; k < 2; ++k) {
-                            const uint64_t off = static_cast<uint64_t>((blk * 64 + k * 32) >> 4);   // bytes >> 4 inside the swizzle row
-                            tc_mma_f16(tmem_base + t * BN, adesc + off, bdesc + off, IDESC_F16, k);
+                            const uint64_t off = static_cast<uint64_t>((e * 64 + k * 32) >> 4);
+                            tc_mma_f16(tmem_base + TM_G + e * BN, gadesc + off, gbdesc + off, IDESC_BF16, k);
                         }
-                        tc_commit(sbase + BAR_TMEM_FULL + 8 * t);      // block sum complete -> epilogue
                     }
-                    tc_commit(sbase + BAR_EMPTY + 8 * s);              // operands consumed -> producers
+                    tc_commit(sbase + BAR_GT_FULL);
+                    tc_commit(sbase + BAR_G_EMPTY + 8 * g);
                 }
             }
         }
@@ -212,136 +285,207 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const TcParams p)
         asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         // ---------------- converters: thread r owns weight row n0 + r ----------------
         const int r = threadIdx.x - 128;
-        int it = 0;
+        int it = 0, gp = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const int n0 = (tile / p.tiles_m) * BN;
             const bool live = n0 + r < p.N;
             const uint4* src = reinterpret_cast<const uint4*>(p.w + static_cast<size_t>(live ? n0 + r : 0) * p.rb);
-            uint4 nxt[9];
-#pragma unroll
-            for (int i = 0; i < 9; ++i) nxt[i] = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
-            for (int sb = 0; sb < p.K / 256 && ok; ++sb) {
-                uint4 cur[9];
-#pragma unroll
-                for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
-                if (live && sb + 1 < p.K / 256) {
-#pragma unroll
-                    for (int i = 0; i < 9; ++i) nxt[i] = __ldg(src + (sb + 1) * 9 + i);
+            const uint4 zero4 = make_uint4(0, 0, 0, 0);
+            // one chunk (32 bytes of nibbles) and one header are fetched ahead of use
+            uint4 hdr_n = live ? __ldg(src) : zero4;
+            uint4 qa_n = live ? __ldg(src + 1) : zero4, qb_n = live ? __ldg(src + 2) : zero4;
+            for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
+                const int g = gp % GST;
+                {
+                    const uint32_t gph = ((gp / GST) & 1) ^ 1;
+                    if (!wait_or_abort(sbase + BAR_G_EMPTY + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_EMPTY) ||
+                        !wait_or_abort(sbase + BAR_G_TAB_EMPTY + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                 }
-                const float d = half_bits_to_float(cur[0].x), dmin = half_bits_to_float(cur[0].x >> 16);
-                // 6-bit scales / mins, eight of each (Laplace src/kernels.h:82-90), one per byte
-                const uint32_t sc_lo = cur[0].y & 0x3f3f3f3fu, mn_lo = cur[0].z & 0x3f3f3f3fu;
-                const uint32_t sc_hi = (cur[0].w & 0x0f0f0f0fu) | ((cur[0].y >> 2) & 0x30303030u);
-                const uint32_t mn_hi = ((cur[0].w >> 4) & 0x0f0f0f0fu) | ((cur[0].z >> 2) & 0x30303030u);
+                for (int e = 0; e < 2 && ok; ++e) {
+                    const int sb = 2 * pr + e;
+                    const bool exists = sb < nsb;
+                    const uint4 hdr = exists ? hdr_n : zero4;
+                    if (live && sb + 1 < nsb) hdr_n = __ldg(src + (sb + 1) * 9);
+                    const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
+                    // 6-bit scales / mins, eight of each (Laplace src/kernels.h:82-90), one per byte
+                    const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, mn_lo = hdr.z & 0x3f3f3f3fu;
+                    const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+                    const uint32_t mn_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+                    {
+                        // G operand: k'' = 3j + piece  ->  mn_j as bf16 (exact), 24 values + 8 zeros = 64 bytes,
+                        // the e-th half of row r. Two j per three 32-bit words: (a,a) (a,b) (b,b).
+                        uint32_t gw[16];
 #pragma unroll
-                for (int c = 0; c < 4; ++c, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = ((it / STAGES) & 1) ^ 1;
-                    if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_EMPTY) ||
-                        !wait_or_abort(sbase + BAR_TAB_EMPTY + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    const uint32_t scw = c < 2 ? sc_lo : sc_hi, mnw = c < 2 ? mn_lo : mn_hi;
-                    const uint32_t sc1 = (scw >> (16 * (c & 1))) & 0xff, sc2 = (scw >> (16 * (c & 1) + 8)) & 0xff;
-                    const uint32_t mn1 = (mnw >> (16 * (c & 1))) & 0xff, mn2 = (mnw >> (16 * (c & 1) + 8)) & 0xff;
-                    // chunk c: 32 bytes of nibbles = uint4 1+2c and 2+2c
-                    const uint32_t qw[8] = {cur[1 + 2 * c].x, cur[1 + 2 * c].y, cur[1 + 2 * c].z, cur[1 + 2 * c].w,
-                                            cur[2 + 2 * c].x, cur[2 + 2 * c].y, cur[2 + 2 * c].z, cur[2 + 2 * c].w};
-                    // fp16 operand row: 32 low-nibble values * sc1, then 32 high-nibble values * sc2.
-                    // Within every 4 values the order is (0, 2, 1, 3); the activation operand uses the same order.
-                    uint32_t h[32];
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const uint32_t mw = jj < 2 ? mn_lo : mn_hi;
+                            const uint32_t a = (mw >> (16 * (jj & 1))) & 0xff, b = (mw >> (16 * (jj & 1) + 8)) & 0xff;
+                            const uint32_t ab = __float_as_uint(static_cast<float>(a)) >> 16;     // bf16 bits of a small integer
+                            const uint32_t bb = __float_as_uint(static_cast<float>(b)) >> 16;
+                            gw[3 * jj] = ab | (ab << 16);
+                            gw[3 * jj + 1] = ab | (bb << 16);
+                            gw[3 * jj + 2] = bb | (bb << 16);
+                        }
+                        gw[12] = gw[13] = gw[14] = gw[15] = 0;
+                        uint8_t* grow = smem + OFF_GB + g * G_TILE + r * 128;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint32_t w = qw[i];
-                        const uint32_t a0 = ((w & 0x000f000fu) * sc1) | 0x64006400u;          // fp16(1024 + v) pairs
-                        const uint32_t a1 = (((w >> 8) & 0x000f000fu) * sc1) | 0x64006400u;
-                        const uint32_t b0 = (((w >> 4) & 0x000f000fu) * sc2) | 0x64006400u;
-                        const uint32_t b1 = (((w >> 12) & 0x000f000fu) * sc2) | 0x64006400u;
-                        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-                        __half2 x;
-                        x = __hsub2(*reinterpret_cast<const __half2*>(&a0), k1024); h[2 * i] = *reinterpret_cast<uint32_t*>(&x);
-                        x = __hsub2(*reinterpret_cast<const __half2*>(&a1), k1024); h[2 * i + 1] = *reinterpret_cast<uint32_t*>(&x);
-                        x = __hsub2(*reinterpret_cast<const __half2*>(&b0), k1024); h[16 + 2 * i] = *reinterpret_cast<uint32_t*>(&x);
-                        x = __hsub2(*reinterpret_cast<const __half2*>(&b1), k1024); h[16 + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&x);
+                        for (int q = 0; q < 4; ++q)
+                            *reinterpret_cast<uint4*>(grow + (((e * 4 + q) ^ (r & 7)) << 4)) =
+                                make_uint4(gw[4 * q], gw[4 * q + 1], gw[4 * q + 2], gw[4 * q + 3]);
+                        float* gtab = reinterpret_cast<float*>(smem + OFF_GTAB + g * GTAB_BYTES) + e * 2 * BN;
+                        gtab[r] = d;
+                        gtab[BN + r] = dmin;
+                        fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's reads
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(sbase + BAR_G_FULL_B + 8 * g);
                     }
-                    uint8_t* brow = smem + OFF_B + s * B_TILE + r * 128;
+                    if (!exists) continue;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<uint4*>(brow + ((j ^ (r & 7)) << 4)) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
-                    float* tab = reinterpret_cast<float*>(smem + OFF_TAB + s * TAB_BYTES);
-                    tab[r] = dmin * static_cast<float>(mn1);
-                    tab[BN + r] = dmin * static_cast<float>(mn2);
-                    tab[2 * BN + r] = d;
-                    fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's reads
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(sbase + BAR_FULL_B + 8 * s);
+                    for (int c = 0; c < 4; ++c, ++it) {
+                        const uint4 qa = qa_n, qb = qb_n;
+                        {
+                            // next chunk: same super-block, or the first of the next one
+                            const int nsbi = c == 3 ? sb + 1 : sb, nc = c == 3 ? 0 : c + 1;
+                            if (live && nsbi < nsb) {
+                                qa_n = __ldg(src + nsbi * 9 + 1 + 2 * nc);
+                                qb_n = __ldg(src + nsbi * 9 + 2 + 2 * nc);
+                            }
+                        }
+                        const int s = it % STAGES;
+                        if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                        const uint32_t scw = c < 2 ? sc_lo : sc_hi;
+                        const uint32_t sc1 = (scw >> (16 * (c & 1))) & 0xff, sc2 = (scw >> (16 * (c & 1) + 8)) & 0xff;
+                        const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                        // fp16 operand row: 32 low-nibble values * sc1, then 32 high-nibble values * sc2.
+                        // Within every 4 values the order is (0, 2, 1, 3); the activation operand uses the same order.
+                        // (v | 0x6400) is fp16(1024 + v); one fused multiply-add turns it into v * sc exactly:
+                        // (1024 + v) * sc - 1024 * sc. High nibbles stay in place as 16 v and use sc / 16.
+                        const __half2 s1 = __half2half2(__ushort2half_rn(static_cast<unsigned short>(sc1)));
+                        const __half2 s2 = __half2half2(__hmul(__ushort2half_rn(static_cast<unsigned short>(sc2)), __float2half_rn(0.0625f)));
+                        const __half2 o1 = __hmul2(s1, __half2half2(__float2half_rn(-1024.f)));
+                        const __half2 o2 = __hmul2(s2, __half2half2(__float2half_rn(-1024.f)));
+                        uint32_t h[32];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const uint32_t w = qw[i], t = w >> 8;
+                            const uint32_t a0 = (w & 0x000f000fu) | 0x64006400u, a1 = (t & 0x000f000fu) | 0x64006400u;
+                            const uint32_t b0 = (w & 0x00f000f0u) | 0x64006400u, b1 = (t & 0x00f000f0u) | 0x64006400u;
+                            __half2 x;
+                            x = __hfma2(*reinterpret_cast<const __half2*>(&a0), s1, o1); h[2 * i] = *reinterpret_cast<uint32_t*>(&x);
+                            x = __hfma2(*reinterpret_cast<const __half2*>(&a1), s1, o1); h[2 * i + 1] = *reinterpret_cast<uint32_t*>(&x);
+                            x = __hfma2(*reinterpret_cast<const __half2*>(&b0), s2, o2); h[16 + 2 * i] = *reinterpret_cast<uint32_t*>(&x);
+                            x = __hfma2(*reinterpret_cast<const __half2*>(&b1), s2, o2); h[16 + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&x);
+                        }
+                        uint8_t* brow = smem + OFF_B + s * B_TILE + r * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<uint4*>(brow + ((j ^ (r & 7)) << 4)) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(sbase + BAR_FULL_B + 8 * s);
+                    }
                 }
             }
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ---------------- epilogue: lane = token row, 64 columns per warp ----------------
-        const int e = warp - 8;
-        const int quad = e & 3, half = e >> 2;
+        const int e8 = warp - 8;
+        const int quad = e8 & 3, half = e8 >> 2;
         const uint32_t t_lane = static_cast<uint32_t>(quad * 32) << 16;
-        int it = 0, bc = 0;
+        int bc = 0, gp = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
             const int m = m0 + quad * 32 + lane;
             const bool row_live = m < p.M;
-            const float* dxr = p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32);
-            const float* sxr = p.sumx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32);
-            float acc[64], acc2[64];
+            const float2* dxr = reinterpret_cast<const float2*>(p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32));
+            float acc[64];
+            float2 acc2[32];
 #pragma unroll
-            for (int c = 0; c < 64; ++c) { acc[c] = 0.f; acc2[c] = 0.f; }
-            for (int kc = 0; kc < chunks && ok; ++kc, ++it) {
-                const int s = it % STAGES;
-                const float2 dx2 = row_live ? __ldg(reinterpret_cast<const float2*>(dxr) + kc) : make_float2(0.f, 0.f);
-                const float2 sx2 = row_live ? __ldg(reinterpret_cast<const float2*>(sxr) + kc) : make_float2(0.f, 0.f);
-                const float* tab = reinterpret_cast<const float*>(smem + OFF_TAB + s * TAB_BYTES);
+            for (int c = 0; c < 64; ++c) acc[c] = 0.f;
 #pragma unroll
-                for (int blk = 0; blk < 2; ++blk, ++bc) {
-                    const int t = bc & 1;
-                    if (!wait_or_abort(sbase + BAR_TMEM_FULL + 8 * t, (bc >> 1) & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
-                    tc_fence_after();
-                    const float dxv = blk ? dx2.y : dx2.x, nsx = blk ? -sx2.y : -sx2.x;
-                    const uint32_t taddr = tmem_base + t_lane + t * BN + half * 64;
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        float f[16];
-                        tc_ld16(taddr + 16 * g, f);
-                        tc_wait_ld();
-                        if (g == 3) {
-                            // the whole tile has been read: hand the TMEM buffer back early
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * t);
+            for (int c = 0; c < 32; ++c) acc2[c] = make_float2(0.f, 0.f);
+            float2 dx_n = row_live ? __ldg(dxr) : make_float2(0.f, 0.f);
+            for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
+                const int g = gp % GST;
+                const uint32_t gtab = sbase + OFF_GTAB + g * GTAB_BYTES;
+                for (int e = 0; e < 2 && ok; ++e) {
+                    const int sb = 2 * pr + e;
+                    if (sb >= nsb) break;
+                    for (int kc = 0; kc < 4 && ok; ++kc) {
+                        const float2 dx2 = dx_n;
+                        {
+                            const int nchunk = sb * 4 + kc + 1;
+                            if (row_live && nchunk < nsb * 4) dx_n = __ldg(dxr + nchunk);
                         }
 #pragma unroll
-                        for (int c4 = 0; c4 < 4; ++c4) {
-                            const float4 mm = *reinterpret_cast<const float4*>(tab + blk * BN + half * 64 + 16 * g + 4 * c4);
-                            const int c = 16 * g + 4 * c4;
-                            acc2[c] = fmaf(dxv, f[4 * c4], acc2[c]);         acc[c] = fmaf(nsx, mm.x, acc[c]);
-                            acc2[c + 1] = fmaf(dxv, f[4 * c4 + 1], acc2[c + 1]); acc[c + 1] = fmaf(nsx, mm.y, acc[c + 1]);
-                            acc2[c + 2] = fmaf(dxv, f[4 * c4 + 2], acc2[c + 2]); acc[c + 2] = fmaf(nsx, mm.z, acc[c + 2]);
-                            acc2[c + 3] = fmaf(dxv, f[4 * c4 + 3], acc2[c + 3]); acc[c + 3] = fmaf(nsx, mm.w, acc[c + 3]);
+                        for (int blk = 0; blk < 2; ++blk, ++bc) {
+                            const int t = bc & 1;
+                            if (!wait_or_abort(sbase + BAR_TMEM_FULL + 8 * t, (bc >> 1) & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
+                            tc_fence_after();
+                            const float dxv = blk ? dx2.y : dx2.x;
+                            const float2 dxx = make_float2(dxv, dxv);
+                            const uint32_t taddr = tmem_base + t_lane + TM_F + t * BN + half * 64;
+                            // 16 columns at a time; the TMEM load of the next group is in flight while this
+                            // group is scaled and accumulated (packed fp32x2 multiply-adds)
+                            float f0[16], f1[16];
+                            tc_ld16(taddr, f0);
+                            tc_wait_ld();
+#pragma unroll
+                            for (int gq = 0; gq < 4; ++gq) {
+                                float (&f)[16] = (gq & 1) ? f1 : f0;
+                                float (&fn)[16] = (gq & 1) ? f0 : f1;
+                                if (gq < 3) tc_ld16(taddr + 16 * (gq + 1), fn);
+#pragma unroll
+                                for (int c2 = 0; c2 < 8; ++c2)
+                                    acc2[8 * gq + c2] = __ffma2_rn(dxx, make_float2(f[2 * c2], f[2 * c2 + 1]), acc2[8 * gq + c2]);
+                                if (gq < 3) tc_wait_ld();
+                                if (gq == 2) {
+                                    // every column of the tile is now in registers: hand the TMEM buffer back
+                                    tc_fence_before();
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * t);
+                                }
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    // end of a super-block: fold in its fp16 scale d (per weight row = per column)
+                    {
+                        const uint32_t dtab = gtab + (e * 2 * BN + half * 64) * 4;
+#pragma unroll
+                        for (int c2 = 0; c2 < 32; ++c2) {
+                            acc[2 * c2] = fmaf(__uint_as_float(lds32(dtab + 8 * c2)), acc2[c2].x, acc[2 * c2]);
+                            acc[2 * c2 + 1] = fmaf(__uint_as_float(lds32(dtab + 8 * c2 + 4)), acc2[c2].y, acc[2 * c2 + 1]);
+                            acc2[c2] = make_float2(0.f, 0.f);
                         }
                     }
                 }
                 if (!ok) break;
-                if ((kc & 3) == 3) {
-                    // end of a super-block: fold in its fp16 scale d (per weight row = per column)
+                // end of a pair: subtract dmin * G for both super-blocks
+                if (!wait_or_abort(sbase + BAR_GT_FULL, gp & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
+                tc_fence_after();
 #pragma unroll
-                    for (int c4 = 0; c4 < 16; ++c4) {
-                        const float4 dd = *reinterpret_cast<const float4*>(tab + 2 * BN + half * 64 + 4 * c4);
-                        acc[4 * c4] = fmaf(dd.x, acc2[4 * c4], acc[4 * c4]);             acc2[4 * c4] = 0.f;
-                        acc[4 * c4 + 1] = fmaf(dd.y, acc2[4 * c4 + 1], acc[4 * c4 + 1]); acc2[4 * c4 + 1] = 0.f;
-                        acc[4 * c4 + 2] = fmaf(dd.z, acc2[4 * c4 + 2], acc[4 * c4 + 2]); acc2[4 * c4 + 2] = 0.f;
-                        acc[4 * c4 + 3] = fmaf(dd.w, acc2[4 * c4 + 3], acc[4 * c4 + 3]); acc2[4 * c4 + 3] = 0.f;
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t taddr = tmem_base + t_lane + TM_G + e * BN + half * 64;
+                    const uint32_t mtab = gtab + (e * 2 * BN + BN + half * 64) * 4;
+#pragma unroll
+                    for (int gq = 0; gq < 4; ++gq) {
+                        float f[16];
+                        tc_ld16(taddr + 16 * gq, f);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            acc[16 * gq + c] = fmaf(-__uint_as_float(lds32(mtab + (16 * gq + c) * 4)), f[c], acc[16 * gq + c]);
                     }
                 }
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sbase + BAR_TAB_EMPTY + 8 * s);     // tables of this stage are free
+                if (lane == 0) {
+                    mbar_arrive(sbase + BAR_GT_EMPTY);
+                    mbar_arrive(sbase + BAR_G_TAB_EMPTY + 8 * g);
+                }
             }
             if (ok && row_live) {
                 float* yr = p.y + static_cast<size_t>(m) * p.N + n0 + half * 64;
@@ -369,9 +513,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const TcParams p)
 // Same arithmetic as quantize_act_kernel (Laplace src/matmul_simd.cpp:348-410); the int8
 // values are written as fp16 (exact) in the operand's k order: within every four
 // consecutive values, (0, 2, 1, 3). Rows M..M_pad-1 of the operand are zero.
+// sum = d * (integer block sum) is written as three bf16 pieces whose sum is sum to 24
+// bits: ag[m][sb*32 + 3*j + piece] for block j of super-block sb (the buffer is zeroed
+// before the launch, so the 8 padding entries per super-block stay 0).
 __global__ void __launch_bounds__(256) quantize_act_f16_kernel(const float* __restrict__ x, int M, int K, long long n_blocks,
                                                                __half* __restrict__ aq, float* __restrict__ dx,
-                                                               float* __restrict__ sumx) {
+                                                               __nv_bfloat16* __restrict__ ag, int ag_stride) {
     const int t8 = threadIdx.x & 7;
     const long long groups = static_cast<long long>(gridDim.x) * (blockDim.x >> 3);
     const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x >> 3) + (threadIdx.x >> 3);
@@ -397,7 +544,16 @@ __global__ void __launch_bounds__(256) quantize_act_f16_kernel(const float* __re
         if (t8 == 0 && live) {
             const short slo = static_cast<short>(hs), shi = static_cast<short>(hs_hi);
             dx[b] = d;
-            sumx[b] = d * static_cast<float>(static_cast<int>(slo) + static_cast<int>(shi));
+            const float sum = d * static_cast<float>(static_cast<int>(slo) + static_cast<int>(shi));
+            const __nv_bfloat16 p0 = __float2bfloat16_rn(sum);
+            const float r1 = sum - __bfloat162float(p0);
+            const __nv_bfloat16 p1 = __float2bfloat16_rn(r1);
+            const __nv_bfloat16 p2 = __float2bfloat16_rn(r1 - __bfloat162float(p1));
+            const int bpr = K / 32;
+            const long long m = b / bpr;
+            const int kb = static_cast<int>(b - m * bpr);
+            __nv_bfloat16* dst = ag + m * ag_stride + (kb >> 3) * 32 + 3 * (kb & 7);
+            dst[0] = p0; dst[1] = p1; dst[2] = p2;
         }
     }
 }
@@ -438,39 +594,62 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const size_t m_pad = static_cast<size_t>(tiles_m) * BM;
     const size_t bpr = static_cast<size_t>(K / 32);
+    const int n_pairs = (K / 256 + 1) / 2;
     const size_t aq_bytes = (m_pad * K * sizeof(__half) + 255) & ~size_t(255);
     const size_t sc_bytes = (static_cast<size_t>(M) * bpr * sizeof(float) + 255) & ~size_t(255);
-    int rc = g_scratch.ensure(aq_bytes + 2 * sc_bytes);
+    const size_t ag_bytes = (m_pad * n_pairs * 64 * sizeof(__nv_bfloat16) + 255) & ~size_t(255);
+    int rc = g_scratch.ensure(aq_bytes + sc_bytes + ag_bytes);
     if (rc) return rc;
     __half* aq = static_cast<__half*>(g_scratch.p);
     float* dx = reinterpret_cast<float*>(static_cast<uint8_t*>(g_scratch.p) + aq_bytes);
-    float* sumx = reinterpret_cast<float*>(static_cast<uint8_t*>(g_scratch.p) + aq_bytes + sc_bytes);
+    __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(g_scratch.p) + aq_bytes + sc_bytes);
 
     {
+        if ((rc = cuda_check(cudaMemsetAsync(ag, 0, ag_bytes, st), "cudaMemsetAsync"))) return rc;
         const long long n_blocks = static_cast<long long>(m_pad) * bpr;
         long long want = (n_blocks + 31) / 32;
         const long long cap = static_cast<long long>(c.sm_count) * 8;
         const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
-        quantize_act_f16_kernel<<<grid, 256, 0, st>>>(x, M, K, n_blocks, aq, dx, sumx);
+        quantize_act_f16_kernel<<<grid, 256, 0, st>>>(x, M, K, n_blocks, aq, dx, ag, n_pairs * 64);
         c.launches++;
         if ((rc = cuda_check(cudaGetLastError(), "quantize_act_f16 launch"))) return rc;
     }
 
-    // 2-D tensor map over the fp16 operand: inner dimension K, outer dimension tokens.
-    CUtensorMap tmap;
+    // 2-D tensor maps: the fp16 operand (inner dimension K) and the bf16 pieces of sum_x
+    // (inner dimension 64 per pair of super-blocks); outer dimension tokens.
+    CUtensorMap tmap, tmap_g;
     {
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(m_pad)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * sizeof(__half)};
+        // The driver entry point is looked up at run time so that the library does not link libcuda.
+        using encode_fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+        static encode_fn cuTensorMapEncodeTiled = nullptr;
+        if (!cuTensorMapEncodeTiled) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+            if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+                return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+            cuTensorMapEncodeTiled = reinterpret_cast<encode_fn>(fn);
+        }
         const cuuint32_t box[2] = {BKC, BM};
         const cuuint32_t estr[2] = {1, 1};
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(m_pad)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * sizeof(__half)};
         CUresult r = cuTensorMapEncodeTiled(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, aq, dims, strides, box, estr,
                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+        const cuuint64_t gdims[2] = {static_cast<cuuint64_t>(n_pairs) * 64, static_cast<cuuint64_t>(m_pad)};
+        const cuuint64_t gstrides[1] = {static_cast<cuuint64_t>(n_pairs) * 64 * sizeof(__nv_bfloat16)};
+        r = cuTensorMapEncodeTiled(&tmap_g, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ag, gdims, gstrides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled (G) failed (%d)", static_cast<int>(r));
     }
 
     TcParams p{};
-    p.w = w; p.dx = dx; p.sumx = sumx; p.y = y; p.err = c.d_err;
+    p.w = w; p.dx = dx; p.y = y; p.err = c.d_err;
     p.M = M; p.N = N; p.K = K; p.rb = static_cast<uint32_t>(row_bytes(type, K));
     p.tiles_m = tiles_m; p.tiles_n = tiles_n;
     static bool configured = false;
@@ -481,7 +660,7 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
     }
     const int n_tiles = tiles_m * tiles_n;
     const int grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
-    gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, p);
+    gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, tmap_g, p);
     c.launches++;
     c.last_path = 2;
     return cuda_check(cudaGetLastError(), "gemm_q4k_tc launch");
