@@ -171,6 +171,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) /* suspend-time hint, ns */ : "memory");
     return ok != 0;
 }
+// Same without a suspend-time hint: for hand-offs on a critical path, where the wake-up
+// must follow the phase completion at once.
+__device__ __forceinline__ bool mbar_try_wait_nohint(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Returns false when the wait gave up (a second or so of polling). After the
 // first miss the warp backs off between polls so that it does not take issue
 // slots from warps that have data.

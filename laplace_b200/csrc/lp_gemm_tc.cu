@@ -43,15 +43,17 @@ namespace lp {
 namespace {
 
 constexpr int BM = 128, BN = 128, BKC = 64;        // tile; BKC = k per pipeline stage (two 32-value blocks)
-constexpr int STAGES = 4;                          // main ring: activation + weight operand tiles
+constexpr int STAGES = 3;                          // main ring: activation + weight operand tiles
+constexpr int RAW_STAGES = 3;                      // ring of packed super-blocks (128 rows x 144 bytes) ahead of the converters
+constexpr int RAW_TILE = BN * Q4_K_BYTES;          // 18 KB
 constexpr int GST = 2;                             // ring of "pair of super-blocks" stages for the G operands
 constexpr int A_TILE = BM * BKC * 2;               // 16 KB, fp16
 constexpr int B_TILE = BN * BKC * 2;               // 16 KB, fp16
 constexpr int G_TILE = 128 * 64 * 2;               // 16 KB, bf16: 32 k per super-block, two super-blocks per row
 constexpr int GTAB_BYTES = 2 * 2 * BN * 4;         // per G stage: [super-block of the pair][d, dmin][column]
 constexpr int THREADS = 512;
-constexpr int TMEM_COLS = 512;                     // F0, F1 (block sums, double buffered), G even, G odd
-constexpr uint32_t TM_F = 0, TM_G = 256;
+constexpr int TMEM_COLS = 512;                     // F0, F1 (block sums, double buffered), G, running y
+constexpr uint32_t TM_F = 0, TM_G = 256, TM_ACC = 384;
 
 // shared-memory map (dynamic, 1024-byte aligned base)
 constexpr uint32_t OFF_A = 0;
@@ -59,13 +61,15 @@ constexpr uint32_t OFF_B = OFF_A + STAGES * A_TILE;
 constexpr uint32_t OFF_GA = OFF_B + STAGES * B_TILE;
 constexpr uint32_t OFF_GB = OFF_GA + GST * G_TILE;
 constexpr uint32_t OFF_GTAB = OFF_GB + GST * G_TILE;
-constexpr uint32_t OFF_BAR = OFF_GTAB + GST * GTAB_BYTES;
+constexpr uint32_t OFF_RAW = OFF_GTAB + GST * GTAB_BYTES;
+constexpr uint32_t OFF_BAR = OFF_RAW + RAW_STAGES * RAW_TILE;
 constexpr uint32_t BAR_FULL_A = OFF_BAR, BAR_FULL_B = BAR_FULL_A + 8 * STAGES, BAR_EMPTY = BAR_FULL_B + 8 * STAGES,
                    BAR_TMEM_FULL = BAR_EMPTY + 8 * STAGES, BAR_TMEM_EMPTY = BAR_TMEM_FULL + 16,
                    BAR_G_FULL_A = BAR_TMEM_EMPTY + 16, BAR_G_FULL_B = BAR_G_FULL_A + 8 * GST,
-                   BAR_G_EMPTY = BAR_G_FULL_B + 8 * GST, BAR_G_TAB_EMPTY = BAR_G_EMPTY + 8 * GST,
+                   BAR_G_EMPTY = BAR_G_FULL_B + 16 * GST, BAR_G_TAB_EMPTY = BAR_G_EMPTY + 8 * GST,
                    BAR_GT_FULL = BAR_G_TAB_EMPTY + 8 * GST, BAR_GT_EMPTY = BAR_GT_FULL + 8,
-                   OFF_TMEM_PTR = BAR_GT_EMPTY + 8, OFF_ABORT = OFF_TMEM_PTR + 8;
+                   BAR_RAW_FULL = BAR_GT_EMPTY + 8, BAR_RAW_EMPTY = BAR_RAW_FULL + 8 * RAW_STAGES,
+                   OFF_TMEM_PTR = BAR_RAW_EMPTY + 8 * RAW_STAGES, OFF_ABORT = OFF_TMEM_PTR + 8;
 constexpr uint32_t SMEM_BYTES = OFF_ABORT + 8 + 1024;   // + slack for the 1024-byte alignment
 
 struct TcParams {
@@ -105,6 +109,16 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const float (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        :: "r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+           "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+           "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+           "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
@@ -126,10 +140,10 @@ constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);
 
 // Waits that also give up when another role has raised the abort flag.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
-    // try_wait suspends the thread in hardware (up to its time hint) and wakes it when the phase
-    // completes; a software sleep here would add its whole quantum to every hand-off between roles.
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
+    // No software sleep and no suspend-time hint: either adds its quantum to every hand-off
+    // between roles, and a block goes through four of them.
+    for (uint32_t it = 0; it < (1u << 26); ++it) {
+        if (mbar_try_wait_nohint(bar, parity)) return true;
         if (*abort_flag) return false;
     }
     *abort_flag = 1;
@@ -146,7 +160,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 // padding super-block has no chunks and contributes zeros to G.
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_g,
-                   const TcParams p) {
+                   const __grid_constant__ CUtensorMap tmap_w, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (sbase - smem_u32(smem_raw));
@@ -165,9 +179,14 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
         for (int g = 0; g < GST; ++g) {
             mbar_init(sbase + BAR_G_FULL_A + 8 * g, 1);
-            mbar_init(sbase + BAR_G_FULL_B + 8 * g, 8);      // 4 converter warps x 2 super-blocks
+            mbar_init(sbase + BAR_G_FULL_B + 16 * g, 4);     // per super-block of the pair: 4 converter warps
+            mbar_init(sbase + BAR_G_FULL_B + 16 * g + 8, 4);
             mbar_init(sbase + BAR_G_EMPTY + 8 * g, 1);       // tcgen05.commit
             mbar_init(sbase + BAR_G_TAB_EMPTY + 8 * g, 8);   // one arrive per epilogue warp
+        }
+        for (int q = 0; q < RAW_STAGES; ++q) {
+            mbar_init(sbase + BAR_RAW_FULL + 8 * q, 1);
+            mbar_init(sbase + BAR_RAW_EMPTY + 8 * q, 4);     // one arrive per converter warp
         }
         mbar_init(sbase + BAR_GT_FULL, 1);                   // tcgen05.commit
         mbar_init(sbase + BAR_GT_EMPTY, 8);
@@ -229,55 +248,75 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     if (v >= 0) mbar_wait_bounded(sbase + BAR_G_FULL_A + 8 * (v % GST), (v / GST) & 1);
                 }
             }
+        } else if (warp == 3 && lane == 0) {
+            // ---------------- TMA producer: packed weights, one super-block of 128 rows per tile ----------------
+            // (rows past N are zero-filled by the copy engine: d = 0, every scale 0)
+            int rq = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const int n0 = (tile / p.tiles_m) * BN;
+                for (int sb = 0; sb < nsb; ++sb, ++rq) {
+                    const int q = rq % RAW_STAGES;
+                    if (!wait_or_abort(sbase + BAR_RAW_EMPTY + 8 * q, ((rq / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(sbase + BAR_RAW_FULL + 8 * q, RAW_TILE);
+                    tma_load_2d(sbase + OFF_RAW + q * RAW_TILE, &tmap_w, sb * Q4_K_BYTES, n0, sbase + BAR_RAW_FULL + 8 * q);
+                }
+            }
+            if (!ok) {
+                for (int k = 0; k < RAW_STAGES; ++k) {
+                    const int v = rq - 1 - k;
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_RAW_FULL + 8 * (v % RAW_STAGES), (v / RAW_STAGES) & 1);
+                }
+            }
         } else if (warp == 1 && lane == 0) {
             // ---------------- MMA issuer ----------------
-            int it = 0, bc = 0, gp = 0;
+            int it = 0, bc = 0, gp = 0, gsb = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
-                    const int sb_in_pair = (2 * pr + 1 < nsb) ? 2 : 1;
-                    for (int kc = 0; kc < 4 * sb_in_pair && ok; ++kc, ++it) {
-                        const int s = it % STAGES;
-                        const uint32_t ph = (it / STAGES) & 1;
-                        if (!wait_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
-                            !wait_or_abort(sbase + BAR_FULL_B + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
-                        tc_fence_after();
-                        const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
-                        const uint64_t bdesc = smem_desc_sw128(sbase + OFF_B + s * B_TILE);
-#pragma unroll
-                        for (int blk = 0; blk < 2; ++blk, ++bc) {
-                            const int t = bc & 1;
-                            if (!wait_or_abort(sbase + BAR_TMEM_EMPTY + 8 * t, ((bc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
-                            tc_fence_after();
-#pragma unroll
-                            for (int k = 0; k < 2; ++k) {
-                                const uint64_t off = static_cast<uint64_t>((blk * 64 + k * 32) >> 4);   // bytes >> 4 inside the swizzle row
-                                tc_mma_f16(tmem_base + TM_F + t * BN, adesc + off, bdesc + off, IDESC_F16, k);
-                            }
-                            tc_commit(sbase + BAR_TMEM_FULL + 8 * t);      // block sum complete -> epilogue
-                        }
-                        tc_commit(sbase + BAR_EMPTY + 8 * s);              // operands consumed -> producers
-                    }
-                    if (!ok) break;
-                    // G of both super-blocks of the pair: K = 32 bf16 each, halves of the same 128-byte rows
                     const int g = gp % GST;
                     const uint32_t gph = (gp / GST) & 1;
-                    if (!wait_or_abort(sbase + BAR_G_FULL_A + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
-                        !wait_or_abort(sbase + BAR_G_FULL_B + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
-                        !wait_or_abort(sbase + BAR_GT_EMPTY, (gp & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint64_t gadesc = smem_desc_sw128(sbase + OFF_GA + g * G_TILE);
-                    const uint64_t gbdesc = smem_desc_sw128(sbase + OFF_GB + g * G_TILE);
+                    for (int e = 0; e < 2 && ok; ++e) {
+                        if (2 * pr + e >= nsb) break;
+                        for (int kc = 0; kc < 4 && ok; ++kc, ++it) {
+                            const int s = it % STAGES;
+                            const uint32_t ph = (it / STAGES) & 1;
+                            if (!wait_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                                !wait_or_abort(sbase + BAR_FULL_B + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                            tc_fence_after();
+                            const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
+                            const uint64_t bdesc = smem_desc_sw128(sbase + OFF_B + s * B_TILE);
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
+                            for (int blk = 0; blk < 2; ++blk, ++bc) {
+                                const int t = bc & 1;
+                                if (!wait_or_abort(sbase + BAR_TMEM_EMPTY + 8 * t, ((bc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                                tc_fence_after();
+#pragma unroll
+                                for (int k = 0; k < 2; ++k) {
+                                    const uint64_t off = static_cast<uint64_t>((blk * 64 + k * 32) >> 4);   // bytes >> 4 inside the swizzle row
+                                    tc_mma_f16(tmem_base + TM_F + t * BN, adesc + off, bdesc + off, IDESC_F16, k);
+                                }
+                                tc_commit(sbase + BAR_TMEM_FULL + 8 * t);      // block sum complete -> epilogue
+                            }
+                            tc_commit(sbase + BAR_EMPTY + 8 * s);              // operands consumed -> producers
+                        }
+                        if (!ok) break;
+                        // G of this super-block: K = 32 bf16, the e-th half of the pair's 128-byte rows
+                        if ((e == 0 && !wait_or_abort(sbase + BAR_G_FULL_A + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_FULL)) ||
+                            !wait_or_abort(sbase + BAR_G_FULL_B + 16 * g + 8 * e, gph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                            !wait_or_abort(sbase + BAR_GT_EMPTY, (gsb & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t gadesc = smem_desc_sw128(sbase + OFF_GA + g * G_TILE);
+                        const uint64_t gbdesc = smem_desc_sw128(sbase + OFF_GB + g * G_TILE);
 #pragma unroll
                         for (int k = 0; k < 2; ++k) {
                             const uint64_t off = static_cast<uint64_t>((e * 64 + k * 32) >> 4);
-                            tc_mma_f16(tmem_base + TM_G + e * BN, gadesc + off, gbdesc + off, IDESC_BF16, k);
+                            tc_mma_f16(tmem_base + TM_G, gadesc + off, gbdesc + off, IDESC_BF16, k);
                         }
+                        tc_commit(sbase + BAR_GT_FULL);
+                        ++gsb;
                     }
-                    tc_commit(sbase + BAR_GT_FULL);
-                    tc_commit(sbase + BAR_G_EMPTY + 8 * g);
+                    if (ok) tc_commit(sbase + BAR_G_EMPTY + 8 * g);     // the pair's G operands are consumed
                 }
             }
         }
@@ -285,16 +324,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         // ---------------- converters: thread r owns weight row n0 + r ----------------
         const int r = threadIdx.x - 128;
-        int it = 0, gp = 0;
+        int it = 0, gp = 0, rq = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const int n0 = (tile / p.tiles_m) * BN;
-            const bool live = n0 + r < p.N;
-            const uint4* src = reinterpret_cast<const uint4*>(p.w + static_cast<size_t>(live ? n0 + r : 0) * p.rb);
             const uint4 zero4 = make_uint4(0, 0, 0, 0);
-            // one chunk (32 bytes of nibbles) and one header are fetched ahead of use
-            uint4 hdr_n = live ? __ldg(src) : zero4;
-            uint4 qa_n = live ? __ldg(src + 1) : zero4, qb_n = live ? __ldg(src + 2) : zero4;
             for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
                 const int g = gp % GST;
                 {
@@ -305,8 +338,10 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 for (int e = 0; e < 2 && ok; ++e) {
                     const int sb = 2 * pr + e;
                     const bool exists = sb < nsb;
-                    const uint4 hdr = exists ? hdr_n : zero4;
-                    if (live && sb + 1 < nsb) hdr_n = __ldg(src + (sb + 1) * 9);
+                    const int q = rq % RAW_STAGES;
+                    const uint32_t raw = sbase + OFF_RAW + q * RAW_TILE + r * Q4_K_BYTES;      // this row's 144 bytes
+                    if (exists && !wait_or_abort(sbase + BAR_RAW_FULL + 8 * q, (rq / RAW_STAGES) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                    const uint4 hdr = exists ? lds128(raw) : zero4;
                     const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
                     // 6-bit scales / mins, eight of each (Laplace src/kernels.h:82-90), one per byte
                     const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, mn_lo = hdr.z & 0x3f3f3f3fu;
@@ -337,20 +372,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         gtab[BN + r] = dmin;
                         fence_proxy_async();          // generic-proxy stores -> visible to the tensor core's reads
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(sbase + BAR_G_FULL_B + 8 * g);
+                        if (lane == 0) mbar_arrive(sbase + BAR_G_FULL_B + 16 * g + 8 * e);
                     }
                     if (!exists) continue;
 #pragma unroll
                     for (int c = 0; c < 4; ++c, ++it) {
-                        const uint4 qa = qa_n, qb = qb_n;
-                        {
-                            // next chunk: same super-block, or the first of the next one
-                            const int nsbi = c == 3 ? sb + 1 : sb, nc = c == 3 ? 0 : c + 1;
-                            if (live && nsbi < nsb) {
-                                qa_n = __ldg(src + nsbi * 9 + 1 + 2 * nc);
-                                qb_n = __ldg(src + nsbi * 9 + 2 + 2 * nc);
-                            }
-                        }
+                        const uint4 qa = lds128(raw + 16 + 32 * c), qb = lds128(raw + 32 + 32 * c);
                         const int s = it % STAGES;
                         if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                         const uint32_t scw = c < 2 ? sc_lo : sc_hi;
@@ -384,26 +411,31 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         __syncwarp();
                         if (lane == 0) mbar_arrive(sbase + BAR_FULL_B + 8 * s);
                     }
+                    // the packed super-block has been read: its slot may be refilled
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sbase + BAR_RAW_EMPTY + 8 * q);
+                    ++rq;
                 }
             }
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ---------------- epilogue: lane = token row, 64 columns per warp ----------------
+        // Registers hold only the current block's sums and the super-block's partial result;
+        // the running y of the tile lives in TMEM (TM_ACC) and is touched once per super-block.
         const int e8 = warp - 8;
         const int quad = e8 & 3, half = e8 >> 2;
         const uint32_t t_lane = static_cast<uint32_t>(quad * 32) << 16;
-        int bc = 0, gp = 0;
+        const uint32_t t_acc = tmem_base + t_lane + TM_ACC + half * 64;
+        const uint32_t t_g = tmem_base + t_lane + TM_G + half * 64;
+        int bc = 0, gp = 0, gsb = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
             const int m = m0 + quad * 32 + lane;
             const bool row_live = m < p.M;
             const float2* dxr = reinterpret_cast<const float2*>(p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32));
-            float acc[64];
             float2 acc2[32];
-#pragma unroll
-            for (int c = 0; c < 64; ++c) acc[c] = 0.f;
 #pragma unroll
             for (int c = 0; c < 32; ++c) acc2[c] = make_float2(0.f, 0.f);
             float2 dx_n = row_live ? __ldg(dxr) : make_float2(0.f, 0.f);
@@ -427,76 +459,80 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                             const float dxv = blk ? dx2.y : dx2.x;
                             const float2 dxx = make_float2(dxv, dxv);
                             const uint32_t taddr = tmem_base + t_lane + TM_F + t * BN + half * 64;
-                            // 16 columns at a time; the TMEM load of the next group is in flight while this
-                            // group is scaled and accumulated (packed fp32x2 multiply-adds)
-                            float f0[16], f1[16];
+                            // all 64 columns in one round trip, then the TMEM buffer goes straight back to the MMA
+                            float f0[16], f1[16], f2[16], f3[16];
                             tc_ld16(taddr, f0);
+                            tc_ld16(taddr + 16, f1);
+                            tc_ld16(taddr + 32, f2);
+                            tc_ld16(taddr + 48, f3);
                             tc_wait_ld();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * t);
 #pragma unroll
-                            for (int gq = 0; gq < 4; ++gq) {
-                                float (&f)[16] = (gq & 1) ? f1 : f0;
-                                float (&fn)[16] = (gq & 1) ? f0 : f1;
-                                if (gq < 3) tc_ld16(taddr + 16 * (gq + 1), fn);
-#pragma unroll
-                                for (int c2 = 0; c2 < 8; ++c2)
-                                    acc2[8 * gq + c2] = __ffma2_rn(dxx, make_float2(f[2 * c2], f[2 * c2 + 1]), acc2[8 * gq + c2]);
-                                if (gq < 3) tc_wait_ld();
-                                if (gq == 2) {
-                                    // every column of the tile is now in registers: hand the TMEM buffer back
-                                    tc_fence_before();
-                                    __syncwarp();
-                                    if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * t);
-                                }
+                            for (int c2 = 0; c2 < 8; ++c2) {
+                                acc2[c2] = __ffma2_rn(dxx, make_float2(f0[2 * c2], f0[2 * c2 + 1]), acc2[c2]);
+                                acc2[8 + c2] = __ffma2_rn(dxx, make_float2(f1[2 * c2], f1[2 * c2 + 1]), acc2[8 + c2]);
+                                acc2[16 + c2] = __ffma2_rn(dxx, make_float2(f2[2 * c2], f2[2 * c2 + 1]), acc2[16 + c2]);
+                                acc2[24 + c2] = __ffma2_rn(dxx, make_float2(f3[2 * c2], f3[2 * c2 + 1]), acc2[24 + c2]);
                             }
                         }
                     }
                     if (!ok) break;
-                    // end of a super-block: fold in its fp16 scale d (per weight row = per column)
-                    {
-                        const uint32_t dtab = gtab + (e * 2 * BN + half * 64) * 4;
-#pragma unroll
-                        for (int c2 = 0; c2 < 32; ++c2) {
-                            acc[2 * c2] = fmaf(__uint_as_float(lds32(dtab + 8 * c2)), acc2[c2].x, acc[2 * c2]);
-                            acc[2 * c2 + 1] = fmaf(__uint_as_float(lds32(dtab + 8 * c2 + 4)), acc2[c2].y, acc[2 * c2 + 1]);
-                            acc2[c2] = make_float2(0.f, 0.f);
-                        }
-                    }
-                }
-                if (!ok) break;
-                // end of a pair: subtract dmin * G for both super-blocks
-                if (!wait_or_abort(sbase + BAR_GT_FULL, gp & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const uint32_t taddr = tmem_base + t_lane + TM_G + e * BN + half * 64;
-                    const uint32_t mtab = gtab + (e * 2 * BN + BN + half * 64) * 4;
+                    // end of a super-block: y += d * partial - dmin * G, 16 columns at a time through TMEM
+                    if (!wait_or_abort(sbase + BAR_GT_FULL, gsb & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t dtab = gtab + (e * 2 * BN + half * 64) * 4, mtab = dtab + BN * 4;
+                    const bool first = sb == 0;
 #pragma unroll
                     for (int gq = 0; gq < 4; ++gq) {
-                        float f[16];
-                        tc_ld16(taddr + 16 * gq, f);
+                        float gv[16], av[16];
+                        tc_ld16(t_g + 16 * gq, gv);
+                        if (!first) tc_ld16(t_acc + 16 * gq, av);
                         tc_wait_ld();
+                        if (gq == 3) {
+                            // G is in registers: the MMA may overwrite it with the next super-block's
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(sbase + BAR_GT_EMPTY);
+                        }
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const float part = (c & 1) ? acc2[8 * gq + (c >> 1)].y : acc2[8 * gq + (c >> 1)].x;
+                            float a = first ? 0.f : av[c];
+                            a = fmaf(__uint_as_float(lds32(dtab + (16 * gq + c) * 4)), part, a);
+                            a = fmaf(-__uint_as_float(lds32(mtab + (16 * gq + c) * 4)), gv[c], a);
+                            av[c] = a;
+                        }
+                        tc_st16(t_acc + 16 * gq, av);
+                    }
+                    tc_wait_st();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) acc2[c] = make_float2(0.f, 0.f);
+                    ++gsb;
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sbase + BAR_G_TAB_EMPTY + 8 * g);    // the pair's d / dmin tables are free
+            }
+            if (ok) {
+                float* yr = p.y + static_cast<size_t>(row_live ? m : 0) * p.N + n0 + half * 64;
+                const bool vec = n0 + half * 64 + 64 <= p.N && (reinterpret_cast<uintptr_t>(yr) & 15) == 0;
+#pragma unroll
+                for (int gq = 0; gq < 4; ++gq) {
+                    float av[16];
+                    tc_ld16(t_acc + 16 * gq, av);        // warp-wide: every lane takes part, live row or not
+                    tc_wait_ld();
+                    if (!row_live) continue;
+                    if (vec) {
+#pragma unroll
+                        for (int c4 = 0; c4 < 4; ++c4)
+                            *reinterpret_cast<float4*>(yr + 16 * gq + 4 * c4) = make_float4(av[4 * c4], av[4 * c4 + 1], av[4 * c4 + 2], av[4 * c4 + 3]);
+                    } else {
 #pragma unroll
                         for (int c = 0; c < 16; ++c)
-                            acc[16 * gq + c] = fmaf(-__uint_as_float(lds32(mtab + (16 * gq + c) * 4)), f[c], acc[16 * gq + c]);
+                            if (n0 + half * 64 + 16 * gq + c < p.N) yr[16 * gq + c] = av[c];
                     }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(sbase + BAR_GT_EMPTY);
-                    mbar_arrive(sbase + BAR_G_TAB_EMPTY + 8 * g);
-                }
-            }
-            if (ok && row_live) {
-                float* yr = p.y + static_cast<size_t>(m) * p.N + n0 + half * 64;
-                if (n0 + half * 64 + 64 <= p.N && (reinterpret_cast<uintptr_t>(yr) & 15) == 0) {
-#pragma unroll
-                    for (int c4 = 0; c4 < 16; ++c4)
-                        *reinterpret_cast<float4*>(yr + 4 * c4) = make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 64; ++c)
-                        if (n0 + half * 64 + c < p.N) yr[c] = acc[c];
                 }
             }
         }
@@ -617,7 +653,7 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
 
     // 2-D tensor maps: the fp16 operand (inner dimension K) and the bf16 pieces of sum_x
     // (inner dimension 64 per pair of super-blocks); outer dimension tokens.
-    CUtensorMap tmap, tmap_g;
+    CUtensorMap tmap, tmap_g, tmap_w;
     {
         // The driver entry point is looked up at run time so that the library does not link libcuda.
         using encode_fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -646,6 +682,14 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled (G) failed (%d)", static_cast<int>(r));
+        // the packed weights as bytes: N rows of rb bytes, boxes of 128 rows x one 144-byte super-block
+        const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(row_bytes(type, K)), static_cast<cuuint64_t>(N)};
+        const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(row_bytes(type, K))};
+        const cuuint32_t wbox[2] = {Q4_K_BYTES, BN};
+        r = cuTensorMapEncodeTiled(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w), wdims, wstrides, wbox, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (%d)", static_cast<int>(r));
     }
 
     TcParams p{};
@@ -660,7 +704,7 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
     }
     const int n_tiles = tiles_m * tiles_n;
     const int grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
-    gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, tmap_g, p);
+    gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, tmap_g, tmap_w, p);
     c.launches++;
     c.last_path = 2;
     return cuda_check(cudaGetLastError(), "gemm_q4k_tc launch");
