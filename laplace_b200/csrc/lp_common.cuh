@@ -168,7 +168,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) /* suspend-time hint, ns */ : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(200u) /* suspend-time hint, ns */ : "memory");
     return ok != 0;
 }
 // Same without a suspend-time hint: for hand-offs on a critical path, where the wake-up

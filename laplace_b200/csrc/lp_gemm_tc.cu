@@ -23,12 +23,15 @@
 //
 // Roles in one 512-thread CTA (one CTA per SM, persistent over 128x128 tiles):
 //   warp 0      TMA: activation tiles (fp16 q values, 128 tokens x 64 k, 128-byte swizzle)
-//   warp 1      MMA issue (one lane) + TMEM allocation
-//   warp 2      TMA: the bf16 pieces of sum_x, one tile per pair of super-blocks
-//   warps 4-7   converters: packed Q4_K super-blocks (global) -> fp16 weight operand
+//   warps 1, 2  MMA issue (one lane each: first / second block of every 64-k chunk, each
+//               owning one TMEM block-sum buffer); warp 1 also issues G and owns TMEM
+//   warp 3      TMA: packed Q4_K super-blocks (128 rows x 144 bytes) and the bf16 pieces
+//               of sum_x (one tile per pair of super-blocks)
+//   warps 4-7   converters: packed super-blocks (shared memory) -> fp16 weight operand
 //               tile, bf16 mins operand and d / dmin tables in shared memory
 //   warps 8-15  epilogue: tcgen05.ld of each block's 128x128 fp32 tile (double
-//               buffered in TMEM), scaling and accumulation in registers, y stores
+//               buffered in TMEM), scaling into a per-super-block partial in registers;
+//               the tile's running y lives in TMEM and is updated once per super-block
 // All mbarrier waits are bounded; a wait that gives up raises the status word
 // and every role leaves its loop.
 #include <cuda.h>
@@ -138,17 +141,24 @@ constexpr uint32_t IDESC_F16 = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) |
 // Same shape with bf16 operands (the G product).
 constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);
 
-// Waits that also give up when another role has raised the abort flag.
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
-    // No software sleep and no suspend-time hint: either adds its quantum to every hand-off
-    // between roles, and a block goes through four of them.
-    for (uint32_t it = 0; it < (1u << 26); ++it) {
-        if (mbar_try_wait_nohint(bar, parity)) return true;
+// Waits that also give up when another role has raised the abort flag. The MMA-issuing
+// thread is the pipeline's metronome: it polls without a suspend hint, and every other
+// role waits suspended in hardware so that it does not take issue slots from it.
+template <bool SPIN>
+__device__ __forceinline__ bool wait_or_abort_t(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    for (uint32_t it = 0; it < (SPIN ? (1u << 26) : (1u << 22)); ++it) {
+        if (SPIN ? mbar_try_wait_nohint(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
     }
     *abort_flag = 1;
     report_status(err, code);
     return false;
+}
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    return wait_or_abort_t<false>(bar, parity, abort_flag, err, code);
+}
+__device__ __forceinline__ bool spin_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    return wait_or_abort_t<true>(bar, parity, abort_flag, err, code);
 }
 
 // ---- the kernel -----------------------------------------------------------------
@@ -171,7 +181,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(sbase + BAR_FULL_A + 8 * s, 1);
             mbar_init(sbase + BAR_FULL_B + 8 * s, 4);        // one arrive per converter warp
-            mbar_init(sbase + BAR_EMPTY + 8 * s, 1);         // tcgen05.commit
+            mbar_init(sbase + BAR_EMPTY + 8 * s, 2);         // tcgen05.commit from each of the two MMA threads
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(sbase + BAR_TMEM_FULL + 8 * t, 1);     // tcgen05.commit
@@ -229,37 +239,26 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     if (v >= 0) mbar_wait_bounded(sbase + BAR_FULL_A + 8 * (v % STAGES), (v / STAGES) & 1);
                 }
             }
-        } else if (warp == 2 && lane == 0) {
-            // ---------------- TMA producer: bf16 pieces of sum_x, one tile per pair ----------------
-            int gp = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * BM;
-                for (int pr = 0; pr < n_pairs; ++pr, ++gp) {
-                    const int g = gp % GST;
-                    if (!wait_or_abort(sbase + BAR_G_EMPTY + 8 * g, ((gp / GST) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    mbar_expect_tx(sbase + BAR_G_FULL_A + 8 * g, G_TILE);
-                    tma_load_2d(sbase + OFF_GA + g * G_TILE, &tmap_g, pr * 64, m0, sbase + BAR_G_FULL_A + 8 * g);
-                }
-            }
-            if (!ok) {
-                for (int k = 0; k < GST; ++k) {
-                    const int v = gp - 1 - k;
-                    if (v >= 0) mbar_wait_bounded(sbase + BAR_G_FULL_A + 8 * (v % GST), (v / GST) & 1);
-                }
-            }
         } else if (warp == 3 && lane == 0) {
             // ---------------- TMA producer: packed weights, one super-block of 128 rows per tile ----------------
             // (rows past N are zero-filled by the copy engine: d = 0, every scale 0)
-            int rq = 0;
+            // The same thread also brings the bf16 pieces of sum_x, one tile per pair of super-blocks.
+            int rq = 0, gp = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int n0 = (tile / p.tiles_m) * BN;
+                const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
                 for (int sb = 0; sb < nsb; ++sb, ++rq) {
                     const int q = rq % RAW_STAGES;
                     if (!wait_or_abort(sbase + BAR_RAW_EMPTY + 8 * q, ((rq / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_RAW_FULL + 8 * q, RAW_TILE);
                     tma_load_2d(sbase + OFF_RAW + q * RAW_TILE, &tmap_w, sb * Q4_K_BYTES, n0, sbase + BAR_RAW_FULL + 8 * q);
+                    if ((sb & 1) == 0) {
+                        const int g = gp % GST;
+                        if (!wait_or_abort(sbase + BAR_G_EMPTY + 8 * g, ((gp / GST) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                        mbar_expect_tx(sbase + BAR_G_FULL_A + 8 * g, G_TILE);
+                        tma_load_2d(sbase + OFF_GA + g * G_TILE, &tmap_g, (sb >> 1) * 64, m0, sbase + BAR_G_FULL_A + 8 * g);
+                        ++gp;
+                    }
                 }
             }
             if (!ok) {
@@ -267,9 +266,15 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     const int v = rq - 1 - k;
                     if (v >= 0) mbar_wait_bounded(sbase + BAR_RAW_FULL + 8 * (v % RAW_STAGES), (v / RAW_STAGES) & 1);
                 }
+                for (int k = 0; k < GST; ++k) {
+                    const int v = gp - 1 - k;
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_G_FULL_A + 8 * (v % GST), (v / GST) & 1);
+                }
             }
-        } else if (warp == 1 && lane == 0) {
-            // ---------------- MMA issuer ----------------
+        } else if ((warp == 1 || warp == 2) && lane == 0) {
+            // ---------------- MMA issuers: warp 1 takes the first block of every chunk (and G),
+            // warp 2 the second; each owns one of the two TMEM block-sum buffers ----------------
+            const int which = warp - 1;
             int it = 0, bc = 0, gp = 0, gsb = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
@@ -281,30 +286,31 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         for (int kc = 0; kc < 4 && ok; ++kc, ++it) {
                             const int s = it % STAGES;
                             const uint32_t ph = (it / STAGES) & 1;
-                            if (!wait_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
-                                !wait_or_abort(sbase + BAR_FULL_B + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                            if (!spin_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                                !spin_or_abort(sbase + BAR_FULL_B + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
                             tc_fence_after();
                             const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
                             const uint64_t bdesc = smem_desc_sw128(sbase + OFF_B + s * B_TILE);
-#pragma unroll
-                            for (int blk = 0; blk < 2; ++blk, ++bc) {
-                                const int t = bc & 1;
-                                if (!wait_or_abort(sbase + BAR_TMEM_EMPTY + 8 * t, ((bc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                            {
+                                // this thread's block of the chunk: block `which`, TMEM buffer `which`, use number `it`
+                                const int t = which;
+                                if (!spin_or_abort(sbase + BAR_TMEM_EMPTY + 8 * t, (it & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
                                 tc_fence_after();
 #pragma unroll
                                 for (int k = 0; k < 2; ++k) {
-                                    const uint64_t off = static_cast<uint64_t>((blk * 64 + k * 32) >> 4);   // bytes >> 4 inside the swizzle row
+                                    const uint64_t off = static_cast<uint64_t>((which * 64 + k * 32) >> 4);   // bytes >> 4 inside the swizzle row
                                     tc_mma_f16(tmem_base + TM_F + t * BN, adesc + off, bdesc + off, IDESC_F16, k);
                                 }
                                 tc_commit(sbase + BAR_TMEM_FULL + 8 * t);      // block sum complete -> epilogue
                             }
-                            tc_commit(sbase + BAR_EMPTY + 8 * s);              // operands consumed -> producers
+                            tc_commit(sbase + BAR_EMPTY + 8 * s);              // operands consumed -> producers (needs both threads)
                         }
                         if (!ok) break;
+                        if (which != 0) continue;
                         // G of this super-block: K = 32 bf16, the e-th half of the pair's 128-byte rows
-                        if ((e == 0 && !wait_or_abort(sbase + BAR_G_FULL_A + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_FULL)) ||
-                            !wait_or_abort(sbase + BAR_G_FULL_B + 16 * g + 8 * e, gph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
-                            !wait_or_abort(sbase + BAR_GT_EMPTY, (gsb & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                        if ((e == 0 && !spin_or_abort(sbase + BAR_G_FULL_A + 8 * g, gph, abort_flag, p.err, DEV_TIMEOUT_FULL)) ||
+                            !spin_or_abort(sbase + BAR_G_FULL_B + 16 * g + 8 * e, gph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                            !spin_or_abort(sbase + BAR_GT_EMPTY, (gsb & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
                         tc_fence_after();
                         const uint64_t gadesc = smem_desc_sw128(sbase + OFF_GA + g * G_TILE);
                         const uint64_t gbdesc = smem_desc_sw128(sbase + OFF_GB + g * G_TILE);
@@ -316,7 +322,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         tc_commit(sbase + BAR_GT_FULL);
                         ++gsb;
                     }
-                    if (ok) tc_commit(sbase + BAR_G_EMPTY + 8 * g);     // the pair's G operands are consumed
+                    if (ok && which == 0) tc_commit(sbase + BAR_G_EMPTY + 8 * g);     // the pair's G operands are consumed
                 }
             }
         }
