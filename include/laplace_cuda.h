@@ -105,6 +105,24 @@ int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type,
                               const int* expert_idx, int n_experts,
                               float* y, int K, int N, int per_expert_x, void* stream);
 
+/* Prefill GEMM (Q4_K, M > 8, K % 256 == 0) that allocates nothing. It has no counterpart in
+ * the reference: it exists for hosts that must not touch the CUDA allocator on the request
+ * path - serving processes whose own pools (KV cache, activations) already hold all HBM, so
+ * that cudaMalloc would fail or fragment them, and latency-bound loops that cannot take the
+ * allocator's locks or the implicit device synchronisation of cudaFree. Same arguments and result as
+ * laplace_cuda_gemm_dev; the quantized activations go to a 6 MiB array built into the
+ * library (held by every GPU that loads it) instead of a cudaMalloc'd buffer.
+ *   - LAPLACE_ERR_LIMIT when the call needs more scratch than the array holds: about
+ *     2.3 * pad128(M) * K + M * K / 8 bytes (M = 512, K = 4096: 4.75 MiB);
+ *     LAPLACE_ERR_ARG for shapes that are not the prefill case (decode calls use no scratch).
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress); make
+ *     that call before any stream capture begins.
+ *   - All calls share the one array and it keeps the last call's contents (what must start
+ *     from zero is cleared by each call): two calls that overlap on the GPU - different
+ *     streams, or the same stream with programmatic overlap - race. Serialise them. */
+int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t type,
+                                  float* y, int M, int K, int N, void* stream);
+
 /* The activation quantizer on its own (src/matmul_simd.cpp:348-427).
  * Outputs, all device memory, M rows: q int8 [M][K]; d fp32 [M][K/32];
  * sum fp32 [M][K/32] (= d * (sum_lo + sum_hi)); isum int16 [M][K/32][2]

@@ -628,23 +628,38 @@ bool gemm_tc_supports(uint32_t type, int M, int K, int N) {
     return type == LAPLACE_TYPE_Q4_K && M > 8 && K % 256 == 0 && N > 0;
 }
 
-int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st) {
+namespace {
+
+// Scratch layout of one call: fp16 activation operand, activation scales, bf16 pieces of sum_x.
+struct ScratchPlan {
+    size_t m_pad, aq_bytes, sc_bytes, ag_bytes;
+    int    tiles_m, tiles_n, n_pairs;
+    size_t total() const { return aq_bytes + sc_bytes + ag_bytes; }
+};
+ScratchPlan plan_scratch(int M, int K, int N) {
+    ScratchPlan s;
+    s.tiles_m = (M + BM - 1) / BM;
+    s.tiles_n = (N + BN - 1) / BN;
+    s.m_pad = static_cast<size_t>(s.tiles_m) * BM;
+    s.n_pairs = (K / 256 + 1) / 2;
+    s.aq_bytes = (s.m_pad * K * sizeof(__half) + 255) & ~size_t(255);
+    s.sc_bytes = (static_cast<size_t>(M) * (K / 32) * sizeof(float) + 255) & ~size_t(255);
+    s.ag_bytes = (s.m_pad * s.n_pairs * 64 * sizeof(__nv_bfloat16) + 255) & ~size_t(255);
+    return s;
+}
+
+// Quantizes x into `scratch` (device memory of at least plan.total() bytes, 256-byte aligned)
+// and runs the tensor-core kernel. Allocates nothing.
+int gemm_tc_on_scratch(uint8_t* scratch, const ScratchPlan& sp, const float* x, const uint8_t* w, uint32_t type, float* y,
+                       int M, int K, int N, cudaStream_t st) {
     Context& c = ctx();
-    if (!gemm_tc_supports(type, M, K, N)) return LAPLACE_UNSUPPORTED;
-    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(LAPLACE_ERR_ARG, "gemm: Q4_K weights must be 16-byte aligned on the device");
-    if (reinterpret_cast<uintptr_t>(x) & 15) return fail(LAPLACE_ERR_ARG, "gemm: x not 16-byte aligned");
-    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-    const size_t m_pad = static_cast<size_t>(tiles_m) * BM;
-    const size_t bpr = static_cast<size_t>(K / 32);
-    const int n_pairs = (K / 256 + 1) / 2;
-    const size_t aq_bytes = (m_pad * K * sizeof(__half) + 255) & ~size_t(255);
-    const size_t sc_bytes = (static_cast<size_t>(M) * bpr * sizeof(float) + 255) & ~size_t(255);
-    const size_t ag_bytes = (m_pad * n_pairs * 64 * sizeof(__nv_bfloat16) + 255) & ~size_t(255);
-    int rc = g_scratch.ensure(aq_bytes + sc_bytes + ag_bytes);
-    if (rc) return rc;
-    __half* aq = static_cast<__half*>(g_scratch.p);
-    float* dx = reinterpret_cast<float*>(static_cast<uint8_t*>(g_scratch.p) + aq_bytes);
-    __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(g_scratch.p) + aq_bytes + sc_bytes);
+    const int tiles_m = sp.tiles_m, tiles_n = sp.tiles_n, n_pairs = sp.n_pairs;
+    const size_t m_pad = sp.m_pad, bpr = static_cast<size_t>(K / 32);
+    const size_t aq_bytes = sp.aq_bytes, sc_bytes = sp.sc_bytes, ag_bytes = sp.ag_bytes;
+    int rc;
+    __half* aq = reinterpret_cast<__half*>(scratch);
+    float* dx = reinterpret_cast<float*>(scratch + aq_bytes);
+    __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(scratch + aq_bytes + sc_bytes);
 
     {
         if ((rc = cuda_check(cudaMemsetAsync(ag, 0, ag_bytes, st), "cudaMemsetAsync"))) return rc;
@@ -716,4 +731,73 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
     return cuda_check(cudaGetLastError(), "gemm_q4k_tc launch");
 }
 
+int check_gemm_tc_args(const float* x, const uint8_t* w, uint32_t type, int M, int K, int N) {
+    if (!gemm_tc_supports(type, M, K, N)) return LAPLACE_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(LAPLACE_ERR_ARG, "gemm: Q4_K weights must be 16-byte aligned on the device");
+    if (reinterpret_cast<uintptr_t>(x) & 15) return fail(LAPLACE_ERR_ARG, "gemm: x not 16-byte aligned");
+    return LAPLACE_OK;
+}
+
+}  // namespace
+
+int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st) {
+    int rc = check_gemm_tc_args(x, w, type, M, K, N);
+    if (rc) return rc;
+    const ScratchPlan sp = plan_scratch(M, K, N);
+    if ((rc = g_scratch.ensure(sp.total()))) return rc;
+    return gemm_tc_on_scratch(static_cast<uint8_t*>(g_scratch.p), sp, x, w, type, y, M, K, N, st);
+}
+
+// ---- the entry point that allocates nothing -------------------------------------------
+// Some hosts of this library must not (or cannot) call the CUDA allocator on the request
+// path: a serving process that has handed all free HBM to its own pools (KV cache,
+// activations), so that cudaMalloc would fail or fragment them, and latency-bound loops that
+// cannot take the allocator's locks or the implicit device synchronisation that comes with
+// cudaFree when a buffer has to grow. For them the scratch of the prefill GEMM
+// (the quantized activations) lives in a fixed array inside the library image instead of a
+// growable cudaMalloc'd buffer.
+//
+// The array is part of every context that loads the library (NOALLOC_SCRATCH_BYTES of HBM
+// per GPU until the process exits). In host code its name is only a handle; the device
+// address comes from cudaGetSymbolAddress, asked once per device with that device current.
+constexpr size_t NOALLOC_SCRATCH_BYTES = 6u << 20;     // 6 MiB: e.g. M = 512, K = 4096 needs 4.75 MiB
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+namespace {
+uint8_t* g_noalloc_ptr = nullptr;     // device address of g_noalloc_scratch on g_noalloc_dev
+int      g_noalloc_dev = -1;
+}  // namespace
+
 }  // namespace lp
+
+extern "C" int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t type, float* y,
+                                             int M, int K, int N, void* stream) {
+    using namespace lp;
+    Context& c = ctx();
+    if (!c.ready) return fail(LAPLACE_ERR_STATE, "laplace_cuda_init has not been called (or found no GPU)");
+    if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm_noalloc: null pointer");
+    int rc = check_gemm_tc_args(x, w, type, M, K, N);
+    if (rc == LAPLACE_UNSUPPORTED)
+        return fail(LAPLACE_ERR_ARG, "gemm_noalloc: only the prefill shape is served here (Q4_K, M > 8, K %% 256 == 0); "
+                                     "decode calls (M <= 8) use no scratch at all, call laplace_cuda_gemm_dev");
+    if (rc) return rc;
+    const ScratchPlan sp = plan_scratch(M, K, N);
+    if (sp.total() > NOALLOC_SCRATCH_BYTES)
+        return fail(LAPLACE_ERR_LIMIT, "gemm_noalloc: M=%d K=%d needs %zu bytes of scratch, the built-in array holds %zu",
+                    M, K, sp.total(), NOALLOC_SCRATCH_BYTES);
+    if (g_noalloc_dev != c.device) {
+        // first call on this device: resolve the array's device address (the library is bound to c.device,
+        // make sure it is the current one for the lookup)
+        int cur = -1;
+        cudaError_t e = cudaGetDevice(&cur);
+        if (e == cudaSuccess && cur != c.device) e = cudaSetDevice(c.device);
+        void* ptr = nullptr;
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e == cudaSuccess && cur >= 0 && cur != c.device) e = cudaSetDevice(cur);
+        if (e != cudaSuccess || !ptr) return cuda_check(e == cudaSuccess ? cudaErrorInvalidSymbol : e, "cudaGetSymbolAddress(scratch)");
+        g_noalloc_ptr = static_cast<uint8_t*>(ptr);
+        g_noalloc_dev = c.device;
+    }
+    return gemm_tc_on_scratch(g_noalloc_ptr, sp, x, w, type, y, M, K, N,
+                              stream ? static_cast<cudaStream_t>(stream) : c.stream);
+}
