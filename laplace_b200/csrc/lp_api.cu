@@ -116,13 +116,17 @@ int dispatch_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float* y,
     if (gemm_tc_supports(type, M, K, N)) return launch_gemm_tc(x, w, type, y, M, K, N, st);
     // Small M (or a type without a tensor-core kernel yet): one streaming pass
     // per group of up to 8 activation rows.
-    for (int m0 = 0; m0 < M; m0 += 8) {
+    // Rows per pass: up to 8, fewer when K is so long that 8 quantized activation rows
+    // (~1.45 bytes per value) would leave the weight rings under half of shared memory.
+    int per = 8;
+    while (per > 1 && static_cast<double>(per) * K * 1.45 > 112.0 * 1024.0) --per;
+    for (int m0 = 0; m0 < M; m0 += per) {
         GemvArgs a{};
         a.x = x + static_cast<size_t>(m0) * K;
         a.w = w;
         a.y = y + static_cast<size_t>(m0) * N;
         a.type = type;
-        a.M = (M - m0) < 8 ? (M - m0) : 8;
+        a.M = (M - m0) < per ? (M - m0) : per;
         a.K = K; a.N = N; a.n_seg = 1; a.per_seg_x = 0; a.expert_idx = nullptr;
         int rc = launch_gemv_stream(a, st);
         if (rc) return rc;

@@ -6,7 +6,7 @@
 // Shape of the kernel (one persistent CTA per SM):
 //   * every consumer warp owns a private ring of shared-memory slots that a
 //     producer warp fills with its weight rows by 1-D bulk copies (TMA engine,
-//     cp.async.bulk, no multicast), a full/empty mbarrier pair per slot. A row
+//     cp.async.bulk to this CTA only), a full/empty mbarrier pair per slot. A row
 //     is one contiguous byte range of the GGUF tensor; long rows are cut into
 //     K-slices on 16-byte boundaries. Consumers never wait for each other
 //     after the prologue, and a CTA keeps ~220 KB of weight bytes in flight;

@@ -34,7 +34,10 @@ def lib(device: int | None = None):
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """torch's current stream as a handle for the ABI. torch's default stream has handle 0, which the ABI
+    reads as "the library's own stream", so it is passed as cudaStreamLegacy (0x1) instead."""
+    h = torch.cuda.current_stream().cuda_stream
+    return h if h else 1
 
 
 def upload_weights(w: np.ndarray) -> torch.Tensor:

@@ -166,3 +166,14 @@ def test_nan_block_propagates(oracle):
     y = run_dev(t, x, w, 1, K, N)
     ref = oracle.gemm(x, w, t, 1, K, N, mode=0)
     assert np.isnan(ref).all() and np.isnan(y).all()
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q6_K, GGMLType.Q8_0])
+def test_long_rows_many_activation_rows(oracle, t):
+    """M = 8 at K = 14336 does not fit one pass (the quantized activations would fill shared memory):
+    the dispatcher splits the rows into smaller passes."""
+    M, K, N = 8, 14336, 24
+    w = synth.weights(t, K, N, seed=1500 + int(t), how="random")
+    x = synth.normal_f32(1501, (M, K))
+    y = run_dev(t, x, w, M, K, N)
+    check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1), f"{t.name} M=8 K=14336")
