@@ -157,37 +157,30 @@ def gpu_arm(args):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     L = device.lib(local)
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
     # ---- inputs: seeded weights (reference test packer), rows split across ranks
     w_full = synth.weights(TYPE_Q4_K, K_DIM, N_DIM, seed=1012, how="ref")
-    b, e = C.c_int(), C.c_int()
-    L.laplace_cuda_nsplit(N_DIM, rank, world, C.byref(b), C.byref(e))
-    r0, r1 = b.value, e.value
-    n_loc = r1 - r0
-    w_loc = np.ascontiguousarray(w_full[r0:r1])
+    from laplace_b200.shard import RowShards
+    shards = RowShards(L, N_DIM, rank, world)
+    n_loc = shards.n_loc
+    w_loc = np.ascontiguousarray(shards.slice_rows(w_full))
     copies = []
     for i in range(N_COPIES):                       # distinct HBM copies, rows rotated so outputs differ
         copies.append(device.upload_weights(np.roll(w_loc, i * 16, axis=0)))
     x_host = synth.normal_f32(2001, (M_ROWS, K_DIM))
     x = torch.from_numpy(x_host).cuda()
     y_loc = torch.empty((N_COPIES, M_ROWS, n_loc), dtype=torch.float32, device="cuda")
-    y_all = torch.empty((world, M_ROWS * (N_DIM // world + 16)), dtype=torch.float32, device="cuda") if world > 1 else None
-    uneven = world > 1 and any(
-        (lambda bb, ee: ee - bb)(*_split(L, N_DIM, r, world)) != n_loc for r in range(world))
+    y_all = torch.empty((M_ROWS, N_DIM), dtype=torch.float32, device="cuda") if world > 1 else None
 
     def step(i):
         c = i % N_COPIES
         device.gemm(x, copies[c], TYPE_Q4_K, M_ROWS, K_DIM, n_loc, y=y_loc[c])
         if world > 1:
-            if uneven:
-                pad = torch.zeros(y_all.shape[1], dtype=torch.float32, device="cuda")
-                pad[: M_ROWS * n_loc] = y_loc[c].reshape(-1)
-                dist.all_gather_into_tensor(y_all, pad)
-            else:
-                dist.all_gather_into_tensor(y_all[:, : M_ROWS * n_loc], y_loc[c].reshape(-1))
+            shards.gather(y_loc[c], y_all)
 
     for i in range(warmup):
         step(i)
@@ -196,9 +189,22 @@ def gpu_arm(args):
     y0 = y_loc[0].cpu().numpy()
     for c in range(1, min(N_COPIES, warmup)):
         assert np.array_equal(np.roll(y0, c * 16, axis=-1), y_loc[c].cpu().numpy()), "rotated weight copies disagree"
+    if world > 1:
+        # the gathered result must be what one GPU computes over the whole matrix (last warm-up step's copy)
+        c_last = (warmup - 1) % N_COPIES
+        w_chk = device.upload_weights(np.roll(w_full, 0, axis=0))
+        y_chk = torch.empty((M_ROWS, N_DIM), dtype=torch.float32, device="cuda")
+        device.gemm(x, w_chk, TYPE_Q4_K, M_ROWS, K_DIM, N_DIM, y=y_chk)
+        device.sync()
+        full = y_chk.cpu().numpy()
+        got = y_all.cpu().numpy()
+        for r, (rb_, re_) in enumerate(shards.ranges):
+            want = np.roll(full[:, rb_:re_], c_last * 16, axis=-1)
+            assert np.allclose(got[:, rb_:re_], want, rtol=1e-6, atol=1e-6), f"gathered slice of rank {r} differs"
+        del w_chk, y_chk
 
-    # ---- device-timed region: exactly `steps` steps, replayed as one CUDA graph when single-GPU
-    use_graph = world == 1
+    # ---- device-timed region: exactly `steps` steps, replayed as one CUDA graph
+    use_graph = world == 1 or not args.no_graph       # NCCL's all-gather is captured with the kernel
     graph = None
     if use_graph:
         graph = torch.cuda.CUDAGraph()
@@ -222,7 +228,16 @@ def gpu_arm(args):
     times = []
     t_begin = time.perf_counter()
     repeats = 0
-    while (repeats < args.repeats) if args.repeats else (repeats < 3 or (time.perf_counter() - t_begin < 1.5 and repeats < 2000)):
+    def more():
+        # every rank must take the same number of repeats: rank 0 decides, the others follow
+        go = (repeats < args.repeats) if args.repeats else (repeats < 3 or (time.perf_counter() - t_begin < 1.5 and repeats < (2000 if world == 1 else 200)))
+        if world > 1:
+            flag = torch.tensor([1 if go else 0], device="cuda", dtype=torch.int32)
+            dist.broadcast(flag, src=0)
+            go = bool(flag.item())
+        return go
+
+    while more():
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
@@ -309,8 +324,15 @@ def gpu_arm(args):
             line["prefill"] = prefill
         print(json.dumps(line))
     if world > 1:
+        # A communicator that captured graphs still reference cannot be torn down cleanly: drop the graph,
+        # agree that every rank is done, and leave without running NCCL's destructors.
+        del graph
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def prefill_leg(device, synth, torch):
@@ -359,12 +381,6 @@ def prefill_leg(device, synth, torch):
             "projections": out}
 
 
-def _split(L, N, r, world):
-    b, e = C.c_int(), C.c_int()
-    L.laplace_cuda_nsplit(N, r, world, C.byref(b), C.byref(e))
-    return b.value, e.value
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -375,6 +391,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer leg (for short profiler runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for short profiler runs)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 prefill leg")
+    ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch the steps eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

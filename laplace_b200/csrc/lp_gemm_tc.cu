@@ -551,7 +551,9 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
 }
 
-// ---- activation quantizer for this kernel --------------------------------------
+#include "lp_gemm_tc_q6k.cuh"
+
+// ---- activation quantizer for both kernels -------------------------------------
 // Same arithmetic as quantize_act_kernel (Laplace src/matmul_simd.cpp:348-410); the int8
 // values are written as fp16 (exact) in the operand's k order: within every four
 // consecutive values, (0, 2, 1, 3). Rows M..M_pad-1 of the operand are zero.
@@ -625,7 +627,12 @@ void release_gemm_tc_scratch() {
 }
 
 bool gemm_tc_supports(uint32_t type, int M, int K, int N) {
-    return type == LAPLACE_TYPE_Q4_K && M > 8 && K % 256 == 0 && N > 0;
+    if (M <= 8 || N <= 0) return false;
+    if (type == LAPLACE_TYPE_Q4_K) return K % 256 == 0;
+    // Q6_K rows are 210 bytes per super-block: the row pitch is a 16-byte multiple (what a tensor map
+    // needs) only when K is a multiple of 8 super-blocks
+    if (type == LAPLACE_TYPE_Q6_K) return K % 2048 == 0;
+    return false;
 }
 
 namespace {
@@ -706,7 +713,7 @@ int gemm_tc_on_scratch(uint8_t* scratch, const ScratchPlan& sp, const float* x, 
         // the packed weights as bytes: N rows of rb bytes, boxes of 128 rows x one 144-byte super-block
         const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(row_bytes(type, K)), static_cast<cuuint64_t>(N)};
         const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(row_bytes(type, K))};
-        const cuuint32_t wbox[2] = {Q4_K_BYTES, BN};
+        const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(type == LAPLACE_TYPE_Q6_K ? q6::RAW_PITCH : Q4_K_BYTES), BN};
         r = cuTensorMapEncodeTiled(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w), wdims, wstrides, wbox, estr,
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -720,20 +727,25 @@ int gemm_tc_on_scratch(uint8_t* scratch, const ScratchPlan& sp, const float* x, 
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(q6::gemm_q6k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(q6::SMEM_BYTES));
         if (e != cudaSuccess) return cuda_check(e, "cudaFuncSetAttribute gemm_tc");
         configured = true;
     }
     const int n_tiles = tiles_m * tiles_n;
     const int grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
-    gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, tmap_g, tmap_w, p);
+    if (type == LAPLACE_TYPE_Q6_K)
+        q6::gemm_q6k_tc_kernel<<<grid, THREADS, q6::SMEM_BYTES, st>>>(tmap, tmap_w, p);
+    else
+        gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, tmap_g, tmap_w, p);
     c.launches++;
     c.last_path = 2;
-    return cuda_check(cudaGetLastError(), "gemm_q4k_tc launch");
+    return cuda_check(cudaGetLastError(), "gemm_tc launch");
 }
 
 int check_gemm_tc_args(const float* x, const uint8_t* w, uint32_t type, int M, int K, int N) {
     if (!gemm_tc_supports(type, M, K, N)) return LAPLACE_UNSUPPORTED;
-    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(LAPLACE_ERR_ARG, "gemm: Q4_K weights must be 16-byte aligned on the device");
+    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(LAPLACE_ERR_ARG, "gemm: weights must be 16-byte aligned on the device");
     if (reinterpret_cast<uintptr_t>(x) & 15) return fail(LAPLACE_ERR_ARG, "gemm: x not 16-byte aligned");
     return LAPLACE_OK;
 }

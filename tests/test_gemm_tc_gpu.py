@@ -64,3 +64,36 @@ def test_other_types_large_m(oracle, t):
     x = synth.normal_f32(82, (M, K))
     y, _ = run_dev(t, x, w, M, K, N)
     check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"{t.name} M=20")
+
+
+@pytest.mark.parametrize("how", ["random", "ref", "affine"])
+@pytest.mark.parametrize("M,K,N", [(128, 2048, 128), (9, 2048, 8), (200, 4096, 200), (130, 6144, 129), (96, 14336, 256)])
+def test_q6k_prefill(oracle, how, M, K, N):
+    """Q6_K on the tensor cores (K a multiple of 2048): split fp16 operands, exact block sums."""
+    t = GGMLType.Q6_K
+    w = synth.weights(t, K, N, seed=90 + M, how=how)
+    x = synth.normal_f32(91 + N, (M, K))
+    y, path = run_dev(t, x, w, M, K, N)
+    assert path == 2, "the tensor-core kernel did not run"
+    ref = oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS)
+    check_close(y, ref, f"Q6_K prefill {how} M={M} K={K} N={N}")
+
+
+@pytest.mark.parametrize("ql,qh,sc", [(0x00, 0x00, -128), (0x00, 0x00, 127), (0xFF, 0xFF, -128), (0xFF, 0xFF, 127), (0x0F, 0xAA, -1)])
+def test_q6k_prefill_extreme_blocks(oracle, ql, qh, sc):
+    """Largest-magnitude weights (sc * (q6 - 32) = +-4096, -3968 ...) against full-scale activations:
+    block sums reach 32 * 127 * 4096, just below 2^24, and must still be exact."""
+    t, M, K, N = GGMLType.Q6_K, 16, 2048, 16
+    blk = np.zeros(210, dtype=np.uint8)
+    blk[0:128] = ql
+    blk[128:192] = qh
+    blk[192:208] = np.uint8(sc & 0xFF)
+    blk[208:210] = np.frombuffer(np.float16(2.0 ** -12).tobytes(), dtype=np.uint8)
+    w = np.tile(blk, (N, K // 256))
+    x = np.full((M, K), 1.27, dtype=np.float32)
+    x[1::2] *= -1.0
+    x[:, ::7] *= 0.5
+    y, path = run_dev(t, x, w, M, K, N)
+    assert path == 2
+    ref = oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS)
+    assert np.allclose(y, ref, rtol=2e-5, atol=0.0), np.abs(y - ref).max()
