@@ -105,6 +105,24 @@ int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type,
                               const int* expert_idx, int n_experts,
                               float* y, int K, int N, int per_expert_x, void* stream);
 
+/* Expert-grouped matmul for a batch of tokens. The reference runs a mixture-of-experts layer
+ * token by token: one fused_moe_gemm_idx call per token for gate/up (src/matmul.h:36-44,
+ * src/arch_gemma4.cpp:604) and one fused_moe_gemm_multi call for down (src/matmul.h:46-54,
+ * src/arch_gemma4.cpp:626). This entry point computes what T such calls compute, in one pass over
+ * the expert weights: for every pair p < n_pairs
+ *     y[p*N + j] = dot(x[pair_row[p]*K ...], row j of expert pair_expert[p]).
+ * pair_row = NULL means pair p reads x row p (the "multi" form: one input per selected expert);
+ * for the shared-input form pass pair_row[p] = token of pair p. Pairs may come in any order; they
+ * are grouped by expert on the device. Q4_K (K % 256 == 0) and Q6_K (K % 2048 == 0); other
+ * types return LAPLACE_UNSUPPORTED and the caller loops laplace_cuda_moe_gemv_dev per token.
+ * An expert index outside [0, n_experts_total) skips that pair and makes the next
+ * laplace_cuda_sync() return LAPLACE_ERR_ARG. x, w and every expert (N*rb bytes) must be
+ * 16-byte aligned. All pointers are device memory. */
+int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type,
+                                 const int* pair_expert, const int* pair_row,
+                                 int n_pairs, int n_experts_total,
+                                 float* y, int K, int N, void* stream);
+
 /* Prefill GEMM (Q4_K, M > 8, K % 256 == 0) that allocates nothing. It has no counterpart in
  * the reference: it exists for hosts that must not touch the CUDA allocator on the request
  * path - serving processes whose own pools (KV cache, activations) already hold all HBM, so
@@ -139,7 +157,7 @@ int laplace_cuda_debug_blocksums_dev(const float* x, const uint8_t* w, uint32_t 
                                      int32_t* out, int M, int K, int N, void* stream);
 
 /* Which kernel family the last *_dev gemm call used: 1 = streaming dp4a GEMV,
- * 2 = tensor-core GEMM. For tests and the benchmark's launch count. */
+ * 2 = tensor-core GEMM, 3 = expert-grouped tensor-core GEMM. For tests and the benchmark's launch count. */
 int laplace_cuda_last_path(void);
 /* Kernel launches issued by this library since the counter was last reset. */
 long long laplace_cuda_launch_count(int reset);

@@ -81,6 +81,7 @@ int check_device_status(cudaStream_t st) {
     const int h = *static_cast<volatile int*>(g_ctx.h_err);
     if (h != DEV_OK) {
         *g_ctx.h_err = DEV_OK;
+        if (h == DEV_BAD_INDEX) return fail(LAPLACE_ERR_ARG, "an expert index on the device was out of range");
         return fail(LAPLACE_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", h);
     }
     return LAPLACE_OK;
@@ -227,6 +228,7 @@ void laplace_cuda_shutdown(void) {
     g_dx.release(); g_dy.release(); g_dw.release(); g_didx.release(); g_dq.release();
     g_hx.release(); g_hy.release();
     release_gemm_tc_scratch();
+    release_moe_grouped_scratch();
     cudaFreeHost(g_ctx.h_err);
     cudaStreamDestroy(g_ctx.stream);
     g_ctx = Context{};
@@ -342,6 +344,19 @@ int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type, c
     if (rc) return rc;
     return dispatch_moe_dev(x, w, type, expert_idx, n_experts, y, K, N, per_expert_x,
                             stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert,
+                                 const int* pair_row, int n_pairs, int n_experts_total, float* y, int K, int N,
+                                 void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w || !y || !pair_expert) return fail(LAPLACE_ERR_ARG, "moe_grouped: null pointer");
+    if (n_pairs <= 0 || n_experts_total <= 0 || N <= 0 || K <= 0 || K % block_elems(type))
+        return fail(LAPLACE_ERR_ARG, "moe_grouped: pairs=%d experts=%d K=%d N=%d", n_pairs, n_experts_total, K, N);
+    return launch_moe_grouped(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N,
+                              stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
 }
 
 int laplace_cuda_quantize_act_dev(const float* x, int M, int K, int8_t* q, float* d, float* sum, int16_t* isum,

@@ -54,7 +54,7 @@ int  cuda_check(cudaError_t e, const char* what);
 
 // Device status codes written to Context::d_err by bounded waits.
 enum : int { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_DRAIN = 3,
-             DEV_TIMEOUT_MMA = 4, DEV_TIMEOUT_TMEM = 5 };
+             DEV_TIMEOUT_MMA = 4, DEV_TIMEOUT_TMEM = 5, DEV_BAD_INDEX = 6 };
 
 // ---- kernel launchers (one per .cu) ----------------------------------------
 struct GemvArgs {
@@ -74,6 +74,11 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st);
 bool gemm_tc_supports(uint32_t type, int M, int K, int N);
 int  launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st);
 void release_gemm_tc_scratch();
+// Expert-grouped matmul over (token, expert) pairs on the tensor cores (lp_moe_grouped.cuh).
+bool moe_grouped_supports(uint32_t type, int K, int N);
+int  launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
+                        int P, int E, float* y, int K, int N, cudaStream_t st);
+void release_moe_grouped_scratch();
 
 int launch_quantize_act(const float* x, int M, int K, int8_t* q, float* d, float* sum,
                         int16_t* isum, cudaStream_t st);

@@ -83,7 +83,24 @@ struct TcParams {
     int            M, N, K;
     uint32_t       rb;
     int            tiles_m, tiles_n;
+    // expert-grouped calls: tiles come from a table built on the device, rows of the activation
+    // operand are scattered back through out_row (-1 = padding row)
+    const int4*    tile_tab;     // {m0, n0, first weight row of the expert, unused}; nullptr = dense tiling
+    const int*     n_tiles_dev;
+    const int*     out_row;
 };
+
+struct TileRef { int m0, n0, wrow0; };
+__device__ __forceinline__ TileRef tile_ref(const TcParams& p, int tile) {
+    if (p.tile_tab) {
+        const int4 t = __ldg(p.tile_tab + tile);
+        return {t.x, t.y, t.z};
+    }
+    return {(tile % p.tiles_m) * BM, (tile / p.tiles_m) * BN, 0};
+}
+__device__ __forceinline__ int tile_count(const TcParams& p) {
+    return p.tile_tab ? __ldg(p.n_tiles_dev) : p.tiles_m * p.tiles_n;
+}
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -213,7 +230,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
 
-    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int n_tiles = tile_count(p);
     const int nsb = p.K / 256;
     const int n_pairs = (nsb + 1) / 2;
 
@@ -224,7 +241,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * BM;
+                const int m0 = tile_ref(p, tile).m0;
                 for (int kc = 0; kc < nsb * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -246,7 +263,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int rq = 0, gp = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+                const TileRef tr = tile_ref(p, tile);
+                const int m0 = tr.m0, n0 = tr.wrow0 + tr.n0;
                 for (int sb = 0; sb < nsb; ++sb, ++rq) {
                     const int q = rq % RAW_STAGES;
                     if (!wait_or_abort(sbase + BAR_RAW_EMPTY + 8 * q, ((rq / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -437,9 +455,11 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         int bc = 0, gp = 0, gsb = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+            const TileRef tr = tile_ref(p, tile);
+            const int m0 = tr.m0, n0 = tr.n0;
             const int m = m0 + quad * 32 + lane;
-            const bool row_live = m < p.M;
+            const int orow = p.out_row ? __ldg(p.out_row + m) : (m < p.M ? m : -1);      // row of y, -1 = padding
+            const bool row_live = orow >= 0;
             const float2* dxr = reinterpret_cast<const float2*>(p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32));
             float2 acc2[32];
 #pragma unroll
@@ -522,7 +542,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 if (lane == 0) mbar_arrive(sbase + BAR_G_TAB_EMPTY + 8 * g);    // the pair's d / dmin tables are free
             }
             if (ok) {
-                float* yr = p.y + static_cast<size_t>(row_live ? m : 0) * p.N + n0 + half * 64;
+                float* yr = p.y + static_cast<size_t>(row_live ? orow : 0) * p.N + n0 + half * 64;
                 const bool vec = n0 + half * 64 + 64 <= p.N && (reinterpret_cast<uintptr_t>(yr) & 15) == 0;
 #pragma unroll
                 for (int gq = 0; gq < 4; ++gq) {
@@ -655,6 +675,84 @@ ScratchPlan plan_scratch(int M, int K, int N) {
     return s;
 }
 
+// One launch of a tensor-core kernel over prepared operands.
+struct TcLaunch {
+    const uint8_t* w; uint32_t type; float* y; int M, K, N;
+    size_t rows_pad;          // rows of the operand buffers aq / ag
+    long long w_rows;         // rows of the (stacked) weight matrix
+    __half* aq; float* dx; __nv_bfloat16* ag;
+    const int4* tile_tab; const int* n_tiles_dev; const int* out_row;
+    int tiles_m, tiles_n, grid;
+};
+
+int run_tc_kernel(const TcLaunch& L, cudaStream_t st) {
+    Context& c = ctx();
+    const int K = L.K, n_pairs = (K / 256 + 1) / 2;
+    const uint32_t type = L.type;
+    // 2-D tensor maps: the fp16 operand (inner dimension K) and the bf16 pieces of sum_x
+    // (inner dimension 64 per pair of super-blocks); outer dimension tokens.
+    CUtensorMap tmap, tmap_g, tmap_w;
+    {
+        // The driver entry point is looked up at run time so that the library does not link libcuda.
+        using encode_fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+        static encode_fn cuTensorMapEncodeTiled = nullptr;
+        if (!cuTensorMapEncodeTiled) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+            if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+                return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+            cuTensorMapEncodeTiled = reinterpret_cast<encode_fn>(fn);
+        }
+        const cuuint32_t box[2] = {BKC, BM};
+        const cuuint32_t estr[2] = {1, 1};
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(L.rows_pad)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * sizeof(__half)};
+        CUresult r = cuTensorMapEncodeTiled(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, L.aq, dims, strides, box, estr,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+        const cuuint64_t gdims[2] = {static_cast<cuuint64_t>(n_pairs) * 64, static_cast<cuuint64_t>(L.rows_pad)};
+        const cuuint64_t gstrides[1] = {static_cast<cuuint64_t>(n_pairs) * 64 * sizeof(__nv_bfloat16)};
+        r = cuTensorMapEncodeTiled(&tmap_g, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, L.ag, gdims, gstrides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled (G) failed (%d)", static_cast<int>(r));
+        // the packed weights as bytes: rows of rb bytes (stacked experts are just more rows), boxes of 128 rows
+        // x one super-block (144 bytes, or 240 for Q6_K: 210 + alignment slop)
+        const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(row_bytes(type, K)), static_cast<cuuint64_t>(L.w_rows)};
+        const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(row_bytes(type, K))};
+        const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(type == LAPLACE_TYPE_Q6_K ? q6::RAW_PITCH : Q4_K_BYTES), BN};
+        r = cuTensorMapEncodeTiled(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(L.w), wdims, wstrides, wbox, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (%d)", static_cast<int>(r));
+    }
+
+    TcParams p{};
+    p.w = L.w; p.dx = L.dx; p.y = L.y; p.err = c.d_err;
+    p.M = L.M; p.N = L.N; p.K = K; p.rb = static_cast<uint32_t>(row_bytes(type, K));
+    p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n;
+    p.tile_tab = L.tile_tab; p.n_tiles_dev = L.n_tiles_dev; p.out_row = L.out_row;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(q6::gemm_q6k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(q6::SMEM_BYTES));
+        if (e != cudaSuccess) return cuda_check(e, "cudaFuncSetAttribute gemm_tc");
+        configured = true;
+    }
+    if (type == LAPLACE_TYPE_Q6_K)
+        q6::gemm_q6k_tc_kernel<<<L.grid, THREADS, q6::SMEM_BYTES, st>>>(tmap, tmap_w, p);
+    else
+        gemm_q4k_tc_kernel<<<L.grid, THREADS, SMEM_BYTES, st>>>(tmap, tmap_g, tmap_w, p);
+    c.launches++;
+    c.last_path = 2;
+    return cuda_check(cudaGetLastError(), "gemm_tc launch");
+}
+
 // Quantizes x into `scratch` (device memory of at least plan.total() bytes, 256-byte aligned)
 // and runs the tensor-core kernel. Allocates nothing.
 int gemm_tc_on_scratch(uint8_t* scratch, const ScratchPlan& sp, const float* x, const uint8_t* w, uint32_t type, float* y,
@@ -679,68 +777,14 @@ int gemm_tc_on_scratch(uint8_t* scratch, const ScratchPlan& sp, const float* x, 
         if ((rc = cuda_check(cudaGetLastError(), "quantize_act_f16 launch"))) return rc;
     }
 
-    // 2-D tensor maps: the fp16 operand (inner dimension K) and the bf16 pieces of sum_x
-    // (inner dimension 64 per pair of super-blocks); outer dimension tokens.
-    CUtensorMap tmap, tmap_g, tmap_w;
-    {
-        // The driver entry point is looked up at run time so that the library does not link libcuda.
-        using encode_fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-        static encode_fn cuTensorMapEncodeTiled = nullptr;
-        if (!cuTensorMapEncodeTiled) {
-            void* fn = nullptr;
-            cudaDriverEntryPointQueryResult q;
-            cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-            if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
-                return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-            cuTensorMapEncodeTiled = reinterpret_cast<encode_fn>(fn);
-        }
-        const cuuint32_t box[2] = {BKC, BM};
-        const cuuint32_t estr[2] = {1, 1};
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(m_pad)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * sizeof(__half)};
-        CUresult r = cuTensorMapEncodeTiled(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, aq, dims, strides, box, estr,
-                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
-        const cuuint64_t gdims[2] = {static_cast<cuuint64_t>(n_pairs) * 64, static_cast<cuuint64_t>(m_pad)};
-        const cuuint64_t gstrides[1] = {static_cast<cuuint64_t>(n_pairs) * 64 * sizeof(__nv_bfloat16)};
-        r = cuTensorMapEncodeTiled(&tmap_g, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ag, gdims, gstrides, box, estr,
-                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled (G) failed (%d)", static_cast<int>(r));
-        // the packed weights as bytes: N rows of rb bytes, boxes of 128 rows x one 144-byte super-block
-        const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(row_bytes(type, K)), static_cast<cuuint64_t>(N)};
-        const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(row_bytes(type, K))};
-        const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(type == LAPLACE_TYPE_Q6_K ? q6::RAW_PITCH : Q4_K_BYTES), BN};
-        r = cuTensorMapEncodeTiled(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w), wdims, wstrides, wbox, estr,
-                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(LAPLACE_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (%d)", static_cast<int>(r));
-    }
-
-    TcParams p{};
-    p.w = w; p.dx = dx; p.y = y; p.err = c.d_err;
-    p.M = M; p.N = N; p.K = K; p.rb = static_cast<uint32_t>(row_bytes(type, K));
-    p.tiles_m = tiles_m; p.tiles_n = tiles_n;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(q6::gemm_q6k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(q6::SMEM_BYTES));
-        if (e != cudaSuccess) return cuda_check(e, "cudaFuncSetAttribute gemm_tc");
-        configured = true;
-    }
+    TcLaunch L{};
+    L.w = w; L.type = type; L.y = y; L.M = M; L.K = K; L.N = N;
+    L.rows_pad = m_pad; L.w_rows = N;
+    L.aq = aq; L.dx = dx; L.ag = ag;
+    L.tiles_m = tiles_m; L.tiles_n = tiles_n;
     const int n_tiles = tiles_m * tiles_n;
-    const int grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
-    if (type == LAPLACE_TYPE_Q6_K)
-        q6::gemm_q6k_tc_kernel<<<grid, THREADS, q6::SMEM_BYTES, st>>>(tmap, tmap_w, p);
-    else
-        gemm_q4k_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmap, tmap_g, tmap_w, p);
-    c.launches++;
-    c.last_path = 2;
-    return cuda_check(cudaGetLastError(), "gemm_tc launch");
+    L.grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
+    return run_tc_kernel(L, st);
 }
 
 int check_gemm_tc_args(const float* x, const uint8_t* w, uint32_t type, int M, int K, int N) {
@@ -759,6 +803,8 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
     if ((rc = g_scratch.ensure(sp.total()))) return rc;
     return gemm_tc_on_scratch(static_cast<uint8_t*>(g_scratch.p), sp, x, w, type, y, M, K, N, st);
 }
+
+#include "lp_moe_grouped.cuh"
 
 // ---- the entry point that allocates nothing -------------------------------------------
 // Some hosts of this library must not (or cannot) call the CUDA allocator on the request

@@ -89,7 +89,7 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
 
-    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int n_tiles = tile_count(p);
     const int nsb = p.K / 256;
 
     if (warp < 4) {
@@ -99,7 +99,7 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * BM;
+                const int m0 = tile_ref(p, tile).m0;
                 for (int kc = 0; kc < nsb * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -121,7 +121,8 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int rq = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int n0 = (tile / p.tiles_m) * BN;
+                const TileRef tr = tile_ref(p, tile);
+                const int n0 = tr.wrow0 + tr.n0;
                 for (int sb = 0; sb < nsb; ++sb, ++rq) {
                     const int q = rq % RAW_STAGES;
                     if (!wait_or_abort(sbase + BAR_RAW_EMPTY + 8 * q, ((rq / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -241,9 +242,11 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         int bc = 0, ds = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+            const TileRef tr = tile_ref(p, tile);
+            const int m0 = tr.m0, n0 = tr.n0;
             const int m = m0 + quad * 32 + lane;
-            const bool row_live = m < p.M;
+            const int orow = p.out_row ? __ldg(p.out_row + m) : (m < p.M ? m : -1);      // row of y, -1 = padding
+            const bool row_live = orow >= 0;
             const float2* dxr = reinterpret_cast<const float2*>(p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32));
             float2 acc2[32];
 #pragma unroll
@@ -309,7 +312,7 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 if (lane == 0) mbar_arrive(sbase + BAR_DT_EMPTY + 8 * dsl);
             }
             if (ok) {
-                float* yr = p.y + static_cast<size_t>(row_live ? m : 0) * p.N + n0 + half * 64;
+                float* yr = p.y + static_cast<size_t>(row_live ? orow : 0) * p.N + n0 + half * 64;
                 const bool vec = n0 + half * 64 + 64 <= p.N && (reinterpret_cast<uintptr_t>(yr) & 15) == 0;
 #pragma unroll
                 for (int gq = 0; gq < 4; ++gq) {

@@ -1,0 +1,207 @@
+// lp_moe_grouped.cuh - expert-grouped matmul for a batch of tokens. Included by lp_gemm_tc.cu
+// inside namespace lp.
+//
+// Laplace runs a mixture-of-experts layer token by token: for each token one fused_moe_gemm_idx
+// call over its top-k experts (gate/up, src/matmul.cpp:467-482, src/arch_gemma4.cpp:604) and
+// one fused_moe_gemm_multi call (down, src/matmul.cpp:484-500, src/arch_gemma4.cpp:626). With a
+// batch of tokens every such call streams the selected experts again. Here all
+// (token, expert) pairs of the batch are grouped by expert on the device and every expert's
+// weights meet all of its tokens in one pass of the tensor-core kernel:
+//   for every pair p:  y[p] = W[pair_expert[p]] . quantize(x[pair_row[p]])
+// which is exactly what the per-token calls compute (the result of a pair does not depend on
+// which other pairs share its tile).
+//
+// Device-side plan (no host synchronisation, the grid is persistent):
+//   1. count pairs per expert, give every pair a slot inside its expert      (moe_count_kernel)
+//   2. prefix over experts of the counts rounded up to 128 rows -> first row of each expert in
+//      the activation operand; tile table {m0, n0, first weight row}        (moe_plan_kernel)
+//   3. destination row of every pair, and the inverse map for the epilogue   (moe_assign_kernel)
+//   4. quantize the gathered rows into the operand                           (quantize_act_f16_mapped_kernel)
+//   5. the GEMM kernel walks the tile table and scatters rows through out_row.
+namespace {
+
+__global__ void moe_count_kernel(const int* __restrict__ pair_expert, int P, int E, int* __restrict__ counts,
+                                 int* __restrict__ slot, int* err) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= P) return;
+    const int e = pair_expert[p];
+    if (e < 0 || e >= E) {
+        slot[p] = -1;                      // the pair is skipped; the host reports a bad argument
+        report_status(err, DEV_BAD_INDEX);
+        return;
+    }
+    slot[p] = atomicAdd(counts + e, 1);
+}
+
+// One block. base[e] = first operand row of expert e; tiles ordered by expert, then by 128-row
+// group of its tokens, then by 128-column block, so that CTAs running at the same time share
+// activation rows and neighbouring weight rows in L2.
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int N, int tiles_n, int* __restrict__ base,
+                                int4* __restrict__ tile_tab, int* __restrict__ n_tiles) {
+    if (threadIdx.x == 0) {
+        int rows = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            base[e] = rows;
+            base[E + 1 + e] = tiles;                       // first tile of expert e
+            const int groups = (counts[e] + BM - 1) / BM;
+            rows += groups * BM;
+            tiles += groups * tiles_n;
+        }
+        base[E] = rows;
+        *n_tiles = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int groups = (counts[e] + BM - 1) / BM;
+        int t = base[E + 1 + e];
+        for (int g = 0; g < groups; ++g)
+            for (int nt = 0; nt < tiles_n; ++nt)
+                tile_tab[t++] = make_int4(base[e] + g * BM, nt * BN, e * N, 0);
+    }
+}
+
+__global__ void moe_assign_kernel(const int* __restrict__ pair_expert, const int* __restrict__ slot, int P,
+                                  const int* __restrict__ base, int* __restrict__ dst_row, int* __restrict__ out_row) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= P) return;
+    const int s = slot[p];
+    if (s < 0) { dst_row[p] = -1; return; }
+    const int r = base[pair_expert[p]] + s;
+    dst_row[p] = r;
+    out_row[r] = p;
+}
+
+// quantize_act_f16_kernel with a row gather on the way in and a row scatter on the way out:
+// pair m reads x row src_rows[m] (m itself when src_rows is null) and writes operand row dst_rows[m].
+__global__ void __launch_bounds__(256) quantize_act_f16_mapped_kernel(const float* __restrict__ x, int P, int K,
+                                                                      const int* __restrict__ src_rows,
+                                                                      const int* __restrict__ dst_rows,
+                                                                      __half* __restrict__ aq, float* __restrict__ dx,
+                                                                      __nv_bfloat16* __restrict__ ag, int ag_stride) {
+    const int t8 = threadIdx.x & 7;
+    const int bpr = K / 32;
+    const long long n_blocks = static_cast<long long>(P) * bpr;
+    const long long groups = static_cast<long long>(gridDim.x) * (blockDim.x >> 3);
+    const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x >> 3) + (threadIdx.x >> 3);
+    const long long iters = (n_blocks + groups - 1) / groups;
+    for (long long itn = 0; itn < iters; ++itn) {
+        const long long b = first + itn * groups;
+        bool live = b < n_blocks;
+        const int m = live ? static_cast<int>(b / bpr) : 0;
+        const int kb = live ? static_cast<int>(b - static_cast<long long>(m) * bpr) : 0;
+        const int dr = live ? dst_rows[m] : -1;
+        live = live && dr >= 0;
+        const long long sr = live ? (src_rows ? src_rows[m] : m) : 0;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) v = __ldg(reinterpret_cast<const float4*>(x + (sr * bpr + kb) * 32) + t8);
+        uint32_t packed; int hs;
+        const float d = quantize_block_8lanes(v, packed, hs);
+        const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
+        if (!live) continue;
+        const int q0 = static_cast<int8_t>(packed & 0xff), q1 = static_cast<int8_t>((packed >> 8) & 0xff);
+        const int q2 = static_cast<int8_t>((packed >> 16) & 0xff), q3 = static_cast<int8_t>(packed >> 24);
+        const __half2 lo = __halves2half2(__int2half_rn(q0), __int2half_rn(q2));
+        const __half2 hi = __halves2half2(__int2half_rn(q1), __int2half_rn(q3));
+        uint2 out;
+        out.x = *reinterpret_cast<const uint32_t*>(&lo);
+        out.y = *reinterpret_cast<const uint32_t*>(&hi);
+        const long long ob = static_cast<long long>(dr) * bpr + kb;
+        reinterpret_cast<uint2*>(aq + ob * 32)[t8] = out;
+        if (t8 == 0) {
+            const short slo = static_cast<short>(hs), shi = static_cast<short>(hs_hi);
+            dx[ob] = d;
+            const float sum = d * static_cast<float>(static_cast<int>(slo) + static_cast<int>(shi));
+            const __nv_bfloat16 p0 = __float2bfloat16_rn(sum);
+            const float r1 = sum - __bfloat162float(p0);
+            const __nv_bfloat16 p1 = __float2bfloat16_rn(r1);
+            const __nv_bfloat16 p2 = __float2bfloat16_rn(r1 - __bfloat162float(p1));
+            __nv_bfloat16* dst = ag + static_cast<long long>(dr) * ag_stride + (kb >> 3) * 32 + 3 * (kb & 7);
+            dst[0] = p0; dst[1] = p1; dst[2] = p2;
+        }
+    }
+}
+
+Scratch g_moe_scratch;
+
+inline size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
+
+}  // namespace
+
+void release_moe_grouped_scratch() {
+    if (g_moe_scratch.p) cudaFree(g_moe_scratch.p);
+    g_moe_scratch.p = nullptr;
+    g_moe_scratch.cap = 0;
+}
+
+bool moe_grouped_supports(uint32_t type, int K, int N) {
+    return gemm_tc_supports(type, 9, K, N);
+}
+
+int launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
+                       int P, int E, float* y, int K, int N, cudaStream_t st) {
+    if (!moe_grouped_supports(type, K, N)) return LAPLACE_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
+        return fail(LAPLACE_ERR_ARG, "moe_grouped: x and w must be 16-byte aligned on the device");
+    if ((static_cast<size_t>(N) * row_bytes(type, K)) % 16)
+        return fail(LAPLACE_ERR_ARG, "moe_grouped: expert stride is not a 16-byte multiple");
+    Context& c = ctx();
+    const int tiles_n = (N + BN - 1) / BN;
+    const int n_sb_pairs = (K / 256 + 1) / 2;
+    const size_t bpr = static_cast<size_t>(K / 32);
+    // every expert's rows are padded to a multiple of 128: at most min(E, P) experts are populated
+    const size_t groups_max = static_cast<size_t>(P) / BM + static_cast<size_t>(E < P ? E : P);
+    const size_t rows_max = groups_max * BM;
+    const size_t tiles_max = groups_max * tiles_n;
+    const size_t aq_bytes = align256(rows_max * K * sizeof(__half));
+    const size_t dx_bytes = align256(rows_max * bpr * sizeof(float));
+    const size_t ag_bytes = align256(rows_max * n_sb_pairs * 64 * sizeof(__nv_bfloat16));
+    const size_t cnt_bytes = align256(sizeof(int) * (2 * static_cast<size_t>(E) + 2));      // counts | n_tiles
+    const size_t base_bytes = align256(sizeof(int) * (2 * static_cast<size_t>(E) + 2));
+    const size_t slot_bytes = align256(sizeof(int) * static_cast<size_t>(P));
+    const size_t out_bytes = align256(sizeof(int) * rows_max);
+    const size_t tab_bytes = align256(sizeof(int4) * tiles_max);
+    const size_t total = aq_bytes + dx_bytes + ag_bytes + cnt_bytes + base_bytes + 2 * slot_bytes + out_bytes + tab_bytes;
+    int rc;
+    if ((rc = g_moe_scratch.ensure(total))) return rc;
+    uint8_t* s = static_cast<uint8_t*>(g_moe_scratch.p);
+    __half* aq = reinterpret_cast<__half*>(s);                     s += aq_bytes;
+    float* dx = reinterpret_cast<float*>(s);                       s += dx_bytes;
+    __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(s);       s += ag_bytes;
+    int* counts = reinterpret_cast<int*>(s);                       s += cnt_bytes;
+    int* base = reinterpret_cast<int*>(s);                         s += base_bytes;
+    int* slot = reinterpret_cast<int*>(s);                         s += slot_bytes;
+    int* dst_row = reinterpret_cast<int*>(s);                      s += slot_bytes;
+    int* out_row = reinterpret_cast<int*>(s);                      s += out_bytes;
+    int4* tile_tab = reinterpret_cast<int4*>(s);
+    int* n_tiles = counts + E;                                      // shares the zeroed block with the counters
+
+    if ((rc = cuda_check(cudaMemsetAsync(counts, 0, cnt_bytes, st), "cudaMemsetAsync")) ||
+        (rc = cuda_check(cudaMemsetAsync(out_row, 0xff, out_bytes, st), "cudaMemsetAsync")) ||
+        (rc = cuda_check(cudaMemsetAsync(ag, 0, ag_bytes, st), "cudaMemsetAsync")))
+        return rc;
+    const int tb = 256, gb = (P + tb - 1) / tb;
+    moe_count_kernel<<<gb, tb, 0, st>>>(pair_expert, P, E, counts, slot, c.d_err);
+    moe_plan_kernel<<<1, 256, 0, st>>>(counts, E, N, tiles_n, base, tile_tab, n_tiles);
+    moe_assign_kernel<<<gb, tb, 0, st>>>(pair_expert, slot, P, base, dst_row, out_row);
+    {
+        const long long n_blocks = static_cast<long long>(P) * static_cast<long long>(bpr);
+        long long want = (n_blocks + 31) / 32;
+        const long long cap = static_cast<long long>(c.sm_count) * 8;
+        const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+        quantize_act_f16_mapped_kernel<<<grid, 256, 0, st>>>(x, P, K, pair_row, dst_row, aq, dx, ag, n_sb_pairs * 64);
+    }
+    c.launches += 4;
+    if ((rc = cuda_check(cudaGetLastError(), "moe_grouped set-up launches"))) return rc;
+
+    TcLaunch L{};
+    L.w = w; L.type = type; L.y = y; L.M = P; L.K = K; L.N = N;
+    L.rows_pad = rows_max; L.w_rows = static_cast<long long>(E) * N;
+    L.aq = aq; L.dx = dx; L.ag = ag;
+    L.tile_tab = tile_tab; L.n_tiles_dev = n_tiles; L.out_row = out_row;
+    L.tiles_m = 1; L.tiles_n = tiles_n;
+    L.grid = static_cast<int>(tiles_max < static_cast<size_t>(c.sm_count) ? tiles_max : static_cast<size_t>(c.sm_count));
+    if (L.grid < 1) L.grid = 1;
+    rc = run_tc_kernel(L, st);
+    if (rc == LAPLACE_OK) c.last_path = 3;
+    return rc;
+}

@@ -70,6 +70,36 @@ def moe_gemv(x: torch.Tensor, w: torch.Tensor, t: int, expert_idx: torch.Tensor,
     return y
 
 
+def moe_grouped(x: torch.Tensor, w: torch.Tensor, t: int, pair_expert: torch.Tensor, pair_row: torch.Tensor | None,
+                n_experts_total: int, K: int, N: int, y: torch.Tensor | None = None) -> torch.Tensor:
+    """y[p] = W[pair_expert[p]] . x[pair_row[p]] for every (token, expert) pair of a batch, grouped by expert on
+    the device (what one fused_moe_gemm_idx / fused_moe_gemm_multi call per token computes, src/matmul.h:36-54).
+    Types the grouped kernel does not take run as one expert-indexed GEMV launch per pair group of the same row."""
+    L = lib()
+    P = pair_expert.numel()
+    assert pair_expert.dtype == torch.int32 and pair_expert.is_cuda and pair_expert.is_contiguous()
+    assert pair_row is None or (pair_row.dtype == torch.int32 and pair_row.is_cuda and pair_row.numel() == P)
+    assert x.dtype == torch.float32 and x.is_cuda and x.is_contiguous()
+    if y is None:
+        y = torch.empty((P, N), dtype=torch.float32, device=x.device)
+    rc = L.laplace_cuda_moe_grouped_dev(x.data_ptr(), w.data_ptr(), int(t), pair_expert.data_ptr(),
+                                        pair_row.data_ptr() if pair_row is not None else None, P, n_experts_total,
+                                        y.data_ptr(), K, N, _stream())
+    if rc == 1:
+        # not a grouped-kernel type: the reference's own shape, one expert-indexed GEMV per input row
+        rows = pair_row.cpu().tolist() if pair_row is not None else list(range(P))
+        start = 0
+        while start < P:
+            end = start
+            while end < P and rows[end] == rows[start]:
+                end += 1
+            moe_gemv(x[rows[start]], w, t, pair_expert[start:end], K, N, per_expert_x=False, y=y[start:end])
+            start = end
+        return y
+    _check(L, rc)
+    return y
+
+
 def quantize_act(x: torch.Tensor, M: int, K: int):
     """Returns (q int8 [M,K], d f32 [M,K/32], sum f32 [M,K/32], isum int16 [M,K/32,2])."""
     L = lib()
