@@ -115,13 +115,34 @@ int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type,
  * for the shared-input form pass pair_row[p] = token of pair p. Pairs may come in any order; they
  * are grouped by expert on the device. Q4_K (K % 256 == 0) and Q6_K (K % 2048 == 0); other
  * types return LAPLACE_UNSUPPORTED and the caller loops laplace_cuda_moe_gemv_dev per token.
- * An expert index outside [0, n_experts_total) skips that pair and makes the next
+ * A negative expert index marks a pair that is not computed here (its y row is left untouched):
+ * with experts placed on several GPUs every GPU passes the whole pair list with the experts of
+ * the other GPUs set to -1. An index >= n_experts_total also skips the pair and makes the next
  * laplace_cuda_sync() return LAPLACE_ERR_ARG. x, w and every expert (N*rb bytes) must be
  * 16-byte aligned. All pointers are device memory. */
 int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type,
                                  const int* pair_expert, const int* pair_row,
                                  int n_pairs, int n_experts_total,
                                  float* y, int K, int N, void* stream);
+
+/* The expert FFN of a mixture-of-experts layer for a batch of tokens, fused: what the reference
+ * does per token in src/arch_gemma4.cpp:600-638 - fused_moe_gemm_idx over the token's experts
+ * (gate and up rows stacked, N = 2*inter), ops::swiglu / ops::geglu (src/ops.cpp:128-176),
+ * fused_moe_gemm_multi (down), out = sum_k top_w[k] * expert_out[k] - with one device-side
+ * grouping shared by both matmuls and the intermediate results kept in grouped order.
+ *   x [n_tokens][hidden]; w_gate_up: experts x (2*inter rows of K = hidden), gate rows first;
+ *   w_down: experts x (hidden rows of K = inter); top_idx / top_w [n_tokens][top_k];
+ *   activation 0 = SwiGLU (silu(gate) * up), 1 = GeGLU (tanh-GELU(gate) * up);
+ *   out [n_tokens][hidden] is OVERWRITTEN with the weighted sum over the experts computed here.
+ * Negative entries of top_idx are experts that live on another GPU: they contribute nothing, so
+ * the per-GPU outputs of an expert-parallel layer add up to the layer's output. h_out (optional,
+ * may be NULL) receives the activation result per pair, [n_tokens*top_k][inter] (rows of skipped
+ * pairs untouched). Types as for laplace_cuda_moe_grouped_dev, else LAPLACE_UNSUPPORTED. */
+int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down,
+                             uint32_t type_gate_up, uint32_t type_down,
+                             const int* top_idx, const float* top_w,
+                             int n_tokens, int top_k, int n_experts_total, int hidden, int inter, int activation,
+                             float* out, float* h_out, void* stream);
 
 /* Prefill GEMM (Q4_K, M > 8, K % 256 == 0) that allocates nothing. It has no counterpart in
  * the reference: it exists for hosts that must not touch the CUDA allocator on the request
@@ -157,7 +178,7 @@ int laplace_cuda_debug_blocksums_dev(const float* x, const uint8_t* w, uint32_t 
                                      int32_t* out, int M, int K, int N, void* stream);
 
 /* Which kernel family the last *_dev gemm call used: 1 = streaming dp4a GEMV,
- * 2 = tensor-core GEMM, 3 = expert-grouped tensor-core GEMM. For tests and the benchmark's launch count. */
+ * 2 = tensor-core GEMM, 3 = expert-grouped tensor-core GEMM, 4 = fused expert FFN. For tests and the benchmark's launch count. */
 int laplace_cuda_last_path(void);
 /* Kernel launches issued by this library since the counter was last reset. */
 long long laplace_cuda_launch_count(int reset);

@@ -229,6 +229,7 @@ void laplace_cuda_shutdown(void) {
     g_hx.release(); g_hy.release();
     release_gemm_tc_scratch();
     release_moe_grouped_scratch();
+    release_moe_ffn_scratch();
     cudaFreeHost(g_ctx.h_err);
     cudaStreamDestroy(g_ctx.stream);
     g_ctx = Context{};
@@ -357,6 +358,22 @@ int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type
         return fail(LAPLACE_ERR_ARG, "moe_grouped: pairs=%d experts=%d K=%d N=%d", n_pairs, n_experts_total, K, N);
     return launch_moe_grouped(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N,
                               stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down,
+                             uint32_t type_gate_up, uint32_t type_down, const int* top_idx, const float* top_w,
+                             int n_tokens, int top_k, int n_experts_total, int hidden, int inter, int activation,
+                             float* out, float* h_out, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!block_elems(type_gate_up) || !block_elems(type_down)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w_gate_up || !w_down || !top_idx || !top_w || !out) return fail(LAPLACE_ERR_ARG, "moe_ffn: null pointer");
+    if (n_tokens <= 0 || top_k <= 0 || n_experts_total <= 0 || hidden <= 0 || inter <= 0 ||
+        hidden % block_elems(type_gate_up) || inter % block_elems(type_down) || (activation != 0 && activation != 1))
+        return fail(LAPLACE_ERR_ARG, "moe_ffn: tokens=%d top_k=%d experts=%d hidden=%d inter=%d activation=%d",
+                    n_tokens, top_k, n_experts_total, hidden, inter, activation);
+    return launch_moe_ffn(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, n_tokens, top_k, n_experts_total,
+                          hidden, inter, activation, out, h_out, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
 }
 
 int laplace_cuda_quantize_act_dev(const float* x, int M, int K, int8_t* q, float* d, float* sum, int16_t* isum,

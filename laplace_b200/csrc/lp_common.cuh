@@ -79,6 +79,11 @@ bool moe_grouped_supports(uint32_t type, int K, int N);
 int  launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
                         int P, int E, float* y, int K, int N, cudaStream_t st);
 void release_moe_grouped_scratch();
+// Fused expert FFN (gate/up matmul, gated activation, down matmul, weighted sum) for a batch of tokens.
+int  launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
+                    const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
+                    float* out, float* h_out, cudaStream_t st);
+void release_moe_ffn_scratch();
 
 int launch_quantize_act(const float* x, int M, int K, int8_t* q, float* d, float* sum,
                         int16_t* isum, cudaStream_t st);

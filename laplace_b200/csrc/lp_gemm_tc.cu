@@ -88,6 +88,7 @@ struct TcParams {
     const int4*    tile_tab;     // {m0, n0, first weight row of the expert, unused}; nullptr = dense tiling
     const int*     n_tiles_dev;
     const int*     out_row;
+    int            out_identity; // 1: a live row m is written to row m of y (y is in operand-row order), not to out_row[m]
 };
 
 struct TileRef { int m0, n0, wrow0; };
@@ -458,7 +459,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const TileRef tr = tile_ref(p, tile);
             const int m0 = tr.m0, n0 = tr.n0;
             const int m = m0 + quad * 32 + lane;
-            const int orow = p.out_row ? __ldg(p.out_row + m) : (m < p.M ? m : -1);      // row of y, -1 = padding
+            int orow = p.out_row ? __ldg(p.out_row + m) : (m < p.M ? m : -1);            // row of y, -1 = padding
+            if (p.out_identity && orow >= 0) orow = m;
             const bool row_live = orow >= 0;
             const float2* dxr = reinterpret_cast<const float2*>(p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32));
             float2 acc2[32];
@@ -681,7 +683,7 @@ struct TcLaunch {
     size_t rows_pad;          // rows of the operand buffers aq / ag
     long long w_rows;         // rows of the (stacked) weight matrix
     __half* aq; float* dx; __nv_bfloat16* ag;
-    const int4* tile_tab; const int* n_tiles_dev; const int* out_row;
+    const int4* tile_tab; const int* n_tiles_dev; const int* out_row; int out_identity;
     int tiles_m, tiles_n, grid;
 };
 
@@ -735,7 +737,7 @@ int run_tc_kernel(const TcLaunch& L, cudaStream_t st) {
     p.w = L.w; p.dx = L.dx; p.y = L.y; p.err = c.d_err;
     p.M = L.M; p.N = L.N; p.K = K; p.rb = static_cast<uint32_t>(row_bytes(type, K));
     p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n;
-    p.tile_tab = L.tile_tab; p.n_tiles_dev = L.n_tiles_dev; p.out_row = L.out_row;
+    p.tile_tab = L.tile_tab; p.n_tiles_dev = L.n_tiles_dev; p.out_row = L.out_row; p.out_identity = L.out_identity;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));

@@ -245,7 +245,8 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const TileRef tr = tile_ref(p, tile);
             const int m0 = tr.m0, n0 = tr.n0;
             const int m = m0 + quad * 32 + lane;
-            const int orow = p.out_row ? __ldg(p.out_row + m) : (m < p.M ? m : -1);      // row of y, -1 = padding
+            int orow = p.out_row ? __ldg(p.out_row + m) : (m < p.M ? m : -1);            // row of y, -1 = padding
+            if (p.out_identity && orow >= 0) orow = m;
             const bool row_live = orow >= 0;
             const float2* dxr = reinterpret_cast<const float2*>(p.dx + static_cast<size_t>(row_live ? m : 0) * (p.K / 32));
             float2 acc2[32];

@@ -100,6 +100,28 @@ def moe_grouped(x: torch.Tensor, w: torch.Tensor, t: int, pair_expert: torch.Ten
     return y
 
 
+SWIGLU, GEGLU = 0, 1
+
+
+def moe_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, t_gate_up: int, t_down: int,
+            top_idx: torch.Tensor, top_w: torch.Tensor, n_experts_total: int, hidden: int, inter: int,
+            activation: int = SWIGLU, out: torch.Tensor | None = None, h_out: torch.Tensor | None = None) -> torch.Tensor:
+    """The fused expert FFN (laplace_cuda_moe_ffn_dev): out[t] = sum over the experts of token t that live here of
+    top_w * down(act(gate_up(x[t]))). Raises for types the grouped kernels do not take."""
+    L = lib()
+    T, k = top_idx.shape
+    assert top_idx.dtype == torch.int32 and top_idx.is_cuda and top_idx.is_contiguous()
+    assert top_w.dtype == torch.float32 and top_w.is_cuda and top_w.is_contiguous() and top_w.shape == top_idx.shape
+    assert x.dtype == torch.float32 and x.is_cuda and x.is_contiguous() and x.shape == (T, hidden)
+    if out is None:
+        out = torch.empty((T, hidden), dtype=torch.float32, device=x.device)
+    _check(L, L.laplace_cuda_moe_ffn_dev(x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), int(t_gate_up), int(t_down),
+                                         top_idx.data_ptr(), top_w.data_ptr(), T, k, n_experts_total, hidden, inter,
+                                         activation, out.data_ptr(), h_out.data_ptr() if h_out is not None else None,
+                                         _stream()))
+    return out
+
+
 def quantize_act(x: torch.Tensor, M: int, K: int):
     """Returns (q int8 [M,K], d f32 [M,K/32], sum f32 [M,K/32], isum int16 [M,K/32,2])."""
     L = lib()

@@ -1,0 +1,95 @@
+"""GPU parity of the fused expert FFN (laplace_cuda_moe_ffn_dev) against the reference's per-token sequence
+(src/arch_gemma4.cpp:600-638: gate/up matmul, gated activation, down matmul, weighted sum), stage by stage.
+
+The activation feeds a quantizer, so a last-bit difference between the device's expf / tanhf and the host's can
+move an int8 value by one step; the down matmul is therefore checked against the oracle run on the activation
+values the device itself produced (h_out), and the activation is checked on its own against the host formula."""
+import numpy as np
+import pytest
+
+from laplace_b200 import synth
+from laplace_b200.ggml import GGMLType
+from laplace_b200.moe import seeded_routing
+from tests.parity import check_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _host_activation(gu, inter, activation):
+    g, u = gu[:, :inter].astype(np.float32), gu[:, inter:].astype(np.float32)
+    if activation == 0:
+        return (g / (np.float32(1.0) + np.exp(-g))) * u                       # ops::swiglu, src/ops.cpp:128-130
+    g3 = (g * g) * g
+    gelu = np.float32(0.5) * g * (np.float32(1.0) + np.tanh(np.float32(0.7978845608028654) * (g + np.float32(0.044715) * g3)))
+    return gelu * u                                                           # ops::geglu, src/ops.cpp:165-171
+
+
+@pytest.mark.parametrize("activation", [0, 1])
+@pytest.mark.parametrize("t_gu,t_dn,H,I", [(GGMLType.Q4_K, GGMLType.Q4_K, 512, 256), (GGMLType.Q4_K, GGMLType.Q4_K, 2048, 768),
+                                           (GGMLType.Q6_K, GGMLType.Q4_K, 2048, 256)])
+def test_fused_ffn_stage_by_stage(oracle, activation, t_gu, t_dn, H, I):
+    import torch
+    from laplace_b200 import device
+    E, k, T = 8, 3, 20
+    w_gu = synth.weights(t_gu, H, E * 2 * I, seed=600 + H, how="random")
+    w_dn = synth.weights(t_dn, I, E * H, seed=601 + I, how="random")
+    x = synth.normal_f32(602, (T, H))
+    idx, wts = seeded_routing(603, T, E, k)
+    xd, wg, wd = torch.from_numpy(x).cuda(), device.upload_weights(w_gu), device.upload_weights(w_dn)
+    idx_d, wts_d = torch.from_numpy(idx).cuda(), torch.from_numpy(wts).cuda()
+    h_dev = torch.zeros((T * k, I), dtype=torch.float32, device="cuda")
+    out = device.moe_ffn(xd, wg, wd, t_gu, t_dn, idx_d, wts_d, E, H, I, activation=activation, h_out=h_dev)
+    device.sync()
+    assert device.lib().laplace_cuda_last_path() == 4
+    out, h_dev = out.cpu().numpy(), h_dev.cpu().numpy()
+    # stage 1 + 2: gate/up from the oracle, activation by the host formula
+    gu_ref = np.concatenate([oracle.moe_gemv(x[tok], w_gu, t_gu, idx[tok], H, 2 * I, multi=False, mode=1) for tok in range(T)])
+    h_ref = _host_activation(gu_ref, I, activation)
+    check_close(h_dev, h_ref, "activation(gate/up)")
+    # stage 3 + 4: down matmul and weighted sum, from the device's own activation values
+    want = np.zeros((T, H), dtype=np.float64)
+    for tok in range(T):
+        dn = oracle.moe_gemv(h_dev[tok * k:(tok + 1) * k], w_dn, t_dn, idx[tok], I, H, multi=True, mode=1)
+        want[tok] = (dn.astype(np.float64) * wts[tok][:, None]).sum(axis=0)
+    check_close(out, want.astype(np.float32), f"fused FFN act={activation} H={H} I={I}")
+
+
+def test_partial_sums_over_expert_shards_add_up(oracle):
+    """Experts split over two 'GPUs' (run one after the other here): the two partial outputs sum to the whole."""
+    import torch
+    from laplace_b200 import device
+    t, E, k, T, H, I = GGMLType.Q4_K, 8, 4, 16, 512, 256
+    w_gu = synth.weights(t, H, E * 2 * I, seed=610, how="random")
+    w_dn = synth.weights(t, I, E * H, seed=611, how="random")
+    x = torch.from_numpy(synth.normal_f32(612, (T, H))).cuda()
+    idx, wts = seeded_routing(613, T, E, k)
+    wts_d = torch.from_numpy(wts).cuda()
+    whole = device.moe_ffn(x, device.upload_weights(w_gu), device.upload_weights(w_dn), t, t,
+                           torch.from_numpy(idx).cuda(), wts_d, E, H, I).clone()
+    parts = []
+    for r in range(2):
+        lo = r * (E // 2)
+        local = np.where((idx >= lo) & (idx < lo + E // 2), idx - lo, -1).astype(np.int32)
+        gu_rows, dn_rows = 2 * I * (E // 2), H * (E // 2)
+        parts.append(device.moe_ffn(x, device.upload_weights(w_gu[r * gu_rows:(r + 1) * gu_rows]),
+                                    device.upload_weights(w_dn[r * dn_rows:(r + 1) * dn_rows]), t, t,
+                                    torch.from_numpy(local).cuda(), wts_d, E // 2, H, I).clone())
+    device.sync()
+    got = (parts[0] + parts[1]).cpu().numpy()
+    want = whole.cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-5 * np.sqrt((want ** 2).mean()) * 10
+
+
+def test_unsupported_type_is_reported():
+    import torch
+    from laplace_b200 import device
+    from laplace_b200.matmul import LaplaceCudaError
+    t, E, k, T, H, I = GGMLType.Q8_0, 2, 1, 2, 256, 256
+    w1 = device.upload_weights(synth.weights(t, H, E * 2 * I, seed=620, how="random"))
+    w2 = device.upload_weights(synth.weights(t, I, E * H, seed=621, how="random"))
+    x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    idx = torch.zeros((T, k), dtype=torch.int32, device="cuda")
+    wts = torch.ones((T, k), dtype=torch.float32, device="cuda")
+    with pytest.raises(LaplaceCudaError) as e:
+        device.moe_ffn(x, w1, w2, t, t, idx, wts, E, H, I)
+    assert e.value.code == 1

@@ -115,3 +115,21 @@ def test_bad_expert_index_is_reported():
         device.sync()
     device.sync()                      # the status word is cleared by the failed sync
     assert torch.count_nonzero(y[1]).item() == 0 and torch.count_nonzero(y[0]).item() > 0
+
+
+def test_negative_expert_index_skips_the_pair(oracle):
+    """Pairs whose expert lives on another GPU are passed as -1: not computed, not an error."""
+    import torch
+    from laplace_b200 import device
+    t, K, N, E = GGMLType.Q4_K, 512, 128, 4
+    w = synth.weights(t, K, N * E, seed=360, how="random")
+    x = synth.normal_f32(361, (6, K))
+    pe = np.array([2, -1, 0, -1, -1, 3], dtype=np.int32)
+    y = torch.full((6, N), 7.0, dtype=torch.float32, device="cuda")
+    device.moe_grouped(torch.from_numpy(x).cuda(), device.upload_weights(w), t, torch.from_numpy(pe).cuda(), None, E, K, N, y=y)
+    device.sync()
+    got = y.cpu().numpy()
+    live = pe >= 0
+    assert np.all(got[~live] == 7.0)
+    ref = oracle.moe_gemv(x[live], w, t, pe[live], K, N, multi=True, mode=1)
+    check_close(got[live], ref, "grouped with skipped pairs")
