@@ -176,19 +176,43 @@ def gpu_arm(args):
     y_loc = torch.empty((N_COPIES, M_ROWS, n_loc), dtype=torch.float32, device="cuda")
     y_all = torch.empty((M_ROWS, N_DIM), dtype=torch.float32, device="cuda") if world > 1 else None
 
+    # N > 1: by default the all-gather is fused into the GEMV (peer stores + step flags, no collective in the
+    # step); --gather nccl keeps the kernel + NCCL all-gather form.
+    fused = world > 1 and args.gather == "fused"
+    pg = None
+    if fused:
+        from laplace_b200.shard import PeerGather
+        pg = PeerGather(L, shards, M_ROWS)
+
     def step(i):
         c = i % N_COPIES
+        if fused:
+            # every GEMV kernel confirms the previous step's slices before it sends its own; the wait for the
+            # last step of a chain is enqueued by finish()
+            pg.gemm(x, copies[c], TYPE_Q4_K, K_DIM, device._stream())
+            return
         device.gemm(x, copies[c], TYPE_Q4_K, M_ROWS, K_DIM, n_loc, y=y_loc[c])
         if world > 1:
             shards.gather(y_loc[c], y_all)
 
+    def finish():
+        if fused:
+            pg.wait(device._stream())
+
     for i in range(warmup):
         step(i)
+    finish()
     device.sync()
     # self-check: copy c holds copy 0's rows rotated by 16c, so its output is copy 0's output rotated
-    y0 = y_loc[0].cpu().numpy()
-    for c in range(1, min(N_COPIES, warmup)):
-        assert np.array_equal(np.roll(y0, c * 16, axis=-1), y_loc[c].cpu().numpy()), "rotated weight copies disagree"
+    if not fused:
+        y0 = y_loc[0].cpu().numpy()
+        for c in range(1, min(N_COPIES, warmup)):
+            assert np.array_equal(np.roll(y0, c * 16, axis=-1), y_loc[c].cpu().numpy()), "rotated weight copies disagree"
+    else:
+        y_all = pg.slot(warmup & 1).clone()              # step numbers start at 1: warm-up step `warmup` is the last one
+        for c in range(N_COPIES):                        # y_loc is still needed by the host-pointer leg's check
+            device.gemm(x, copies[c], TYPE_Q4_K, M_ROWS, K_DIM, n_loc, y=y_loc[c])
+        device.sync()
     if world > 1:
         # the gathered result must be what one GPU computes over the whole matrix (last warm-up step's copy)
         c_last = (warmup - 1) % N_COPIES
@@ -214,6 +238,7 @@ def gpu_arm(args):
             with torch.cuda.graph(graph, stream=s):
                 for i in range(steps):
                     step(i)
+                finish()
         torch.cuda.current_stream().wait_stream(s)
 
     def barrier():
@@ -246,6 +271,7 @@ def gpu_arm(args):
         else:
             for i in range(steps):
                 step(i)
+            finish()
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
@@ -303,11 +329,13 @@ def gpu_arm(args):
             "config": {"workload": WORKLOAD, "weights": "seeded N(0,0.02^2), reference test packer (Q4_K, 144 B / 256)",
                        "activations": "seeded N(0,1), quantized per 32 inside the kernel",
                        "l2": f"{N_COPIES} rotating weight copies ({N_COPIES * WEIGHT_BYTES // world >> 20} MiB per GPU) exceed the 126 MB L2",
-                       "parallelism": "single GPU" if world == 1 else f"N-split over {world} GPUs + NCCL all-gather of y",
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"N-split over {world} GPUs; all-gather fused into the GEMV (peer stores over NVLink + step flags; each kernel confirms the previous step, one bounded wait kernel closes the chain)"
+                           if fused else f"N-split over {world} GPUs + NCCL all-gather of y"),
                        "timing": f"CUDA events around {'one CUDA graph of ' if use_graph else ''}{steps} steps; median of {repeats} repeats; max over ranks"},
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "laplace_cuda_gemm with host x and y, synchronous, weights registered (resident) as at model load"},
-            "gpu_launches": steps if use_graph else int(launches_eager // max(repeats, 1)),
+            "gpu_launches": (steps + 1 if fused else steps) if use_graph else int(launches_eager // max(repeats, 1)),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved if achieved else value / world, "peak": peak, "unit": "GB/s",
                          "frac": (achieved if achieved else value / world) / peak, "traffic": None, "peak_source": peak_src,
@@ -328,6 +356,8 @@ def gpu_arm(args):
         # agree that every rank is done, and leave without running NCCL's destructors.
         del graph
         torch.cuda.synchronize()
+        if pg is not None:
+            pg.close()
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()
@@ -534,6 +564,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for short profiler runs)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 prefill leg")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch the steps eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N>1, gemv workload: how the output slices are combined")
     ap.add_argument("--workload", default="gemv", choices=["gemv", "moe"],
                     help="gemv: the headline Q4_K M=1 GEMV (+ prefill leg); moe: the expert matmuls of one MoE layer")
     args = ap.parse_args()

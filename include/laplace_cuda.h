@@ -162,6 +162,39 @@ int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uin
 int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t type,
                                   float* y, int M, int K, int N, void* stream);
 
+/* ---- fused all-gather for the row-split (tensor-parallel) decode matmul ---------------
+ * No reference counterpart (the reference is single-device). With a weight matrix split
+ * along N over `world` GPUs, every GPU's GEMV stores its slice of y straight into EVERY
+ * GPU's full-width result buffer through peer-mapped pointers (coalesced NVLink stores from the
+ * kernel's own epilogue, no fence on the kernel's critical path). A step's slices are announced
+ * (flag [rank] of every GPU raised to the step number) by the NEXT gemm_allgather kernel's
+ * prologue, or by laplace_cuda_allgather_wait_dev, which closes a chain of steps: it announces the
+ * current step and waits (bounded) until all `world` flags of this GPU have reached it; the full y
+ * of step s is then in slot (s & 1) of this GPU's buffer. A kernel stores step s only after it has
+ * seen every GPU's step s - 1, so a consumer that runs after step s + 1's kernel may read step s
+ * without the wait call. Replaces "GEMV + ncclAllGather" for decode, where the collective's latency
+ * is 2-3x the kernel.
+ *
+ * Memory: each GPU allocates one buffer with laplace_cuda_peer_alloc (zeroed; returns a 64-byte
+ * IPC handle to pass to the other processes by any host channel) and opens the others' with
+ * laplace_cuda_peer_open. Layout is up to the caller; the calls take pointers:
+ *   peer_y[r]     GPU r's result area, float [2][M][n_total]
+ *   peer_flags[r] GPU r's flag array, int [world]
+ *   step_counter  this GPU's int, done_counter this GPU's unsigned (both start at 0)
+ * Steps are counted on the device, so the calls can be replayed from a CUDA graph. Every GPU must
+ * issue the same sequence of steps. A wait that gives up (a peer never arrived) surfaces as
+ * LAPLACE_ERR_TIMEOUT from laplace_cuda_sync(); nothing spins forever. M <= 8. */
+int laplace_cuda_peer_alloc(size_t bytes, void** dev_ptr, unsigned char* handle64);
+int laplace_cuda_peer_open(const unsigned char* handle64, void** dev_ptr);
+int laplace_cuda_peer_close(void* dev_ptr);
+int laplace_cuda_peer_free(void* dev_ptr);
+int laplace_cuda_gemm_allgather_dev(const float* x, const uint8_t* w, uint32_t type,
+                                    float* const* peer_y, int* const* peer_flags,
+                                    int* step_counter, unsigned* done_counter,
+                                    int rank, int world, int row_begin, int n_total,
+                                    int M, int K, int n_local, void* stream);
+int laplace_cuda_allgather_wait_dev(int* const* peer_flags, int* step_counter, int rank, int world, void* stream);
+
 /* The activation quantizer on its own (src/matmul_simd.cpp:348-427).
  * Outputs, all device memory, M rows: q int8 [M][K]; d fp32 [M][K/32];
  * sum fp32 [M][K/32] (= d * (sum_lo + sum_hi)); isum int16 [M][K/32][2]

@@ -26,6 +26,12 @@ SYMBOLS = {
     "laplace_cuda_moe_gemv_dev": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_moe_grouped_dev": (_i, [_vp, _vp, _u32, _vp, _vp, _i, _i, _vp, _i, _i, _vp]),
     "laplace_cuda_moe_ffn_dev": (_i, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "laplace_cuda_peer_alloc": (_i, [_sz, C.POINTER(_vp), _vp]),
+    "laplace_cuda_peer_open": (_i, [_vp, C.POINTER(_vp)]),
+    "laplace_cuda_peer_close": (_i, [_vp]),
+    "laplace_cuda_peer_free": (_i, [_vp]),
+    "laplace_cuda_gemm_allgather_dev": (_i, [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "laplace_cuda_allgather_wait_dev": (_i, [_vp, _vp, _i, _i, _vp]),
     "laplace_cuda_quantize_act_dev": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "laplace_cuda_debug_blocksums_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_last_path": (_i, []),

@@ -376,6 +376,85 @@ int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uin
                           hidden, inter, activation, out, h_out, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
 }
 
+/* ---- fused all-gather of a row-split decode matmul over peer memory ---- */
+
+int laplace_cuda_peer_alloc(size_t bytes, void** dev_ptr, unsigned char* handle64) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!dev_ptr || !handle64 || bytes == 0) return fail(LAPLACE_ERR_ARG, "peer_alloc: bad argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    void* p = nullptr;
+    if ((rc = cuda_check(cudaMalloc(&p, bytes), "cudaMalloc peer buffer"))) return rc;
+    if ((rc = cuda_check(cudaMemset(p, 0, bytes), "cudaMemset peer buffer")) ||
+        (rc = cuda_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize"))) { cudaFree(p); return rc; }   // zeroed before anyone maps it
+    cudaIpcMemHandle_t h;
+    if ((rc = cuda_check(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle"))) { cudaFree(p); return rc; }
+    std::memcpy(handle64, &h, 64);
+    *dev_ptr = p;
+    return LAPLACE_OK;
+}
+
+int laplace_cuda_peer_open(const unsigned char* handle64, void** dev_ptr) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!dev_ptr || !handle64) return fail(LAPLACE_ERR_ARG, "peer_open: bad argument");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    if ((rc = cuda_check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle"))) return rc;
+    *dev_ptr = p;
+    return LAPLACE_OK;
+}
+
+int laplace_cuda_peer_close(void* dev_ptr) {
+    return dev_ptr ? cuda_check(cudaIpcCloseMemHandle(dev_ptr), "cudaIpcCloseMemHandle") : LAPLACE_OK;
+}
+
+int laplace_cuda_peer_free(void* dev_ptr) {
+    return dev_ptr ? cuda_check(cudaFree(dev_ptr), "cudaFree peer buffer") : LAPLACE_OK;
+}
+
+int laplace_cuda_gemm_allgather_dev(const float* x, const uint8_t* w, uint32_t type,
+                                    float* const* peer_y, int* const* peer_flags, int* step_counter,
+                                    unsigned* done_counter, int rank, int world, int row_begin, int n_total,
+                                    int M, int K, int n_local, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !w || !peer_y || !peer_flags || !step_counter || !done_counter)
+        return fail(LAPLACE_ERR_ARG, "gemm_allgather: null pointer");
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || M < 1 || M > 8 || n_local <= 0 || K <= 0 ||
+        K % block_elems(type) || row_begin < 0 || row_begin + n_local > n_total)
+        return fail(LAPLACE_ERR_ARG, "gemm_allgather: rank=%d world=%d M=%d K=%d rows [%d,%d) of %d", rank, world, M, K,
+                    row_begin, row_begin + n_local, n_total);
+    PeerOut po{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_y[r] || !peer_flags[r]) return fail(LAPLACE_ERR_ARG, "gemm_allgather: null peer pointer %d", r);
+        po.y[r] = peer_y[r];
+        po.flags[r] = peer_flags[r];
+    }
+    po.step_ctr = step_counter; po.done_ctr = done_counter;
+    po.world = world; po.rank = rank; po.ld = n_total; po.col0 = row_begin;
+    GemvArgs a{};
+    a.x = x; a.w = w; a.y = nullptr; a.type = type; a.M = M; a.K = K; a.N = n_local; a.n_seg = 1;
+    a.peers = &po;
+    return launch_gemv_stream(a, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_allgather_wait_dev(int* const* peer_flags, int* step_counter, int rank, int world, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!peer_flags || !step_counter || world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return fail(LAPLACE_ERR_ARG, "allgather_wait: bad argument");
+    PeerOut po{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_flags[r]) return fail(LAPLACE_ERR_ARG, "allgather_wait: null peer pointer %d", r);
+        po.flags[r] = peer_flags[r];
+    }
+    po.step_ctr = step_counter; po.world = world; po.rank = rank;
+    return launch_allgather_wait(po, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
 int laplace_cuda_quantize_act_dev(const float* x, int M, int K, int8_t* q, float* d, float* sum, int16_t* isum,
                                   void* stream) {
     int rc = require_ready();

@@ -54,7 +54,7 @@ int  cuda_check(cudaError_t e, const char* what);
 
 // Device status codes written to Context::d_err by bounded waits.
 enum : int { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_DRAIN = 3,
-             DEV_TIMEOUT_MMA = 4, DEV_TIMEOUT_TMEM = 5, DEV_BAD_INDEX = 6 };
+             DEV_TIMEOUT_MMA = 4, DEV_TIMEOUT_TMEM = 5, DEV_BAD_INDEX = 6, DEV_TIMEOUT_PEER = 7 };
 
 // ---- kernel launchers (one per .cu) ----------------------------------------
 struct GemvArgs {
@@ -67,8 +67,22 @@ struct GemvArgs {
     int            K, N;
     int            n_seg;        // 1, or the number of selected experts
     int            per_seg_x;    // 0: all segments read rows [0,M); 1: segment s reads row s (M == 1)
+    const struct PeerOut* peers; // nullptr, or: results go to every GPU's buffer instead of y (fused all-gather)
+};
+// Fused all-gather of a row-split matmul: every GPU stores its slice of the result straight into
+// every GPU's full-width buffer through peer-mapped pointers, then raises a per-source step flag.
+constexpr int MAX_PEERS = 8;
+struct PeerOut {
+    float*    y[MAX_PEERS];      // every GPU's result buffer: [2 slots][M][ld], slot = step & 1
+    int*      flags[MAX_PEERS];  // every GPU's flag array [world]; GPU r writes entry r of each
+    int*      step_ctr;          // this GPU's step counter
+    unsigned* done_ctr;          // this GPU's "CTAs that have read the step counter" count (zero between launches)
+    int       world, rank;
+    int       ld;                // columns of the full result (N of the whole matrix)
+    int       col0;              // first column of this GPU's slice
 };
 int launch_gemv_stream(const GemvArgs& a, cudaStream_t st);
+int launch_allgather_wait(const PeerOut& po, cudaStream_t st);
 
 // Tensor-core prefill GEMM (lp_gemm_tc.cu). Uses library-owned scratch for the quantized activations.
 bool gemm_tc_supports(uint32_t type, int M, int K, int N);

@@ -53,7 +53,18 @@ struct KParams {
     uint32_t       off_isum, off_ring;
     int            rows_q, rows_r;  // CTA b owns rows_q (+1 if b < rows_r) rows
     int            pdl;
+    PeerOut        peers;           // peers.world == 0: results go to y
+    uint32_t       off_stage;       // fused all-gather: this CTA's results are staged here, [M][stage_ld] floats
+    int            stage_ld;
 };
+
+// Result store: to y, or (fused all-gather) into this CTA's staging area in shared memory, from where
+// one warp writes the CTA's contiguous column range to every GPU in 128-byte coalesced stores.
+// `row` counts result rows, `col` the column inside this GPU's slice, `cta_col0` the CTA's first column.
+__device__ __forceinline__ void store_result(const KParams& p, uint8_t* smem, int cta_col0, size_t row, int col, float v) {
+    if (p.peers.world == 0) p.y[row * p.N + col] = v;
+    else reinterpret_cast<float*>(smem + p.off_stage)[row * p.stage_ld + (col - cta_col0)] = v;
+}
 
 // Shared-memory map: [0, 64 * warps) slot barriers (per consumer warp: 4 "full"
 // then 4 "empty"), then activations, half-sums, the rings.
@@ -401,6 +412,23 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
     // -------------------------------- consumer warps --------------------------------
     // x may be produced, and y read, by the kernel before this one in the stream.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Fused all-gather: this launch is step (counter + 1); its results go to slot (step & 1) of every buffer.
+    // The previous launch's slices are complete now (grid dependency), so one thread of the grid announces
+    // them: flag [rank] of every GPU is raised to the previous step. Nothing else in the kernel waits for that.
+    size_t peer_slot_off = 0;
+    int peer_prev = 0;
+    if (p.peers.world) {
+        peer_prev = *reinterpret_cast<volatile const int*>(p.peers.step_ctr);
+        peer_slot_off = static_cast<size_t>((peer_prev + 1) & 1) * static_cast<size_t>(p.n_seg) * M * p.peers.ld;
+        if (threadIdx.x == 0) {
+            asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" :: "l"(p.peers.done_ctr) : "memory");   // "this CTA has read the counter"
+            if (blockIdx.x == gridDim.x - 1) {
+                __threadfence_system();
+                for (int r = 0; r < p.peers.world; ++r)
+                    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" :: "l"(p.peers.flags[r] + p.peers.rank), "r"(peer_prev) : "memory");
+            }
+        }
+    }
     // (1) quantize the activations into shared memory while the rings fill. Each
     // group of 8 lanes owns 32-value blocks grp, grp + GROUPS, ...
     {
@@ -478,7 +506,7 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
                     a0 += __shfl_xor_sync(0xffffffffu, a0, o);
                     a1 += __shfl_xor_sync(0xffffffffu, a1, o);
                 }
-                if (lane == 0) { p.y[un.j + r] = a0; p.y[un.j + r + 1] = a1; }
+                if (lane == 0) { store_result(p, smem, g0, 0, un.j + r, a0); store_result(p, smem, g0, 0, un.j + r + 1, a1); }
             }
             if (r < un.nrows) {
                 float a0 = 0.f;
@@ -489,7 +517,7 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-                if (lane == 0) p.y[un.j + r] = a0;
+                if (lane == 0) store_result(p, smem, g0, 0, un.j + r, a0);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(warp, slot));                  // slot may be refilled
@@ -517,7 +545,7 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
                         float a = acc[m];
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                        if (lane == 0) p.y[(static_cast<size_t>(un.seg) * M + m) * p.N + un.j + r] = a;
+                        if (lane == 0) store_result(p, smem, g0, static_cast<size_t>(un.seg) * M + m, un.j + r, a);
                         acc[m] = 0.f;
                     }
                 }
@@ -527,7 +555,64 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
         }
     }
     if (!ok && lane == 0) report_status(p.err, DEV_TIMEOUT_FULL);   // the producer drains the copies
+    if (p.peers.world) {
+        // Fused all-gather, sending: the CTA's results are staged in shared memory; warp 0 writes the CTA's
+        // contiguous column range to every GPU in coalesced stores. No fence follows: the stores are
+        // complete when the grid is, and the NEXT launch (or the closing wait kernel) announces them.
+        named_bar_sync(3, WARPS * 32);                          // all consumer warps of this CTA have staged their results
+        if (warp == 0) {
+            // Before this step's slices go out, the previous step must be complete HERE: every GPU stores
+            // step s only after it has seen all of step s - 1, which is what makes two slots enough.
+            if (lane < p.peers.world) {
+                bool seen = false;
+                for (uint32_t it = 0; it < (1u << 21) && !seen; ++it) {
+                    int v;
+                    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.peers.flags[p.peers.rank] + lane) : "memory");
+                    seen = v - peer_prev >= 0;
+                    if (!seen && it > 64) __nanosleep(100);
+                }
+                if (!seen) report_status(p.err, DEV_TIMEOUT_PEER);
+            }
+            __syncwarp();
+            const float* stage = reinterpret_cast<const float*>(smem + p.off_stage);
+            for (int m = 0; m < M; ++m) {
+                const size_t at = peer_slot_off + static_cast<size_t>(m) * p.peers.ld + p.peers.col0 + g0;
+                for (int i = lane; i < cta_rows; i += 32) {
+                    const float v = stage[m * p.stage_ld + i];
+                    for (int r = 0; r < p.peers.world; ++r) p.peers.y[r][at + i] = v;
+                }
+            }
+            // one thread of the grid advances the step counter, once every CTA has read the old value
+            if (blockIdx.x == 0 && lane == 0) {
+                bool all_read = false;
+                for (uint32_t it = 0; it < (1u << 21) && !all_read; ++it)
+                    all_read = *reinterpret_cast<volatile unsigned*>(p.peers.done_ctr) == gridDim.x;
+                if (!all_read) report_status(p.err, DEV_TIMEOUT_PEER);
+                *reinterpret_cast<volatile unsigned*>(p.peers.done_ctr) = 0u;
+                *reinterpret_cast<volatile int*>(p.peers.step_ctr) = peer_prev + 1;
+            }
+        }
+    }
     if (p.pdl == 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Closes a chain of fused all-gather steps: announces this GPU's slices of the current step (complete,
+// since this kernel runs after the GEMV that stored them) to every GPU, then waits (bounded) until every
+// source's flag has reached this GPU's step: all slices of the step are in this GPU's buffer.
+// One warp; lane r talks to GPU r.
+__global__ void allgather_wait_kernel(PeerOut po, int* err) {
+    const int r = threadIdx.x;
+    if (r >= po.world) return;
+    const int step = *reinterpret_cast<volatile const int*>(po.step_ctr);
+    __threadfence_system();
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" :: "l"(po.flags[r] + po.rank), "r"(step) : "memory");
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(po.flags[po.rank] + r) : "memory");
+        if (v - step >= 0) return;
+        if (it > 64) __nanosleep(100);
+    }
+    report_status(err, DEV_TIMEOUT_PEER);
 }
 
 template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false>
@@ -599,6 +684,10 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     const int warps = resident ? 16 : (a.M <= 2 ? 24 : 16);   // consumer warps; one more warp issues the copies
     KParams p{};
     p.x = a.x; p.w = a.w; p.y = a.y; p.expert_idx = a.expert_idx; p.err = c.d_err;
+    if (a.peers) {
+        if (a.peers->world < 1 || a.peers->world > MAX_PEERS) return fail(LAPLACE_ERR_ARG, "gemv: %d peers", a.peers->world);
+        p.peers = *a.peers;
+    }
     p.K = a.K; p.N = a.N; p.n_seg = a.n_seg; p.per_seg_x = a.per_seg_x;
     p.act_rows = a.per_seg_x ? a.n_seg : a.M;
     p.rb = static_cast<uint32_t>(row_bytes(a.type, a.K));
@@ -618,7 +707,16 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     const int items_per_block = a.type == LAPLACE_TYPE_Q4_K ? 2 : (a.type == LAPLACE_TYPE_Q6_K ? 4 : 1);
     const uint32_t bpb = static_cast<uint32_t>(block_bytes(a.type));
     const int n_blocks = a.K / epb;
-    const size_t budget = c.smem_optin;
+    // fused all-gather: room for this CTA's results ([M][rows per CTA] floats) at the end of shared memory
+    size_t stage_bytes = 0;
+    if (a.peers) {
+        if (a.n_seg != 1) return fail(LAPLACE_ERR_ARG, "gemv: the fused all-gather takes a plain matrix");
+        const int cta_rows_max = (a.N + c.sm_count - 1) / c.sm_count + warps * 8;     // grid may be smaller than the SM count
+        p.stage_ld = (cta_rows_max + 3) & ~3;
+        stage_bytes = (static_cast<size_t>(a.M) * p.stage_ld * sizeof(float) + 127) & ~size_t(127);
+        if (stage_bytes > 48 * 1024) return fail(LAPLACE_ERR_LIMIT, "gemv: N=%d is too wide for the fused all-gather", a.N);
+    }
+    const size_t budget = c.smem_optin - stage_bytes;
     if (p.off_ring + static_cast<size_t>(warps) * 2 * 256 > budget)
         return fail(LAPLACE_ERR_LIMIT, "gemv: M=%d K=%d: the quantized activations do not fit shared memory", a.M, a.K);
     const size_t per_warp = ((budget - p.off_ring) / warps) & ~size_t(15);
@@ -655,7 +753,8 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     }
     // spare room: a deeper ring
     while (p.n_slots < MAX_SLOTS && static_cast<size_t>(p.n_slots + 1) * p.slot_bytes <= per_warp) p.n_slots++;
-    const size_t smem = p.off_ring + static_cast<size_t>(warps) * p.n_slots * p.slot_bytes;
+    size_t smem = p.off_ring + static_cast<size_t>(warps) * p.n_slots * p.slot_bytes;
+    if (stage_bytes) { smem = (smem + 127) & ~size_t(127); p.off_stage = static_cast<uint32_t>(smem); smem += stage_bytes; }
     if (resident && (p.n_slices != 1 || slack != 0))
         return fail(LAPLACE_ERR_STATE, "gemv: internal planning error (resident path needs whole aligned rows)");
 
@@ -667,6 +766,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     { static int mode = -1; if (mode < 0) { const char* e = getenv("LAPLACE_PDL"); mode = e ? atoi(e) : 2; } p.pdl = mode; }
     p.rows_q = static_cast<int>(total_rows / grid);
     p.rows_r = static_cast<int>(total_rows % grid);
+    if (a.peers && p.rows_q + 1 > p.stage_ld) return fail(LAPLACE_ERR_STATE, "gemv: internal planning error (staging area too small)");
 
     cudaError_t e;
     switch (a.type) {
@@ -679,6 +779,14 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     c.launches++;
     c.last_path = 1;
     return cuda_check(e, "gemv_stream launch");
+}
+
+int launch_allgather_wait(const PeerOut& po, cudaStream_t st) {
+    Context& c = ctx();
+    if (po.world < 1 || po.world > MAX_PEERS) return fail(LAPLACE_ERR_ARG, "allgather_wait: %d peers", po.world);
+    allgather_wait_kernel<<<1, 32, 0, st>>>(po, c.d_err);
+    c.launches++;
+    return cuda_check(cudaGetLastError(), "allgather_wait launch");
 }
 
 }  // namespace lp

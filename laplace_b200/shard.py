@@ -59,3 +59,83 @@ class RowShards:
             if e > b:
                 y_full[:, b:e].copy_(self._recv[r * need: r * need + M * (e - b)].view(M, e - b))
         return y_full
+
+
+class _DevMem:
+    """A raw device allocation exposed to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+class PeerGather:
+    """The fused all-gather of a row-split decode matmul (laplace_cuda_gemm_allgather_dev): every rank's GEMV
+    stores its slice into every rank's result buffer over NVLink and raises a step flag; `wait` makes the
+    stream wait for all slices. One buffer per rank, shared with the other processes by CUDA IPC handles that
+    travel over the process group (host plumbing only; no collective runs in a step)."""
+
+    def __init__(self, lib, shards: RowShards, M: int, group=None):
+        self.L, self.sh, self.M, self.group = lib, shards, int(M), group
+        world, rank, N = shards.world, shards.rank, shards.N
+        self.y_bytes = (2 * self.M * N * 4 + 255) & ~255
+        self.total = self.y_bytes + 512                       # + flags[world] (256 B) + step / done counters (256 B)
+        ptr = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        self._check(lib.laplace_cuda_peer_alloc(self.total, C.byref(ptr), handle))
+        self.own = ptr.value
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, bytes(handle), group=group)
+        self.bases, self._opened = [], []
+        for r in range(world):
+            if r == rank:
+                self.bases.append(self.own)
+                continue
+            q = C.c_void_p()
+            hb = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+            self._check(lib.laplace_cuda_peer_open(hb, C.byref(q)))
+            self.bases.append(q.value)
+            self._opened.append(q.value)
+        self.peer_y = (C.c_void_p * world)(*self.bases)
+        self.peer_flags = (C.c_void_p * world)(*[b + self.y_bytes for b in self.bases])
+        self.flags = self.own + self.y_bytes
+        self.step_ctr = self.own + self.y_bytes + 256
+        self.done_ctr = self.step_ctr + 4
+        self.steps = 0
+        if world > 1:
+            dist.barrier(group=group)                         # every rank has mapped every buffer
+
+    def _check(self, rc):
+        if rc:
+            raise RuntimeError(f"laplace_cuda error {rc}: {self.L.laplace_cuda_last_error().decode()}")
+
+    def gemm(self, x: torch.Tensor, w: torch.Tensor, t: int, K: int, stream: int) -> None:
+        """Enqueues this rank's slice of y = W x; results land in slot (step & 1) of every rank's buffer."""
+        sh = self.sh
+        self._check(self.L.laplace_cuda_gemm_allgather_dev(x.data_ptr(), w.data_ptr(), int(t), self.peer_y, self.peer_flags,
+                                                          self.step_ctr, self.done_ctr, sh.rank, sh.world, sh.begin, sh.N,
+                                                          self.M, K, sh.n_loc, stream))
+        self.steps += 1
+
+    def wait(self, stream: int) -> None:
+        """Closes a chain of steps: announces this rank's slices of the current step and enqueues the
+        (bounded) wait for all ranks' slices."""
+        self._check(self.L.laplace_cuda_allgather_wait_dev(self.peer_flags, self.step_ctr, self.sh.rank, self.sh.world, stream))
+
+    def slot(self, which: int) -> torch.Tensor:
+        """Slot `which` (0 or 1) of this rank's result buffer as a [M, N] tensor; step s lands in slot s & 1."""
+        mem = _DevMem(self.own + (which & 1) * self.M * self.sh.N * 4, (self.M, self.sh.N), "<f4")
+        return torch.as_tensor(mem, device="cuda")
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        if self.sh.world > 1:
+            dist.barrier(group=self.group)                    # nobody stores into a buffer that is being unmapped
+        for q in self._opened:
+            self.L.laplace_cuda_peer_close(q)
+        self._opened = []
+        if self.sh.world > 1:
+            dist.barrier(group=self.group)
+        if self.own:
+            self.L.laplace_cuda_peer_free(self.own)
+            self.own = 0

@@ -177,3 +177,30 @@ def test_long_rows_many_activation_rows(oracle, t):
     x = synth.normal_f32(1501, (M, K))
     y = run_dev(t, x, w, M, K, N)
     check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1), f"{t.name} M=8 K=14336")
+
+
+@pytest.mark.parametrize("t,M,K,N", [(GGMLType.Q4_K, 1, 4096, 512), (GGMLType.Q6_K, 4, 512, 96), (GGMLType.Q4_0, 8, 256, 40)])
+def test_fused_allgather_on_one_gpu(oracle, t, M, K, N):
+    """The fused all-gather path with a world of one: results go through the peer-store epilogue into the
+    step's slot of the rank's own buffer, the step flag is raised and the wait kernel sees it."""
+    import torch
+    from laplace_b200 import device
+    from laplace_b200.shard import PeerGather, RowShards
+    L = device.lib()
+    w = synth.weights(t, K, N, seed=700 + M, how="random")
+    wd = device.upload_weights(w)
+    pg = PeerGather(L, RowShards(L, N, 0, 1), M)
+    try:
+        for step in range(1, 4):
+            x = synth.normal_f32(710 + step, (M, K))
+            xd = torch.from_numpy(x).cuda()
+            pg.gemm(xd, wd, t, K, device._stream())
+            pg.wait(device._stream())
+            device.sync()
+            got = pg.slot(step & 1).cpu().numpy()
+            want = device.gemm(xd, wd, t, M, K, N)
+            device.sync()
+            assert np.array_equal(got, want.cpu().numpy()), f"step {step}"
+            check_close(got, oracle.gemm(x, w, t, M, K, N, mode=1), f"fused all-gather {t.name} step {step}")
+    finally:
+        pg.close()
