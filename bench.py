@@ -180,9 +180,20 @@ def gpu_arm(args):
     # step); --gather nccl keeps the kernel + NCCL all-gather form.
     fused = world > 1 and args.gather == "fused"
     pg = None
+    gather_note = None
     if fused:
+        # peer buffers by CUDA IPC; if any rank cannot map its peers, every rank falls back to the NCCL form
         from laplace_b200.shard import PeerGather
-        pg = PeerGather(L, shards, M_ROWS)
+        ok_here = 1
+        try:
+            pg = PeerGather(L, shards, M_ROWS)
+        except Exception as exc:                    # noqa: BLE001 - reported in the JSON line
+            ok_here, gather_note = 0, f"fused all-gather unavailable ({exc}); NCCL all-gather used"
+        flag = torch.tensor([ok_here], device="cuda", dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            fused, pg = False, None
+            gather_note = gather_note or "fused all-gather unavailable on another rank; NCCL all-gather used"
 
     def step(i):
         c = i % N_COPIES
@@ -335,6 +346,7 @@ def gpu_arm(args):
                        "timing": f"CUDA events around {'one CUDA graph of ' if use_graph else ''}{steps} steps; median of {repeats} repeats; max over ranks"},
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "laplace_cuda_gemm with host x and y, synchronous, weights registered (resident) as at model load"},
+            **({"note": gather_note} if gather_note else {}),
             "gpu_launches": (steps + 1 if fused else steps) if use_graph else int(launches_eager // max(repeats, 1)),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved if achieved else value / world, "peak": peak, "unit": "GB/s",
