@@ -327,6 +327,7 @@ def gpu_arm(args):
         assert np.array_equal(yh, y_loc[last].cpu().numpy()), "host-pointer result differs from the device-pointer result"
         lb.matmul_unregister_weights(region)
     prefill = prefill_leg(device, synth, torch) if (world == 1 and not args.no_prefill) else None
+    decode = decode_leg(device, synth, torch) if (world == 1 and not args.no_prefill) else None
     clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
@@ -362,6 +363,8 @@ def gpu_arm(args):
                                     "sample": f"{n} full GEMVs of the same workload (~{n * dt:.0f} s), all host threads"}
         if prefill:
             line["prefill"] = prefill
+        if decode:
+            line["decode_shapes"] = decode
         print(json.dumps(line))
     if world > 1:
         # A communicator that captured graphs still reference cannot be torn down cleanly: drop the graph,
@@ -375,6 +378,53 @@ def gpu_arm(args):
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+def decode_leg(device, synth, torch):
+    """The other decode shapes BASELINE.json names (configs[0..2]), reported beside the headline: packed-weight GB/s
+    of one GEMV, weights rotated over enough copies to exceed L2, a CUDA graph of 40 launches timed with CUDA events
+    (best of 5 replays)."""
+    shapes = [("Q4_0", 2, 1, 4096, 4096), ("Q4_K", 12, 1, 4096, 4096), ("Q4_K", 12, 1, 4096, 1024),
+              ("Q6_K", 14, 1, 14336, 4096), ("Q6_K", 14, 1, 4096, 14336), ("Q8_0", 8, 1, 4096, 14336),
+              ("Q4_K", 12, 2, 4096, 14336), ("Q4_K", 12, 4, 4096, 14336), ("Q4_K", 12, 8, 4096, 14336)]
+    geom = {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210)}
+    out = []
+    for name, t, M, K, N in shapes:
+        eb, bb = geom[t]
+        wbytes = N * (K // eb) * bb
+        n_copies = max(2, min(24, -(-(160 << 20) // wbytes)))
+        base = synth.weights(t, K, N, seed=1500 + t + N, how="random")
+        ws = [device.upload_weights(np.roll(base, 16 * i, axis=0)) for i in range(n_copies)]
+        x = torch.from_numpy(synth.normal_f32(1600 + M, (M, K))).cuda()
+        y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+        for i in range(n_copies):
+            device.gemm(x, ws[i], t, M, K, N, y=y)
+        torch.cuda.synchronize()
+        iters = 40
+        g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                for i in range(iters):
+                    device.gemm(x, ws[i % n_copies], t, M, K, N, y=y)
+        torch.cuda.current_stream().wait_stream(st)
+        g.replay()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        us = best / iters * 1e3
+        del g
+        out.append({"type": name, "M": M, "K": K, "N": N, "us": round(us, 2), "weight_gbs": round(wbytes / us / 1e3, 1)})
+        del ws
+    device.sync()
+    return out
 
 
 def prefill_leg(device, synth, torch):

@@ -150,6 +150,38 @@ __device__ __forceinline__ float q4k_dot(const Q4KWts& w, const Q4KAct& x) {
     }
     return a - am;
 }
+// The same for two activation rows at once: the masked nibbles and the scale products of the
+// weight item are formed once and meet both rows (each result is bit-identical to q4k_dot's).
+__device__ __forceinline__ float2 q4k_dot2(const Q4KWts& w, const Q4KAct& x, const Q4KAct& z) {
+    float a = 0.f, am = 0.f, b = 0.f, bm = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        int u1a = 0, u1b = 0, u2a = 0, u2b = 0, v1a = 0, v1b = 0, v2a = 0, v2b = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const uint32_t l0 = w.q[8 * c + t] & 0x0f0f0f0fu, l1 = w.q[8 * c + 4 + t] & 0x0f0f0f0fu;
+            const uint32_t h0 = w.q[8 * c + t] & 0xf0f0f0f0u, h1 = w.q[8 * c + 4 + t] & 0xf0f0f0f0u;
+            u1a = dp4a_us(l0, x.q[16 * c + t], u1a);      v1a = dp4a_us(l0, z.q[16 * c + t], v1a);
+            u1b = dp4a_us(l1, x.q[16 * c + 4 + t], u1b);  v1b = dp4a_us(l1, z.q[16 * c + 4 + t], v1b);
+            u2a = dp4a_us(h0, x.q[16 * c + 8 + t], u2a);  v2a = dp4a_us(h0, z.q[16 * c + 8 + t], v2a);
+            u2b = dp4a_us(h1, x.q[16 * c + 12 + t], u2b); v2b = dp4a_us(h1, z.q[16 * c + 12 + t], v2b);
+        }
+        const int u1 = u1a + u1b, u2 = (u2a + u2b) >> 4, v1 = v1a + v1b, v2 = (v2a + v2b) >> 4;
+        const float d1 = w.d * static_cast<float>((w.sc4 >> (16 * c)) & 0xff);
+        const float d2 = w.d * static_cast<float>((w.sc4 >> (16 * c + 8)) & 0xff);
+        const float m1 = w.dmin * static_cast<float>((w.mn4 >> (16 * c)) & 0xff);
+        const float m2 = w.dmin * static_cast<float>((w.mn4 >> (16 * c + 8)) & 0xff);
+        a = fmaf(d1 * x.d[2 * c], static_cast<float>(u1), a);
+        a = fmaf(d2 * x.d[2 * c + 1], static_cast<float>(u2), a);
+        am = fmaf(m1, x.s[2 * c], am);
+        am = fmaf(m2, x.s[2 * c + 1], am);
+        b = fmaf(d1 * z.d[2 * c], static_cast<float>(v1), b);
+        b = fmaf(d2 * z.d[2 * c + 1], static_cast<float>(v2), b);
+        bm = fmaf(m1, z.s[2 * c], bm);
+        bm = fmaf(m2, z.s[2 * c + 1], bm);
+    }
+    return make_float2(a - am, b - bm);
+}
 template <> struct Traits<LAPLACE_TYPE_Q4_K> {
     static constexpr int ITEMS_PER_BLOCK = 2;
     template <int M>
@@ -318,9 +350,13 @@ struct Walker {
 // themselves, several warps issue in parallel, and copies are made as large as
 // the ring allows (two 2.3 KB rows per copy move ~1.5x faster than one).
 //
-// RESIDENT: M == 1, Q4_K, one item per lane and row (K <= 4096): the lane's
-// activation record never changes, so it lives in registers for the whole
-// kernel and the row loop reads only weights from shared memory.
+// RESIDENT: Q4_K, one item per lane and row (K <= 4096): the lane's activation
+// record never changes, so it lives in registers for the whole kernel and the
+// row loop reads only weights from shared memory. With M > 1 a warp keeps TWO
+// activation rows in registers and G = ceil(M / 2) warps form a group that
+// shares one ring: every warp of the group meets every weight row of the group
+// with its own two rows of x, so shared memory serves each weight row G times
+// instead of each activation row once per weight row.
 template <uint32_t TYPE, int M, int WARPS, bool RESIDENT>
 __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_kernel(const KParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -334,8 +370,12 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
     const int bx = static_cast<int>(blockIdx.x);
     const int g0 = bx * p.rows_q + (bx < p.rows_r ? bx : p.rows_r);
     const int cta_rows = p.rows_q + (bx < p.rows_r ? 1 : 0);
+    constexpr int RW = (RESIDENT && M > 1) ? 2 : 1;          // activation rows a warp keeps in registers
+    constexpr int G = RESIDENT ? (M + RW - 1) / RW : 1;       // warps per ring group
+    constexpr int GROUPS = WARPS / G;
+    static_assert(WARPS % G == 0, "consumer warps must split into whole groups");
     auto walker_of = [&](int w) {
-        const int q = cta_rows / WARPS, r = cta_rows - q * WARPS;
+        const int q = cta_rows / GROUPS, r = cta_rows - q * GROUPS;
         Walker wk;
         wk.g = g0 + w * q + (w < r ? w : r);
         wk.g_end = wk.g + q + (w < r ? 1 : 0);
@@ -348,11 +388,11 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
 
     if (warp >= WARPS) {
         // ------------------------------ producer warps -----------------------------
-        constexpr int PER = (WARPS + PRODUCER_WARPS - 1) / PRODUCER_WARPS;   // consumers served per producer warp
+        constexpr int PER = (GROUPS + PRODUCER_WARPS - 1) / PRODUCER_WARPS;   // ring groups served per producer warp
         const int w = (warp - WARPS) * PER + lane;
-        const bool serving = lane < PER && w < WARPS;
+        const bool serving = lane < PER && w < GROUPS;
         if (serving) {
-            for (int s = 0; s < p.n_slots; ++s) { mbar_init(bar_full(w, s), 1); mbar_init(bar_empty(w, s), 1); }
+            for (int s = 0; s < p.n_slots; ++s) { mbar_init(bar_full(w, s), 1); mbar_init(bar_empty(w, s), G); }
         }
         fence_barrier_init();
         __syncwarp();
@@ -474,22 +514,56 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
         named_bar_sync(1, (WARPS + PRODUCER_WARPS) * 32);      // all consumers + the producer's arrive
     }
 
-    // (2) stream this warp's units
-    Walker wk = walker_of(warp);
+    // (2) stream this warp's (group's) units
+    const int grp = warp / G, sub = warp - grp * G;
+    Walker wk = walker_of(grp);
     Unit un;
-    const uint32_t ring = ring_of(warp);
+    const uint32_t ring = ring_of(grp);
     const int n_items = (p.K / block_elems(TYPE)) * Traits<TYPE>::ITEMS_PER_BLOCK;
     const uint32_t act0 = sbase + OFF_ACT, isum0 = sbase + p.off_isum;
     int u = 0;
     bool ok = true;
 
-    if constexpr (RESIDENT) {
+    if constexpr (RESIDENT && M > 1) {
+        // two activation rows in registers; every weight row of the group's ring meets both
+        const int m0 = 2 * sub, m1 = (m0 + 1 < M) ? m0 + 1 : m0;
+        const bool has_item = lane < n_items;
+        Q4KAct x0, x1;
+        if (has_item) {
+            q4k_load_act(act0 + m0 * p.act_row_stride + lane * REC_BYTES, x0);
+            q4k_load_act(act0 + m1 * p.act_row_stride + lane * REC_BYTES, x1);
+        }
+        for (; wk.next(p, un); ++u) {
+            const int slot = u % p.n_slots;
+            if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
+            for (int r = 0; r < un.nrows; ++r) {
+                float2 a = make_float2(0.f, 0.f);
+                if (has_item) {
+                    Q4KWts w0;
+                    q4k_load_wts(base + r * p.rb, lane, w0);
+                    a = q4k_dot2(w0, x0, x1);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    a.x += __shfl_xor_sync(0xffffffffu, a.x, o);
+                    a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
+                }
+                if (lane == 0) {
+                    store_result(p, smem, g0, m0, un.j + r, a.x);
+                    if (m1 != m0) store_result(p, smem, g0, m1, un.j + r, a.y);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty(grp, slot));                   // one of the group's G releases
+        }
+    } else if constexpr (RESIDENT) {
         Q4KAct xr;
         const bool has_item = lane < n_items;
         if (has_item) q4k_load_act(act0 + lane * REC_BYTES, xr);
         for (; wk.next(p, un); ++u) {
             const int slot = u % p.n_slots;
-            if (!mbar_wait_bounded(bar_full(warp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
             const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
             int r = 0;
             for (; r + 2 <= un.nrows; r += 2) {                   // two rows at a time: independent chains
@@ -520,7 +594,7 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
                 if (lane == 0) store_result(p, smem, g0, 0, un.j + r, a0);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty(warp, slot));                  // slot may be refilled
+            if (lane == 0) mbar_arrive(bar_empty(grp, slot));                  // slot may be refilled
         }
     } else {
         float acc[M];
@@ -528,7 +602,7 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
         for (int m = 0; m < M; ++m) acc[m] = 0.f;
         for (; wk.next(p, un); ++u) {
             const int slot = u % p.n_slots;
-            if (!mbar_wait_bounded(bar_full(warp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
             const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.w + un.src_off) & 15u);
             const int arow = p.per_seg_x ? un.seg : 0;
             const uint32_t act = act0 + arow * p.act_row_stride, isum = isum0 + arow * p.isum_row_stride;
@@ -551,7 +625,7 @@ __global__ void __launch_bounds__((WARPS + PRODUCER_WARPS) * 32, 1) gemv_stream_
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty(warp, slot));                  // slot may be refilled
+            if (lane == 0) mbar_arrive(bar_empty(grp, slot));                  // slot may be refilled
         }
     }
     if (!ok && lane == 0) report_status(p.err, DEV_TIMEOUT_FULL);   // the producer drains the copies
@@ -644,6 +718,8 @@ cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st
     return cudaLaunchKernelEx(&cfg, k, p);
 }
 
+constexpr int RESIDENT_WARPS = 12;      // consumer warps of the register-resident path with M > 1: splits into groups of 1, 2, 3 or 4
+
 template <uint32_t TYPE>
 cudaError_t launch_typed(int M, bool resident, const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     switch (M) {
@@ -652,13 +728,16 @@ cudaError_t launch_typed(int M, bool resident, const KParams& p, dim3 grid, size
                 if (resident) return launch_one<TYPE, 1, 16, true>(p, grid, smem, st);
             }
             return launch_one<TYPE, 1, 24>(p, grid, smem, st);
-        case 2: return launch_one<TYPE, 2, 24>(p, grid, smem, st);
-        case 3: return launch_one<TYPE, 3, 16>(p, grid, smem, st);
-        case 4: return launch_one<TYPE, 4, 16>(p, grid, smem, st);
-        case 5: return launch_one<TYPE, 5, 16>(p, grid, smem, st);
-        case 6: return launch_one<TYPE, 6, 16>(p, grid, smem, st);
-        case 7: return launch_one<TYPE, 7, 16>(p, grid, smem, st);
-        case 8: return launch_one<TYPE, 8, 16>(p, grid, smem, st);
+#define LP_RESIDENT_CASE(m) \
+        if constexpr (TYPE == LAPLACE_TYPE_Q4_K) { if (resident) return launch_one<TYPE, m, RESIDENT_WARPS, true>(p, grid, smem, st); }
+        case 2: LP_RESIDENT_CASE(2) return launch_one<TYPE, 2, 24>(p, grid, smem, st);
+        case 3: LP_RESIDENT_CASE(3) return launch_one<TYPE, 3, 16>(p, grid, smem, st);
+        case 4: LP_RESIDENT_CASE(4) return launch_one<TYPE, 4, 16>(p, grid, smem, st);
+        case 5: LP_RESIDENT_CASE(5) return launch_one<TYPE, 5, 16>(p, grid, smem, st);
+        case 6: LP_RESIDENT_CASE(6) return launch_one<TYPE, 6, 16>(p, grid, smem, st);
+        case 7: LP_RESIDENT_CASE(7) return launch_one<TYPE, 7, 16>(p, grid, smem, st);
+        case 8: LP_RESIDENT_CASE(8) return launch_one<TYPE, 8, 16>(p, grid, smem, st);
+#undef LP_RESIDENT_CASE
         default: return cudaErrorInvalidValue;
     }
 }
@@ -679,9 +758,11 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
 
     // Register-resident activations (see the kernel): Q4_K, one activation row,
     // a plain matrix whose 16-byte-aligned rows hold at most 32 items.
-    const bool resident = a.type == LAPLACE_TYPE_Q4_K && a.M == 1 && !a.expert_idx && a.K <= 4096 &&
+    const bool resident = a.type == LAPLACE_TYPE_Q4_K && !a.expert_idx && a.K <= 4096 &&
                           (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
-    const int warps = resident ? 16 : (a.M <= 2 ? 24 : 16);   // consumer warps; one more warp issues the copies
+    // consumer warps, and how many of them share one ring (resident path with M > 1: ceil(M / 2))
+    const int cwarps = resident ? (a.M == 1 ? 16 : RESIDENT_WARPS) : (a.M <= 2 ? 24 : 16);
+    const int warps = (resident && a.M > 1) ? cwarps / ((a.M + 1) / 2) : cwarps;      // ring groups
     KParams p{};
     p.x = a.x; p.w = a.w; p.y = a.y; p.expert_idx = a.expert_idx; p.err = c.d_err;
     if (a.peers) {
@@ -729,7 +810,8 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     p.rows_per_unit = 1;
     if (p.rb + slack <= slot_cap(2)) {
         // whole rows; as many per copy as give ~4.6 KB copies and still leave two slots (three if possible)
-        int R = static_cast<int>((4608 + p.rb / 2) / p.rb);
+        // (a group of G warps drains a unit G times as fast as one warp: proportionally larger copies)
+        int R = static_cast<int>((4608 * static_cast<size_t>(cwarps / warps) + p.rb / 2) / p.rb);
         if (R < 1) R = 1;
         if (R > 8) R = 8;
         while (R > 1 && static_cast<size_t>(R) * p.rb + slack > slot_cap(3)) --R;
