@@ -351,7 +351,9 @@ def gpu_arm(args):
             "gpu_launches": (steps + 1 if fused else steps) if use_graph else int(launches_eager // max(repeats, 1)),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved if achieved else value / world, "peak": peak, "unit": "GB/s",
-                         "frac": (achieved if achieved else value / world) / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": (achieved if achieved else value / world) / peak,
+                         "traffic": 33095936 if world == 1 else None,      # dram read + write bytes of one launch, from the ncu capture under profiles/
+                         "peak_source": peak_src,
                          "kernel": "gemv_stream_kernel<Q4_K, M=1>", "algorithmic_bytes_per_launch": WEIGHT_BYTES // world},
         }
         if world == 1 and not args.no_cpu:
