@@ -84,3 +84,56 @@ def test_expert_parallel_layer(tmp_path, world):
     for r in range(world):
         err = float((tmp_path / f"r{r}.txt").read_text())
         assert err < 1e-5, f"rank {r}: max-abs / RMS = {err}"
+
+
+def _oracle_ffn(orc):
+    """The fused-FFN callable of ExpertParallelMoE played by the oracle (per-pair gate/up, SwiGLU, down, weighted sum)."""
+    def ffn(x, w_gate_up, w_down, idx_local, top_w, n_experts, hidden, inter, out):
+        xe, idx, wts = x.numpy(), idx_local.numpy(), top_w.numpy()
+        wg, wd = w_gate_up.numpy(), w_down.numpy()
+        out.zero_()
+        for tok in range(idx.shape[0]):
+            acc = np.zeros(hidden, dtype=np.float32)
+            for j in range(idx.shape[1]):
+                e = int(idx[tok, j])
+                if e < 0:
+                    continue
+                gu = orc.moe_gemv(xe[tok], wg, T_TYPE, np.array([e], np.int32), hidden, 2 * inter, multi=False, mode=0)
+                h = silu_mul(torch.from_numpy(gu), inter).numpy()
+                dn = orc.moe_gemv(h, wd, T_TYPE, np.array([e], np.int32), inter, hidden, multi=True, mode=0)[0]
+                acc += wts[tok, j] * dn
+            out[tok] = torch.from_numpy(acc)
+        return out
+    return ffn
+
+
+def _worker_fused(rank, world, port, E, k, H, I, T_loc, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        orc = Oracle()
+        T = T_loc * world
+        w_gu, w_dn, x, idx, wts = _inputs(E, k, H, I, T)
+        E_loc = E // world
+        gu_rows, dn_rows = 2 * I * E_loc, H * E_loc
+        layer = ExpertParallelMoE(torch.from_numpy(w_gu[rank * gu_rows:(rank + 1) * gu_rows].copy()),
+                                  torch.from_numpy(w_dn[rank * dn_rows:(rank + 1) * dn_rows].copy()),
+                                  E, k, H, I, None, rank, world, fused_ffn=_oracle_ffn(orc))
+        sl = slice(rank * T_loc, (rank + 1) * T_loc)
+        out = layer.forward(torch.from_numpy(x[sl].copy()), torch.from_numpy(idx[sl].copy()), torch.from_numpy(wts[sl].copy()))
+        want = _reference_layer(orc, w_gu, w_dn, x, idx, wts, E, k, H, I)[sl]
+        err = float(np.abs(out.numpy() - want).max() / (np.sqrt((want ** 2).mean()) + 1e-30))
+        with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
+            f.write(f"{err}\n")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_expert_parallel_layer_fused_path(tmp_path, world):
+    """The same layer through the fused-FFN hook (what bench.py --workload moe uses on GPUs)."""
+    E, k, H, I, T_loc = 8, 3, 256, 256, 3
+    mp.spawn(_worker_fused, args=(world, _free_port(), E, k, H, I, T_loc, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        err = float((tmp_path / f"r{r}.txt").read_text())
+        assert err < 1e-5, f"rank {r}: max-abs / RMS = {err}"
