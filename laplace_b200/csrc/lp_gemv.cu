@@ -411,7 +411,9 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         // memory pipeline before any bulk copy, and the bulk of the copies only
         // once x has arrived - a load issued behind ~220 KB of queued copy
         // traffic waits microseconds for its turn.
-        named_bar_sync(2, (WARPS + PW) * 32);   // consumers are issuing their loads of x
+        // (Paired mode: the copies start at once, while the consumers may still be waiting for the previous launch;
+        // by the time x is loaded the first copies have landed.)
+        if constexpr (OCC == 1) named_bar_sync(2, (WARPS + PW) * 32);   // consumers are issuing their loads of x
         const uint32_t ring = ring_of(w);
         Walker wk = walker_of(serving ? w : 0);
         if (!serving) wk.g_end = wk.g;
@@ -494,7 +496,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         };
         // Tell the producers first: they need ~100 cycles from here to their
         // first copy, the loads below are issued within a few.
-        asm volatile("bar.arrive 2, %0;" :: "r"((WARPS + PW) * 32) : "memory");
+        if constexpr (OCC == 1) asm volatile("bar.arrive 2, %0;" :: "r"((WARPS + PW) * 32) : "memory");
         float4 nxt = load_x(grp), nxt2 = load_x(grp + GROUPS);                   // two rounds ahead
         // whole warps iterate together so the 8-lane shuffles stay converged
         for (int base = 0; base < nblk; base += GROUPS) {
@@ -715,11 +717,6 @@ cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st
             if (e != cudaSuccess) return e;
         }
         configured = true;
-        if (getenv("LAPLACE_OCC_DEBUG")) {
-            int nb = -1;
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k, (WARPS + PW) * 32, smem);
-            fprintf(stderr, "occupancy: %d blocks/SM at %zu bytes, %d threads\n", nb, smem, (WARPS + PW) * 32);
-        }
     }
     // Programmatic dependent launch: this grid may start (and prefetch weights,
     // which no earlier kernel writes) while the previous kernel in the stream
