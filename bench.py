@@ -326,7 +326,7 @@ def gpu_arm(args):
         last = (n_e2e - 1) % 4
         assert np.array_equal(yh, y_loc[last].cpu().numpy()), "host-pointer result differs from the device-pointer result"
         lb.matmul_unregister_weights(region)
-    prefill = prefill_leg(device, synth, torch) if (world == 1 and not args.no_prefill) else None
+    prefill = prefill_leg(device, synth, torch, rank, world, dist) if not args.no_prefill else None
     decode = decode_leg(device, synth, torch) if (world == 1 and not args.no_prefill) else None
     clocks = sampler.stop() if rank == 0 else None
 
@@ -429,9 +429,12 @@ def decode_leg(device, synth, torch):
     return out
 
 
-def prefill_leg(device, synth, torch):
+def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
     """Second half of the metric: the seven projections of one Llama-3-8B decoder layer at M=512
-    (BASELINE.json configs[3]); q/k/v/o/gate/up are Q4_K, down is Q6_K. Reported beside the headline."""
+    (BASELINE.json configs[3]); q/k/v/o/gate/up are Q4_K, down is Q6_K. Reported beside the headline.
+    With more than one GPU every projection is split along N (laplace_cuda_nsplit) and the [512, N/G] slices are
+    all-gathered with NCCL inside the timed region; times are the maximum over ranks."""
+    from laplace_b200.shard import RowShards
     M = 512
     projs = [("q", 12, 4096, 4096), ("k", 12, 4096, 1024), ("v", 12, 4096, 1024), ("o", 12, 4096, 4096),
              ("gate", 12, 4096, 14336), ("up", 12, 4096, 14336), ("down", 14, 14336, 4096)]
@@ -439,20 +442,35 @@ def prefill_leg(device, synth, torch):
     out, total_ms, total_ops = {}, 0.0, 0.0
     xs = {K: torch.from_numpy(synth.normal_f32(2004 + K, (M, K))).cuda() for K in (4096, 14336)}
     for name, t, K, N in projs:
-        w = device.upload_weights(synth.weights(t, K, N, seed=1040 + N + K, how="random"))
-        y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+        sh = RowShards(L, N, rank, world)
+        w_np = synth.weights(t, K, N, seed=1040 + N + K, how="random")
+        w = device.upload_weights(np.ascontiguousarray(sh.slice_rows(w_np)))
+        y = torch.empty((M, sh.n_loc), dtype=torch.float32, device="cuda")
+        y_full = torch.empty((M, N), dtype=torch.float32, device="cuda") if world > 1 else None
+
+        def run():
+            device.gemm(xs[K], w, t, M, K, sh.n_loc, y=y)
+            if world > 1:
+                sh.gather(y, y_full)
+
         for _ in range(3):
-            device.gemm(xs[K], w, t, M, K, N, y=y)
+            run()
         path = L.laplace_cuda_last_path()
         iters = 10 if path == 2 else 3
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(iters):
-            device.gemm(xs[K], w, t, M, K, N, y=y)
+            run()
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / iters
+        if world > 1:
+            tt = torch.tensor([ms], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
         ops = 2.0 * M * N * K
         out[name] = {"type": "Q4_K" if t == 12 else "Q6_K", "K": K, "N": N, "ms": ms, "tops": ops / ms / 1e9,
                      "kernel": "tcgen05 kind::f16 (exact block sums)" if path == 2 else "8-row streaming passes (no tensor-core kernel for this type yet)"}
@@ -466,10 +484,12 @@ def prefill_leg(device, synth, torch):
         peak_bf16 = float(json.loads(p.read_text())["bf16_tflops"])
     q4k_ops = sum(2.0 * M * N * K for _, t, K, N in projs if t == 12)
     q4k_ms = sum(out[n]["ms"] for n, t, _, _ in projs if t == 12)
-    return {"workload": "Llama-3-8B decoder layer, 7 projections, M=512 tokens (223.34 Gop)", "ms_per_layer": total_ms,
+    return {"workload": "Llama-3-8B decoder layer, 7 projections, M=512 tokens (223.34 Gop)" +
+                        ("" if world == 1 else f", N-split over {world} GPUs + NCCL all-gather of the [512, N/{world}] slices"),
+            "ms_per_layer": total_ms,
             "tops": total_ops / total_ms / 1e9, "q4k_only_tops": q4k_ops / q4k_ms / 1e9,
-            "roofline": {"bound": "tensor", "achieved": q4k_ops / q4k_ms / 1e9, "peak": peak_bf16, "unit": "TFLOP/s",
-                         "frac": q4k_ops / q4k_ms / 1e9 / peak_bf16,
+            "roofline": {"bound": "tensor", "achieved": q4k_ops / q4k_ms / 1e9 / world, "peak": peak_bf16, "unit": "TFLOP/s (per GPU)",
+                         "frac": q4k_ops / q4k_ms / 1e9 / peak_bf16 / world,
                          "note": "the Q4_K kernel issues fp16 MMAs (exact integer block sums in fp32), so the measured bf16/fp16 "
                                  "cuBLAS burst peak is its tensor roofline; against the derived int8 figure (2x) the fraction halves"},
             "projections": out}
