@@ -49,6 +49,14 @@ class RowShards:
         if M == 1 and self.even and y_full.is_contiguous() and y_loc.is_contiguous():
             dist.all_gather_into_tensor(y_full.view(-1), y_loc.view(-1), group=group)
             return y_full
+        if self.even and y_loc.is_contiguous() and y_full.is_contiguous():
+            # equal slices: gather [G, M, n_loc] and interleave the ranks' columns with one strided copy
+            need = M * self.n_max
+            if self._recv is None or self._recv.numel() != self.world * need or self._recv.device != y_loc.device:
+                self._recv = torch.empty(self.world * need, dtype=y_loc.dtype, device=y_loc.device)
+            dist.all_gather_into_tensor(self._recv, y_loc.view(-1), group=group)
+            y_full.view(M, self.world, self.n_max).copy_(self._recv.view(self.world, M, self.n_max).permute(1, 0, 2))
+            return y_full
         need = M * self.n_max
         if self._send is None or self._send.numel() != need or self._send.device != y_loc.device:
             self._send = torch.zeros(need, dtype=y_loc.dtype, device=y_loc.device)

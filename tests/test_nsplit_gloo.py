@@ -43,7 +43,7 @@ def _worker(rank, world, port, t, M, K, N, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,M,N", [(2, 1, 256), (2, 3, 272), (3, 1, 80), (2, 1, 8), (4, 2, 1000)])
+@pytest.mark.parametrize("world,M,N", [(2, 1, 256), (2, 3, 272), (2, 3, 256), (4, 5, 512), (3, 1, 80), (2, 1, 8), (4, 2, 1000)])
 def test_split_and_gather(tmp_path, world, M, N):
     t, K = int(ggml.GGMLType.Q4_K), 512
     mp.spawn(_worker, args=(world, _free_port(), t, M, K, N, str(tmp_path)), nprocs=world, join=True)
