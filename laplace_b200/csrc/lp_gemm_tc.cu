@@ -516,7 +516,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     for (int gq = 0; gq < 4; ++gq) {
                         float gv[16], av[16];
                         tc_ld16(t_g + 16 * gq, gv);
-                        if (!first) tc_ld16(t_acc + 16 * gq, av);
+                        if (!first) {
+                            tc_ld16(t_acc + 16 * gq, av);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) av[c] = 0.f;
+                        }
                         tc_wait_ld();
                         if (gq == 3) {
                             // G is in registers: the MMA may overwrite it with the next super-block's
@@ -525,12 +530,16 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                             if (lane == 0) mbar_arrive(sbase + BAR_GT_EMPTY);
                         }
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const float part = (c & 1) ? acc2[8 * gq + (c >> 1)].y : acc2[8 * gq + (c >> 1)].x;
-                            float a = first ? 0.f : av[c];
-                            a = fmaf(__uint_as_float(lds32(dtab + (16 * gq + c) * 4)), part, a);
-                            a = fmaf(-__uint_as_float(lds32(mtab + (16 * gq + c) * 4)), gv[c], a);
-                            av[c] = a;
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            const uint4 d4 = lds128(dtab + (16 * gq + 4 * c4) * 4), m4 = lds128(mtab + (16 * gq + 4 * c4) * 4);
+                            const float dd[4] = {__uint_as_float(d4.x), __uint_as_float(d4.y), __uint_as_float(d4.z), __uint_as_float(d4.w)};
+                            const float mm[4] = {__uint_as_float(m4.x), __uint_as_float(m4.y), __uint_as_float(m4.z), __uint_as_float(m4.w)};
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const int c = 4 * c4 + k;
+                                const float part = (c & 1) ? acc2[8 * gq + (c >> 1)].y : acc2[8 * gq + (c >> 1)].x;
+                                av[c] = fmaf(-mm[k], gv[c], fmaf(dd[k], part, av[c]));
+                            }
                         }
                         tc_st16(t_acc + 16 * gq, av);
                     }

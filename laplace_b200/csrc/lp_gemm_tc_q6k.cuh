@@ -298,11 +298,20 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     if (!first) {
                         tc_ld16(t_acc + 16 * gq, av);
                         tc_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) av[c] = 0.f;
                     }
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const float part = (c & 1) ? acc2[8 * gq + (c >> 1)].y : acc2[8 * gq + (c >> 1)].x;
-                        av[c] = fmaf(__uint_as_float(lds32(dtab + (16 * gq + c) * 4)), part, first ? 0.f : av[c]);
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const uint4 d4 = lds128(dtab + (16 * gq + 4 * c4) * 4);
+                        const float dd[4] = {__uint_as_float(d4.x), __uint_as_float(d4.y), __uint_as_float(d4.z), __uint_as_float(d4.w)};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int c = 4 * c4 + k;
+                            const float part = (c & 1) ? acc2[8 * gq + (c >> 1)].y : acc2[8 * gq + (c >> 1)].x;
+                            av[c] = fmaf(dd[k], part, av[c]);
+                        }
                     }
                     tc_st16(t_acc + 16 * gq, av);
                 }
