@@ -550,7 +550,33 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
             const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
-            for (int r = 0; r < un.nrows; ++r) {
+            int r = 0;
+            for (; r + 2 <= un.nrows; r += 2) {                   // two weight rows at a time: independent chains
+                float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+                if (has_item) {
+                    Q4KWts w0, w1;
+                    q4k_load_wts(base + r * p.rb, lane, w0);
+                    q4k_load_wts(base + (r + 1) * p.rb, lane, w1);
+                    a = q4k_dot2(w0, x0, x1);
+                    b = q4k_dot2(w1, x0, x1);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    a.x += __shfl_xor_sync(0xffffffffu, a.x, o);
+                    a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
+                    b.x += __shfl_xor_sync(0xffffffffu, b.x, o);
+                    b.y += __shfl_xor_sync(0xffffffffu, b.y, o);
+                }
+                if (lane == 0) {
+                    store_result(p, smem, g0, m0, un.j + r, a.x);
+                    store_result(p, smem, g0, m0, un.j + r + 1, b.x);
+                    if (m1 != m0) {
+                        store_result(p, smem, g0, m1, un.j + r, a.y);
+                        store_result(p, smem, g0, m1, un.j + r + 1, b.y);
+                    }
+                }
+            }
+            if (r < un.nrows) {
                 float2 a = make_float2(0.f, 0.f);
                 if (has_item) {
                     Q4KWts w0;
@@ -736,6 +762,7 @@ cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st
 }
 
 constexpr int PAIRED_WARPS = 7, PAIRED_PRODUCER_WARPS = 2;     // per CTA in paired mode: two such CTAs per SM
+constexpr int RESIDENT_PRODUCER_WARPS = 2;  // 448 threads per CTA leave 146 registers per thread: two weight rows in flight
 constexpr int RESIDENT_WARPS = 12;      // consumer warps of the register-resident path with M > 1: splits into groups of 1, 2, 3 or 4
 
 template <uint32_t TYPE>
@@ -747,7 +774,7 @@ cudaError_t launch_typed(int M, bool resident, const KParams& p, dim3 grid, size
             }
             return launch_one<TYPE, 1, 24>(p, grid, smem, st);
 #define LP_RESIDENT_CASE(m) \
-        if constexpr (TYPE == LAPLACE_TYPE_Q4_K) { if (resident) return launch_one<TYPE, m, RESIDENT_WARPS, true>(p, grid, smem, st); }
+        if constexpr (TYPE == LAPLACE_TYPE_Q4_K) { if (resident) return launch_one<TYPE, m, RESIDENT_WARPS, true, RESIDENT_PRODUCER_WARPS>(p, grid, smem, st); }
         case 2: LP_RESIDENT_CASE(2) return launch_one<TYPE, 2, 24>(p, grid, smem, st);
         case 3: LP_RESIDENT_CASE(3) return launch_one<TYPE, 3, 16>(p, grid, smem, st);
         case 4: LP_RESIDENT_CASE(4) return launch_one<TYPE, 4, 16>(p, grid, smem, st);
