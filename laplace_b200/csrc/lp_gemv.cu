@@ -766,12 +766,13 @@ constexpr int RESIDENT_PRODUCER_WARPS = 2;  // 448 threads per CTA leave 146 reg
 constexpr int RESIDENT_WARPS = 12;      // consumer warps of the register-resident path with M > 1: splits into groups of 1, 2, 3 or 4
 
 template <uint32_t TYPE>
-cudaError_t launch_typed(int M, bool resident, const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_typed(int M, bool resident, bool long_rows, const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     switch (M) {
         case 1:
             if constexpr (TYPE == LAPLACE_TYPE_Q4_K) {
                 if (resident) return launch_one<TYPE, 1, 16, true>(p, grid, smem, st);
             }
+            if (long_rows) return launch_one<TYPE, 1, 16>(p, grid, smem, st);
             return launch_one<TYPE, 1, 24>(p, grid, smem, st);
 #define LP_RESIDENT_CASE(m) \
         if constexpr (TYPE == LAPLACE_TYPE_Q4_K) { if (resident) return launch_one<TYPE, m, RESIDENT_WARPS, true, RESIDENT_PRODUCER_WARPS>(p, grid, smem, st); }
@@ -819,7 +820,10 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     }
     const bool paired = paired_env && resident && a.M == 1 && !a.peers &&
                         static_cast<long long>(a.N) >= 2LL * c.sm_count * PAIRED_WARPS * 4;
-    const int cwarps = paired ? PAIRED_WARPS : resident ? (a.M == 1 ? 16 : RESIDENT_WARPS) : (a.M <= 2 ? 24 : 16);
+    // one activation row, rows of 8 KB and more (K = 14336): fewer consumer warps, so that a warp's ring slot
+    // holds a K-slice of a few KB (small bulk copies are issue-bound)
+    const bool long_rows = !resident && a.M == 1 && row_bytes(a.type, a.K) >= 8192;
+    const int cwarps = paired ? PAIRED_WARPS : resident ? (a.M == 1 ? 16 : RESIDENT_WARPS) : (a.M <= 2 && !long_rows ? 24 : 16);
     const int warps = (resident && a.M > 1) ? cwarps / ((a.M + 1) / 2) : cwarps;      // ring groups
     KParams p{};
     p.x = a.x; p.w = a.w; p.y = a.y; p.expert_idx = a.expert_idx; p.err = c.d_err;
@@ -925,11 +929,11 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     switch (a.type) {
         case LAPLACE_TYPE_Q4_K:
             if (paired) e = launch_one<LAPLACE_TYPE_Q4_K, 1, PAIRED_WARPS, true, PAIRED_PRODUCER_WARPS, 2>(p, dim3(grid), smem, st);
-            else e = launch_typed<LAPLACE_TYPE_Q4_K>(a.M, resident, p, dim3(grid), smem, st);
+            else e = launch_typed<LAPLACE_TYPE_Q4_K>(a.M, resident, long_rows, p, dim3(grid), smem, st);
             break;
-        case LAPLACE_TYPE_Q6_K: e = launch_typed<LAPLACE_TYPE_Q6_K>(a.M, false, p, dim3(grid), smem, st); break;
-        case LAPLACE_TYPE_Q4_0: e = launch_typed<LAPLACE_TYPE_Q4_0>(a.M, false, p, dim3(grid), smem, st); break;
-        case LAPLACE_TYPE_Q8_0: e = launch_typed<LAPLACE_TYPE_Q8_0>(a.M, false, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q6_K: e = launch_typed<LAPLACE_TYPE_Q6_K>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q4_0: e = launch_typed<LAPLACE_TYPE_Q4_0>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q8_0: e = launch_typed<LAPLACE_TYPE_Q8_0>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
         default: return LAPLACE_UNSUPPORTED;
     }
     c.launches++;
