@@ -97,3 +97,26 @@ def test_q6k_prefill_extreme_blocks(oracle, ql, qh, sc):
     assert path == 2
     ref = oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS)
     assert np.allclose(y, ref, rtol=2e-5, atol=0.0), np.abs(y - ref).max()
+
+
+@pytest.mark.parametrize("t,K", [(GGMLType.Q4_K, 512), (GGMLType.Q6_K, 2048)])
+def test_prefill_special_rows(oracle, t, K):
+    """Edge rows of a prefill call: an all-zero activation row (scale 0, result exactly 0), a row with one NaN
+    (the block's scale becomes NaN as with NEON FMAX, so the whole output row is NaN), a row of a single
+    large value; the other rows are unaffected."""
+    M, N = 40, 128
+    w = synth.weights(t, K, N, seed=95, how="random")
+    x = synth.normal_f32(96, (M, K))
+    x[3] = 0.0
+    x[7, 33] = np.nan
+    x[11] = 0.0
+    x[11, K - 1] = 1.0e6
+    y, path = run_dev(t, x, w, M, K, N)
+    assert path == 2
+    ref = oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS)
+    assert np.isnan(ref[7]).all() and np.isnan(y[7]).all()
+    assert not y[3].any() and not ref[3].any()
+    keep = np.ones(M, dtype=bool)
+    keep[7] = False
+    check_close(y[keep], ref[keep], f"{t.name} prefill with special rows")
+    assert np.allclose(y[11], ref[11], rtol=2e-6, atol=0.0)
