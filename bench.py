@@ -363,6 +363,26 @@ def gpu_arm(args):
             dt = time_cpu(run, n, 1)
             line["cpu_baseline"] = {"value": WEIGHT_BYTES / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
                                     "sample": f"{n} full GEMVs of the same workload (~{n * dt:.0f} s), all host threads"}
+            # beside it: the same code on one thread, and the int8 (Q8-activation) restatement whose numbers the
+            # GPU path has to match, on all threads; short samples
+            try:
+                from tests import oracle_lib
+                from laplace_b200 import synth as _synth
+                extra = {}
+                wq = _synth.weights(TYPE_Q4_K, K_DIM, N_DIM, seed=1012, how="ref")
+                xq = _synth.normal_f32(2001, (M_ROWS, K_DIM))
+                if kind == "reference":
+                    ref = oracle_lib.Reference()
+                    ref.set_threads(1)
+                    one = time_cpu(lambda: ref.matmul_rows(xq, wq, TYPE_Q4_K, M_ROWS, K_DIM, N_DIM), 20, 1)
+                    ref.set_threads(cores)
+                    extra["reference_1_thread_gbs"] = WEIGHT_BYTES / one / 1e9
+                orc = oracle_lib.Oracle()
+                t8 = time_cpu(lambda: orc.gemm(xq, wq, TYPE_Q4_K, M_ROWS, K_DIM, N_DIM, mode=0, threads=cores), 100, 2)
+                extra["int8_restatement_all_threads_gbs"] = WEIGHT_BYTES / t8 / 1e9
+                line["cpu_baseline"]["also"] = extra
+            except Exception as exc:      # noqa: BLE001 - the extra figures are optional
+                line["cpu_baseline"]["also"] = {"error": str(exc)}
         if prefill:
             line["prefill"] = prefill
         if decode:
