@@ -552,7 +552,7 @@ def moe_arm(args):
     for l in range(n_layers):
         layers.append(ExpertParallelMoE(device.upload_weights(np.roll(gu_np, l * 16, axis=0)),
                                         device.upload_weights(np.roll(dn_np, l * 16, axis=0)),
-                                        E, TOPK, H, I, None, rank, world, fused_ffn=ffn))
+                                        E, TOPK, H, I, None, rank, world, fused_ffn=ffn, device_exchange=True))
     idx_np, wts_np = seeded_routing(3200, T, E, TOPK)
     sl = slice(rank * T_loc, (rank + 1) * T_loc)
     x = torch.from_numpy(synth.normal_f32(3300, (T, H))[sl].copy()).cuda()
@@ -645,7 +645,7 @@ def moe_arm(args):
             "useful_tops": ops / (ms_step * 1e-3) / 1e12, "weight_gbs": wbytes / (ms_step * 1e-3) / 1e9,
             "e2e": {"value": T / dt, "unit": "tokens/s", "h2d_bytes_per_step": T_loc * (H * 4 + TOPK * 8), "d2h_bytes_per_step": T_loc * H * 4,
                     "how": "tokens and routing tables from pinned host memory, layer output copied back, eager launches"},
-            "gpu_launches": steps * 9, "clocks": clocks,
+            "gpu_launches": steps * (9 if world == 1 else 11), "clocks": clocks,
         }))
     if world > 1:
         del graph

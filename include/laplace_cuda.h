@@ -144,6 +144,18 @@ int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uin
                              int n_tokens, int top_k, int n_experts_total, int hidden, int inter, int activation,
                              float* out, float* h_out, void* stream);
 
+/* Exchange helpers of an expert-parallel MoE layer (no reference counterpart): one all-gather moves
+ * [x (hidden floats) | expert ids (top_k ints, bit pattern) | weights (top_k floats)] per token.
+ * pack builds this GPU's rows, [n_tokens][hidden + 2*top_k]; unpack splits gathered rows into
+ * x [n_tokens][hidden], top_w [n_tokens][top_k] and idx_local [n_tokens][top_k], where a global
+ * expert id e becomes e - expert_first if it lies in [expert_first, expert_first + expert_count)
+ * and -1 otherwise (the form laplace_cuda_moe_ffn_dev takes). Device pointers. */
+int laplace_cuda_moe_pack_dev(const float* x, const int* top_idx, const float* top_w,
+                              int n_tokens, int hidden, int top_k, float* packed, void* stream);
+int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, int top_k,
+                                int expert_first, int expert_count,
+                                float* x, int* idx_local, float* top_w, void* stream);
+
 /* Prefill GEMM (Q4_K, M > 8, K % 256 == 0) that allocates nothing. It has no counterpart in
  * the reference: it exists for hosts that must not touch the CUDA allocator on the request
  * path - serving processes whose own pools (KV cache, activations) already hold all HBM, so

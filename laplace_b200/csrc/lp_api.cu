@@ -376,6 +376,25 @@ int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uin
                           hidden, inter, activation, out, h_out, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
 }
 
+int laplace_cuda_moe_pack_dev(const float* x, const int* top_idx, const float* top_w, int n_tokens, int hidden, int top_k,
+                              float* packed, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!x || !top_idx || !top_w || !packed || n_tokens <= 0 || hidden <= 0 || top_k <= 0)
+        return fail(LAPLACE_ERR_ARG, "moe_pack: bad argument");
+    return launch_moe_pack(x, top_idx, top_w, n_tokens, hidden, top_k, packed, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, int top_k, int expert_first, int expert_count,
+                                float* x, int* idx_local, float* top_w, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!packed || !x || !idx_local || !top_w || n_tokens <= 0 || hidden <= 0 || top_k <= 0 || expert_count <= 0)
+        return fail(LAPLACE_ERR_ARG, "moe_unpack: bad argument");
+    return launch_moe_unpack(packed, n_tokens, hidden, top_k, expert_first, expert_count, x, idx_local, top_w,
+                             stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
 /* ---- fused all-gather of a row-split decode matmul over peer memory ---- */
 
 int laplace_cuda_peer_alloc(size_t bytes, void** dev_ptr, unsigned char* handle64) {

@@ -98,6 +98,9 @@ int  launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_d
                     const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
                     float* out, float* h_out, cudaStream_t st);
 void release_moe_ffn_scratch();
+int  launch_moe_pack(const float* x, const int* idx, const float* wts, int T, int H, int k, float* packed, cudaStream_t st);
+int  launch_moe_unpack(const float* packed, int T, int H, int k, int first, int count, float* x, int* idx_local, float* wts,
+                       cudaStream_t st);
 
 int launch_quantize_act(const float* x, int M, int K, int8_t* q, float* d, float* sum,
                         int16_t* isum, cudaStream_t st);

@@ -422,3 +422,63 @@ int launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_do
     c.last_path = 4;
     return cuda_check(cudaGetLastError(), "moe_combine launch");
 }
+
+
+// ---- exchange helpers of the expert-parallel layer ---------------------------------------
+// One all-gather moves [x | expert ids | weights] per token. pack builds a rank's send rows,
+// unpack splits the gathered rows and turns global expert ids into local ones (-1 = another GPU's).
+namespace {
+
+__global__ void moe_pack_kernel(const float* __restrict__ x, const int* __restrict__ idx, const float* __restrict__ wts,
+                                int T, int H, int k, float* __restrict__ packed) {
+    const int stride = H + 2 * k;
+    const long long total = static_cast<long long>(T) * stride;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / stride), c = static_cast<int>(i - static_cast<long long>(t) * stride);
+        float v;
+        if (c < H) v = x[static_cast<long long>(t) * H + c];
+        else if (c < H + k) v = __int_as_float(idx[t * k + (c - H)]);
+        else v = wts[t * k + (c - H - k)];
+        packed[i] = v;
+    }
+}
+
+__global__ void moe_unpack_kernel(const float* __restrict__ packed, int T, int H, int k, int first, int count,
+                                  float* __restrict__ x, int* __restrict__ idx_local, float* __restrict__ wts) {
+    const int stride = H + 2 * k;
+    const long long total = static_cast<long long>(T) * stride;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / stride), c = static_cast<int>(i - static_cast<long long>(t) * stride);
+        const float v = packed[i];
+        if (c < H) x[static_cast<long long>(t) * H + c] = v;
+        else if (c < H + k) {
+            const int e = __float_as_int(v) - first;
+            idx_local[t * k + (c - H)] = (e >= 0 && e < count) ? e : -1;
+        } else wts[t * k + (c - H - k)] = v;
+    }
+}
+
+}  // namespace
+
+int launch_moe_pack(const float* x, const int* idx, const float* wts, int T, int H, int k, float* packed, cudaStream_t st) {
+    Context& c = ctx();
+    const long long total = static_cast<long long>(T) * (H + 2 * k);
+    long long blocks = (total + 255) / 256;
+    if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
+    moe_pack_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(x, idx, wts, T, H, k, packed);
+    c.launches++;
+    return cuda_check(cudaGetLastError(), "moe_pack launch");
+}
+
+int launch_moe_unpack(const float* packed, int T, int H, int k, int first, int count, float* x, int* idx_local, float* wts,
+                      cudaStream_t st) {
+    Context& c = ctx();
+    const long long total = static_cast<long long>(T) * (H + 2 * k);
+    long long blocks = (total + 255) / 256;
+    if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
+    moe_unpack_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(packed, T, H, k, first, count, x, idx_local, wts);
+    c.launches++;
+    return cuda_check(cudaGetLastError(), "moe_unpack launch");
+}

@@ -122,6 +122,28 @@ def moe_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, t_ga
     return out
 
 
+def moe_pack(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, packed: torch.Tensor) -> torch.Tensor:
+    """[x | expert ids | weights] rows of this rank's tokens for the one all-gather of the expert-parallel layer."""
+    L = lib()
+    T, H = x.shape
+    k = top_idx.shape[1]
+    assert packed.shape == (T, H + 2 * k) and packed.is_contiguous() and x.is_contiguous()
+    assert top_idx.is_contiguous() and top_w.is_contiguous() and top_idx.dtype == torch.int32
+    _check(L, L.laplace_cuda_moe_pack_dev(x.data_ptr(), top_idx.data_ptr(), top_w.data_ptr(), T, H, k, packed.data_ptr(), _stream()))
+    return packed
+
+
+def moe_unpack(packed: torch.Tensor, hidden: int, top_k: int, expert_first: int, expert_count: int,
+               x: torch.Tensor, idx_local: torch.Tensor, top_w: torch.Tensor) -> None:
+    """Splits gathered rows into x, local expert ids (-1 = another rank's expert) and weights."""
+    L = lib()
+    T = packed.shape[0]
+    assert packed.is_contiguous() and packed.shape[1] == hidden + 2 * top_k
+    assert x.shape == (T, hidden) and idx_local.dtype == torch.int32 and idx_local.shape == (T, top_k) and top_w.shape == (T, top_k)
+    _check(L, L.laplace_cuda_moe_unpack_dev(packed.data_ptr(), T, hidden, top_k, expert_first, expert_count, x.data_ptr(),
+                                            idx_local.data_ptr(), top_w.data_ptr(), _stream()))
+
+
 def quantize_act(x: torch.Tensor, M: int, K: int):
     """Returns (q int8 [M,K], d f32 [M,K/32], sum f32 [M,K/32], isum int16 [M,K/32,2])."""
     L = lib()

@@ -38,7 +38,7 @@ class ExpertParallelMoE:
 
     def __init__(self, w_gate_up, w_down, n_experts: int, top_k: int, hidden: int, inter: int,
                  grouped_matmul: Optional[Callable] = None, rank: int = 0, world: int = 1, group=None,
-                 fused_ffn: Optional[Callable] = None):
+                 fused_ffn: Optional[Callable] = None, device_exchange: bool = False):
         if n_experts % world:
             raise ValueError(f"{n_experts} experts do not split evenly over {world} GPUs")
         if grouped_matmul is None and fused_ffn is None:
@@ -48,6 +48,7 @@ class ExpertParallelMoE:
         self.rank, self.world, self.group = rank, world, group
         self.E_loc = n_experts // world
         self.mm, self.ffn = grouped_matmul, fused_ffn
+        self.device_exchange = device_exchange        # pack / unpack with the library's kernels instead of torch ops
         self._buf = {}
         self._rows_ready = None
 
@@ -79,9 +80,25 @@ class ExpertParallelMoE:
         T_loc, dev = x.shape[0], x.device
         G, k, H, I = self.world, self.k, self.H, self.I
         T = T_loc * G
+        first = self.rank * self.E_loc
+        if self.device_exchange and self.ffn is not None and G > 1:
+            # one pack kernel, one all-gather, one unpack kernel (which also makes the expert ids local)
+            from . import device
+            send = self._buffer("send", (T_loc, H + 2 * k), torch.float32, dev)
+            recv = self._buffer("recv", (T, H + 2 * k), torch.float32, dev)
+            x_all = self._buffer("x_all", (T, H), torch.float32, dev)
+            idx_local = self._buffer("idx_local", (T, k), torch.int32, dev)
+            w_all = self._buffer("w_all", (T, k), torch.float32, dev)
+            device.moe_pack(x.contiguous(), top_idx.contiguous(), top_w.contiguous(), send)
+            dist.all_gather_into_tensor(recv, send, group=self.group)
+            device.moe_unpack(recv, H, k, first, self.E_loc, x_all, idx_local, w_all)
+            partial = self.ffn(x_all, self.w_gate_up, self.w_down, idx_local, w_all, self.E_loc, H, I,
+                               self._buffer("partial", (T, H), torch.float32, dev))
+            out = self._buffer("out", (T_loc, H), torch.float32, dev)
+            dist.reduce_scatter_tensor(out, partial, group=self.group)
+            return out
         x_all, idx_all, w_all = self._exchange_in(x, top_idx, top_w)
         # pairs of this rank's experts keep a local expert id, the others become -1
-        first = self.rank * self.E_loc
         mine = (idx_all >= first) & (idx_all < first + self.E_loc)
         idx_local = torch.where(mine, idx_all - first, torch.full_like(idx_all, -1)).to(torch.int32).contiguous()
         if self.ffn is not None:

@@ -93,3 +93,24 @@ def test_unsupported_type_is_reported():
     with pytest.raises(LaplaceCudaError) as e:
         device.moe_ffn(x, w1, w2, t, t, idx, wts, E, H, I)
     assert e.value.code == 1
+
+
+def test_pack_unpack_round_trip():
+    """Exchange helpers: pack [x | ids | weights], unpack with the ids made local to an expert range."""
+    import torch
+    from laplace_b200 import device
+    T, H, k, E = 37, 512, 4, 16
+    x = torch.from_numpy(synth.normal_f32(630, (T, H))).cuda()
+    idx, wts = seeded_routing(631, T, E, k)
+    idx_d, wts_d = torch.from_numpy(idx).cuda(), torch.from_numpy(wts).cuda()
+    packed = torch.empty((T, H + 2 * k), dtype=torch.float32, device="cuda")
+    device.moe_pack(x, idx_d, wts_d, packed)
+    x2 = torch.empty_like(x)
+    loc = torch.empty((T, k), dtype=torch.int32, device="cuda")
+    w2 = torch.empty_like(wts_d)
+    first, count = 4, 6
+    device.moe_unpack(packed, H, k, first, count, x2, loc, w2)
+    device.sync()
+    assert torch.equal(x2, x) and torch.equal(w2, wts_d)
+    want = np.where((idx >= first) & (idx < first + count), idx - first, -1).astype(np.int32)
+    assert np.array_equal(loc.cpu().numpy(), want)
