@@ -314,9 +314,22 @@ int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y,
     if ((rc = g_hx.ensure(xb)) || (rc = g_hy.ensure(yb)) || (rc = g_dx.ensure(xb)) || (rc = g_dy.ensure(yb))) return rc;
     std::memcpy(g_hx.p, x, xb);
     cudaMemcpyAsync(g_dx.p, g_hx.p, xb, cudaMemcpyHostToDevice, st);
-    rc = dispatch_gemm_dev(static_cast<const float*>(g_dx.p), dw, type, static_cast<float*>(g_dy.p), M, K, N, st);
+    // Decode calls: the kernel writes y straight into the pinned host buffer (which the device can address) in
+    // coalesced stores from its epilogue, so no device-to-host copy has to be queued behind it.
+    const bool direct = M <= 8 && static_cast<size_t>(M) * (static_cast<size_t>(N) / g_ctx.sm_count + 256) * sizeof(float) < 40 * 1024;
+    if (direct) {
+        PeerOut po{};
+        po.y[0] = static_cast<float*>(g_hy.p);
+        po.world = 1; po.rank = 0; po.ld = N; po.col0 = 0;
+        GemvArgs a{};
+        a.x = static_cast<const float*>(g_dx.p); a.w = dw; a.y = nullptr; a.type = type; a.M = M; a.K = K; a.N = N; a.n_seg = 1;
+        a.peers = &po;
+        rc = launch_gemv_stream(a, st);
+    } else {
+        rc = dispatch_gemm_dev(static_cast<const float*>(g_dx.p), dw, type, static_cast<float*>(g_dy.p), M, K, N, st);
+        if (rc == LAPLACE_OK) cudaMemcpyAsync(g_hy.p, g_dy.p, yb, cudaMemcpyDeviceToHost, st);
+    }
     if (rc) return rc;
-    cudaMemcpyAsync(g_hy.p, g_dy.p, yb, cudaMemcpyDeviceToHost, st);
     if ((rc = check_device_status(st))) return rc;
     std::memcpy(y, g_hy.p, yb);
     return LAPLACE_OK;

@@ -75,7 +75,8 @@ constexpr int MAX_PEERS = 8;
 struct PeerOut {
     float*    y[MAX_PEERS];      // every GPU's result buffer: [2 slots][M][ld], slot = step & 1
     int*      flags[MAX_PEERS];  // every GPU's flag array [world]; GPU r writes entry r of each
-    int*      step_ctr;          // this GPU's step counter
+    int*      step_ctr;          // this GPU's step counter; nullptr = no step protocol at all: the results are only
+                                 // staged and written, coalesced, to y[0] (used for output in host-mapped memory)
     unsigned* done_ctr;          // this GPU's "CTAs that have read the step counter" count (zero between launches)
     int       world, rank;
     int       ld;                // columns of the full result (N of the whole matrix)

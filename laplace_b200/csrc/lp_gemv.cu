@@ -470,7 +470,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
     // them: flag [rank] of every GPU is raised to the previous step. Nothing else in the kernel waits for that.
     size_t peer_slot_off = 0;
     int peer_prev = 0;
-    if (p.peers.world) {
+    if (p.peers.world && p.peers.step_ctr) {
         peer_prev = *reinterpret_cast<volatile const int*>(p.peers.step_ctr);
         peer_slot_off = static_cast<size_t>((peer_prev + 1) & 1) * static_cast<size_t>(p.n_seg) * M * p.peers.ld;
         if (threadIdx.x == 0) {
@@ -676,7 +676,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         if (warp == 0) {
             // Before this step's slices go out, the previous step must be complete HERE: every GPU stores
             // step s only after it has seen all of step s - 1, which is what makes two slots enough.
-            if (lane < p.peers.world) {
+            if (lane < p.peers.world && p.peers.step_ctr) {
                 bool seen = false;
                 for (uint32_t it = 0; it < (1u << 21) && !seen; ++it) {
                     int v;
@@ -696,7 +696,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
                 }
             }
             // one thread of the grid advances the step counter, once every CTA has read the old value
-            if (blockIdx.x == 0 && lane == 0) {
+            if (blockIdx.x == 0 && lane == 0 && p.peers.step_ctr) {
                 bool all_read = false;
                 for (uint32_t it = 0; it < (1u << 21) && !all_read; ++it)
                     all_read = *reinterpret_cast<volatile unsigned*>(p.peers.done_ctr) == gridDim.x;
