@@ -3,6 +3,7 @@
 // pointers (src/kernels.h:92-119), and their device-pointer twins.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
