@@ -65,8 +65,9 @@ struct KParams {
 // Result store: to y, or (fused all-gather) into this CTA's staging area in shared memory, from where
 // one warp writes the CTA's contiguous column range to every GPU in 128-byte coalesced stores.
 // `row` counts result rows, `col` the column inside this GPU's slice, `cta_col0` the CTA's first column.
+template <bool PEERS>
 __device__ __forceinline__ void store_result(const KParams& p, uint8_t* smem, int cta_col0, size_t row, int col, float v) {
-    if (p.peers.world == 0) p.y[row * p.N + col] = v;
+    if (!PEERS || p.peers.world == 0) p.y[row * p.N + col] = v;
     else reinterpret_cast<float*>(smem + p.off_stage)[row * p.stage_ld + (col - cta_col0)] = v;
 }
 
@@ -361,7 +362,7 @@ struct Walker {
 // shares one ring: every warp of the group meets every weight row of the group
 // with its own two rows of x, so shared memory serves each weight row G times
 // instead of each activation row once per weight row.
-template <uint32_t TYPE, int M, int WARPS, bool RESIDENT, int PW = PRODUCER_WARPS, int OCC = 1>
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT, int PW = PRODUCER_WARPS, int OCC = 1, bool PEERS = true>
 __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(const KParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -470,7 +471,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
     // them: flag [rank] of every GPU is raised to the previous step. Nothing else in the kernel waits for that.
     size_t peer_slot_off = 0;
     int peer_prev = 0;
-    if (p.peers.world && p.peers.step_ctr) {
+    if (PEERS && p.peers.world && p.peers.step_ctr) {
         peer_prev = *reinterpret_cast<volatile const int*>(p.peers.step_ctr);
         peer_slot_off = static_cast<size_t>((peer_prev + 1) & 1) * static_cast<size_t>(p.n_seg) * M * p.peers.ld;
         if (threadIdx.x == 0) {
@@ -568,11 +569,11 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
                     b.y += __shfl_xor_sync(0xffffffffu, b.y, o);
                 }
                 if (lane == 0) {
-                    store_result(p, smem, g0, m0, un.j + r, a.x);
-                    store_result(p, smem, g0, m0, un.j + r + 1, b.x);
+                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x);
+                    store_result<PEERS>(p, smem, g0, m0, un.j + r + 1, b.x);
                     if (m1 != m0) {
-                        store_result(p, smem, g0, m1, un.j + r, a.y);
-                        store_result(p, smem, g0, m1, un.j + r + 1, b.y);
+                        store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y);
+                        store_result<PEERS>(p, smem, g0, m1, un.j + r + 1, b.y);
                     }
                 }
             }
@@ -589,8 +590,8 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
                     a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
                 }
                 if (lane == 0) {
-                    store_result(p, smem, g0, m0, un.j + r, a.x);
-                    if (m1 != m0) store_result(p, smem, g0, m1, un.j + r, a.y);
+                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x);
+                    if (m1 != m0) store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y);
                 }
             }
             __syncwarp();
@@ -619,7 +620,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
                     a0 += __shfl_xor_sync(0xffffffffu, a0, o);
                     a1 += __shfl_xor_sync(0xffffffffu, a1, o);
                 }
-                if (lane == 0) { store_result(p, smem, g0, 0, un.j + r, a0); store_result(p, smem, g0, 0, un.j + r + 1, a1); }
+                if (lane == 0) { store_result<PEERS>(p, smem, g0, 0, un.j + r, a0); store_result<PEERS>(p, smem, g0, 0, un.j + r + 1, a1); }
             }
             if (r < un.nrows) {
                 float a0 = 0.f;
@@ -630,7 +631,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-                if (lane == 0) store_result(p, smem, g0, 0, un.j + r, a0);
+                if (lane == 0) store_result<PEERS>(p, smem, g0, 0, un.j + r, a0);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(grp, slot));                  // slot may be refilled
@@ -658,7 +659,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
                         float a = acc[m];
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                        if (lane == 0) store_result(p, smem, g0, static_cast<size_t>(un.seg) * M + m, un.j + r, a);
+                        if (lane == 0) store_result<PEERS>(p, smem, g0, static_cast<size_t>(un.seg) * M + m, un.j + r, a);
                         acc[m] = 0.f;
                     }
                 }
@@ -668,7 +669,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         }
     }
     if (!ok && lane == 0) report_status(p.err, DEV_TIMEOUT_FULL);   // the producer drains the copies
-    if (p.peers.world) {
+    if (PEERS && p.peers.world) {
         // Fused all-gather, sending: the CTA's results are staged in shared memory; warp 0 writes the CTA's
         // contiguous column range to every GPU in coalesced stores. No fence follows: the stores are
         // complete when the grid is, and the NEXT launch (or the closing wait kernel) announces them.
@@ -728,12 +729,12 @@ __global__ void allgather_wait_kernel(PeerOut po, int* err) {
     report_status(err, DEV_TIMEOUT_PEER);
 }
 
-template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false, int PW = PRODUCER_WARPS, int OCC = 1>
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false, int PW = PRODUCER_WARPS, int OCC = 1, bool PEERS = true>
 cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     // The opt-in shared-memory size is raised once per instantiation (not on
     // every launch, so launches stay legal inside a stream capture).
     static bool configured = false;
-    auto k = gemv_stream_kernel<TYPE, M, WARPS, RESIDENT, PW, OCC>;
+    auto k = gemv_stream_kernel<TYPE, M, WARPS, RESIDENT, PW, OCC, PEERS>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(ctx().smem_optin));
@@ -770,7 +771,9 @@ cudaError_t launch_typed(int M, bool resident, bool long_rows, const KParams& p,
     switch (M) {
         case 1:
             if constexpr (TYPE == LAPLACE_TYPE_Q4_K) {
-                if (resident) return launch_one<TYPE, 1, 16, true>(p, grid, smem, st);
+                // the common case (results to y) gets a kernel without the fused all-gather's code
+                if (resident) return p.peers.world ? launch_one<TYPE, 1, 16, true>(p, grid, smem, st)
+                                                   : launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, 1, false>(p, grid, smem, st);
             }
             if (long_rows) return launch_one<TYPE, 1, 16>(p, grid, smem, st);
             return launch_one<TYPE, 1, 24>(p, grid, smem, st);
