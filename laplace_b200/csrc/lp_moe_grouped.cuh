@@ -229,26 +229,26 @@ __device__ __forceinline__ float act_geglu(float g, float u) {
 }
 
 // Operand rows of the down matmul from the gate/up result: row r of gu holds [gate(I) | up(I)];
-// h = act(gate) * up is quantized per 32 values like any activation row. Only live rows
-// (out_row[r] >= 0, r < rows_used) are touched. h_out (optional) receives h in pair order.
+// h = act(gate) * up is quantized per 32 values like any activation row. The kernel walks the pairs
+// (dst_row[pair] = the pair's operand row, -1 = skipped). h_out (optional) receives h in pair order.
 __global__ void __launch_bounds__(256) moe_act_quant_kernel(const float* __restrict__ gu, int I, int activation,
-                                                            const int* __restrict__ rows_used, const int* __restrict__ out_row,
+                                                            int n_pairs, const int* __restrict__ dst_row,
                                                             __half* __restrict__ aq, float* __restrict__ dx,
                                                             __nv_bfloat16* __restrict__ ag, int ag_stride,
                                                             float* __restrict__ h_out) {
     const int t8 = threadIdx.x & 7;
     const int bpr = I / 32;
-    const long long n_blocks = static_cast<long long>(__ldg(rows_used)) * bpr;
+    const long long n_blocks = static_cast<long long>(n_pairs) * bpr;        // walk the pairs, not the padded operand rows
     const long long groups = static_cast<long long>(gridDim.x) * (blockDim.x >> 3);
     const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x >> 3) + (threadIdx.x >> 3);
     const long long iters = (n_blocks + groups - 1) / groups;
     for (long long itn = 0; itn < iters; ++itn) {
         const long long b = first + itn * groups;
         bool live = b < n_blocks;
-        const int r = live ? static_cast<int>(b / bpr) : 0;
-        const int kb = live ? static_cast<int>(b - static_cast<long long>(r) * bpr) : 0;
-        const int pair = live ? __ldg(out_row + r) : -1;
-        live = live && pair >= 0;
+        const int pair = live ? static_cast<int>(b / bpr) : 0;
+        const int kb = live ? static_cast<int>(b - static_cast<long long>(pair) * bpr) : 0;
+        const int r = live ? __ldg(dst_row + pair) : -1;                      // operand row of the pair, -1 = skipped pair
+        live = live && r >= 0;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (live) {
             const float* row = gu + static_cast<long long>(r) * (2 * I) + kb * 32;
@@ -397,8 +397,8 @@ int launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_do
     L.tiles_m = 1; L.tiles_n = tiles_n1; L.grid = grid_max < 1 ? 1 : grid_max;
     if ((rc = run_tc_kernel(L, st))) return rc;
 
-    moe_act_quant_kernel<<<grid_for(static_cast<long long>(rows_max) * bpr2), 256, 0, st>>>(
-        gu, I, activation, base + E, out_row, aq2, dx2, ag2, sbp2 * 64, h_out);
+    moe_act_quant_kernel<<<grid_for(static_cast<long long>(P) * bpr2), 256, 0, st>>>(
+        gu, I, activation, P, dst_row, aq2, dx2, ag2, sbp2 * 64, h_out);
     c.launches++;
     if ((rc = cuda_check(cudaGetLastError(), "moe_act_quant launch"))) return rc;
 
