@@ -160,8 +160,9 @@ int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, i
  * the reference: it exists for hosts that must not touch the CUDA allocator on the request
  * path - serving processes whose own pools (KV cache, activations) already hold all HBM, so
  * that cudaMalloc would fail or fragment them, and latency-bound loops that cannot take the
- * allocator's locks or the implicit device synchronisation of cudaFree. Same arguments and result as
- * laplace_cuda_gemm_dev; the quantized activations go to a 6 MiB array built into the
+ * allocator's locks or the implicit device synchronisation of cudaFree. Same arguments as
+ * laplace_cuda_gemm_dev and the same result (bit-identical whenever the call fits the array with the same
+ * K-split that entry point would choose, else equal to fp32 rounding); the quantized activations go to a 6 MiB array built into the
  * library (held by every GPU that loads it) instead of a cudaMalloc'd buffer.
  *   - LAPLACE_ERR_LIMIT when the call needs more scratch than the array holds: about
  *     2.3 * pad128(M) * K + M * K / 8 bytes (M = 512, K = 4096: 4.75 MiB);

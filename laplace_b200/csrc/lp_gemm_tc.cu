@@ -89,18 +89,28 @@ struct TcParams {
     const int*     n_tiles_dev;
     const int*     out_row;
     int            out_identity; // 1: a live row m is written to row m of y (y is in operand-row order), not to out_row[m]
+    // split-K (dense tiling with few output tiles): ksplit CTAs share an output tile, each takes sb_per
+    // super-blocks (an even number) and writes its partial result to y_part[k-slice][M][N]; a second kernel
+    // adds the slices in a fixed order
+    int            ksplit, sb_per;
+    float*         y_part;
 };
 
-struct TileRef { int m0, n0, wrow0; };
+struct TileRef { int m0, n0, wrow0, sb0, sb1, ks; };
 __device__ __forceinline__ TileRef tile_ref(const TcParams& p, int tile) {
+    const int nsb = p.K / 256;
     if (p.tile_tab) {
         const int4 t = __ldg(p.tile_tab + tile);
-        return {t.x, t.y, t.z};
+        return {t.x, t.y, t.z, 0, nsb, 0};
     }
-    return {(tile % p.tiles_m) * BM, (tile / p.tiles_m) * BN, 0};
+    const int out_tiles = p.tiles_m * p.tiles_n;
+    const int ks = tile / out_tiles, t = tile - ks * out_tiles;
+    const int sb0 = ks * p.sb_per;
+    const int sb1 = sb0 + p.sb_per < nsb ? sb0 + p.sb_per : nsb;
+    return {(t % p.tiles_m) * BM, (t / p.tiles_m) * BN, 0, sb0, sb1, ks};
 }
 __device__ __forceinline__ int tile_count(const TcParams& p) {
-    return p.tile_tab ? __ldg(p.n_tiles_dev) : p.tiles_m * p.tiles_n;
+    return p.tile_tab ? __ldg(p.n_tiles_dev) : p.tiles_m * p.tiles_n * p.ksplit;
 }
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------
@@ -242,8 +252,9 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = tile_ref(p, tile).m0;
-                for (int kc = 0; kc < nsb * 4; ++kc, ++it) {
+                const TileRef tr = tile_ref(p, tile);
+                const int m0 = tr.m0;
+                for (int kc = tr.sb0 * 4; kc < tr.sb1 * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, A_TILE);
@@ -266,7 +277,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const TileRef tr = tile_ref(p, tile);
                 const int m0 = tr.m0, n0 = tr.wrow0 + tr.n0;
-                for (int sb = 0; sb < nsb; ++sb, ++rq) {
+                for (int sb = tr.sb0; sb < tr.sb1; ++sb, ++rq) {
                     const int q = rq % RAW_STAGES;
                     if (!wait_or_abort(sbase + BAR_RAW_EMPTY + 8 * q, ((rq / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_RAW_FULL + 8 * q, RAW_TILE);
@@ -297,11 +308,12 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int it = 0, bc = 0, gp = 0, gsb = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
+                const TileRef tr = tile_ref(p, tile);
+                for (int pr = tr.sb0 / 2; pr < (tr.sb1 + 1) / 2 && ok; ++pr, ++gp) {
                     const int g = gp % GST;
                     const uint32_t gph = (gp / GST) & 1;
                     for (int e = 0; e < 2 && ok; ++e) {
-                        if (2 * pr + e >= nsb) break;
+                        if (2 * pr + e >= tr.sb1) break;
                         for (int kc = 0; kc < 4 && ok; ++kc, ++it) {
                             const int s = it % STAGES;
                             const uint32_t ph = (it / STAGES) & 1;
@@ -353,7 +365,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const uint4 zero4 = make_uint4(0, 0, 0, 0);
-            for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
+            const TileRef tr = tile_ref(p, tile);
+            for (int pr = tr.sb0 / 2; pr < (tr.sb1 + 1) / 2 && ok; ++pr, ++gp) {
                 const int g = gp % GST;
                 {
                     const uint32_t gph = ((gp / GST) & 1) ^ 1;
@@ -362,7 +375,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 }
                 for (int e = 0; e < 2 && ok; ++e) {
                     const int sb = 2 * pr + e;
-                    const bool exists = sb < nsb;
+                    const bool exists = sb < tr.sb1;
                     const int q = rq % RAW_STAGES;
                     const uint32_t raw = sbase + OFF_RAW + q * RAW_TILE + r * Q4_K_BYTES;      // this row's 144 bytes
                     if (exists && !wait_or_abort(sbase + BAR_RAW_FULL + 8 * q, (rq / RAW_STAGES) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
@@ -466,18 +479,18 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             float2 acc2[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) acc2[c] = make_float2(0.f, 0.f);
-            float2 dx_n = row_live ? __ldg(dxr) : make_float2(0.f, 0.f);
-            for (int pr = 0; pr < n_pairs && ok; ++pr, ++gp) {
+            float2 dx_n = row_live ? __ldg(dxr + tr.sb0 * 4) : make_float2(0.f, 0.f);
+            for (int pr = tr.sb0 / 2; pr < (tr.sb1 + 1) / 2 && ok; ++pr, ++gp) {
                 const int g = gp % GST;
                 const uint32_t gtab = sbase + OFF_GTAB + g * GTAB_BYTES;
                 for (int e = 0; e < 2 && ok; ++e) {
                     const int sb = 2 * pr + e;
-                    if (sb >= nsb) break;
+                    if (sb >= tr.sb1) break;
                     for (int kc = 0; kc < 4 && ok; ++kc) {
                         const float2 dx2 = dx_n;
                         {
                             const int nchunk = sb * 4 + kc + 1;
-                            if (row_live && nchunk < nsb * 4) dx_n = __ldg(dxr + nchunk);
+                            if (row_live && nchunk < tr.sb1 * 4) dx_n = __ldg(dxr + nchunk);
                         }
 #pragma unroll
                         for (int blk = 0; blk < 2; ++blk, ++bc) {
@@ -511,7 +524,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     if (!wait_or_abort(sbase + BAR_GT_FULL, gsb & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t dtab = gtab + (e * 2 * BN + half * 64) * 4, mtab = dtab + BN * 4;
-                    const bool first = sb == 0;
+                    const bool first = sb == tr.sb0;
 #pragma unroll
                     for (int gq = 0; gq < 4; ++gq) {
                         float gv[16], av[16];
@@ -553,7 +566,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 if (lane == 0) mbar_arrive(sbase + BAR_G_TAB_EMPTY + 8 * g);    // the pair's d / dmin tables are free
             }
             if (ok) {
-                float* yr = p.y + static_cast<size_t>(row_live ? orow : 0) * p.N + n0 + half * 64;
+                float* ybase = p.ksplit > 1 ? p.y_part + static_cast<size_t>(tr.ks) * p.M * p.N : p.y;
+                float* yr = ybase + static_cast<size_t>(row_live ? orow : 0) * p.N + n0 + half * 64;
                 const bool vec = n0 + half * 64 + 64 <= p.N && (reinterpret_cast<uintptr_t>(yr) & 15) == 0;
 #pragma unroll
                 for (int gq = 0; gq < 4; ++gq) {
@@ -670,11 +684,12 @@ namespace {
 
 // Scratch layout of one call: fp16 activation operand, activation scales, bf16 pieces of sum_x.
 struct ScratchPlan {
-    size_t m_pad, aq_bytes, sc_bytes, ag_bytes;
+    size_t m_pad, aq_bytes, sc_bytes, ag_bytes, part_bytes;
     int    tiles_m, tiles_n, n_pairs;
-    size_t total() const { return aq_bytes + sc_bytes + ag_bytes; }
+    int    ksplit, sb_per;           // split-K: CTAs per output tile, super-blocks per CTA (1, K/256: no split)
+    size_t total() const { return aq_bytes + sc_bytes + ag_bytes + part_bytes; }
 };
-ScratchPlan plan_scratch(int M, int K, int N) {
+ScratchPlan plan_scratch(int M, int K, int N, uint32_t type = LAPLACE_TYPE_Q4_K, bool allow_split = true) {
     ScratchPlan s;
     s.tiles_m = (M + BM - 1) / BM;
     s.tiles_n = (N + BN - 1) / BN;
@@ -683,7 +698,38 @@ ScratchPlan plan_scratch(int M, int K, int N) {
     s.aq_bytes = (s.m_pad * K * sizeof(__half) + 255) & ~size_t(255);
     s.sc_bytes = (static_cast<size_t>(M) * (K / 32) * sizeof(float) + 255) & ~size_t(255);
     s.ag_bytes = (s.m_pad * s.n_pairs * 64 * sizeof(__nv_bfloat16) + 255) & ~size_t(255);
+    // Few output tiles (narrow matrices, or a slice of one on each of several GPUs) leave most SMs idle: let up to
+    // four CTAs share a tile, each over an even number of super-blocks; partial results are added by a second kernel
+    // in a fixed order, so the result stays reproducible.
+    const int nsb = K / 256, out_tiles = s.tiles_m * s.tiles_n, sms = ctx().sm_count;
+    s.ksplit = 1; s.sb_per = nsb; s.part_bytes = 0;
+    if (allow_split && type == LAPLACE_TYPE_Q4_K && nsb >= 8 && out_tiles * 2 <= sms) {
+        int want = sms / out_tiles;
+        if (want > 4) want = 4;
+        int per = (nsb + want - 1) / want;
+        per += per & 1;
+        if (per < 4) per = 4;
+        const int ks = (nsb + per - 1) / per;
+        if (ks > 1) {
+            s.ksplit = ks; s.sb_per = per;
+            s.part_bytes = (static_cast<size_t>(ks) * M * N * sizeof(float) + 255) & ~size_t(255);
+        }
+    }
     return s;
+}
+
+// y = sum of the k-slices' partial results, slices added in index order.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float4* __restrict__ part, long long n4, int ksplit,
+                                                            float4* __restrict__ y) {
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float4 a = __ldg(part + i);
+        for (int k = 1; k < ksplit; ++k) {
+            const float4 b = __ldg(part + static_cast<long long>(k) * n4 + i);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        y[i] = a;
+    }
 }
 
 // One launch of a tensor-core kernel over prepared operands.
@@ -694,6 +740,7 @@ struct TcLaunch {
     __half* aq; float* dx; __nv_bfloat16* ag;
     const int4* tile_tab; const int* n_tiles_dev; const int* out_row; int out_identity;
     int tiles_m, tiles_n, grid;
+    int ksplit, sb_per; float* y_part;
 };
 
 int run_tc_kernel(const TcLaunch& L, cudaStream_t st) {
@@ -747,6 +794,7 @@ int run_tc_kernel(const TcLaunch& L, cudaStream_t st) {
     p.M = L.M; p.N = L.N; p.K = K; p.rb = static_cast<uint32_t>(row_bytes(type, K));
     p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n;
     p.tile_tab = L.tile_tab; p.n_tiles_dev = L.n_tiles_dev; p.out_row = L.out_row; p.out_identity = L.out_identity;
+    p.ksplit = L.ksplit > 1 ? L.ksplit : 1; p.sb_per = L.ksplit > 1 ? L.sb_per : K / 256; p.y_part = L.y_part;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
@@ -793,9 +841,24 @@ int gemm_tc_on_scratch(uint8_t* scratch, const ScratchPlan& sp, const float* x, 
     L.rows_pad = m_pad; L.w_rows = N;
     L.aq = aq; L.dx = dx; L.ag = ag;
     L.tiles_m = tiles_m; L.tiles_n = tiles_n;
-    const int n_tiles = tiles_m * tiles_n;
+    L.ksplit = sp.ksplit; L.sb_per = sp.sb_per;
+    L.y_part = sp.ksplit > 1 ? reinterpret_cast<float*>(scratch + aq_bytes + sc_bytes + ag_bytes) : nullptr;
+    const int n_tiles = tiles_m * tiles_n * (sp.ksplit > 1 ? sp.ksplit : 1);
     L.grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
-    return run_tc_kernel(L, st);
+    if ((rc = run_tc_kernel(L, st))) return rc;
+    if (sp.ksplit > 1) {
+        const long long n = static_cast<long long>(M) * N;
+        if (n % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+            long long blocks = (n / 4 + 255) / 256;
+            if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
+            splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(reinterpret_cast<const float4*>(L.y_part), n / 4, sp.ksplit,
+                                                                        reinterpret_cast<float4*>(y));
+            c.launches++;
+            return cuda_check(cudaGetLastError(), "splitk_reduce launch");
+        }
+        return fail(LAPLACE_ERR_STATE, "gemm: internal planning error (split-K needs M*N %% 4 == 0 and an aligned y)");
+    }
+    return LAPLACE_OK;
 }
 
 int check_gemm_tc_args(const float* x, const uint8_t* w, uint32_t type, int M, int K, int N) {
@@ -810,7 +873,9 @@ int check_gemm_tc_args(const float* x, const uint8_t* w, uint32_t type, int M, i
 int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st) {
     int rc = check_gemm_tc_args(x, w, type, M, K, N);
     if (rc) return rc;
-    const ScratchPlan sp = plan_scratch(M, K, N);
+    // split-K only when its result buffer can be added up with vector loads
+    const bool can_split = (static_cast<long long>(M) * N) % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+    const ScratchPlan sp = plan_scratch(M, K, N, type, can_split);
     if ((rc = g_scratch.ensure(sp.total()))) return rc;
     return gemm_tc_on_scratch(static_cast<uint8_t*>(g_scratch.p), sp, x, w, type, y, M, K, N, st);
 }
@@ -850,7 +915,11 @@ extern "C" int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, u
         return fail(LAPLACE_ERR_ARG, "gemm_noalloc: only the prefill shape is served here (Q4_K, M > 8, K %% 256 == 0); "
                                      "decode calls (M <= 8) use no scratch at all, call laplace_cuda_gemm_dev");
     if (rc) return rc;
-    const ScratchPlan sp = plan_scratch(M, K, N);
+    // the same K-split as laplace_cuda_gemm_dev (hence bit-identical results) whenever its partial results fit
+    // the array too; otherwise no split (results then agree to fp32 rounding)
+    const bool can_split = (static_cast<long long>(M) * N) % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+    ScratchPlan sp = plan_scratch(M, K, N, type, can_split);
+    if (sp.total() > NOALLOC_SCRATCH_BYTES) sp = plan_scratch(M, K, N, type, false);
     if (sp.total() > NOALLOC_SCRATCH_BYTES)
         return fail(LAPLACE_ERR_LIMIT, "gemm_noalloc: M=%d K=%d needs %zu bytes of scratch, the built-in array holds %zu",
                     M, K, sp.total(), NOALLOC_SCRATCH_BYTES);

@@ -21,7 +21,8 @@ def run_dev(t, x, w, M, K, N):
 
 
 @pytest.mark.parametrize("how", ["random", "ref", "affine"])
-@pytest.mark.parametrize("M,K,N", [(128, 512, 128), (9, 256, 8), (64, 1024, 256), (200, 2816, 200), (512, 4096, 384), (130, 768, 129)])
+@pytest.mark.parametrize("M,K,N", [(128, 512, 128), (9, 256, 8), (64, 1024, 256), (200, 2816, 200), (512, 4096, 384), (130, 768, 129),
+                                   (512, 4096, 1024), (100, 2048, 130), (33, 4608, 100)])
 def test_q4k_prefill(oracle, how, M, K, N):
     t = GGMLType.Q4_K
     w = synth.weights(t, K, N, seed=40 + M, how=how)
