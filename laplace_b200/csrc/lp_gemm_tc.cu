@@ -705,7 +705,7 @@ ScratchPlan plan_scratch(int M, int K, int N, uint32_t type = LAPLACE_TYPE_Q4_K,
     s.ksplit = 1; s.sb_per = nsb; s.part_bytes = 0;
     // (Splitting calls that already fill the machine - e.g. 448 tiles, to even out the last wave - was measured
     // slower: 0.259 -> 0.280 ms; only calls that leave at least half the SMs idle are split.)
-    if (allow_split && type == LAPLACE_TYPE_Q4_K && nsb >= 8 && out_tiles * 2 <= sms) {
+    if (allow_split && nsb >= 8 && out_tiles * 2 <= sms) {
         // cost in "super-blocks of one tile" (~4.7 us each): waves x super-blocks per CTA, plus the reduction's
         // traffic ((slices + 1) x M x N floats at ~6 TB/s).
         double best = static_cast<double>((out_tiles + sms - 1) / sms) * nsb;

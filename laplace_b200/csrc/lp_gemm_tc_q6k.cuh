@@ -90,7 +90,6 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
 
     const int n_tiles = tile_count(p);
-    const int nsb = p.K / 256;
 
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -99,8 +98,9 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int m0 = tile_ref(p, tile).m0;
-                for (int kc = 0; kc < nsb * 4; ++kc, ++it) {
+                const TileRef tr = tile_ref(p, tile);
+                const int m0 = tr.m0;
+                for (int kc = tr.sb0 * 4; kc < tr.sb1 * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, A_TILE);
@@ -123,7 +123,7 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const TileRef tr = tile_ref(p, tile);
                 const int n0 = tr.wrow0 + tr.n0;
-                for (int sb = 0; sb < nsb; ++sb, ++rq) {
+                for (int sb = tr.sb0; sb < tr.sb1; ++sb, ++rq) {
                     const int q = rq % RAW_STAGES;
                     if (!wait_or_abort(sbase + BAR_RAW_EMPTY + 8 * q, ((rq / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_RAW_FULL + 8 * q, RAW_TILE);
@@ -142,7 +142,8 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                for (int kc = 0; kc < nsb * 4 && ok; ++kc, ++it) {
+                const TileRef tr = tile_ref(p, tile);
+                for (int kc = tr.sb0 * 4; kc < tr.sb1 * 4 && ok; ++kc, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!spin_or_abort(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
@@ -174,7 +175,8 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         int it = 0, rq = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            for (int sb = 0; sb < nsb && ok; ++sb, ++rq) {
+            const TileRef tr = tile_ref(p, tile);
+            for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++rq) {
                 const int q = rq % RAW_STAGES, dsl = rq % DT;
                 if (!wait_or_abort(sbase + BAR_RAW_FULL + 8 * q, (rq / RAW_STAGES) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
                     !wait_or_abort(sbase + BAR_DT_EMPTY + 8 * dsl, ((rq / DT) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -252,13 +254,13 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             float2 acc2[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) acc2[c] = make_float2(0.f, 0.f);
-            float2 dx_n = row_live ? __ldg(dxr) : make_float2(0.f, 0.f);
-            for (int sb = 0; sb < nsb && ok; ++sb, ++ds) {
+            float2 dx_n = row_live ? __ldg(dxr + tr.sb0 * 4) : make_float2(0.f, 0.f);
+            for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++ds) {
                 for (int kc = 0; kc < 4 && ok; ++kc) {
                     const float2 dx2 = dx_n;
                     {
                         const int nchunk = sb * 4 + kc + 1;
-                        if (row_live && nchunk < nsb * 4) dx_n = __ldg(dxr + nchunk);
+                        if (row_live && nchunk < tr.sb1 * 4) dx_n = __ldg(dxr + nchunk);
                     }
 #pragma unroll
                     for (int blk = 0; blk < 2; ++blk, ++bc) {
@@ -291,7 +293,7 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 const int dsl = ds % DT;
                 if (!wait_or_abort(sbase + BAR_DT_FULL + 8 * dsl, (ds / DT) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
                 const uint32_t dtab = sbase + OFF_DTAB + (dsl * BN + half * 64) * 4;
-                const bool first = sb == 0;
+                const bool first = sb == tr.sb0;
 #pragma unroll
                 for (int gq = 0; gq < 4; ++gq) {
                     float av[16];
@@ -322,7 +324,8 @@ gemm_q6k_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 if (lane == 0) mbar_arrive(sbase + BAR_DT_EMPTY + 8 * dsl);
             }
             if (ok) {
-                float* yr = p.y + static_cast<size_t>(row_live ? orow : 0) * p.N + n0 + half * 64;
+                float* ybase = p.ksplit > 1 ? p.y_part + static_cast<size_t>(tr.ks) * p.M * p.N : p.y;
+                float* yr = ybase + static_cast<size_t>(row_live ? orow : 0) * p.N + n0 + half * 64;
                 const bool vec = n0 + half * 64 + 64 <= p.N && (reinterpret_cast<uintptr_t>(yr) & 15) == 0;
 #pragma unroll
                 for (int gq = 0; gq < 4; ++gq) {
