@@ -183,10 +183,11 @@ int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t typ
  * (flag [rank] of every GPU raised to the step number) by the NEXT gemm_allgather kernel's
  * prologue, or by laplace_cuda_allgather_wait_dev, which closes a chain of steps: it announces the
  * current step and waits (bounded) until all `world` flags of this GPU have reached it; the full y
- * of step s is then in slot (s & 1) of this GPU's buffer. A kernel stores step s only after it has
- * seen every GPU's step s - 1, so a consumer that runs after step s + 1's kernel may read step s
- * without the wait call. Replaces "GEMV + ncclAllGather" for decode, where the collective's latency
- * is 2-3x the kernel.
+ * of step s is then in slot (s & 1) of this GPU's buffer; consumers of y run after that call. A kernel
+ * stores step s only after it has seen every GPU's announcement of step s - 1 (made when that GPU's
+ * step-s kernel starts, i.e. when nothing on it reads the slot about to be overwritten any more),
+ * which is what makes two slots enough. Replaces "GEMV + ncclAllGather" for decode, where the
+ * collective's latency is 2-3x the kernel.
  *
  * Memory: each GPU allocates one buffer with laplace_cuda_peer_alloc (zeroed; returns a 64-byte
  * IPC handle to pass to the other processes by any host channel) and opens the others' with

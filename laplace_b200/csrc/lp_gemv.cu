@@ -528,6 +528,17 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         named_bar_sync(1, (WARPS + PW) * 32);      // all consumers + the producer's arrive
     }
 
+    // Fused all-gather: lanes 0 .. world-1 of warp 0 look at the other GPUs' flags for the previous step now and
+    // then while the warp streams (relaxed loads whose latency nobody waits for); see the sending phase below.
+    bool peer_seen = !(PEERS && p.peers.world && p.peers.step_ctr && warp == 0 && lane < p.peers.world);
+    int peer_pending = peer_prev - 1;                      // value of the load issued by the previous poll
+    auto peer_poll = [&]() {
+        if (PEERS && !peer_seen) {
+            peer_seen = peer_pending - peer_prev >= 0;     // the previous poll's load has long returned
+            if (!peer_seen)
+                asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(peer_pending) : "l"(p.peers.flags[p.peers.rank] + lane) : "memory");
+        }
+    };
     // (2) stream this warp's (group's) units
     const int grp = warp / G, sub = warp - grp * G;
     Walker wk = walker_of(grp);
@@ -550,6 +561,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         for (; wk.next(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            peer_poll();
             const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
             int r = 0;
             for (; r + 2 <= un.nrows; r += 2) {                   // two weight rows at a time: independent chains
@@ -604,6 +616,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         for (; wk.next(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            peer_poll();
             const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
             int r = 0;
             for (; r + 2 <= un.nrows; r += 2) {                   // two rows at a time: independent chains
@@ -643,6 +656,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         for (; wk.next(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+            peer_poll();
             const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.w + un.src_off) & 15u);
             const int arow = p.per_seg_x ? un.seg : 0;
             const uint32_t act = act0 + arow * p.act_row_stride, isum = isum0 + arow * p.isum_row_stride;
@@ -677,16 +691,15 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         if (warp == 0) {
             // Before this step's slices go out, the previous step must be complete HERE: every GPU stores
             // step s only after it has seen all of step s - 1, which is what makes two slots enough.
-            if (lane < p.peers.world && p.peers.step_ctr) {
-                bool seen = false;
-                for (uint32_t it = 0; it < (1u << 21) && !seen; ++it) {
-                    int v;
-                    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.peers.flags[p.peers.rank] + lane) : "memory");
-                    seen = v - peer_prev >= 0;
-                    if (!seen && it > 64) __nanosleep(100);
-                }
-                if (!seen) report_status(p.err, DEV_TIMEOUT_PEER);
+            // Every GPU announces step s - 1 when its step-s kernel starts, i.e. when nothing on it reads the slot
+            // that step s is about to overwrite any more. Seeing that flag (a control dependency: the stores below
+            // do not start before the loads have returned) is what makes two slots enough. Normally all flags
+            // have been seen by the polls above.
+            for (uint32_t it = 0; it < (1u << 21) && !peer_seen; ++it) {
+                peer_poll();
+                if (!peer_seen && it > 64) __nanosleep(100);
             }
+            if (!peer_seen) report_status(p.err, DEV_TIMEOUT_PEER);
             __syncwarp();
             const float* stage = reinterpret_cast<const float*>(smem + p.off_stage);
             for (int m = 0; m < M; ++m) {
