@@ -19,6 +19,17 @@
 // HBM traffic is the packed weights once, plus x and y. Every wait is bounded:
 // a wait that gives up raises a status word, the warp drains its own copies
 // and leaves.
+//
+// Variants inside the same kernel template:
+//   * RESIDENT (Q4_K, K <= 4096): activation records live in registers; with 2..8
+//     activation rows a warp keeps two of them and ceil(M/2) warps share a ring;
+//   * fused all-gather (PeerOut): results are staged in shared memory and one warp
+//     writes the CTA's column range to every GPU's buffer with coalesced peer stores;
+//     step flags are announced by the next launch's prologue (no fence on the critical
+//     path) and polled with relaxed loads while the kernel streams. The same staging
+//     writes y into pinned host memory for host-pointer calls;
+//   * paired mode (LAPLACE_PAIRED=1, off by default: measured slower): two CTAs of half
+//     the shared memory per SM with unequal row shares and an early launch trigger.
 #include <cstdlib>
 #include <cstdio>
 
