@@ -97,7 +97,7 @@ class ClockSampler:
 def cpu_gemv_runner():
     """The reference's own CPU implementation of the path when its build is present
     (oracle/_ref: scalar fp32-activation matmul_rows), else the int8 oracle port."""
-    from laplace_b200 import synth
+    from tests import synth
     from tests import oracle_lib
     cores = os.cpu_count() or 1
     w = synth.weights(TYPE_Q4_K, K_DIM, N_DIM, seed=1012, how="ref")
@@ -147,7 +147,8 @@ def gpu_arm(args):
     import torch
     import torch.distributed as dist
 
-    from laplace_b200 import _lib, device, synth
+    from laplace_b200 import _lib, device
+    from tests import synth
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -367,7 +368,7 @@ def gpu_arm(args):
             # GPU path has to match, on all threads; short samples
             try:
                 from tests import oracle_lib
-                from laplace_b200 import synth as _synth
+                from tests import synth as _synth
                 extra = {}
                 wq = _synth.weights(TYPE_Q4_K, K_DIM, N_DIM, seed=1012, how="ref")
                 xq = _synth.normal_f32(2001, (M_ROWS, K_DIM))
@@ -533,7 +534,8 @@ def moe_arm(args):
     the fused expert FFN (grouped gate/up matmul, gated activation, grouped down matmul, weighted sum), exchange out."""
     import torch
     import torch.distributed as dist
-    from laplace_b200 import device, synth
+    from laplace_b200 import device
+    from tests import synth
     from laplace_b200.moe import ExpertParallelMoE, device_fused_ffn, seeded_routing
 
     rank = int(os.environ.get("RANK", "0"))

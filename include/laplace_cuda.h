@@ -156,7 +156,7 @@ int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, i
                                 int expert_first, int expert_count,
                                 float* x, int* idx_local, float* top_w, void* stream);
 
-/* Prefill GEMM (Q4_K, M > 8, K % 256 == 0) that allocates nothing. It has no counterpart in
+/* Prefill GEMM (M > 8; Q4_K with K % 256 == 0, Q6_K with K % 2048 == 0) that allocates nothing. It has no counterpart in
  * the reference: it exists for hosts that must not touch the CUDA allocator on the request
  * path - serving processes whose own pools (KV cache, activations) already hold all HBM, so
  * that cudaMalloc would fail or fragment them, and latency-bound loops that cannot take the

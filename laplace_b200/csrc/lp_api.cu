@@ -96,11 +96,12 @@ const uint8_t* resolve_registered(const uint8_t* w, size_t bytes) {
 
 // Device address of `bytes` of weights at host pointer w: inside a registered
 // region by offset, otherwise uploaded for this call. Q4_K rows are read with
-// 16-byte vector loads, so a registered Q4_K tensor at an odd offset is
-// re-staged as well.
-int weights_on_device(const uint8_t* w, size_t bytes, uint32_t type, const uint8_t** out) {
+// 16-byte vector loads and the tensor-core kernels (need_align16) read every type
+// through a tensor map, so a registered tensor at an odd offset is re-staged for
+// those calls as well.
+int weights_on_device(const uint8_t* w, size_t bytes, uint32_t type, bool need_align16, const uint8_t** out) {
     const uint8_t* d = resolve_registered(w, bytes);
-    if (d && !(type == LAPLACE_TYPE_Q4_K && (reinterpret_cast<uintptr_t>(d) & 15))) { *out = d; return LAPLACE_OK; }
+    if (d && !((type == LAPLACE_TYPE_Q4_K || need_align16) && (reinterpret_cast<uintptr_t>(d) & 15))) { *out = d; return LAPLACE_OK; }
     int rc = g_dw.ensure(bytes + 64);
     if (rc) return rc;
     rc = cuda_check(cudaMemcpyAsync(g_dw.p, w, bytes, cudaMemcpyHostToDevice, g_ctx.stream), "weight upload");
@@ -164,7 +165,7 @@ int moe_host(const float* x, const uint8_t* w, uint32_t type, const int* expert_
     cudaStream_t st = g_ctx.stream;
     const size_t per_expert = static_cast<size_t>(N) * row_bytes(type, K);
     const uint8_t* dw = nullptr;
-    if ((rc = weights_on_device(w, per_expert * (static_cast<size_t>(max_e) + 1), type, &dw))) return rc;
+    if ((rc = weights_on_device(w, per_expert * (static_cast<size_t>(max_e) + 1), type, false, &dw))) return rc;
     const size_t xb = sizeof(float) * static_cast<size_t>(per_expert_x ? n_experts : 1) * K;
     const size_t yb = sizeof(float) * static_cast<size_t>(n_experts) * N;
     if ((rc = g_hx.ensure(xb + sizeof(int) * n_experts)) || (rc = g_hy.ensure(yb)) || (rc = g_dx.ensure(xb)) ||
@@ -310,7 +311,7 @@ int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y,
     if (M <= 0 || N <= 0 || K <= 0 || K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
     cudaStream_t st = g_ctx.stream;
     const uint8_t* dw = nullptr;
-    if ((rc = weights_on_device(w, static_cast<size_t>(N) * row_bytes(type, K), type, &dw))) return rc;
+    if ((rc = weights_on_device(w, static_cast<size_t>(N) * row_bytes(type, K), type, gemm_tc_supports(type, M, K, N), &dw))) return rc;
     const size_t xb = sizeof(float) * static_cast<size_t>(M) * K, yb = sizeof(float) * static_cast<size_t>(M) * N;
     if ((rc = g_hx.ensure(xb)) || (rc = g_hy.ensure(yb)) || (rc = g_dx.ensure(xb)) || (rc = g_dy.ensure(yb))) return rc;
     std::memcpy(g_hx.p, x, xb);

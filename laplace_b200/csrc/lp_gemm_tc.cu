@@ -38,6 +38,7 @@
 #include <cuda_bf16.h>
 
 #include <cstring>
+#include <vector>
 
 #include "lp_common.cuh"
 
@@ -647,29 +648,40 @@ __global__ void __launch_bounds__(256) quantize_act_f16_kernel(const float* __re
     }
 }
 
-// scratch owned by this translation unit
+// Scratch owned by this translation unit. A buffer that has been handed to a launch may be baked into a
+// captured CUDA graph (its address and the tensor maps built from it), so a buffer is never freed when a
+// larger one is needed: superseded buffers are kept until laplace_cuda_shutdown. Growing calls the
+// allocator, which is illegal while the call's stream is being captured: such a call is refused and the
+// capture stays valid (run the call once outside the capture first, as a warm-up, so that the buffer exists).
 struct Scratch {
     void*  p = nullptr;
     size_t cap = 0;
-    int ensure(size_t n) {
+    std::vector<void*> retired;
+    int ensure(size_t n, cudaStream_t st) {
         if (n <= cap) return LAPLACE_OK;
-        if (p) cudaFree(p);
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone)
+            return fail(LAPLACE_ERR_STATE, "the call needs %zu bytes of scratch but only %zu are allocated, and its stream is being "
+                                           "captured: make the same call once before the capture begins", n, cap);
+        if (p) retired.push_back(p);
         p = nullptr; cap = 0;
         cudaError_t e = cudaMalloc(&p, n + n / 8);
-        if (e != cudaSuccess) return cuda_check(e, "cudaMalloc prefill scratch");
+        if (e != cudaSuccess) return cuda_check(e, "cudaMalloc scratch");
         cap = n + n / 8;
         return LAPLACE_OK;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        for (void* q : retired) cudaFree(q);
+        retired.clear();
+        p = nullptr; cap = 0;
     }
 };
 Scratch g_scratch;
 
 }  // namespace
 
-void release_gemm_tc_scratch() {
-    if (g_scratch.p) cudaFree(g_scratch.p);
-    g_scratch.p = nullptr;
-    g_scratch.cap = 0;
-}
+void release_gemm_tc_scratch() { g_scratch.release(); }
 
 bool gemm_tc_supports(uint32_t type, int M, int K, int N) {
     if (M <= 8 || N <= 0) return false;
@@ -886,7 +898,7 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
     // split-K only when its result buffer can be added up with vector loads
     const bool can_split = (static_cast<long long>(M) * N) % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
     const ScratchPlan sp = plan_scratch(M, K, N, type, can_split);
-    if ((rc = g_scratch.ensure(sp.total()))) return rc;
+    if ((rc = g_scratch.ensure(sp.total(), st))) return rc;
     return gemm_tc_on_scratch(static_cast<uint8_t*>(g_scratch.p), sp, x, w, type, y, M, K, N, st);
 }
 
@@ -922,8 +934,9 @@ extern "C" int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, u
     if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm_noalloc: null pointer");
     int rc = check_gemm_tc_args(x, w, type, M, K, N);
     if (rc == LAPLACE_UNSUPPORTED)
-        return fail(LAPLACE_ERR_ARG, "gemm_noalloc: only the prefill shape is served here (Q4_K, M > 8, K %% 256 == 0); "
-                                     "decode calls (M <= 8) use no scratch at all, call laplace_cuda_gemm_dev");
+        return fail(LAPLACE_ERR_ARG, "gemm_noalloc: only the prefill shapes are served here (M > 8; Q4_K with K %% 256 == 0 or "
+                                     "Q6_K with K %% 2048 == 0); decode calls (M <= 8) use no scratch at all, call "
+                                     "laplace_cuda_gemm_dev");
     if (rc) return rc;
     // the same K-split as laplace_cuda_gemm_dev (hence bit-identical results) whenever its partial results fit
     // the array too; otherwise no split (results then agree to fp32 rounding)

@@ -27,10 +27,7 @@
 //     writes the CTA's column range to every GPU's buffer with coalesced peer stores;
 //     step flags are announced by the next launch's prologue (no fence on the critical
 //     path) and polled with relaxed loads while the kernel streams. The same staging
-//     writes y into pinned host memory for host-pointer calls;
-//   * paired mode (LAPLACE_PAIRED=1, off by default: measured slower): two CTAs of half
-//     the shared memory per SM with unequal row shares and an early launch trigger.
-#include <cstdlib>
+//     writes y into pinned host memory for host-pointer calls.
 #include <cstdio>
 
 #include "lp_common.cuh"
@@ -64,10 +61,7 @@ struct KParams {
     uint32_t       act_row_stride;  // bytes between quantized activation rows
     uint32_t       isum_row_stride; // bytes between rows of the int16 half-sums (Q6_K only, else 0)
     uint32_t       off_isum, off_ring;
-    int            rows_q, rows_r;  // CTA b < split owns rows_q (+1 if b < rows_r) rows
-    int            split;           // CTAs [split, grid) form a second class with its own share (paired mode)
-    int            rows_q2, rows_r2, rows_first;   // second class: rows per CTA, remainder, rows owned by the first class
-    int            pdl;
+    int            rows_q, rows_r;  // CTA b owns rows_q (+1 if b < rows_r) rows
     PeerOut        peers;           // peers.world == 0: results go to y
     uint32_t       off_stage;       // fused all-gather: this CTA's results are staged here, [M][stage_ld] floats
     int            stage_ld;
@@ -373,26 +367,16 @@ struct Walker {
 // shares one ring: every warp of the group meets every weight row of the group
 // with its own two rows of x, so shared memory serves each weight row G times
 // instead of each activation row once per weight row.
-template <uint32_t TYPE, int M, int WARPS, bool RESIDENT, int PW = PRODUCER_WARPS, int OCC = 1, bool PEERS = true>
-__global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(const KParams p) {
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT, int PW = PRODUCER_WARPS, bool PEERS = true>
+__global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const KParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Let the next kernel in the stream start launching as SMs free up.
-    if (p.pdl == 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
     // This CTA's contiguous share of the n_seg * N weight rows (fewer than 2^31),
     // cut again into one contiguous range per consumer warp.
     const int bx = static_cast<int>(blockIdx.x);
-    int g0, cta_rows;
-    if (bx < p.split) {
-        g0 = bx * p.rows_q + (bx < p.rows_r ? bx : p.rows_r);
-        cta_rows = p.rows_q + (bx < p.rows_r ? 1 : 0);
-    } else {
-        const int b2 = bx - p.split;
-        g0 = p.rows_first + b2 * p.rows_q2 + (b2 < p.rows_r2 ? b2 : p.rows_r2);
-        cta_rows = p.rows_q2 + (b2 < p.rows_r2 ? 1 : 0);
-    }
+    const int g0 = bx * p.rows_q + (bx < p.rows_r ? bx : p.rows_r);
+    const int cta_rows = p.rows_q + (bx < p.rows_r ? 1 : 0);
     constexpr int RW = (RESIDENT && M > 1) ? 2 : 1;          // activation rows a warp keeps in registers
     constexpr int G = RESIDENT ? (M + RW - 1) / RW : 1;       // warps per ring group
     constexpr int GROUPS = WARPS / G;
@@ -423,9 +407,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         // memory pipeline before any bulk copy, and the bulk of the copies only
         // once x has arrived - a load issued behind ~220 KB of queued copy
         // traffic waits microseconds for its turn.
-        // (Paired mode: the copies start at once, while the consumers may still be waiting for the previous launch;
-        // by the time x is loaded the first copies have landed.)
-        if constexpr (OCC == 1) named_bar_sync(2, (WARPS + PW) * 32);   // consumers are issuing their loads of x
+        named_bar_sync(2, (WARPS + PW) * 32);   // consumers are issuing their loads of x
         const uint32_t ring = ring_of(w);
         Walker wk = walker_of(serving ? w : 0);
         if (!serving) wk.g_end = wk.g;
@@ -508,7 +490,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
         };
         // Tell the producers first: they need ~100 cycles from here to their
         // first copy, the loads below are issued within a few.
-        if constexpr (OCC == 1) asm volatile("bar.arrive 2, %0;" :: "r"((WARPS + PW) * 32) : "memory");
+        asm volatile("bar.arrive 2, %0;" :: "r"((WARPS + PW) * 32) : "memory");
         float4 nxt = load_x(grp), nxt2 = load_x(grp + GROUPS);                   // two rounds ahead
         // whole warps iterate together so the 8-lane shuffles stay converged
         for (int base = 0; base < nblk; base += GROUPS) {
@@ -731,7 +713,8 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, OCC) gemv_stream_kernel(con
             }
         }
     }
-    if (p.pdl == 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Let the next kernel in the stream start launching as this grid's SMs free up.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // Closes a chain of fused all-gather steps: announces this GPU's slices of the current step (complete,
@@ -753,20 +736,16 @@ __global__ void allgather_wait_kernel(PeerOut po, int* err) {
     report_status(err, DEV_TIMEOUT_PEER);
 }
 
-template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false, int PW = PRODUCER_WARPS, int OCC = 1, bool PEERS = true>
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false, int PW = PRODUCER_WARPS, bool PEERS = true>
 cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     // The opt-in shared-memory size is raised once per instantiation (not on
     // every launch, so launches stay legal inside a stream capture).
     static bool configured = false;
-    auto k = gemv_stream_kernel<TYPE, M, WARPS, RESIDENT, PW, OCC, PEERS>;
+    auto k = gemv_stream_kernel<TYPE, M, WARPS, RESIDENT, PW, PEERS>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(ctx().smem_optin));
         if (e != cudaSuccess) return e;
-        if (OCC > 1) {      // co-resident CTAs need the SM's whole shared-memory carve-out
-            e = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-            if (e != cudaSuccess) return e;
-        }
         configured = true;
     }
     // Programmatic dependent launch: this grid may start (and prefetch weights,
@@ -782,11 +761,10 @@ cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = p.pdl ? 1 : 0;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, k, p);
 }
 
-constexpr int PAIRED_WARPS = 7, PAIRED_PRODUCER_WARPS = 2;     // per CTA in paired mode: two such CTAs per SM
 constexpr int RESIDENT_PRODUCER_WARPS = 2;  // 448 threads per CTA leave 146 registers per thread: two weight rows in flight
 constexpr int RESIDENT_WARPS = 12;      // consumer warps of the register-resident path with M > 1: splits into groups of 1, 2, 3 or 4
 
@@ -797,7 +775,7 @@ cudaError_t launch_typed(int M, bool resident, bool long_rows, const KParams& p,
             if constexpr (TYPE == LAPLACE_TYPE_Q4_K) {
                 // the common case (results to y) gets a kernel without the fused all-gather's code
                 if (resident) return p.peers.world ? launch_one<TYPE, 1, 16, true>(p, grid, smem, st)
-                                                   : launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, 1, false>(p, grid, smem, st);
+                                                   : launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, false>(p, grid, smem, st);
             }
             if (long_rows) return launch_one<TYPE, 1, 16>(p, grid, smem, st);
             return launch_one<TYPE, 1, 24>(p, grid, smem, st);
@@ -834,23 +812,10 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     const bool resident = a.type == LAPLACE_TYPE_Q4_K && !a.expert_idx && a.K <= 4096 &&
                           (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
     // consumer warps, and how many of them share one ring (resident path with M > 1: ceil(M / 2))
-    // Paired mode (one activation row, a matrix large enough to give every CTA work): two CTAs of half the
-    // shared memory per SM with UNEQUAL shares of the rows. The small-share CTAs leave early, the next launch's
-    // small-share CTAs move in (programmatic launch, early trigger) and prefetch their weights while this
-    // launch's large-share CTAs still stream, so HBM does not idle between launches.
-    static int paired_env = -1;
-    static float paired_frac = 0.35f;
-    if (paired_env < 0) {
-        const char* e = getenv("LAPLACE_PAIRED"); paired_env = e ? atoi(e) : 0;      // off unless asked for: measured slower so far
-        const char* f = getenv("LAPLACE_PAIRED_FRAC"); if (f) paired_frac = static_cast<float>(atof(f));
-        if (!(paired_frac > 0.05f && paired_frac < 0.95f)) paired_frac = 0.35f;
-    }
-    const bool paired = paired_env && resident && a.M == 1 && !a.peers &&
-                        static_cast<long long>(a.N) >= 2LL * c.sm_count * PAIRED_WARPS * 4;
     // one activation row, rows of 8 KB and more (K = 14336): fewer consumer warps, so that a warp's ring slot
     // holds a K-slice of a few KB (small bulk copies are issue-bound)
     const bool long_rows = !resident && a.M == 1 && row_bytes(a.type, a.K) >= 8192;
-    const int cwarps = paired ? PAIRED_WARPS : resident ? (a.M == 1 ? 16 : RESIDENT_WARPS) : (a.M <= 2 && !long_rows ? 24 : 16);
+    const int cwarps = resident ? (a.M == 1 ? 16 : RESIDENT_WARPS) : (a.M <= 2 && !long_rows ? 24 : 16);
     const int warps = (resident && a.M > 1) ? cwarps / ((a.M + 1) / 2) : cwarps;      // ring groups
     KParams p{};
     p.x = a.x; p.w = a.w; p.y = a.y; p.expert_idx = a.expert_idx; p.err = c.d_err;
@@ -886,8 +851,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
         stage_bytes = (static_cast<size_t>(a.M) * p.stage_ld * sizeof(float) + 127) & ~size_t(127);
         if (stage_bytes > 48 * 1024) return fail(LAPLACE_ERR_LIMIT, "gemv: N=%d is too wide for the fused all-gather", a.N);
     }
-    // paired mode: two CTAs share the SM's shared memory (1 KB per CTA is reserved by the system)
-    const size_t budget = paired ? ((c.smem_per_sm - 2048) / 2) & ~size_t(127) : c.smem_optin - stage_bytes;
+    const size_t budget = c.smem_optin - stage_bytes;
     if (p.off_ring + static_cast<size_t>(warps) * 2 * 256 > budget)
         return fail(LAPLACE_ERR_LIMIT, "gemv: M=%d K=%d: the quantized activations do not fit shared memory", a.M, a.K);
     const size_t per_warp = ((budget - p.off_ring) / warps) & ~size_t(15);
@@ -935,28 +899,14 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     const long long want = (total_rows + warps * p.rows_per_unit - 1) / (warps * p.rows_per_unit);
     int grid = c.sm_count;
     if (want < grid) grid = static_cast<int>(want);
-    { static int mode = -1; if (mode < 0) { const char* e = getenv("LAPLACE_PDL"); mode = e ? atoi(e) : 2; } p.pdl = mode; }
     p.rows_q = static_cast<int>(total_rows / grid);
     p.rows_r = static_cast<int>(total_rows % grid);
-    p.split = grid;
-    if (paired) {
-        const int sms = c.sm_count;
-        grid = 2 * sms;
-        long long first = static_cast<long long>(static_cast<double>(total_rows) * paired_frac);
-        first -= first % 2;                                 // units are pairs of rows
-        p.split = sms;
-        p.rows_first = static_cast<int>(first);
-        p.rows_q = static_cast<int>(first / sms);            p.rows_r = static_cast<int>(first % sms);
-        p.rows_q2 = static_cast<int>((total_rows - first) / sms); p.rows_r2 = static_cast<int>((total_rows - first) % sms);
-        p.pdl = 1;                                          // early trigger: the next launch's CTAs queue behind this one's
-    }
     if (a.peers && p.rows_q + 1 > p.stage_ld) return fail(LAPLACE_ERR_STATE, "gemv: internal planning error (staging area too small)");
 
     cudaError_t e;
     switch (a.type) {
         case LAPLACE_TYPE_Q4_K:
-            if (paired) e = launch_one<LAPLACE_TYPE_Q4_K, 1, PAIRED_WARPS, true, PAIRED_PRODUCER_WARPS, 2>(p, dim3(grid), smem, st);
-            else e = launch_typed<LAPLACE_TYPE_Q4_K>(a.M, resident, long_rows, p, dim3(grid), smem, st);
+            e = launch_typed<LAPLACE_TYPE_Q4_K>(a.M, resident, long_rows, p, dim3(grid), smem, st);
             break;
         case LAPLACE_TYPE_Q6_K: e = launch_typed<LAPLACE_TYPE_Q6_K>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
         case LAPLACE_TYPE_Q4_0: e = launch_typed<LAPLACE_TYPE_Q4_0>(a.M, false, long_rows, p, dim3(grid), smem, st); break;

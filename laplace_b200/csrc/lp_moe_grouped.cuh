@@ -134,11 +134,7 @@ inline size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
 
 }  // namespace
 
-void release_moe_grouped_scratch() {
-    if (g_moe_scratch.p) cudaFree(g_moe_scratch.p);
-    g_moe_scratch.p = nullptr;
-    g_moe_scratch.cap = 0;
-}
+void release_moe_grouped_scratch() { g_moe_scratch.release(); }
 
 bool moe_grouped_supports(uint32_t type, int K, int N) {
     return gemm_tc_supports(type, 9, K, N);
@@ -169,7 +165,7 @@ int launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const in
     const size_t tab_bytes = align256(sizeof(int4) * tiles_max);
     const size_t total = aq_bytes + dx_bytes + ag_bytes + cnt_bytes + base_bytes + 2 * slot_bytes + out_bytes + tab_bytes;
     int rc;
-    if ((rc = g_moe_scratch.ensure(total))) return rc;
+    if ((rc = g_moe_scratch.ensure(total, st))) return rc;
     uint8_t* s = static_cast<uint8_t*>(g_moe_scratch.p);
     __half* aq = reinterpret_cast<__half*>(s);                     s += aq_bytes;
     float* dx = reinterpret_cast<float*>(s);                       s += dx_bytes;
@@ -311,11 +307,7 @@ Scratch g_ffn_scratch;
 
 }  // namespace
 
-void release_moe_ffn_scratch() {
-    if (g_ffn_scratch.p) cudaFree(g_ffn_scratch.p);
-    g_ffn_scratch.p = nullptr;
-    g_ffn_scratch.cap = 0;
-}
+void release_moe_ffn_scratch() { g_ffn_scratch.release(); }
 
 int launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
                    const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
@@ -349,7 +341,7 @@ int launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_do
     const size_t total = zero_bytes + out_bytes + aq1_bytes + aq2_bytes + dx1_bytes + dx2_bytes + gu_bytes + dn_bytes +
                          base_bytes + 2 * slot_bytes + tab1_bytes + tab2_bytes;
     int rc;
-    if ((rc = g_ffn_scratch.ensure(total))) return rc;
+    if ((rc = g_ffn_scratch.ensure(total, st))) return rc;
     uint8_t* s = static_cast<uint8_t*>(g_ffn_scratch.p);
     uint8_t* zero_block = s;
     __nv_bfloat16* ag1 = reinterpret_cast<__nv_bfloat16*>(s);      s += ag1_bytes;

@@ -6,8 +6,10 @@
 // arch_*.cpp, laplace_moe.cpp and matmul.cpp compile and link unchanged. A
 // return value of `false` keeps the reference's contract (kernels.h:94-96):
 // "this back-end does not handle the call, fall back to the scalar path" -
-// that happens for weight types other than Q4_0 / Q8_0 / Q4_K / Q6_K and when
-// the CUDA library reports an error (which is also printed).
+// that happens only for weight types other than Q4_0 / Q8_0 / Q4_K / Q6_K. An
+// error from the CUDA library (a failed CUDA call, a device-side timeout, a bad
+// argument) is NOT turned into a fall-back: the scalar path computes with fp32
+// activations, i.e. different numbers, so the process prints the error and aborts.
 //
 // LAPLACE_CUDA_DEVICE selects the GPU (default 0). LAPLACE_NOSIMD=1 keeps its
 // meaning: the front-end never asks for these getters (src/matmul.cpp:48-55).
@@ -39,8 +41,10 @@ struct CallCounter {
 
 bool handled(int rc, const char* what) {
     if (rc == LAPLACE_OK) { g_calls.n++; return true; }
-    if (rc != LAPLACE_UNSUPPORTED)
+    if (rc != LAPLACE_UNSUPPORTED) {
         std::fprintf(stderr, "laplace_cuda: %s failed (%d): %s\n", what, rc, laplace_cuda_last_error());
+        std::abort();
+    }
     return false;
 }
 
@@ -73,8 +77,8 @@ moe_gemv_multi_fn get_simd_moe_gemv_multi() { return ensure_init() ? cuda_moe_ge
 
 }  // namespace kernels
 
-// Hook for matmul_register_weights (src/matmul.h:26): call this from it (one line,
-// see INTEGRATION.md) so that the mmap'd GGUF region is uploaded to HBM once.
+// Hook for matmul_register_weights (src/matmul.h:26): that function gains one line calling this
+// one, so that the mmap'd GGUF region is uploaded to HBM once, at model load.
 void cuda_register_weights(const void* base, size_t size) {
     if (!ensure_init()) return;
     const int rc = laplace_cuda_register_weights(base, size);

@@ -147,9 +147,8 @@ def device_grouped_matmul(ggml_type: int) -> Callable:
 
 def seeded_routing(seed: int, T: int, E: int, top_k: int):
     """Router stand-in: logits ~ N(0,1) from a seed, top-k experts per token, softmax over the selected logits."""
-    from . import synth
     import numpy as np
-    logits = synth.normal_f32(seed, (T, E))
+    logits = np.random.Generator(np.random.Philox(seed)).standard_normal((T, E), dtype=np.float32)
     idx = np.argsort(-logits, axis=1)[:, :top_k].astype(np.int32)
     sel = np.take_along_axis(logits, idx, axis=1)
     ex = np.exp(sel - sel.max(axis=1, keepdims=True))

@@ -5,12 +5,13 @@
 The file pins two things for machines that have no reference checkout:
   * outputs of the reference's OWN code (oracle/_ref/libref_matmul.so, built
     from its sources): dequantize(), the scalar fp32-activation matmul_rows,
-    and its fp16 conversions, on small seeded inputs;
+    and its fp16 conversions, on small seeded inputs; and (lossless_golden.npz) its
+    matmul_rows on mid-size inputs whose activations Q8 represents exactly;
   * outputs of the C restatement of its int8 path (liboracle_q8.so) on the same
     inputs: quantized activation blocks, integer block sums, fp32 (lane-order)
     and float64 results, so that a later edit of the oracle cannot drift
     silently and GPU tests can compare against stored vectors.
-Inputs are regenerated from seeds by laplace_b200.synth and are stored too.
+Inputs are regenerated from seeds by tests.synth and are stored too.
 """
 import sys
 from pathlib import Path
@@ -20,7 +21,7 @@ import numpy as np
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 
-from laplace_b200 import synth  # noqa: E402
+from tests import synth  # noqa: E402
 from tests.oracle_lib import Oracle, Reference  # noqa: E402
 
 CASES = [  # (type, how, M, K, N, seed)
@@ -68,6 +69,31 @@ def main():
     out["moe_y_idx_f64"] = o.moe_gemv(x[0], w, t, idx, K, N, multi=False, mode=1)
     out["moe_y_multi_f64"] = o.moe_gemv(x, w, t, idx, K, N, multi=True, mode=1)
     path = Path(__file__).with_name("hotpath_golden.npz")
+    np.savez_compressed(path, **out)
+    print(path, path.stat().st_size, "bytes")
+    lossless(r)
+
+
+# Reference-build outputs for activations that Q8 represents exactly (tests.synth.lossless_q8_activations): with
+# those the reference's scalar fp32-activation path and its int8 path are the same arithmetic up to fp32
+# summation order, so implementations of the int8 path are held to these vectors at 1e-5. Weights and
+# activations are regenerated from the stored seeds; only the reference's outputs are stored.
+LOSSLESS_CASES = [  # (type, M, K, N, weight seed, activation seed)
+    (2, 1, 4096, 512, 9601, 9701), (8, 1, 4096, 256, 9602, 9702), (12, 1, 4096, 1024, 9603, 9703),
+    (14, 1, 4096, 512, 9604, 9704), (12, 8, 4096, 512, 9605, 9705), (12, 64, 2048, 256, 9606, 9706),
+    (14, 64, 2048, 256, 9607, 9707), (2, 40, 1024, 128, 9608, 9708), (8, 40, 1024, 128, 9609, 9709),
+    (12, 1, 14336, 128, 9610, 9710), (14, 1, 14336, 128, 9611, 9711),
+]
+
+
+def lossless(r):
+    out = {"n_cases": np.array(len(LOSSLESS_CASES))}
+    for i, (t, M, K, N, ws, xs) in enumerate(LOSSLESS_CASES):
+        w = synth.weights(t, K, N, seed=ws, how="affine")
+        x = synth.lossless_q8_activations(xs, M, K)
+        out[f"l{i}_meta"] = np.array([t, M, K, N, ws, xs], dtype=np.int64)
+        out[f"l{i}_ref_y"] = r.matmul_rows(x, w, t, M, K, N)
+    path = Path(__file__).with_name("lossless_golden.npz")
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes")
 

@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import numpy as np
 
-from .ggml import GGMLType, row_bytes
+from laplace_b200.ggml import GGMLType, row_bytes
 
 # ------------------------------------------------------------------ RNG
 
@@ -291,3 +291,64 @@ def weights(t: int, K: int, N: int, seed: int, how: str = "ref") -> np.ndarray:
         return random_blocks(t, K, N, seed)
     w = normal_f32(seed, (N, K), 0.02)
     return (PACK_REF if how == "ref" else PACK_AFFINE)[GGMLType(t)](w)
+
+
+def lossless_q8_activations(seed: int, M: int, K: int) -> np.ndarray:
+    """fp32 activations that the per-32 Q8 quantizer represents exactly: every block is d * q with q integers in
+    [-127, 127], one of them +-127, and d a power of two. The quantizer then recovers exactly (d, q), so the
+    reference's fp32-activation scalar path and its int8 path compute the same dot products up to fp32 summation
+    order - which lets code that follows the int8 path be compared with the compiled scalar path at 1e-5."""
+    g = rng(seed)
+    q = g.integers(-127, 128, size=(M, K // 32, 32)).astype(np.int32)
+    pos = g.integers(0, 32, size=(M, K // 32))
+    sign = g.integers(0, 2, size=(M, K // 32)) * 2 - 1
+    np.put_along_axis(q, pos[..., None], (127 * sign)[..., None], axis=2)
+    e = g.integers(-9, -5, size=(M, K // 32, 1))
+    return (q.astype(np.float32) * np.exp2(e).astype(np.float32)).reshape(M, K)
+
+
+def single_live_block(t: int, K: int, N: int, seed: int, live: int):
+    """Weights with random payload in which every scale is zero except the ones that cover 32-value block `live`
+    of each row (for Q6_K: the two 16-value groups of that block), plus one activation row whose only non-zero
+    block is `live`, holding integers q in [-127, 127] (one of them 127) times 2^-3. Every other term of the dot
+    is exactly zero, so y[j] = (weight scale product) * 2^-3 * (integer block sum), bit for bit, on any correct
+    implementation of the int8 path; returns (w, x, scale[N] or scale[N, 2] for Q6_K)."""
+    t = GGMLType(t)
+    g = rng(seed)
+    w = random_blocks(t, K, N, seed + 1)
+    rb = row_bytes(t, K)
+    x = np.zeros((1, K), dtype=np.float32)
+    q = g.integers(-127, 128, size=32).astype(np.float32)
+    q[int(g.integers(0, 32))] = 127.0
+    x[0, live * 32:(live + 1) * 32] = q * np.float32(0.125)
+    one = np.frombuffer(np.float16(1.0).tobytes(), dtype=np.uint8)
+    if t in (GGMLType.Q4_0, GGMLType.Q8_0):
+        bb = 18 if t == GGMLType.Q4_0 else 34
+        blk = w.reshape(N, rb // bb, bb)
+        blk[:, :, 0:2] = 0
+        blk[:, live, 0:2] = one
+        return w, x, np.ones(N, dtype=np.float32)
+    sb, j = live // 8, live % 8
+    if t == GGMLType.Q4_K:
+        blk = w.reshape(N, rb // 144, 144)
+        blk[:, :, 0:4] = 0                       # d = dmin = 0 everywhere ...
+        blk[:, sb, 0:2] = one                    # ... except d of the live super-block (dmin stays 0)
+        sc = np.zeros((N, 8), dtype=np.int64)
+        live_sc = g.integers(1, 64, size=N)
+        sc[:, j] = live_sc
+        packed = np.zeros((N, 12), dtype=np.uint8)   # 6-bit packing of Laplace src/kernels.h:82-90, mins all zero
+        for i in range(4):
+            packed[:, i] = (sc[:, i] & 63) | ((sc[:, i + 4] >> 4) << 6)
+            packed[:, 8 + i] = sc[:, i + 4] & 15
+        blk[:, sb, 4:16] = packed
+        return w, x, live_sc.astype(np.float32)
+    blk = w.reshape(N, rb // 210, 210)
+    blk[:, :, 208:210] = 0
+    blk[:, sb, 208:210] = one
+    scales = np.zeros((N, 16), dtype=np.int8)
+    live_sc = g.integers(-128, 128, size=(N, 2)).astype(np.int8)
+    half, gq = j // 4, j % 4
+    scales[:, 8 * half + 2 * gq] = live_sc[:, 0]
+    scales[:, 8 * half + 2 * gq + 1] = live_sc[:, 1]
+    blk[:, sb, 192:208] = scales.view(np.uint8)
+    return w, x, live_sc.astype(np.float32)

@@ -25,7 +25,8 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
                             timeout=datetime.timedelta(seconds=60))
-    from laplace_b200 import device, synth
+    from laplace_b200 import device
+    from tests import synth
     from laplace_b200.ggml import GGMLType
     from laplace_b200.shard import PeerGather, RowShards
     L = device.lib(rank)

@@ -4,7 +4,7 @@ import os
 import numpy as np
 import pytest
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType
 from tests.parity import check_close
 
@@ -121,3 +121,37 @@ def test_prefill_special_rows(oracle, t, K):
     keep[7] = False
     check_close(y[keep], ref[keep], f"{t.name} prefill with special rows")
     assert np.allclose(y[11], ref[11], rtol=2e-6, atol=0.0)
+
+
+def test_scratch_growth_is_refused_during_stream_capture(oracle):
+    """A prefill call whose scratch would have to grow calls the allocator, which is illegal while the call's
+    stream is being captured into a CUDA graph: the call is refused with LAPLACE_ERR_STATE, the capture stays
+    valid, and the same call succeeds once made outside a capture (after which a capture of it works)."""
+    import torch
+    from laplace_b200 import device
+    L = device.lib()
+    t, M, K, N = GGMLType.Q4_K, 1536, 14336, 128            # needs far more scratch than any other test
+    w = synth.weights(t, K, N, seed=97, how="random")
+    x = synth.normal_f32(98, (M, K))
+    xd, wd = torch.from_numpy(x).cuda(), device.upload_weights(w)
+    y = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    s = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        g.capture_begin()
+        rc = L.laplace_cuda_gemm_dev(xd.data_ptr(), wd.data_ptr(), int(t), y.data_ptr(), M, K, N, s.cuda_stream)
+        g.capture_end()
+    assert rc == -3 and b"captured" in L.laplace_cuda_last_error()
+    with torch.cuda.stream(s):
+        rc = L.laplace_cuda_gemm_dev(xd.data_ptr(), wd.data_ptr(), int(t), y.data_ptr(), M, K, N, s.cuda_stream)     # grows the scratch
+        assert rc == 0, L.laplace_cuda_last_error()
+        s.synchronize()
+        y.zero_()
+        g2 = torch.cuda.CUDAGraph()
+        g2.capture_begin()
+        rc = L.laplace_cuda_gemm_dev(xd.data_ptr(), wd.data_ptr(), int(t), y.data_ptr(), M, K, N, s.cuda_stream)
+        g2.capture_end()
+        assert rc == 0, L.laplace_cuda_last_error()
+        g2.replay()
+    device.sync()
+    check_close(y.cpu().numpy(), oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), "captured prefill call")

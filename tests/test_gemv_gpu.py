@@ -6,7 +6,7 @@ Bars: integer block sums bit-exact; fp32 outputs within 1e-5 relative L2 and
 import numpy as np
 import pytest
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType
 
 pytestmark = pytest.mark.gpu

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType, row_bytes
 from laplace_b200.moe import ExpertParallelMoE, seeded_routing, silu_mul
 from tests.oracle_lib import Oracle

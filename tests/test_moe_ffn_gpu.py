@@ -7,7 +7,7 @@ values the device itself produced (h_out), and the activation is checked on its 
 import numpy as np
 import pytest
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType
 from laplace_b200.moe import seeded_routing
 from tests.parity import check_close

@@ -6,7 +6,7 @@ must reproduce every one of those per-token results."""
 import numpy as np
 import pytest
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType
 from tests.parity import check_close
 

@@ -11,7 +11,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from laplace_b200 import _lib, ggml, synth
+from laplace_b200 import _lib, ggml
+from tests import synth
 from laplace_b200.shard import RowShards
 from tests.oracle_lib import Oracle
 

@@ -4,7 +4,7 @@ consistency of the restatement."""
 import numpy as np
 import pytest
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType, blocksums_per_row, row_bytes
 from tests.oracle_lib import ACTQ8, Reference
 
@@ -211,3 +211,35 @@ def test_moe_indexing(oracle):
 
 def test_actq8_layout():
     assert ACTQ8.itemsize == 44 and ACTQ8.fields["qs"][1] == 12
+
+
+def test_oracle_matches_stored_reference_outputs_on_lossless_activations(oracle, golden_dir):
+    """Activations that Q8 represents exactly make the reference's compiled scalar path and its int8 path the
+    same arithmetic up to fp32 summation order: the restated int8 path (both its fp32 lane-order mode and its
+    float64 mode) must reproduce the reference build's stored outputs to 1e-5 relative L2."""
+    g = np.load(golden_dir / "lossless_golden.npz")
+    for i in range(int(g["n_cases"])):
+        t, M, K, N, wseed, xseed = (int(v) for v in g[f"l{i}_meta"])
+        w = synth.weights(t, K, N, seed=wseed, how="affine")
+        x = synth.lossless_q8_activations(xseed, M, K)
+        qa = oracle.quantize(x)
+        assert np.array_equal((qa["qs"].astype(np.float32) * qa["d"][..., None]).reshape(M, K), x), "inputs are not lossless"
+        ref = g[f"l{i}_ref_y"].astype(np.float64)
+        for mode in (0, 1):
+            y = oracle.gemm(x, w, t, M, K, N, mode=mode, threads=4).astype(np.float64)
+            rel = np.linalg.norm(y - ref) / np.linalg.norm(ref)
+            assert rel <= 1e-5, f"type {t} {M}x{K}x{N} mode {mode}: rel L2 {rel:.2e}"
+            assert np.abs(y - ref).max() <= 1e-3 * np.sqrt(np.mean(ref ** 2))
+
+
+@pytest.mark.skipif(not Reference.available(), reason="oracle/_ref not built (no reference checkout here)")
+@pytest.mark.parametrize("t,M,K,N", [(GGMLType.Q4_0, 1, 4096, 4096), (GGMLType.Q4_K, 1, 4096, 14336), (GGMLType.Q6_K, 1, 14336, 4096),
+                                     (GGMLType.Q8_0, 2, 4096, 1024), (GGMLType.Q4_K, 8, 4096, 14336)])
+def test_oracle_matches_reference_build_live_at_benchmark_shapes(oracle, t, M, K, N):
+    ref = Reference()
+    ref.set_threads(4)
+    w = synth.weights(t, K, N, seed=31 + int(t), how="affine")
+    x = synth.lossless_q8_activations(32 + M, M, K)
+    want = ref.matmul_rows(x, w, t, M, K, N).astype(np.float64)
+    y = oracle.gemm(x, w, t, M, K, N, mode=1, threads=4).astype(np.float64)
+    assert np.linalg.norm(y - want) / np.linalg.norm(want) <= 1e-5

@@ -3,7 +3,7 @@ literal scalar transcription of what those helpers do on a tiny case."""
 import numpy as np
 import pytest
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType, row_bytes
 
 TYPES = [GGMLType.Q4_0, GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q6_K]

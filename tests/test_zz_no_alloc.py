@@ -7,39 +7,61 @@ go to an array built into the library instead of a cudaMalloc'd buffer. This fil
 to be collected last, so a run that stops at the first failure has already run everything
 else; the test passes alone in a fresh process as well as after the other tests.
 """
+import os
+
 import numpy as np
 import pytest
 
-from laplace_b200 import synth
+from tests import synth
 from laplace_b200.ggml import GGMLType
+from tests.parity import check_close
 
 pytestmark = pytest.mark.gpu
+THREADS = os.cpu_count() or 1
 
 
-def test_noalloc_matches_the_allocating_entry_point_twice():
+def _call(L, t, x, w, M, K, N):
     import torch
     from laplace_b200 import device
+    xd = torch.from_numpy(x).cuda()
+    wd = device.upload_weights(w)
+    y_ref = device.gemm(xd, wd, t, M, K, N)                       # existing entry point (tensor-core path)
+    assert L.laplace_cuda_last_path() == 2
+    y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    rc = L.laplace_cuda_gemm_noalloc_dev(xd.data_ptr(), wd.data_ptr(), int(t), y.data_ptr(), M, K, N,
+                                         torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.laplace_cuda_last_error()
+    device.sync()
+    return y.cpu().numpy(), y_ref.cpu().numpy()
+
+
+def test_noalloc_matches_the_allocating_entry_point_twice(oracle):
+    from laplace_b200 import device
     L = device.lib()
-    t = int(GGMLType.Q4_K)
-    stream = torch.cuda.current_stream().cuda_stream
     # two calls in a row with different shapes and data: the shared array keeps the previous
     # call's contents, so the second call also checks that nothing stale leaks through
-    for M, K, N, seed in ((200, 1024, 136, 91), (96, 2816, 256, 93)):
+    for t, M, K, N, seed in ((GGMLType.Q4_K, 200, 1024, 136, 91), (GGMLType.Q4_K, 96, 2816, 256, 93)):
         w = synth.weights(t, K, N, seed=seed, how="random")
         x = synth.normal_f32(seed + 1, (M, K))
-        xd = torch.from_numpy(x).cuda()
-        wd = device.upload_weights(w)
-        y_ref = device.gemm(xd, wd, t, M, K, N)                       # existing entry point (tensor-core path)
-        assert L.laplace_cuda_last_path() == 2
-        y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
-        rc = L.laplace_cuda_gemm_noalloc_dev(xd.data_ptr(), wd.data_ptr(), t, y.data_ptr(), M, K, N, stream)
-        assert rc == 0, L.laplace_cuda_last_error()
-        device.sync()
-        a, b = y.cpu().numpy(), y_ref.cpu().numpy()
+        a, b = _call(L, t, x, w, M, K, N)
         # same kernels on the same inputs: the tests' tolerance (1e-5 relative L2) is met with equality
         assert np.isfinite(a).all()
         assert np.linalg.norm(a.astype(np.float64) - b) <= 1e-5 * np.linalg.norm(b)
         assert np.array_equal(a, b)
+        check_close(a, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"noalloc vs oracle {M}x{K}x{N}")
+
+
+@pytest.mark.parametrize("t,M,K,N", [(GGMLType.Q4_K, 512, 4096, 1024),      # the K-split's partial sums do not fit the array: runs unsplit
+                                     (GGMLType.Q6_K, 72, 2048, 200),        # the other type the prefill kernels take
+                                     (GGMLType.Q4_K, 640, 4096, 128)])      # scratch just under the array's size
+def test_noalloc_other_plans_and_types(oracle, t, M, K, N):
+    from laplace_b200 import device
+    L = device.lib()
+    w = synth.weights(t, K, N, seed=95, how="affine")
+    x = synth.normal_f32(96, (M, K))
+    a, b = _call(L, t, x, w, M, K, N)
+    check_close(a, b.astype(np.float64), "noalloc vs the allocating entry point")
+    check_close(a, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"noalloc vs oracle {t.name} {M}x{K}x{N}")
 
 
 def test_noalloc_rejects_what_it_cannot_serve():
