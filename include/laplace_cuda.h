@@ -162,11 +162,11 @@ int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, i
  * that cudaMalloc would fail or fragment them, and latency-bound loops that cannot take the
  * allocator's locks or the implicit device synchronisation of cudaFree. Same arguments as
  * laplace_cuda_gemm_dev and the same result (bit-identical whenever the call fits the array with the same
- * K-split that entry point would choose, else equal to fp32 rounding); the quantized activations go to a 6 MiB array built into the
- * library (held by every GPU that loads it) instead of a cudaMalloc'd buffer.
+ * K-split that entry point would choose, else equal to fp32 rounding); the quantized activations go to a
+ * 10 MiB array built into the library (held by every GPU that loads it) instead of a cudaMalloc'd buffer.
  *   - LAPLACE_ERR_LIMIT when the call needs more scratch than the array holds: about
- *     2.3 * pad128(M) * K + M * K / 8 bytes (M = 512, K = 4096: 4.75 MiB);
- *     LAPLACE_ERR_ARG for shapes that are not the prefill case (decode calls use no scratch).
+ *     4.13 * pad128(M) * K bytes for Q4_K (M = 512, K = 4096: 8.3 MiB), 2.3 * pad128(M) * K + M * K / 8
+ *     for Q6_K; LAPLACE_ERR_ARG for shapes that are not the prefill case (decode calls use no scratch).
  *   - The first call on a device looks the array's address up (cudaGetSymbolAddress); make
  *     that call before any stream capture begins.
  *   - All calls share the one array and it keeps the last call's contents (what must start

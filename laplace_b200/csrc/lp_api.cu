@@ -116,6 +116,7 @@ int dispatch_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float* y,
     if (M <= 0 || N <= 0 || K <= 0) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
     if (K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm: K=%d is not a multiple of %d", K, block_elems(type));
     // Prefill: tensor-core GEMM where one exists for the type.
+    if (gemm_sa_supports(type, M, K, N)) return launch_gemm_sa(x, w, type, y, M, K, N, st);
     if (gemm_tc_supports(type, M, K, N)) return launch_gemm_tc(x, w, type, y, M, K, N, st);
     // Small M (or a type without a tensor-core kernel yet): one streaming pass
     // per group of up to 8 activation rows.
@@ -230,6 +231,7 @@ void laplace_cuda_shutdown(void) {
     g_dx.release(); g_dy.release(); g_dw.release(); g_didx.release(); g_dq.release();
     g_hx.release(); g_hy.release();
     release_gemm_tc_scratch();
+    release_gemm_sa_scratch();
     release_moe_grouped_scratch();
     release_moe_ffn_scratch();
     cudaFreeHost(g_ctx.h_err);

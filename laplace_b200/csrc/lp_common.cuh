@@ -89,6 +89,12 @@ int launch_allgather_wait(const PeerOut& po, cudaStream_t st);
 bool gemm_tc_supports(uint32_t type, int M, int K, int N);
 int  launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st);
 void release_gemm_tc_scratch();
+// Tensor-core prefill GEMM with the activation scales folded into the operand (lp_gemm_sa.cu): Q4_K.
+bool gemm_sa_supports(uint32_t type, int M, int K, int N);
+int  launch_gemm_sa(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st);
+int  launch_gemm_sa_prealloc(uint8_t* scratch, size_t cap, const float* x, const uint8_t* w, uint32_t type, float* y,
+                             int M, int K, int N, cudaStream_t st);
+void release_gemm_sa_scratch();
 // Expert-grouped matmul over (token, expert) pairs on the tensor cores (lp_moe_grouped.cuh).
 bool moe_grouped_supports(uint32_t type, int K, int N);
 int  launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,

@@ -916,7 +916,7 @@ int launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, in
 // The array is part of every context that loads the library (NOALLOC_SCRATCH_BYTES of HBM
 // per GPU until the process exits). In host code its name is only a handle; the device
 // address comes from cudaGetSymbolAddress, asked once per device with that device current.
-constexpr size_t NOALLOC_SCRATCH_BYTES = 6u << 20;     // 6 MiB: e.g. M = 512, K = 4096 needs 4.75 MiB
+constexpr size_t NOALLOC_SCRATCH_BYTES = 10u << 20;    // 10 MiB: e.g. Q4_K, M = 512, K = 4096 needs 8.2 MiB
 static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
 
 namespace {
@@ -932,7 +932,8 @@ extern "C" int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, u
     Context& c = ctx();
     if (!c.ready) return fail(LAPLACE_ERR_STATE, "laplace_cuda_init has not been called (or found no GPU)");
     if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm_noalloc: null pointer");
-    int rc = check_gemm_tc_args(x, w, type, M, K, N);
+    const bool sa = gemm_sa_supports(type, M, K, N);          // which prefill kernel laplace_cuda_gemm_dev would run
+    int rc = sa ? LAPLACE_OK : check_gemm_tc_args(x, w, type, M, K, N);
     if (rc == LAPLACE_UNSUPPORTED)
         return fail(LAPLACE_ERR_ARG, "gemm_noalloc: only the prefill shapes are served here (M > 8; Q4_K with K %% 256 == 0 or "
                                      "Q6_K with K %% 2048 == 0); decode calls (M <= 8) use no scratch at all, call "
@@ -941,11 +942,14 @@ extern "C" int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, u
     // the same K-split as laplace_cuda_gemm_dev (hence bit-identical results) whenever its partial results fit
     // the array too; otherwise no split (results then agree to fp32 rounding)
     const bool can_split = (static_cast<long long>(M) * N) % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
-    ScratchPlan sp = plan_scratch(M, K, N, type, can_split);
-    if (sp.total() > NOALLOC_SCRATCH_BYTES) sp = plan_scratch(M, K, N, type, false);
-    if (sp.total() > NOALLOC_SCRATCH_BYTES)
-        return fail(LAPLACE_ERR_LIMIT, "gemm_noalloc: M=%d K=%d needs %zu bytes of scratch, the built-in array holds %zu",
-                    M, K, sp.total(), NOALLOC_SCRATCH_BYTES);
+    ScratchPlan sp{};
+    if (!sa) {
+        sp = plan_scratch(M, K, N, type, can_split);
+        if (sp.total() > NOALLOC_SCRATCH_BYTES) sp = plan_scratch(M, K, N, type, false);
+        if (sp.total() > NOALLOC_SCRATCH_BYTES)
+            return fail(LAPLACE_ERR_LIMIT, "gemm_noalloc: M=%d K=%d needs %zu bytes of scratch, the built-in array holds %zu",
+                        M, K, sp.total(), NOALLOC_SCRATCH_BYTES);
+    }
     if (g_noalloc_dev != c.device) {
         // first call on this device: resolve the array's device address (the library is bound to c.device,
         // make sure it is the current one for the lookup)
@@ -959,6 +963,7 @@ extern "C" int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, u
         g_noalloc_ptr = static_cast<uint8_t*>(ptr);
         g_noalloc_dev = c.device;
     }
-    return gemm_tc_on_scratch(g_noalloc_ptr, sp, x, w, type, y, M, K, N,
-                              stream ? static_cast<cudaStream_t>(stream) : c.stream);
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : c.stream;
+    if (sa) return launch_gemm_sa_prealloc(g_noalloc_ptr, NOALLOC_SCRATCH_BYTES, x, w, type, y, M, K, N, st);
+    return gemm_tc_on_scratch(g_noalloc_ptr, sp, x, w, type, y, M, K, N, st);
 }

@@ -53,7 +53,7 @@ def test_noalloc_matches_the_allocating_entry_point_twice(oracle):
 
 @pytest.mark.parametrize("t,M,K,N", [(GGMLType.Q4_K, 512, 4096, 1024),      # the K-split's partial sums do not fit the array: runs unsplit
                                      (GGMLType.Q6_K, 72, 2048, 200),        # the other type the prefill kernels take
-                                     (GGMLType.Q4_K, 640, 4096, 128)])      # scratch just under the array's size
+                                     (GGMLType.Q4_K, 500, 4096, 128)])      # scratch close to the array's size, K-split kept
 def test_noalloc_other_plans_and_types(oracle, t, M, K, N):
     from laplace_b200 import device
     L = device.lib()
@@ -71,7 +71,7 @@ def test_noalloc_rejects_what_it_cannot_serve():
     t = int(GGMLType.Q4_K)
     xd = torch.zeros(16, device="cuda")
     wd = torch.zeros(4096, dtype=torch.uint8, device="cuda")
-    # beyond the built-in array: 1024 x 8192 needs ~19 MiB
+    # beyond the built-in array: 1024 x 8192 needs ~33 MiB
     rc = L.laplace_cuda_gemm_noalloc_dev(xd.data_ptr(), wd.data_ptr(), t, xd.data_ptr(), 1024, 8192, 128, None)
     assert rc == -5 and b"scratch" in L.laplace_cuda_last_error()
     # a decode shape is not served here (it needs no scratch in the first place)
