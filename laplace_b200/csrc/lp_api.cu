@@ -232,6 +232,7 @@ void laplace_cuda_shutdown(void) {
     g_hx.release(); g_hy.release();
     release_gemm_tc_scratch();
     release_gemm_sa_scratch();
+    release_moe_sa_scratch();
     release_moe_grouped_scratch();
     release_moe_ffn_scratch();
     cudaFreeHost(g_ctx.h_err);
@@ -373,8 +374,9 @@ int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type
     if (!x || !w || !y || !pair_expert) return fail(LAPLACE_ERR_ARG, "moe_grouped: null pointer");
     if (n_pairs <= 0 || n_experts_total <= 0 || N <= 0 || K <= 0 || K % block_elems(type))
         return fail(LAPLACE_ERR_ARG, "moe_grouped: pairs=%d experts=%d K=%d N=%d", n_pairs, n_experts_total, K, N);
-    return launch_moe_grouped(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N,
-                              stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream;
+    if (moe_sa_supports(type, K, N)) return launch_moe_grouped_sa(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N, st);
+    return launch_moe_grouped(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N, st);
 }
 
 int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down,
@@ -389,8 +391,12 @@ int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uin
         hidden % block_elems(type_gate_up) || inter % block_elems(type_down) || (activation != 0 && activation != 1))
         return fail(LAPLACE_ERR_ARG, "moe_ffn: tokens=%d top_k=%d experts=%d hidden=%d inter=%d activation=%d",
                     n_tokens, top_k, n_experts_total, hidden, inter, activation);
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream;
+    if (moe_sa_supports(type_gate_up, hidden, 2 * inter) && moe_sa_supports(type_down, inter, hidden))
+        return launch_moe_ffn_sa(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, n_tokens, top_k, n_experts_total,
+                                 hidden, inter, activation, out, h_out, st);
     return launch_moe_ffn(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, n_tokens, top_k, n_experts_total,
-                          hidden, inter, activation, out, h_out, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+                          hidden, inter, activation, out, h_out, st);
 }
 
 int laplace_cuda_moe_pack_dev(const float* x, const int* top_idx, const float* top_w, int n_tokens, int hidden, int top_k,

@@ -95,6 +95,13 @@ int  launch_gemm_sa(const float* x, const uint8_t* w, uint32_t type, float* y, i
 int  launch_gemm_sa_prealloc(uint8_t* scratch, size_t cap, const float* x, const uint8_t* w, uint32_t type, float* y,
                              int M, int K, int N, cudaStream_t st);
 void release_gemm_sa_scratch();
+bool moe_sa_supports(uint32_t type, int K, int N);
+int  launch_moe_grouped_sa(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
+                           int P, int E, float* y, int K, int N, cudaStream_t st);
+int  launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
+                       const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
+                       float* out, float* h_out, cudaStream_t st);
+void release_moe_sa_scratch();
 // Expert-grouped matmul over (token, expert) pairs on the tensor cores (lp_moe_grouped.cuh).
 bool moe_grouped_supports(uint32_t type, int K, int N);
 int  launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,

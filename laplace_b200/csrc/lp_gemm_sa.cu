@@ -10,26 +10,29 @@
 // multiply-add per element per block, as much work as the MMA itself, plus a hand-off per block. Here the scale
 // goes INTO the activation operand instead: a[m,k] = 2^e_m * d_x[m,b] * q_x[m,k] (fp32, e_m a per-row exponent that
 // brings the row's largest value to 2^13), split into two fp16 pieces a = hi + lo that carry 22 bits of it. The
-// weight operand is sc * nibble <= 945, exact in fp16. Two MMAs per 16-value step then accumulate, in fp32, a whole
-// super-block (256 values) per drain:
-//   F[n,m]  = sum_{k in sb} (sc*nibble)[n,k] * (hi + lo)[m,k]                    (tcgen05.mma kind::f16, 2 x 16 steps)
-//   G[n,m]  = sum_{j<8} mn[n,sb,j] * (ghi + glo)[m,8sb+j],  g = 2^e_m / 64 * sum_x   (one more K = 16 step)
-//   y[m,n] += 2^-e_m * ( d[n,sb] * F - 64 dmin[n,sb] * G )                          (CUDA cores, once per super-block)
-// Products are exact; what is rounded is the split of a (2^-22 relative) and the fp32 accumulation, which the
-// reference also does in fp32 in another order. Integer block sums are still exact whenever the activations are:
-// a block whose scale is a power of two gives lo = 0 and an exact hi, hence an exact integer times the scale.
+// weight operand is sc * nibble <= 945, exact in fp16. The tensor core accumulates, in fp32, a whole super-block
+// (256 values) per drain:
+//   F_hi[n,m], F_lo[n,m] = sum_{k in sb} (sc*nibble)[n,k] * hi[m,k], ... * lo[m,k]        (tcgen05.mma kind::f16)
+//   y[m,n] += 2^-e_m * ( d[n,sb] * (F_hi + F_lo) - sum_{j<8} (dmin * mn_j)[n,sb] * g[m,8sb+j] ),   g = 2^e_m * sum_x
+// on CUDA cores once per super-block; the min term is the reference's own fp32 arithmetic. Products are exact;
+// what is rounded is the split of a (2^-22 relative) and the fp32 accumulation, which the reference also does in fp32
+// in another order. Integer block sums are still exact whenever the activations are: a block whose scale is a power
+// of two gives lo = 0 and an exact hi, hence an exact integer times the scale.
 //
-// Roles of the operands: WEIGHT rows sit on the MMA's M side (128 TMEM lanes), TOKENS on its N side (16 .. 128
-// columns), so a tile with few tokens - an expert of a mixture-of-experts layer with 16 tokens - costs a
-// proportionally short MMA, and the per-super-block weight scales are per-lane scalars in the drain.
+// Roles of the operands: WEIGHT rows sit on the MMA's M side (128 TMEM lanes), TOKENS on its N side, the lo piece
+// stacked behind the hi piece (up to 2 x 128 columns), so a tile with few tokens - an expert of a mixture-of-experts
+// layer with 16 tokens - costs a proportionally short MMA, the per-super-block weight scales are per-lane scalars in
+// the drain, and each 16-value step is ONE instruction: a single thread issues a tcgen05.mma about every 115 cycles
+// however small it is, so few wide instructions beat many narrow ones.
 //
 // One 512-thread CTA per SM, persistent over tiles of 128 weight rows x up to 128 tokens:
 //   warp 0      TMA: activation operand tiles (hi and lo piece, 64 k x tokens, 128-byte swizzle)
 //   warp 1      MMA issue (one lane); owns the TMEM allocation
-//   warp 3      TMA: packed Q4_K super-blocks (128 rows x 144 bytes) and the g operand (4 super-blocks per tile)
-//   warps 4-7   converters: packed super-block -> fp16 weight operand tile (thread = weight row), the row's
-//               d / dmin into a table, its mins into the G operand
-//   warps 8-15  drain: tcgen05.ld of F and G (double buffered in TMEM) once per super-block, running y in registers
+//   warp 3      TMA: packed Q4_K super-blocks (128 rows x 144 bytes) and the tiles of activation block sums
+//   warps 4-7   converters: packed super-block -> fp16 weight operand tile (thread = weight row), and the row's
+//               d and dmin * mn_j into a table for the drain
+//   warps 8-15  drain: tcgen05.ld of the accumulator (double buffered in TMEM) once per super-block, running y in
+//               registers
 // All mbarrier waits are bounded; a wait that gives up raises the status word and every role leaves its loop.
 #include <cuda_fp16.h>
 
@@ -44,33 +47,34 @@ namespace {
 using namespace tc;
 
 constexpr int TW = 128;                            // weight rows per tile (MMA M)
-constexpr int TT = 128;                            // most tokens per tile (MMA N)
+constexpr int TT = 128;                            // most tokens per tile
 constexpr int BKC = 64;                            // k per pipeline stage
 constexpr int STAGES = 3;
 constexpr int RAW_STAGES = 2;
 constexpr int RAW_TILE = TW * Q4_K_BYTES;          // 18 KB
-constexpr int OP_TILE = 128 * BKC * 2;             // 16 KB: 128 rows of 64 fp16
-constexpr int TABN = 4;                            // ring of per-super-block (d, -64 dmin) tables
+constexpr int W_TILE = TW * BKC * 2;               // 16 KB: 128 rows of 64 fp16
+constexpr int A_TILE = 2 * TT * BKC * 2;           // 32 KB: the hi rows, then the lo rows
+constexpr int TABN = 4;                            // ring of per-super-block weight-scale tables and g tiles
+constexpr int TAB_ROW = 12;                        // floats per weight row: d, -dmin*mn[0..7], 3 unused
+constexpr int G_TILE = (TT / 2) * 16 * 4;          // 4 KB: per token pair 8 x (g[even token], g[odd token])
 constexpr int THREADS = 512;
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TM_F = 0, TM_G = 256;           // two buffers of 128 columns each
+constexpr uint32_t TMEM_COLS = 512;                // two accumulators of 256 columns (hi | lo)
 
 constexpr uint32_t OFF_W = 0;
-constexpr uint32_t OFF_AH = OFF_W + STAGES * OP_TILE;
-constexpr uint32_t OFF_AL = OFF_AH + STAGES * OP_TILE;
-constexpr uint32_t OFF_GM = OFF_AL + STAGES * OP_TILE;      // mins operand: 128 weight rows x (4 super-blocks x 16 k)
-constexpr uint32_t OFF_GS = OFF_GM + OP_TILE;               // g operand: tokens x (4 super-blocks x 16 k)
-constexpr uint32_t OFF_RAW = OFF_GS + OP_TILE;
+constexpr uint32_t OFF_A = OFF_W + STAGES * W_TILE;
+constexpr uint32_t OFF_RAW = OFF_A + STAGES * A_TILE;
 constexpr uint32_t OFF_TAB = OFF_RAW + RAW_STAGES * RAW_TILE;
-constexpr uint32_t OFF_BAR = OFF_TAB + TABN * TW * 8;
+constexpr uint32_t OFF_G = OFF_TAB + TABN * TW * TAB_ROW * 4;
+constexpr uint32_t OFF_BAR = OFF_G + TABN * G_TILE;
 constexpr uint32_t BAR_FULL_A = OFF_BAR, BAR_FULL_W = BAR_FULL_A + 8 * STAGES, BAR_EMPTY = BAR_FULL_W + 8 * STAGES,
                    BAR_RAW_FULL = BAR_EMPTY + 8 * STAGES, BAR_RAW_EMPTY = BAR_RAW_FULL + 8 * RAW_STAGES,
                    BAR_TMEM_FULL = BAR_RAW_EMPTY + 8 * RAW_STAGES, BAR_TMEM_EMPTY = BAR_TMEM_FULL + 16,
-                   BAR_G_FULL_S = BAR_TMEM_EMPTY + 16, BAR_G_FULL_M = BAR_G_FULL_S + 8, BAR_G_EMPTY = BAR_G_FULL_M + 32,
-                   BAR_TAB_EMPTY = BAR_G_EMPTY + 8, OFF_TMEM_PTR = BAR_TAB_EMPTY + 8 * TABN, OFF_ABORT = OFF_TMEM_PTR + 8;
+                   BAR_G_FULL = BAR_TMEM_EMPTY + 16, BAR_TAB_EMPTY = BAR_G_FULL + 8 * TABN,
+                   OFF_TMEM_PTR = BAR_TAB_EMPTY + 8 * TABN, OFF_ABORT = OFF_TMEM_PTR + 8;
 constexpr uint32_t SMEM_BYTES = OFF_ABORT + 8 + 1024;       // + slack for the 1024-byte alignment
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-static_assert(OFF_RAW % 128 == 0 && RAW_TILE % 128 == 0, "TMA destinations are 128-byte aligned");
+static_assert(OFF_RAW % 128 == 0 && RAW_TILE % 128 == 0 && OFF_G % 128 == 0, "TMA destinations are 128-byte aligned");
+static_assert(OFF_A % 1024 == 0 && A_TILE % 1024 == 0 && W_TILE % 1024 == 0, "swizzled tiles are 1024-byte aligned");
 
 struct SaParams {
     float*       y;            // [rows of y][N]
@@ -91,7 +95,7 @@ struct SaParams {
     float*       y_part;
 };
 
-struct TileRef { int m0, n0, wrow0, nt, sb0, sb1, ks; };     // nt = tokens of the tile (the MMA's N is nt rounded up to 16)
+struct TileRef { int m0, n0, wrow0, nt, sb0, sb1, ks; };     // nt = tokens of the tile
 __device__ __forceinline__ TileRef tile_ref(const SaParams& p, int tile) {
     const int nsb = p.K / 256;
     if (p.tile_tab) {
@@ -108,12 +112,13 @@ __device__ __forceinline__ TileRef tile_ref(const SaParams& p, int tile) {
 __device__ __forceinline__ int tile_count(const SaParams& p) {
     return p.tile_tab ? __ldg(p.n_tiles_dev) : p.tiles_m * p.tiles_n * p.ksplit;
 }
-// Activation boxes come in four heights; a tile uses the smallest that holds its tokens.
+// Activation boxes come in four heights (16, 32, 64, 128 rows); a tile uses the smallest that holds its tokens.
+// In shared memory and in TMEM the lo piece follows the hi piece at a distance of one box height.
 __device__ __forceinline__ int box_bucket(int nt) { return nt <= 16 ? 0 : nt <= 32 ? 1 : nt <= 64 ? 2 : 3; }
 
 struct SaMaps {
     CUtensorMap a[4];      // activation pieces, [2 * m_pad][K] fp16, boxes of 64 k x {16, 32, 64, 128} rows, 128-byte swizzle
-    CUtensorMap g[4];      // g pieces, [m_pad][K/256 * 16] fp16, same boxes
+    CUtensorMap g[4];      // block sums, [m_pad / 2][K/256 * 16] fp32, boxes of 16 x {8, 16, 32, 64} token pairs
     CUtensorMap w;         // packed weights as bytes, rows of K/256 * 144 bytes, boxes of 144 bytes x 128 rows
 };
 
@@ -139,10 +144,10 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             mbar_init(sbase + BAR_TMEM_FULL + 8 * t, 1);     // tcgen05.commit
             mbar_init(sbase + BAR_TMEM_EMPTY + 8 * t, 8);    // one arrive per drain warp
         }
-        mbar_init(sbase + BAR_G_FULL_S, 1);
-        for (int j = 0; j < 4; ++j) mbar_init(sbase + BAR_G_FULL_M + 8 * j, 4);
-        mbar_init(sbase + BAR_G_EMPTY, 1);                   // tcgen05.commit
-        for (int t = 0; t < TABN; ++t) mbar_init(sbase + BAR_TAB_EMPTY + 8 * t, 8);
+        for (int t = 0; t < TABN; ++t) {
+            mbar_init(sbase + BAR_G_FULL + 8 * t, 1);
+            mbar_init(sbase + BAR_TAB_EMPTY + 8 * t, 8);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -159,9 +164,7 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
 
     // Counters every role advances in the same order:
     //   it   64-k chunk counter, main-ring stage = it % STAGES
-    //   sbc  super-block counter: TMEM buffer = sbc & 1, raw slot = sbc % RAW_STAGES, table slot = sbc % TABN
-    //   gg   group counter: a group is up to four consecutive super-blocks of one tile, sharing one G operand tile;
-    //        super-block j of its group uses the j-th 32-byte slice of the tile's 128-byte rows
+    //   sbc  super-block counter: accumulator = sbc & 1, raw slot = sbc % RAW_STAGES, table / g slot = sbc % TABN
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp == 0 && lane == 0) {
@@ -171,13 +174,13 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const TileRef tr = tile_ref(p, tile);
                 const int bk = box_bucket(tr.nt);
-                const uint32_t bytes = static_cast<uint32_t>(16 << bk) * 128u * 2u;
+                const uint32_t piece = static_cast<uint32_t>(16 << bk) * 128u;
                 for (int kc = tr.sb0 * 4; kc < tr.sb1 * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort<false>(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, bytes);
-                    tma_load_2d(sbase + OFF_AH + s * OP_TILE, &maps.a[bk], kc * BKC, tr.m0, sbase + BAR_FULL_A + 8 * s);
-                    tma_load_2d(sbase + OFF_AL + s * OP_TILE, &maps.a[bk], kc * BKC, p.m_pad + tr.m0, sbase + BAR_FULL_A + 8 * s);
+                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, 2 * piece);
+                    tma_load_2d(sbase + OFF_A + s * A_TILE, &maps.a[bk], kc * BKC, tr.m0, sbase + BAR_FULL_A + 8 * s);
+                    tma_load_2d(sbase + OFF_A + s * A_TILE + piece, &maps.a[bk], kc * BKC, p.m_pad + tr.m0, sbase + BAR_FULL_A + 8 * s);
                 }
             }
             if (!ok) {
@@ -188,27 +191,21 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                 }
             }
         } else if (warp == 3 && lane == 0) {
-            // ---------------- TMA producer: packed weights (rows past N are zero-filled: d = 0, every scale 0),
-            // and per group the g operand tile. The latter is asked for after the raw tile of the group's second
-            // super-block, so that waiting for the previous group's G products never delays a weight copy.
-            int sbc = 0, gg = 0;
+            // ---------------- TMA producer: packed weights (rows past N are zero-filled: d = 0, every scale 0)
+            // and, per super-block, the tile of activation block sums ----------------
+            int sbc = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const TileRef tr = tile_ref(p, tile);
                 const int bk = box_bucket(tr.nt);
                 for (int sb = tr.sb0; sb < tr.sb1; ++sb, ++sbc) {
-                    const int q = sbc % RAW_STAGES;
+                    const int q = sbc % RAW_STAGES, slot = sbc % TABN;
                     if (!wait_or_abort<false>(sbase + BAR_RAW_EMPTY + 8 * q, ((sbc / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_RAW_FULL + 8 * q, RAW_TILE);
                     tma_load_2d(sbase + OFF_RAW + q * RAW_TILE, &maps.w, sb * Q4_K_BYTES, tr.wrow0 + tr.n0, sbase + BAR_RAW_FULL + 8 * q);
-                    const int j = (sb - tr.sb0) & 3;
-                    const int group_size = tr.sb1 - (sb - j) < 4 ? tr.sb1 - (sb - j) : 4;
-                    if (j == (group_size > 1 ? 1 : 0)) {
-                        if (!wait_or_abort<false>(sbase + BAR_G_EMPTY, (gg & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                        mbar_expect_tx(sbase + BAR_G_FULL_S, static_cast<uint32_t>(16 << bk) * 128u);
-                        tma_load_2d(sbase + OFF_GS, &maps.g[bk], (sb - j) * 16, tr.m0, sbase + BAR_G_FULL_S);
-                        ++gg;
-                    }
+                    if (!wait_or_abort<false>(sbase + BAR_TAB_EMPTY + 8 * slot, ((sbc / TABN) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(sbase + BAR_G_FULL + 8 * slot, static_cast<uint32_t>(8 << bk) * 64u);
+                    tma_load_2d(sbase + OFF_G + slot * G_TILE, &maps.g[bk], sb * 16, tr.m0 >> 1, sbase + BAR_G_FULL + 8 * slot);
                 }
             }
             if (!ok) {
@@ -216,48 +213,42 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                     const int v = sbc - 1 - k;
                     if (v >= 0) mbar_wait_bounded(sbase + BAR_RAW_FULL + 8 * (v % RAW_STAGES), (v / RAW_STAGES) & 1);
                 }
-                if (gg > 0) mbar_wait_bounded(sbase + BAR_G_FULL_S, (gg - 1) & 1);
+                for (int k = 0; k < TABN; ++k) {
+                    const int v = sbc - 1 - k;
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_G_FULL + 8 * (v % TABN), (v / TABN) & 1);
+                }
             }
         } else if (warp == 1 && lane == 0) {
-            // ---------------- MMA issue ----------------
-            int it = 0, sbc = 0, gg = 0;
-            uint32_t gpar = 0;                     // bit j: parity of the next completion of the j-th "mins written" barrier
+            // ---------------- MMA issue: per 16-value step one instruction over the stacked pieces, D columns
+            // [0, nt) = weights x hi, [box, box + nt) = weights x lo. (One thread issues an instruction roughly every
+            // 115 cycles however small it is, so one wide instruction beats two narrow ones.) ----------------
+            int it = 0, sbc = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const TileRef tr = tile_ref(p, tile);
-                const uint32_t idesc = idesc_f16_m128((tr.nt + 15) & ~15);
+                const uint32_t idesc = idesc_f16_m128((16 << box_bucket(tr.nt)) + ((tr.nt + 15) & ~15));
                 for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
-                    const int b = sbc & 1, j = (sb - tr.sb0) & 3;
+                    const int b = sbc & 1;
                     if (!wait_or_abort<true>(sbase + BAR_TMEM_EMPTY + 8 * b, ((sbc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
                     fence_after();
-                    const uint32_t f_tmem = tmem_base + TM_F + b * TT, g_tmem = tmem_base + TM_G + b * TT;
+                    const uint32_t f_tmem = tmem_base + b * 256;
                     for (int c = 0; c < 4; ++c, ++it) {
                         const int s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
                         if (!wait_or_abort<true>(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
                             !wait_or_abort<true>(sbase + BAR_FULL_W + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
                         fence_after();
-                        const uint64_t wdesc = smem_desc_sw128(sbase + OFF_W + s * OP_TILE);
-                        const uint64_t hdesc = smem_desc_sw128(sbase + OFF_AH + s * OP_TILE);
-                        const uint64_t ldesc = smem_desc_sw128(sbase + OFF_AL + s * OP_TILE);
+                        const uint64_t wdesc = smem_desc_sw128(sbase + OFF_W + s * W_TILE);
+                        const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
                             const uint64_t off = static_cast<uint64_t>(ks * 2);      // 32 bytes >> 4 inside the swizzle row
-                            mma_f16(f_tmem, wdesc + off, hdesc + off, idesc, (c | ks) != 0);
-                            mma_f16(f_tmem, wdesc + off, ldesc + off, idesc, 1);
+                            mma_f16(f_tmem, wdesc + off, adesc + off, idesc, (c | ks) != 0);
                         }
                         commit(sbase + BAR_EMPTY + 8 * s);                  // operands consumed -> producers
                     }
                     if (!ok) break;
-                    // G of this super-block: one K = 16 step on the j-th slice of the group's operand tiles
-                    if ((j == 0 && !wait_or_abort<true>(sbase + BAR_G_FULL_S, gg & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) ||
-                        !wait_or_abort<true>(sbase + BAR_G_FULL_M + 8 * j, (gpar >> j) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
-                    gpar ^= 1u << j;
-                    fence_after();
-                    mma_f16(g_tmem, smem_desc_sw128(sbase + OFF_GM) + static_cast<uint64_t>(j * 2),
-                            smem_desc_sw128(sbase + OFF_GS) + static_cast<uint64_t>(j * 2), idesc, 0);
-                    commit(sbase + BAR_TMEM_FULL + 8 * b);                  // F and G of the super-block complete -> drain
-                    if (j == 3 || sb == tr.sb1 - 1) { commit(sbase + BAR_G_EMPTY); ++gg; }      // the group's G operands are consumed
+                    commit(sbase + BAR_TMEM_FULL + 8 * b);                  // the super-block's products are complete -> drain
                 }
             }
         }
@@ -265,12 +256,12 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         // ---------------- converters: thread r owns weight row n0 + r ----------------
         const int r = threadIdx.x - 128;
-        int it = 0, sbc = 0, gg = 0;
+        int it = 0, sbc = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const TileRef tr = tile_ref(p, tile);
             for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
-                const int q = sbc % RAW_STAGES, slot = sbc % TABN, j = (sb - tr.sb0) & 3;
+                const int q = sbc % RAW_STAGES, slot = sbc % TABN;
                 const uint32_t raw = sbase + OFF_RAW + q * RAW_TILE + r * Q4_K_BYTES;      // this row's 144 bytes
                 if (!wait_or_abort<false>(sbase + BAR_RAW_FULL + 8 * q, (sbc / RAW_STAGES) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
                 const uint4 hdr = lds128(raw);
@@ -279,8 +270,16 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                 const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
                 const uint32_t mn_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
                 if (!wait_or_abort<false>(sbase + BAR_TAB_EMPTY + 8 * slot, ((sbc / TABN) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                reinterpret_cast<float2*>(smem + OFF_TAB)[slot * TW + r] =
-                    make_float2(half_bits_to_float(hdr.x), -64.0f * half_bits_to_float(hdr.x >> 16));
+                {
+                    // the row's scales for the drain: d, and -dmin * mn_j (exact in fp32, as the reference forms them)
+                    const float d = half_bits_to_float(hdr.x), ndmin = -half_bits_to_float(hdr.x >> 16);
+                    float4* trow = reinterpret_cast<float4*>(smem + OFF_TAB + (slot * TW + r) * (TAB_ROW * 4));
+                    trow[0] = make_float4(d, ndmin * static_cast<float>(mn_lo & 0xff), ndmin * static_cast<float>((mn_lo >> 8) & 0xff),
+                                          ndmin * static_cast<float>((mn_lo >> 16) & 0xff));
+                    trow[1] = make_float4(ndmin * static_cast<float>(mn_lo >> 24), ndmin * static_cast<float>(mn_hi & 0xff),
+                                          ndmin * static_cast<float>((mn_hi >> 8) & 0xff), ndmin * static_cast<float>((mn_hi >> 16) & 0xff));
+                    trow[2] = make_float4(ndmin * static_cast<float>(mn_hi >> 24), 0.f, 0.f, 0.f);
+                }
 #pragma unroll
                 for (int c = 0; c < 4; ++c, ++it) {
                     const uint4 qa = lds128(raw + 16 + 32 * c), qb = lds128(raw + 32 + 32 * c);
@@ -309,7 +308,7 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         x = __hfma2(*reinterpret_cast<const __half2*>(&b0), s2, o2); h[16 + 2 * i] = *reinterpret_cast<uint32_t*>(&x);
                         x = __hfma2(*reinterpret_cast<const __half2*>(&b1), s2, o2); h[16 + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&x);
                     }
-                    uint8_t* wrow = smem + OFF_W + s * OP_TILE + r * 128;
+                    uint8_t* wrow = smem + OFF_W + s * W_TILE + r * 128;
 #pragma unroll
                     for (int jj = 0; jj < 8; ++jj)
                         *reinterpret_cast<uint4*>(wrow + ((jj ^ (r & 7)) << 4)) = make_uint4(h[4 * jj], h[4 * jj + 1], h[4 * jj + 2], h[4 * jj + 3]);
@@ -321,33 +320,14 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                 // the packed super-block has been read: its slot may be refilled
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sbase + BAR_RAW_EMPTY + 8 * q);
-                // G operand, written last so that the wait for the previous group's products is short: k = 2 jj + piece
-                // -> mn_jj as fp16 (exact), 16 values = the j-th 32-byte slice of this row
-                if (j == 0) {
-                    if (!wait_or_abort<false>(sbase + BAR_G_EMPTY, (gg & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                }
-                {
-                    uint32_t gw[8];
-#pragma unroll
-                    for (int jj = 0; jj < 8; ++jj) {
-                        const uint32_t mw = jj < 4 ? mn_lo : mn_hi;
-                        const __half hv = __ushort2half_rn(static_cast<unsigned short>((mw >> (8 * (jj & 3))) & 0xff));
-                        const uint32_t hb = __half_as_ushort(hv);
-                        gw[jj] = hb | (hb << 16);
-                    }
-                    uint8_t* grow = smem + OFF_GM + r * 128;
-                    *reinterpret_cast<uint4*>(grow + (((2 * j) ^ (r & 7)) << 4)) = make_uint4(gw[0], gw[1], gw[2], gw[3]);
-                    *reinterpret_cast<uint4*>(grow + (((2 * j + 1) ^ (r & 7)) << 4)) = make_uint4(gw[4], gw[5], gw[6], gw[7]);
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(sbase + BAR_G_FULL_M + 8 * j);
-                }
-                if (j == 3 || sb == tr.sb1 - 1) ++gg;
             }
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ---------------- drain: lane = weight row (output column), 64 token columns per warp ----------------
+        // Once per super-block: y += d * (F_hi + F_lo) + sum_j (-dmin mn_j) * g_j, two token columns per packed
+        // instruction. The min term is the reference's own fp32 arithmetic (src/matmul_simd.cpp:263-279:
+        // acc_min += (dmin * m) * sum_x), not a tensor-core product.
         const int e8 = warp - 8;
         const int quad = e8 & 3, half = e8 >> 2;
         const uint32_t t_lane = static_cast<uint32_t>(quad * 32) << 16;
@@ -356,32 +336,58 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const TileRef tr = tile_ref(p, tile);
-            float acc[64];
+            const int box = 16 << box_bucket(tr.nt);
+            float2 acc[32];
 #pragma unroll
-            for (int c = 0; c < 64; ++c) acc[c] = 0.f;
+            for (int c = 0; c < 32; ++c) acc[c] = make_float2(0.f, 0.f);
             for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
                 const int b = sbc & 1, slot = sbc % TABN;
-                if (!wait_or_abort<false>(sbase + BAR_TMEM_FULL + 8 * b, (sbc >> 1) & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
+                if (!wait_or_abort<false>(sbase + BAR_TMEM_FULL + 8 * b, (sbc >> 1) & 1, abort_flag, p.err, DEV_TIMEOUT_MMA) ||
+                    !wait_or_abort<false>(sbase + BAR_G_FULL + 8 * slot, (sbc / TABN) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
                 fence_after();
-                const float2 dm = reinterpret_cast<const float2*>(smem + OFF_TAB)[slot * TW + wr];
+                const uint32_t trow = sbase + OFF_TAB + (slot * TW + wr) * (TAB_ROW * 4);
+                const uint4 t0 = lds128(trow), t1 = lds128(trow + 16);
+                const float dm8 = __uint_as_float(lds32(trow + 32));
+                const float2 dd = make_float2(__uint_as_float(t0.x), __uint_as_float(t0.x));
+                const float dm[8] = {__uint_as_float(t0.y), __uint_as_float(t0.z), __uint_as_float(t0.w), __uint_as_float(t1.x),
+                                     __uint_as_float(t1.y), __uint_as_float(t1.z), __uint_as_float(t1.w), dm8};
+                const uint32_t gbase = sbase + OFF_G + slot * G_TILE + half * 32 * 64;      // this warp's 32 token pairs
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (half * 64 + h * 32 < tr.nt) {                  // warp-uniform: columns past the tile's tokens hold nothing
-                        float f[32], g[32];
-                        ld32(tmem_base + t_lane + TM_F + b * TT + half * 64 + h * 32, f);
-                        ld32(tmem_base + t_lane + TM_G + b * TT + half * 64 + h * 32, g);
+                        float fh[32], fl[32];
+                        ld32(tmem_base + t_lane + b * 256 + half * 64 + h * 32, fh);
+                        ld32(tmem_base + t_lane + b * 256 + box + half * 64 + h * 32, fl);
                         wait_ld();
+                        if (h == 1 || half * 64 + 32 >= tr.nt) {
+                            // the accumulator is in registers: the MMA may overwrite it
+                            fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * b);
+                        }
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) acc[h * 32 + c] = fmaf(dm.y, g[c], fmaf(dm.x, f[c], acc[h * 32 + c]));
+                        for (int c2 = 0; c2 < 16; ++c2) {
+                            const int cp = h * 16 + c2;                // token pair of this warp
+                            float2 a = acc[cp];
+                            a = __ffma2_rn(dd, __fadd2_rn(make_float2(fh[2 * c2], fh[2 * c2 + 1]), make_float2(fl[2 * c2], fl[2 * c2 + 1])), a);
+#pragma unroll
+                            for (int jq = 0; jq < 4; ++jq) {
+                                const uint4 gv = lds128(gbase + cp * 64 + jq * 16);      // (g_j[even], g_j[odd], g_j+1[even], g_j+1[odd])
+                                a = __ffma2_rn(make_float2(dm[2 * jq], dm[2 * jq]), make_float2(__uint_as_float(gv.x), __uint_as_float(gv.y)), a);
+                                a = __ffma2_rn(make_float2(dm[2 * jq + 1], dm[2 * jq + 1]), make_float2(__uint_as_float(gv.z), __uint_as_float(gv.w)), a);
+                            }
+                            acc[cp] = a;
+                        }
+                    } else if (h == 0) {
+                        // nothing to read for this warp: release the accumulator at once
+                        fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * b);
                     }
                 }
-                // F, G and the table entry are in registers: the MMA and the converters may reuse them
-                fence_before();
+                // the table entry and the g tile have been read: the converters and the copy engine may reuse them
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * b);
-                    mbar_arrive(sbase + BAR_TAB_EMPTY + 8 * slot);
-                }
+                if (lane == 0) mbar_arrive(sbase + BAR_TAB_EMPTY + 8 * slot);
             }
             if (!ok) break;
             // y[token][n] = 2^-e_token * acc: for a fixed token the warp's 32 lanes write 32 consecutive floats
@@ -395,7 +401,8 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         const int row = tr.m0 + col;
                         int orow = p.out_row ? __ldg(p.out_row + row) : row;
                         if (p.out_identity && orow >= 0) orow = row;
-                        if (orow >= 0) ybase[static_cast<size_t>(orow) * p.N + n] = acc[c] * __ldg(p.inv_s + row);
+                        const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                        if (orow >= 0) ybase[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
                     }
                 }
             }
@@ -415,13 +422,14 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
 // written is the tensor-core operand built from them:
 //   hi, lo [k]      fp16 pieces of 2^e * (d * q[k]), e chosen so that the row's largest |x| lands in [2^13, 2^14);
 //                   within every four consecutive k the order is (0, 2, 1, 3), like the weight operand
-//   g [16 sb + 2 j + piece]   fp16 pieces of 2^e / 64 * (d * integer sum) of block 8 sb + j
+//   g               fp32 2^e * (d * integer sum) per block - the reference's ActQ8::sum, scaled like the row -
+//                   stored per PAIR of rows: g_pair[16 sb + 2 j + (row & 1)] for block 8 sb + j
 //   inv_s           2^-e
 // `load(b, t8)` returns values 4 t8 .. 4 t8 + 3 of block b of the row. The row is read twice (maximum, then
 // quantization); the second read hits L1 / L2.
 template <class Load>
 __device__ __forceinline__ void quantize_row_sa(Load load, int K, __half* __restrict__ hi_row, __half* __restrict__ lo_row,
-                                                __half* __restrict__ g_row, float* __restrict__ inv_s) {
+                                                float* __restrict__ g_pair, int odd, float* __restrict__ inv_s) {
     __shared__ float red[8];
     const int bpr = K / 32, grp = threadIdx.x >> 3, t8 = threadIdx.x & 7, groups = blockDim.x >> 3;
     float amax = 0.f;
@@ -441,7 +449,6 @@ __device__ __forceinline__ void quantize_row_sa(Load load, int K, __half* __rest
     if (ex == 0 || ex == 255) field = 127;
     field = field < 1 ? 1 : (field > 253 ? 253 : field);
     const float s = __uint_as_float(static_cast<uint32_t>(field) << 23);
-    const float gs = s * 0.015625f;
     if (threadIdx.x == 0) *inv_s = __uint_as_float(static_cast<uint32_t>(254 - field) << 23);
     const int iters = (bpr + groups - 1) / groups;
     for (int itn = 0; itn < iters; ++itn) {                    // whole warps iterate together: the 8-lane shuffles stay converged
@@ -472,17 +479,14 @@ __device__ __forceinline__ void quantize_row_sa(Load load, int K, __half* __rest
         if (t8 == 0) {
             const short slo = static_cast<short>(hs), shi = static_cast<short>(hs_hi);
             const float sum = __fmul_rn(d, static_cast<float>(static_cast<int>(slo) + static_cast<int>(shi)));
-            const float gv = __fmul_rn(sum, gs);
-            const __half gh = __float2half_rn(gv);
-            const __half gl = __float2half_rn(gv - __half2float(gh));
-            reinterpret_cast<__half2*>(g_row)[b] = __halves2half2(gh, gl);        // element 16 (b / 8) + 2 (b % 8) + piece = 2 b + piece
+            g_pair[2 * b + odd] = __fmul_rn(sum, s);          // element 16 (b / 8) + 2 (b % 8) + odd
         }
     }
 }
 
 struct SaOperand {          // operand buffers of one matmul
     __half* a;              // [2][m_pad][K]: hi rows, then lo rows
-    __half* g;              // [m_pad][K / 16]
+    float*  g;              // [m_pad / 2][K / 16]: block sums of a pair of rows, interleaved
     float*  inv_s;          // [m_pad]
     int     m_pad;
 };
@@ -492,7 +496,7 @@ __global__ void __launch_bounds__(256) quantize_sa_kernel(const float* __restric
     const float* xr = x + static_cast<size_t>(m) * K;
     quantize_row_sa([&](int b, int t8) { return __ldg(reinterpret_cast<const float4*>(xr + b * 32) + t8); }, K,
                     op.a + static_cast<size_t>(m) * K, op.a + (static_cast<size_t>(op.m_pad) + m) * K,
-                    op.g + static_cast<size_t>(m) * (K / 16), op.inv_s + m);
+                    op.g + static_cast<size_t>(m >> 1) * (K / 16), m & 1, op.inv_s + m);
 }
 
 // y = sum of the k-slices' partial results, slices added in index order.
@@ -543,13 +547,13 @@ Scratch g_scratch;
 
 struct OperandBytes { size_t a, g, s; size_t total() const { return a + g + s; } };
 OperandBytes operand_bytes(size_t m_pad, int K) {
-    return {align256(2 * m_pad * K * sizeof(__half)), align256(m_pad * (K / 16) * sizeof(__half)), align256(m_pad * sizeof(float))};
+    return {align256(2 * m_pad * K * sizeof(__half)), align256(m_pad / 2 * (K / 16) * sizeof(float)), align256(m_pad * sizeof(float))};
 }
 SaOperand carve_operand(uint8_t*& s, size_t m_pad, int K) {
     const OperandBytes ob = operand_bytes(m_pad, K);
     SaOperand op;
     op.a = reinterpret_cast<__half*>(s);      s += ob.a;
-    op.g = reinterpret_cast<__half*>(s);      s += ob.g;
+    op.g = reinterpret_cast<float*>(s);       s += ob.g;
     op.inv_s = reinterpret_cast<float*>(s);   s += ob.s;
     op.m_pad = static_cast<int>(m_pad);
     return op;
@@ -571,8 +575,8 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
     for (int bk = 0; bk < 4; ++bk) {
         if (!make_map_2d(&maps.a[bk], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, L.op.a, static_cast<uint64_t>(K), 2ull * L.op.m_pad,
                          static_cast<uint64_t>(K) * 2, BKC, 16u << bk, CU_TENSOR_MAP_SWIZZLE_128B, "activations") ||
-            !make_map_2d(&maps.g[bk], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, L.op.g, static_cast<uint64_t>(K / 16), static_cast<uint64_t>(L.op.m_pad),
-                         static_cast<uint64_t>(K / 16) * 2, 64, 16u << bk, CU_TENSOR_MAP_SWIZZLE_128B, "g operand"))
+            !make_map_2d(&maps.g[bk], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, L.op.g, static_cast<uint64_t>(K / 16), static_cast<uint64_t>(L.op.m_pad / 2),
+                         static_cast<uint64_t>(K / 16) * 4, 16, 8u << bk, CU_TENSOR_MAP_SWIZZLE_NONE, "block sums"))
             return LAPLACE_ERR_CUDA;
     }
     const uint64_t rb = row_bytes(LAPLACE_TYPE_Q4_K, K);
@@ -710,6 +714,270 @@ int launch_gemm_sa_prealloc(uint8_t* scratch, size_t cap, const float* x, const 
     if (pl.total() > cap)
         return fail(LAPLACE_ERR_LIMIT, "gemm: M=%d K=%d needs %zu bytes of scratch, the caller's area holds %zu", M, K, pl.total(), cap);
     return gemm_sa_on_scratch(scratch, pl, x, w, y, M, K, N, st);
+}
+
+
+// ---- expert-grouped matmul and fused expert FFN ---------------------------------------------------------------
+// Laplace runs a mixture-of-experts layer token by token: per token one fused_moe_gemm_idx call over its top-k
+// experts (gate/up, src/matmul.cpp:467-482, src/arch_gemma4.cpp:604), the gated activation (src/ops.cpp:128-176),
+// one fused_moe_gemm_multi call (down, src/matmul.cpp:484-500, src/arch_gemma4.cpp:626) and a weighted sum
+// (:634-638). With a batch of tokens every such call streams the selected experts again. Here all (token, expert)
+// pairs of the batch are grouped by expert on the device and every expert's weights meet all of its tokens in one
+// pass of the kernel above: for every pair p, y[p] = W[pair_expert[p]] . quantize(x[pair_row[p]]), which is what the
+// per-token calls compute (a pair's result does not depend on which other pairs share its tile). An expert's tokens
+// sit on the MMA's N side, padded to a multiple of 16 only, so an expert with 16 tokens costs an eighth of a full tile.
+namespace {
+
+// One block plans the whole call: pairs per expert, every pair's slot inside its expert, the first operand row of
+// every expert (counts padded to 16 rows), the operand row of every pair and the inverse map, and the tile tables
+// {first operand row, first weight row inside the expert, first weight row of the expert, tokens}: for every expert,
+// for every group of up to 128 of its tokens, one tile per 128 weight rows. A second table (another N over the same
+// row groups) serves the second matmul of a fused FFN; tiles_n2 = 0 leaves it out. Which slot a pair gets depends on
+// the order the atomics land in; results do not.
+__global__ void __launch_bounds__(1024) moe_plan_sa_kernel(const int* __restrict__ pair_expert, int P, int E, int rows_max,
+                                                           int* __restrict__ dst_row, int* __restrict__ out_row,
+                                                           int N1, int tiles_n1, int4* __restrict__ tab1, int* __restrict__ n_tiles1,
+                                                           int N2, int tiles_n2, int4* __restrict__ tab2, int* __restrict__ n_tiles2,
+                                                           int* err) {
+    extern __shared__ int sm[];
+    int* cnt = sm;              // [E] pairs per expert
+    int* base = sm + E;         // [E] first operand row
+    int* grp0 = sm + 2 * E;     // [E] row groups before the expert
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    for (int r = threadIdx.x; r < rows_max; r += blockDim.x) out_row[r] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = pair_expert[p];
+        int slot = -1;                     // the pair is skipped: negative = "not mine" (experts placed on another GPU),
+        if (e >= 0 && e < E) slot = atomicAdd(cnt + e, 1);
+        else if (e >= E) report_status(err, DEV_BAD_INDEX);      // too large = the host reports a bad argument
+        dst_row[p] = slot;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int rows = 0, groups = 0;
+        for (int e = 0; e < E; ++e) {
+            base[e] = rows;
+            grp0[e] = groups;
+            rows += (cnt[e] + 15) & ~15;
+            groups += (cnt[e] + TT - 1) / TT;
+        }
+        *n_tiles1 = groups * tiles_n1;
+        if (tiles_n2) *n_tiles2 = groups * tiles_n2;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int groups = (cnt[e] + TT - 1) / TT;
+        for (int g = 0; g < groups; ++g) {
+            const int nt = cnt[e] - g * TT < TT ? cnt[e] - g * TT : TT;
+            for (int t = 0; t < tiles_n1; ++t) tab1[(grp0[e] + g) * tiles_n1 + t] = make_int4(base[e] + g * TT, t * TW, e * N1, nt);
+            for (int t = 0; t < tiles_n2; ++t) tab2[(grp0[e] + g) * tiles_n2 + t] = make_int4(base[e] + g * TT, t * TW, e * N2, nt);
+        }
+    }
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int slot = dst_row[p];
+        if (slot < 0) continue;
+        const int r = base[pair_expert[p]] + slot;
+        dst_row[p] = r;
+        out_row[r] = p;
+    }
+}
+
+// quantize_sa_kernel with a row gather on the way in and a row scatter on the way out: pair p reads x row
+// src_rows[p] (p / src_div when src_rows is null: the top-k pairs of a token are consecutive) and writes operand
+// row dst_rows[p] (negative: a skipped pair).
+__global__ void __launch_bounds__(256) quantize_sa_mapped_kernel(const float* __restrict__ x, int K, const int* __restrict__ src_rows,
+                                                                 int src_div, const int* __restrict__ dst_rows, SaOperand op) {
+    const int p = blockIdx.x;
+    const int dr = __ldg(dst_rows + p);
+    if (dr < 0) return;
+    const float* xr = x + static_cast<size_t>(src_rows ? __ldg(src_rows + p) : p / src_div) * K;
+    quantize_row_sa([&](int b, int t8) { return __ldg(reinterpret_cast<const float4*>(xr + b * 32) + t8); }, K,
+                    op.a + static_cast<size_t>(dr) * K, op.a + (static_cast<size_t>(op.m_pad) + dr) * K,
+                    op.g + static_cast<size_t>(dr >> 1) * (K / 16), dr & 1, op.inv_s + dr);
+}
+
+__device__ __forceinline__ float act_swiglu(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+__device__ __forceinline__ float act_geglu(float g, float u) {
+    const float g3 = (g * g) * g;
+    const float gelu = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g3)));
+    return gelu * u;
+}
+
+// Operand rows of the down matmul from the gate/up result: operand row r of gu holds [gate(I) | up(I)];
+// h = act(gate) * up (ops::swiglu / ops::geglu, Laplace src/ops.cpp:128-176) is quantized like any activation row.
+// One CTA per pair; h_out (optional) receives h in pair order.
+__global__ void __launch_bounds__(256) moe_act_quant_sa_kernel(const float* __restrict__ gu, int I, int activation,
+                                                               const int* __restrict__ dst_rows, SaOperand op, float* __restrict__ h_out) {
+    const int p = blockIdx.x;
+    const int r = __ldg(dst_rows + p);
+    if (r < 0) return;
+    const float* row = gu + static_cast<size_t>(r) * (2 * I);
+    auto load = [&](int b, int t8) {
+        const float4 g = __ldg(reinterpret_cast<const float4*>(row + b * 32) + t8);
+        const float4 u = __ldg(reinterpret_cast<const float4*>(row + I + b * 32) + t8);
+        return activation == 1 ? make_float4(act_geglu(g.x, u.x), act_geglu(g.y, u.y), act_geglu(g.z, u.z), act_geglu(g.w, u.w))
+                               : make_float4(act_swiglu(g.x, u.x), act_swiglu(g.y, u.y), act_swiglu(g.z, u.z), act_swiglu(g.w, u.w));
+    };
+    if (h_out)
+        for (int i = threadIdx.x; i < I / 4; i += blockDim.x)
+            reinterpret_cast<float4*>(h_out + static_cast<size_t>(p) * I)[i] = load(i >> 3, i & 7);
+    quantize_row_sa(load, I, op.a + static_cast<size_t>(r) * I, op.a + (static_cast<size_t>(op.m_pad) + r) * I,
+                    op.g + static_cast<size_t>(r >> 1) * (I / 16), r & 1, op.inv_s + r);
+}
+
+// out[t][:] = sum over the token's live pairs, in slot order, of top_w[t][j] * dn[row of pair][:]
+__global__ void __launch_bounds__(256) moe_combine_sa_kernel(const float* __restrict__ dn, const int* __restrict__ dst_row,
+                                                             const float* __restrict__ top_w, int T, int top_k, int H,
+                                                             float* __restrict__ out) {
+    const int h4 = H / 4;
+    const long long total = static_cast<long long>(T) * h4;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / h4), c = static_cast<int>(i - static_cast<long long>(t) * h4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < top_k; ++j) {
+            const int r = __ldg(dst_row + t * top_k + j);
+            if (r < 0) continue;
+            const float wgt = __ldg(top_w + t * top_k + j);
+            const float4 v = __ldg(reinterpret_cast<const float4*>(dn + static_cast<long long>(r) * H) + c);
+            acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y);
+            acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
+        }
+        reinterpret_cast<float4*>(out + static_cast<long long>(t) * H)[c] = acc;
+    }
+}
+
+Scratch g_moe_scratch;
+
+// Upper bounds that hold for every routing of P pairs over E experts.
+struct GroupBounds { size_t rows, groups; };
+GroupBounds group_bounds(int P, int E) {
+    const size_t live = static_cast<size_t>(E < P ? E : P);
+    GroupBounds b;
+    b.rows = ((static_cast<size_t>(P) + 15 * live + TT - 1) / TT + 1) * TT;       // every expert pads to 16 rows; one box of slack
+    b.groups = static_cast<size_t>(P) / TT + live;
+    return b;
+}
+
+int launch_plan(const int* pair_expert, int P, int E, int rows_max, int* dst_row, int* out_row, int N1, int tiles_n1, int4* tab1,
+                int* n_tiles1, int N2, int tiles_n2, int4* tab2, int* n_tiles2, cudaStream_t st) {
+    Context& c = ctx();
+    const size_t sm = 3 * static_cast<size_t>(E) * sizeof(int);
+    if (sm > 40 * 1024) return fail(LAPLACE_ERR_LIMIT, "moe: %d experts are more than the planning kernel holds", E);
+    moe_plan_sa_kernel<<<1, 1024, sm, st>>>(pair_expert, P, E, rows_max, dst_row, out_row, N1, tiles_n1, tab1, n_tiles1,
+                                            N2, tiles_n2, tab2, n_tiles2, c.d_err);
+    c.launches++;
+    return cuda_check(cudaGetLastError(), "moe_plan launch");
+}
+
+int grid_for_tiles(size_t tiles_max) {
+    const size_t sms = static_cast<size_t>(ctx().sm_count);
+    return static_cast<int>(tiles_max < 1 ? 1 : (tiles_max < sms ? tiles_max : sms));
+}
+
+}  // namespace
+
+void release_moe_sa_scratch() { g_moe_scratch.release(); }
+
+bool moe_sa_supports(uint32_t type, int K, int N) { return gemm_sa_supports(type, 9, K, N); }
+
+int launch_moe_grouped_sa(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
+                          int P, int E, float* y, int K, int N, cudaStream_t st) {
+    if (!moe_sa_supports(type, K, N)) return LAPLACE_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
+        return fail(LAPLACE_ERR_ARG, "moe_grouped: x and w must be 16-byte aligned on the device");
+    if ((static_cast<size_t>(N) * row_bytes(type, K)) % 16)
+        return fail(LAPLACE_ERR_ARG, "moe_grouped: expert stride is not a 16-byte multiple");
+    Context& c = ctx();
+    const int tiles_n = (N + TW - 1) / TW;
+    const GroupBounds gb = group_bounds(P, E);
+    const size_t pair_bytes = align256(sizeof(int) * static_cast<size_t>(P)), out_bytes = align256(sizeof(int) * gb.rows);
+    const size_t tab_bytes = align256(sizeof(int4) * gb.groups * tiles_n);
+    const size_t total = operand_bytes(gb.rows, K).total() + pair_bytes + out_bytes + tab_bytes + 256;
+    int rc;
+    if ((rc = g_moe_scratch.ensure(total, st))) return rc;
+    uint8_t* s = static_cast<uint8_t*>(g_moe_scratch.p);
+    const SaOperand op = carve_operand(s, gb.rows, K);
+    int* dst_row = reinterpret_cast<int*>(s);       s += pair_bytes;
+    int* out_row = reinterpret_cast<int*>(s);       s += out_bytes;
+    int4* tab = reinterpret_cast<int4*>(s);         s += tab_bytes;
+    int* n_tiles = reinterpret_cast<int*>(s);
+    if ((rc = launch_plan(pair_expert, P, E, static_cast<int>(gb.rows), dst_row, out_row, N, tiles_n, tab, n_tiles, 0, 0, nullptr, nullptr, st)))
+        return rc;
+    quantize_sa_mapped_kernel<<<P, 256, 0, st>>>(x, K, pair_row, 1, dst_row, op);
+    c.launches++;
+    if ((rc = cuda_check(cudaGetLastError(), "moe quantize launch"))) return rc;
+    SaLaunch L{};
+    L.w = w; L.y = y; L.M = P; L.K = K; L.N = N; L.w_rows = static_cast<long long>(E) * N; L.op = op;
+    L.tile_tab = tab; L.n_tiles_dev = n_tiles; L.out_row = out_row;
+    L.tiles_m = 1; L.tiles_n = tiles_n; L.grid = grid_for_tiles(gb.groups * tiles_n);
+    rc = run_sa_kernel(L, st);
+    if (rc == LAPLACE_OK) c.last_path = 3;
+    return rc;
+}
+
+int launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
+                      const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
+                      float* out, float* h_out, cudaStream_t st) {
+    if (!moe_sa_supports(type_gu, H, 2 * I) || !moe_sa_supports(type_dn, I, H)) return LAPLACE_UNSUPPORTED;
+    if (I % 32 || H % 4) return fail(LAPLACE_ERR_ARG, "moe_ffn: H=%d I=%d", H, I);
+    if ((reinterpret_cast<uintptr_t>(w_gate_up) & 15) || (reinterpret_cast<uintptr_t>(w_down) & 15) ||
+        (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+        return fail(LAPLACE_ERR_ARG, "moe_ffn: x, out and the weights must be 16-byte aligned on the device");
+    if ((static_cast<size_t>(2 * I) * row_bytes(type_gu, H)) % 16 || (static_cast<size_t>(H) * row_bytes(type_dn, I)) % 16)
+        return fail(LAPLACE_ERR_ARG, "moe_ffn: expert stride is not a 16-byte multiple");
+    Context& c = ctx();
+    const int P = T * top_k;
+    const int tiles_n1 = (2 * I + TW - 1) / TW, tiles_n2 = (H + TW - 1) / TW;
+    const GroupBounds gb = group_bounds(P, E);
+    const size_t pair_bytes = align256(sizeof(int) * static_cast<size_t>(P)), out_bytes = align256(sizeof(int) * gb.rows);
+    const size_t tab1_bytes = align256(sizeof(int4) * gb.groups * tiles_n1), tab2_bytes = align256(sizeof(int4) * gb.groups * tiles_n2);
+    const size_t gu_bytes = align256(gb.rows * 2 * I * sizeof(float)), dn_bytes = align256(gb.rows * H * sizeof(float));
+    const size_t total = operand_bytes(gb.rows, H).total() + operand_bytes(gb.rows, I).total() + pair_bytes + out_bytes +
+                         tab1_bytes + tab2_bytes + gu_bytes + dn_bytes + 256;
+    int rc;
+    if ((rc = g_moe_scratch.ensure(total, st))) return rc;
+    uint8_t* s = static_cast<uint8_t*>(g_moe_scratch.p);
+    const SaOperand op1 = carve_operand(s, gb.rows, H);
+    const SaOperand op2 = carve_operand(s, gb.rows, I);
+    int* dst_row = reinterpret_cast<int*>(s);       s += pair_bytes;
+    int* out_row = reinterpret_cast<int*>(s);       s += out_bytes;
+    int4* tab1 = reinterpret_cast<int4*>(s);        s += tab1_bytes;
+    int4* tab2 = reinterpret_cast<int4*>(s);        s += tab2_bytes;
+    float* gu = reinterpret_cast<float*>(s);        s += gu_bytes;
+    float* dn = reinterpret_cast<float*>(s);        s += dn_bytes;
+    int* n_tiles1 = reinterpret_cast<int*>(s);
+    int* n_tiles2 = n_tiles1 + 1;
+    if ((rc = launch_plan(top_idx, P, E, static_cast<int>(gb.rows), dst_row, out_row, 2 * I, tiles_n1, tab1, n_tiles1, H, tiles_n2, tab2, n_tiles2, st)))
+        return rc;
+    quantize_sa_mapped_kernel<<<P, 256, 0, st>>>(x, H, nullptr, top_k, dst_row, op1);
+    c.launches++;
+    if ((rc = cuda_check(cudaGetLastError(), "moe quantize launch"))) return rc;
+
+    SaLaunch L{};
+    L.w = w_gate_up; L.y = gu; L.M = P; L.K = H; L.N = 2 * I; L.w_rows = static_cast<long long>(E) * 2 * I; L.op = op1;
+    L.tile_tab = tab1; L.n_tiles_dev = n_tiles1; L.out_row = out_row; L.out_identity = 1;      // gu stays in operand-row order
+    L.tiles_m = 1; L.tiles_n = tiles_n1; L.grid = grid_for_tiles(gb.groups * tiles_n1);
+    if ((rc = run_sa_kernel(L, st))) return rc;
+
+    moe_act_quant_sa_kernel<<<P, 256, 0, st>>>(gu, I, activation, dst_row, op2, h_out);
+    c.launches++;
+    if ((rc = cuda_check(cudaGetLastError(), "moe_act_quant launch"))) return rc;
+
+    SaLaunch L2{};
+    L2.w = w_down; L2.y = dn; L2.M = P; L2.K = I; L2.N = H; L2.w_rows = static_cast<long long>(E) * H; L2.op = op2;
+    L2.tile_tab = tab2; L2.n_tiles_dev = n_tiles2; L2.out_row = out_row; L2.out_identity = 1;
+    L2.tiles_m = 1; L2.tiles_n = tiles_n2; L2.grid = grid_for_tiles(gb.groups * tiles_n2);
+    if ((rc = run_sa_kernel(L2, st))) return rc;
+
+    const long long total4 = static_cast<long long>(T) * (H / 4);
+    long long blocks = (total4 + 255) / 256;
+    if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
+    moe_combine_sa_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(dn, dst_row, top_w, T, top_k, H, out);
+    c.launches++;
+    c.last_path = 4;
+    return cuda_check(cudaGetLastError(), "moe_combine launch");
 }
 
 }  // namespace lp
