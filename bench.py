@@ -48,6 +48,34 @@ def peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def parity_of(y, ref64):
+    """The parity figures printed with every measurement: relative L2 error and max-abs error over the output RMS
+    of the device result against the CPU oracle (float64 mode) on the very tensors that are timed."""
+    y = np.asarray(y, dtype=np.float64)
+    ref = np.asarray(ref64, dtype=np.float64)
+    rel = float(np.linalg.norm(y - ref) / max(np.linalg.norm(ref), 1e-30))
+    mx = float(np.abs(y - ref).max() / max(np.sqrt(np.mean(ref ** 2)), 1e-30))
+    return {"rel_l2": rel, "maxabs_rms": mx, "against": "CPU oracle (float64 accumulation of the reference's int8 path)",
+            "bar": {"rel_l2": 1e-5, "maxabs_rms": 1e-3}}
+
+
+def check_parity(y, ref64, what):
+    p = parity_of(y, ref64)
+    assert p["rel_l2"] <= 1e-5 and p["maxabs_rms"] <= 1e-3, f"{what}: parity against the oracle failed: {p}"
+    return p
+
+
+def profiled_traffic():
+    """DRAM bytes (read + write) of one launch of the headline kernel, from the ncu summary under profiles/."""
+    import re
+    f = ROOT / "profiles" / "gemv_stream_q4k_m1_k4096_n14336.md"
+    if f.exists():
+        m = re.search(r"dram bytes per launch \(read \+ write\):\s*([0-9]+)", f.read_text())
+        if m:
+            return int(m.group(1))
+    return None
+
+
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while the timed regions run."""
@@ -225,6 +253,11 @@ def gpu_arm(args):
         for c in range(N_COPIES):                        # y_loc is still needed by the host-pointer leg's check
             device.gemm(x, copies[c], TYPE_Q4_K, M_ROWS, K_DIM, n_loc, y=y_loc[c])
         device.sync()
+    # parity gate on the tensors that are timed: this rank's slice of copy 0 against the oracle
+    from tests import oracle_lib
+    orc = oracle_lib.Oracle()
+    parity = check_parity(y_loc[0].cpu().numpy(), orc.gemm(x_host, w_loc, TYPE_Q4_K, M_ROWS, K_DIM, n_loc, mode=1,
+                                                            threads=os.cpu_count() or 1), "headline GEMV")
     if world > 1:
         # the gathered result must be what one GPU computes over the whole matrix (last warm-up step's copy)
         c_last = (warmup - 1) % N_COPIES
@@ -328,6 +361,7 @@ def gpu_arm(args):
         assert np.array_equal(yh, y_loc[last].cpu().numpy()), "host-pointer result differs from the device-pointer result"
         lb.matmul_unregister_weights(region)
     prefill = prefill_leg(device, synth, torch, rank, world, dist) if not args.no_prefill else None
+    moe = moe_leg(device, synth, torch, dist, rank, world, steps=16, warmup=3, repeats=8, e2e=False) if not args.no_prefill else None
     decode = decode_leg(device, synth, torch) if (world == 1 and not args.no_prefill) else None
     clocks = sampler.stop() if rank == 0 else None
 
@@ -348,12 +382,13 @@ def gpu_arm(args):
                        "timing": f"CUDA events around {'one CUDA graph of ' if use_graph else ''}{steps} steps; median of {repeats} repeats; max over ranks"},
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "laplace_cuda_gemm with host x and y, synchronous, weights registered (resident) as at model load"},
+            "parity": parity,
             **({"note": gather_note} if gather_note else {}),
             "gpu_launches": (steps + 1 if fused else steps) if use_graph else int(launches_eager // max(repeats, 1)),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved if achieved else value / world, "peak": peak, "unit": "GB/s",
                          "frac": (achieved if achieved else value / world) / peak,
-                         "traffic": 33095936 if world == 1 else None,      # dram read + write bytes of one launch, from the ncu capture under profiles/
+                         "traffic": profiled_traffic() if world == 1 else None,      # dram read + write bytes of one launch (ncu summary under profiles/)
                          "peak_source": peak_src,
                          "kernel": "gemv_stream_kernel<Q4_K, M=1>", "algorithmic_bytes_per_launch": WEIGHT_BYTES // world},
         }
@@ -386,6 +421,8 @@ def gpu_arm(args):
                 line["cpu_baseline"]["also"] = {"error": str(exc)}
         if prefill:
             line["prefill"] = prefill
+        if moe:
+            line["moe"] = moe
         if decode:
             line["decode_shapes"] = decode
         print(json.dumps(line))
@@ -459,13 +496,17 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
     M = 512
     projs = [("q", 12, 4096, 4096), ("k", 12, 4096, 1024), ("v", 12, 4096, 1024), ("o", 12, 4096, 4096),
              ("gate", 12, 4096, 14336), ("up", 12, 4096, 14336), ("down", 14, 14336, 4096)]
+    from tests import oracle_lib
+    orc = oracle_lib.Oracle()
     L = device.lib()
     out, total_ms, total_ops = {}, 0.0, 0.0
-    xs = {K: torch.from_numpy(synth.normal_f32(2004 + K, (M, K))).cuda() for K in (4096, 14336)}
+    xs_host = {K: synth.normal_f32(2004 + K, (M, K)) for K in (4096, 14336)}
+    xs = {K: torch.from_numpy(xs_host[K]).cuda() for K in (4096, 14336)}
     for name, t, K, N in projs:
         sh = RowShards(L, N, rank, world)
         w_np = synth.weights(t, K, N, seed=1040 + N + K, how="random")
-        w = device.upload_weights(np.ascontiguousarray(sh.slice_rows(w_np)))
+        w_loc_np = np.ascontiguousarray(sh.slice_rows(w_np))
+        w = device.upload_weights(w_loc_np)
         y = torch.empty((M, sh.n_loc), dtype=torch.float32, device="cuda")
         y_full = torch.empty((M, N), dtype=torch.float32, device="cuda") if world > 1 else None
 
@@ -479,6 +520,9 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
         path = L.laplace_cuda_last_path()
         iters = 10 if path == 2 else 3
         torch.cuda.synchronize()
+        # parity gate on the tensors that are timed (this rank's slice)
+        par = check_parity(y.cpu().numpy(), orc.gemm(xs_host[K], w_loc_np, t, M, K, sh.n_loc, mode=1, threads=os.cpu_count() or 1),
+                           f"prefill {name}")
         # the timed calls are replayed from one CUDA graph (as a serving loop would), so that host launch cost
         # does not sit between the kernels and the collective
         g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
@@ -505,7 +549,8 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
             ms = float(tt.item())
         ops = 2.0 * M * N * K
         out[name] = {"type": "Q4_K" if t == 12 else "Q6_K", "K": K, "N": N, "ms": ms, "tops": ops / ms / 1e9,
-                     "kernel": "tcgen05 kind::f16 (exact block sums)" if path == 2 else "8-row streaming passes (no tensor-core kernel for this type yet)"}
+                     "kernel": "tcgen05 kind::f16" if path == 2 else "8-row streaming passes (no tensor-core kernel for this type yet)",
+                     "parity": {"rel_l2": par["rel_l2"], "maxabs_rms": par["maxabs_rms"]}}
         total_ms += ms
         total_ops += ops
         del w
@@ -516,42 +561,38 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
         peak_bf16 = float(json.loads(p.read_text())["bf16_tflops"])
     q4k_ops = sum(2.0 * M * N * K for _, t, K, N in projs if t == 12)
     q4k_ms = sum(out[n]["ms"] for n, t, _, _ in projs if t == 12)
+    # the dense tensor peaks of this GPU, measured now with a bare tcgen05.mma loop (int8: the denominator the target is
+    # stated on; fp16: the kind of MMA the kernel issues)
+    import ctypes as _C
+    peak_i8, peak_f16 = _C.c_double(0.0), _C.c_double(0.0)
+    assert L.laplace_cuda_debug_tensor_peak(1, _C.byref(peak_i8)) == 0, L.laplace_cuda_last_error()
+    assert L.laplace_cuda_debug_tensor_peak(0, _C.byref(peak_f16)) == 0, L.laplace_cuda_last_error()
+    layer_tops = total_ops / total_ms / 1e9
     return {"workload": "Llama-3-8B decoder layer, 7 projections, M=512 tokens (223.34 Gop)" +
                         ("" if world == 1 else f", N-split over {world} GPUs + NCCL all-gather of the [512, N/{world}] slices"),
             "ms_per_layer": total_ms,
             "tops": total_ops / total_ms / 1e9, "q4k_only_tops": q4k_ops / q4k_ms / 1e9,
-            "roofline": {"bound": "tensor", "achieved": q4k_ops / q4k_ms / 1e9 / world, "peak": peak_bf16, "unit": "TFLOP/s (per GPU)",
-                         "frac": q4k_ops / q4k_ms / 1e9 / peak_bf16 / world,
-                         "note": "the Q4_K kernel issues fp16 MMAs (exact integer block sums in fp32), so the measured bf16/fp16 "
-                                 "cuBLAS burst peak is its tensor roofline; against the derived int8 figure (2x) the fraction halves"},
+            "roofline": {"bound": "tensor", "achieved": layer_tops / world, "peak": peak_i8.value, "unit": "Top/s (per GPU)",
+                         "frac": layer_tops / world / peak_i8.value,
+                         "peak_source": "dense int8 rate measured in this run by a bare tcgen05.mma.kind::i8 loop on every SM",
+                         "also": {"fp16_peak_measured_bare_loop": peak_f16.value, "bf16_peak_cublas_burst": peak_bf16,
+                                  "frac_of_fp16_bare_loop": layer_tops / world / peak_f16.value,
+                                  "frac_of_bf16_cublas": layer_tops / world / peak_bf16,
+                                  "note": "the kernels issue fp16 MMAs, two per 16-value step (the activation travels as two fp16 "
+                                          "pieces that carry its block scale); operations counted are 2*M*N*K of the matmul"}},
             "projections": out}
 
 
-def moe_arm(args):
-    """`--workload moe`: the expert matmuls of one Qwen3-MoE-style layer (BASELINE.json configs[4]): 128 experts,
-    top-8, d_model 2048, expert width 768, Q4_K, 256 tokens. At N GPUs experts are placed E/N per GPU
-    (laplace_b200/moe.py); total work is fixed, so scaling is "strong". A step is one layer: exchange in,
-    the fused expert FFN (grouped gate/up matmul, gated activation, grouped down matmul, weighted sum), exchange out."""
-    import torch
-    import torch.distributed as dist
-    from laplace_b200 import device
-    from tests import synth
+def moe_leg(device, synth, torch, dist, rank, world, steps=32, warmup=4, repeats=12, e2e=True):
+    """The expert matmuls of one Qwen3-MoE-style layer (BASELINE.json configs[4]): 128 experts, top-8, d_model 2048,
+    expert width 768, Q4_K, 256 tokens. At N GPUs experts are placed E/N per GPU (laplace_b200/moe.py); total work is
+    fixed, so scaling is "strong". A step is one layer: exchange in, the fused expert FFN (grouped gate/up matmul,
+    gated activation, grouped down matmul, weighted sum), exchange out. Returns the figures of this leg (rank 0)."""
     from laplace_b200.moe import ExpertParallelMoE, device_fused_ffn, seeded_routing
+    from tests import oracle_lib
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        import datetime
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
-    L = device.lib(local)
     E, TOPK, H, I, T = 128, 8, 2048, 768, 256
     E_loc, T_loc = E // world, T // world
-    steps, warmup = max(1, min(args.steps, 64)), max(3, min(args.warmup, 8))
     # seeded Q4_K experts: 8 distinct experts of each matrix, repeated to E_loc (contents do not change the work)
     base_gu = synth.weights(TYPE_Q4_K, H, 8 * 2 * I, seed=3000 + rank, how="random")
     base_dn = synth.weights(TYPE_Q4_K, I, 8 * H, seed=3100 + rank, how="random")
@@ -561,18 +602,21 @@ def moe_arm(args):
     per_rank_bytes = gu_np.nbytes + dn_np.nbytes
     n_layers = max(2, -(-(300 << 20) // per_rank_bytes))          # rotate layers so that weights come from HBM, not L2
     ffn = device_fused_ffn(TYPE_Q4_K, TYPE_Q4_K, activation=0)
-    layers = []
-    for l in range(n_layers):
-        layers.append(ExpertParallelMoE(device.upload_weights(np.roll(gu_np, l * 16, axis=0)),
-                                        device.upload_weights(np.roll(dn_np, l * 16, axis=0)),
-                                        E, TOPK, H, I, None, rank, world, fused_ffn=ffn, device_exchange=True))
+
+    def make_layers(exchange):
+        return [ExpertParallelMoE(device.upload_weights(np.roll(gu_np, l * 16, axis=0)),
+                                  device.upload_weights(np.roll(dn_np, l * 16, axis=0)),
+                                  E, TOPK, H, I, None, rank, world, fused_ffn=ffn, device_exchange=True, exchange=exchange)
+                for l in range(n_layers)]
+
+    layers = make_layers("allgather")
     idx_np, wts_np = seeded_routing(3200, T, E, TOPK)
+    x_np = synth.normal_f32(3300, (T, H))
     sl = slice(rank * T_loc, (rank + 1) * T_loc)
-    x = torch.from_numpy(synth.normal_f32(3300, (T, H))[sl].copy()).cuda()
+    x = torch.from_numpy(x_np[sl].copy()).cuda()
     idx = torch.from_numpy(idx_np[sl].copy()).cuda()
     wts = torch.from_numpy(wts_np[sl].copy()).cuda()
     counts = np.bincount(idx_np.reshape(-1), minlength=E)
-
     outs = [None] * n_layers
 
     def step(i):
@@ -581,17 +625,28 @@ def moe_arm(args):
     for i in range(max(warmup, n_layers)):
         step(i)
     device.sync()
-    # self-check on rank 0: token 0 of layer 0 through the reference-shaped per-token calls on the same GPU data
+    parity = None
     if world == 1:
-        lay = layers[0]
-        gu = device.moe_gemv(x[0], lay.w_gate_up, TYPE_Q4_K, idx[0].contiguous(), H, 2 * I, per_expert_x=False)
-        from laplace_b200.moe import silu_mul
-        dn = device.moe_gemv(silu_mul(gu, I), lay.w_down, TYPE_Q4_K, idx[0].contiguous(), I, H, per_expert_x=True)
-        want = (dn * wts[0][:, None]).sum(dim=0)
-        got = layers[0].forward(x, idx, wts)[0]
+        # parity gate on the tensors that are timed: layer 0 against the oracle's per-token sequence (gate/up over the
+        # token's experts, SwiGLU, down, weighted sum; the down stage from the device's own activation values, since a
+        # last-bit difference of expf moves an int8 step)
+        orc = oracle_lib.Oracle()
+        threads = os.cpu_count() or 1
+        h_dev = torch.zeros((T * TOPK, I), dtype=torch.float32, device="cuda")
+        got = device.moe_ffn(x, layers[0].w_gate_up, layers[0].w_down, TYPE_Q4_K, TYPE_Q4_K, idx, wts, E, H, I, activation=0, h_out=h_dev)
         device.sync()
-        rel = float((got - want).abs().max() / want.pow(2).mean().sqrt())
-        assert rel < 2e-3, f"fused layer differs from per-token calls: {rel}"      # sanity only; parity lives in tests/
+        got, h_host = got.cpu().numpy(), h_dev.cpu().numpy()
+        gu = np.concatenate([orc.moe_gemv(x_np[t], gu_np, TYPE_Q4_K, idx_np[t], H, 2 * I, multi=False, mode=1, threads=threads) for t in range(T)])
+        g, u = gu[:, :I].astype(np.float32), gu[:, I:].astype(np.float32)
+        with np.errstate(over="ignore"):
+            p1 = check_parity(h_host, (g / (np.float32(1.0) + np.exp(-g))) * u, "MoE gate/up + SwiGLU")
+        want = np.zeros((T, H), dtype=np.float64)
+        for t in range(T):
+            dn = orc.moe_gemv(h_host[t * TOPK:(t + 1) * TOPK], dn_np, TYPE_Q4_K, idx_np[t], I, H, multi=True, mode=1, threads=threads)
+            want[t] = (dn.astype(np.float64) * wts_np[t][:, None]).sum(axis=0)
+        p2 = check_parity(got, want, "MoE down + weighted sum")
+        parity = {"rel_l2": max(p1["rel_l2"], p2["rel_l2"]), "maxabs_rms": max(p1["maxabs_rms"], p2["maxabs_rms"]),
+                  "against": "CPU oracle, per-token expert GEMVs (gate/up + SwiGLU, then down + weighted sum)"}
 
     graph = torch.cuda.CUDAGraph()
     s = torch.cuda.Stream()
@@ -607,61 +662,116 @@ def moe_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    def max_over_ranks(v):
+        if world > 1:
+            t = torch.tensor([v], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
+
     times = []
-    for _ in range(args.repeats if args.repeats else 20):
+    for _ in range(repeats):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         graph.replay()
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        times.append(ms)
+        times.append(max_over_ranks(e0.elapsed_time(e1)))
     device.sync()
     ms_step = statistics.median(times) / steps
-    # end to end: routing tables and tokens start in pinned host memory, the result is read back
-    xh, ih, wh = x.cpu().pin_memory(), idx.cpu().pin_memory(), wts.cpu().pin_memory()
-    oh = torch.empty((T_loc, H), dtype=torch.float32).pin_memory()
-    n_e2e = 30
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(n_e2e):
-        xd, idd, wd = xh.cuda(non_blocking=True), ih.cuda(non_blocking=True), wh.cuda(non_blocking=True)
-        oh.copy_(layers[i % n_layers].forward(xd, idd, wd), non_blocking=True)
-        torch.cuda.synchronize()
-    dt = (time.perf_counter() - t0) / n_e2e
+    del graph
+    res = {"workload": "MoE layer expert matmuls: 128 experts, top-8, d_model 2048, expert width 768, Q4_K, 256 tokens",
+           "routing": f"seeded N(0,1) logits, top-8; tokens per expert min/mean/max {int(counts.min())}/{counts.mean():.1f}/{int(counts.max())}",
+           "parallelism": "single GPU" if world == 1 else f"{E_loc} experts per GPU; all-gather in, reduce-scatter out (NCCL), captured in the graph",
+           "l2": f"{n_layers} rotating layers ({n_layers * per_rank_bytes >> 20} MiB of expert weights per GPU) exceed the 126 MB L2",
+           "timing": f"CUDA events around one CUDA graph of {steps} layers; median of {len(times)} repeats; max over ranks",
+           "ms_per_layer": ms_step, "tokens_per_s": T / (ms_step * 1e-3),
+           "useful_tops": 2.0 * T * TOPK * (H * 2 * I + I * H) / (ms_step * 1e-3) / 1e12,
+           "weight_gbs": E * (2 * I * (H // 256) * 144 + H * (I // 256) * 144) / (ms_step * 1e-3) / 1e9,
+           "gpu_launches_per_layer": 6 if world == 1 else 8}
+    if parity:
+        res["parity"] = parity
     if world > 1:
-        t = torch.tensor([dt], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
+        # the token all-to-all form (deduplicated dispatch; one host synchronisation per layer for the split sizes, so
+        # eager launches), on the same inputs; its result must agree with the all-gather form's
+        a2a = make_layers("alltoall")
+        ref_out = layers[0].forward(x, idx, wts).clone()
+        got = a2a[0].forward(x, idx, wts)
+        device.sync()
+        diff = float((got - ref_out).abs().max() / ref_out.pow(2).mean().sqrt().clamp_min(1e-30))
+        assert diff < 1e-5, f"token all-to-all and all-gather exchanges disagree: {diff}"
+        for i in range(3):
+            a2a[i % n_layers].forward(x, idx, wts)
+        barrier()
+        n_it = 24
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n_it):
+            a2a[i % n_layers].forward(x, idx, wts)
+        e1.record()
+        barrier()
+        rows = torch.tensor([float(a2a[0].last_dispatch_rows)], device="cuda")
+        dist.all_reduce(rows)
+        res["token_alltoall"] = {"ms_per_layer": max_over_ranks(e0.elapsed_time(e1) / n_it), "launches": "eager (host reads the split sizes once per layer)",
+                                 "rows_sent_all_ranks": int(rows.item()), "rows_if_sent_per_expert": T * TOPK, "rows_if_all_gathered": T * world,
+                                 "agrees_with_allgather_form_maxabs_rms": diff}
+        del a2a
+    if e2e:
+        # end to end: routing tables and tokens start in pinned host memory, the result is read back
+        xh, ih, wh = x.cpu().pin_memory(), idx.cpu().pin_memory(), wts.cpu().pin_memory()
+        oh = torch.empty((T_loc, H), dtype=torch.float32).pin_memory()
+        n_e2e = 30
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            xd, idd, wd = xh.cuda(non_blocking=True), ih.cuda(non_blocking=True), wh.cuda(non_blocking=True)
+            oh.copy_(layers[i % n_layers].forward(xd, idd, wd), non_blocking=True)
+            torch.cuda.synchronize()
+        dt = max_over_ranks((time.perf_counter() - t0) / n_e2e)
+        res["e2e"] = {"value": T / dt, "unit": "tokens/s", "h2d_bytes_per_step": T_loc * (H * 4 + TOPK * 8), "d2h_bytes_per_step": T_loc * H * 4,
+                      "how": "tokens and routing tables from pinned host memory, layer output copied back, eager launches"}
+    del layers
+    torch.cuda.synchronize()
+    return res
+
+
+def moe_arm(args):
+    """`--workload moe`: the MoE leg alone, as its own JSON line."""
+    import torch
+    import torch.distributed as dist
+    from laplace_b200 import device
+    from tests import synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        import datetime
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
+    device.lib(local)
+    steps, warmup = max(1, min(args.steps, 64)), max(3, min(args.warmup, 8))
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    res = moe_leg(device, synth, torch, dist, rank, world, steps=steps, warmup=warmup, repeats=args.repeats if args.repeats else 20)
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        ops = 2.0 * T * TOPK * (H * 2 * I + I * H)
-        wbytes = E * (2 * I * (H // 256) * 144 + H * (I // 256) * 144)
         print(json.dumps({
-            "metric": "MoE expert-matmul layer throughput (tokens/s)", "value": T / (ms_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "u4 x s8 -> exact block sums (fp16 MMA, fp32 accumulate)",
-            "data": "synthetic",
-            "config": {"workload": "MoE layer expert matmuls: 128 experts, top-8, d_model 2048, expert width 768, Q4_K, 256 tokens",
-                       "routing": f"seeded N(0,1) logits, top-8; tokens per expert min/mean/max {int(counts.min())}/{counts.mean():.1f}/{int(counts.max())}",
-                       "parallelism": "single GPU" if world == 1 else f"{E_loc} experts per GPU; all-gather in, reduce-scatter out (NCCL)",
-                       "l2": f"{n_layers} rotating layers ({n_layers * per_rank_bytes >> 20} MiB of expert weights per GPU) exceed the 126 MB L2",
-                       "timing": f"CUDA events around one CUDA graph of {steps} layers; median of {len(times)} repeats; max over ranks"},
-            "useful_tops": ops / (ms_step * 1e-3) / 1e12, "weight_gbs": wbytes / (ms_step * 1e-3) / 1e9,
-            "e2e": {"value": T / dt, "unit": "tokens/s", "h2d_bytes_per_step": T_loc * (H * 4 + TOPK * 8), "d2h_bytes_per_step": T_loc * H * 4,
-                    "how": "tokens and routing tables from pinned host memory, layer output copied back, eager launches"},
-            "gpu_launches": steps * (9 if world == 1 else 11), "clocks": clocks,
+            "metric": "MoE expert-matmul layer throughput (tokens/s)", "value": res["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": res["ms_per_layer"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u4 x s8 (fp16 MMA over scaled activation pieces, fp32 accumulate)",
+            "data": "synthetic", "config": {k: res[k] for k in ("workload", "routing", "parallelism", "l2", "timing")},
+            "useful_tops": res["useful_tops"], "weight_gbs": res["weight_gbs"], "e2e": res.get("e2e"),
+            **({"parity": res["parity"]} if "parity" in res else {}),
+            **({"token_alltoall": res["token_alltoall"]} if "token_alltoall" in res else {}),
+            "gpu_launches": steps * res["gpu_launches_per_layer"], "clocks": clocks,
         }))
     if world > 1:
-        del graph
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()

@@ -224,6 +224,12 @@ int laplace_cuda_quantize_act_dev(const float* x, int M, int K,
 int laplace_cuda_debug_blocksums_dev(const float* x, const uint8_t* w, uint32_t type,
                                      int32_t* out, int M, int K, int N, void* stream);
 
+/* Dense tensor-core rate of the bound GPU, measured with a bare tcgen05.mma loop on every SM (M = 128, N = 128
+ * instructions from two issuing threads): kind 0 = fp16 operands / fp32 accumulate, 1 = int8 / int32. Result in
+ * Tera-operations per second, 2 per multiply-add. For the benchmark's roofline; no reference counterpart.
+ * Synchronous (a few milliseconds). */
+int laplace_cuda_debug_tensor_peak(int kind, double* tops);
+
 /* Which kernel family the last *_dev gemm call used: 1 = streaming dp4a GEMV,
  * 2 = tensor-core GEMM, 3 = expert-grouped tensor-core GEMM, 4 = fused expert FFN. For tests and the benchmark's launch count. */
 int laplace_cuda_last_path(void);

@@ -36,6 +36,7 @@ SYMBOLS = {
     "laplace_cuda_moe_unpack_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "laplace_cuda_quantize_act_dev": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "laplace_cuda_debug_blocksums_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
+    "laplace_cuda_debug_tensor_peak": (_i, [_i, C.POINTER(C.c_double)]),
     "laplace_cuda_last_path": (_i, []),
     "laplace_cuda_launch_count": (C.c_longlong, [_i]),
 }

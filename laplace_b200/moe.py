@@ -13,6 +13,11 @@ expert-grouped matmuls of include/laplace_cuda.h; with more than one GPU, expert
                      marked -1 (skipped on the device), then the weighted sum over the local experts of each token;
     3. exchange out: reduce-scatter of the per-token partial sums back to the tokens' owners.
 
+A second exchange, `exchange="alltoall"`, is the token all-to-all proper: a token is sent ONCE to every GPU that
+holds at least one of its experts (not once per expert), the partial sums come back the same way and are added in
+rank order. Split sizes are data dependent, so this form synchronises with the host once per layer (the counts)
+and cannot be captured in a CUDA graph; it moves fewer bytes and is the cross-check of the all-gather form.
+
 The compute is injected: `fused_ffn` (one call of laplace_cuda_moe_ffn_dev: both matmuls, the activation and the
 weighted sum) or `grouped_matmul` (two calls of laplace_cuda_moe_grouped_dev with torch glue between them), so the
 exchange logic runs on CPU tensors under gloo in the tests.
@@ -38,7 +43,7 @@ class ExpertParallelMoE:
 
     def __init__(self, w_gate_up, w_down, n_experts: int, top_k: int, hidden: int, inter: int,
                  grouped_matmul: Optional[Callable] = None, rank: int = 0, world: int = 1, group=None,
-                 fused_ffn: Optional[Callable] = None, device_exchange: bool = False):
+                 fused_ffn: Optional[Callable] = None, device_exchange: bool = False, exchange: str = "allgather"):
         if n_experts % world:
             raise ValueError(f"{n_experts} experts do not split evenly over {world} GPUs")
         if grouped_matmul is None and fused_ffn is None:
@@ -49,6 +54,10 @@ class ExpertParallelMoE:
         self.E_loc = n_experts // world
         self.mm, self.ffn = grouped_matmul, fused_ffn
         self.device_exchange = device_exchange        # pack / unpack with the library's kernels instead of torch ops
+        if exchange not in ("allgather", "alltoall"):
+            raise ValueError("exchange is 'allgather' or 'alltoall'")
+        self.exchange = exchange
+        self.last_dispatch_rows = None                # rows this rank sent in the last all-to-all dispatch
         self._buf = {}
         self._rows_ready = None
 
@@ -74,9 +83,65 @@ class ExpertParallelMoE:
         dist.all_gather_into_tensor(recv, send, group=self.group)
         return recv[:, :H].contiguous(), recv[:, H:H + k].contiguous().view(torch.int32), recv[:, H + k:].contiguous()
 
+    def _forward_alltoall(self, x, top_idx, top_w):
+        """Token all-to-all: rows [x | expert ids | weights] go once to every GPU that owns one of the token's
+        experts; every GPU runs the expert FFN over what it received (other GPUs' experts marked -1) and returns one
+        partial sum per received row; the owner adds the partial sums of a token in rank order."""
+        T_loc, dev = x.shape[0], x.device
+        G, k, H, I = self.world, self.k, self.H, self.I
+        owner = torch.div(top_idx, self.E_loc, rounding_mode="floor")                            # [T_loc, k] GPU of each expert
+        needs = (owner.unsqueeze(2) == torch.arange(G, device=dev).view(1, 1, G)).any(dim=1)      # [T_loc, G]
+        send_counts = needs.sum(dim=0).to(torch.int64)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()                                       # the one host synchronisation
+        self.last_dispatch_rows = int(sum(sc))
+        # rows ordered by destination GPU, tokens in order inside a destination
+        dest, tok = needs.t().nonzero(as_tuple=True)                                              # sorted by destination, then token
+        row = torch.cat([x, top_idx.contiguous().view(torch.float32), top_w], dim=1)             # [T_loc, H + 2k]
+        send = row.index_select(0, tok).contiguous()
+        recv = torch.empty((int(sum(rc)), H + 2 * k), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(recv, send, output_split_sizes=rc, input_split_sizes=sc, group=self.group)
+        R = recv.shape[0]
+        first = self.rank * self.E_loc
+        if R:
+            xr = recv[:, :H].contiguous()
+            idr = recv[:, H:H + k].contiguous().view(torch.int32)
+            wr = recv[:, H + k:].contiguous()
+            mine = (idr >= first) & (idr < first + self.E_loc)
+            idx_local = torch.where(mine, idr - first, torch.full_like(idr, -1)).to(torch.int32).contiguous()
+            if self.ffn is not None:
+                part = self.ffn(xr, self.w_gate_up, self.w_down, idx_local, wr, self.E_loc, H, I,
+                                torch.empty((R, H), dtype=torch.float32, device=dev))
+            else:
+                pair_expert = idx_local.reshape(-1)
+                pair_row = torch.arange(R, dtype=torch.int32, device=dev).repeat_interleave(k)
+                gu = torch.zeros((R * k, 2 * I), dtype=torch.float32, device=dev)
+                dn = torch.zeros((R * k, H), dtype=torch.float32, device=dev)
+                self.mm(xr, self.w_gate_up, pair_expert, pair_row, self.E_loc, H, 2 * I, gu)
+                self.mm(silu_mul(gu, I), self.w_down, pair_expert, None, self.E_loc, I, H, dn)
+                wt = (wr * mine.to(wr.dtype)).reshape(R, k, 1)
+                live = torch.where(mine.reshape(R, k, 1), dn.reshape(R, k, H), torch.zeros((), dtype=dn.dtype, device=dev))
+                part = (live * wt).sum(dim=1)
+        else:
+            part = torch.empty((0, H), dtype=torch.float32, device=dev)
+        back = torch.empty((int(sum(sc)), H), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(back, part.contiguous(), output_split_sizes=sc, input_split_sizes=rc, group=self.group)
+        # one partial sum per (token, GPU that served it), grouped by GPU: add them in rank order (reproducible)
+        out = torch.zeros((T_loc, H), dtype=torch.float32, device=dev)
+        start = 0
+        for g in range(G):
+            n = sc[g]
+            if n:
+                out.index_add_(0, tok[start:start + n], back[start:start + n])                   # a token appears once per GPU
+            start += n
+        return out
+
     def forward(self, x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
         """x [T_loc, H] fp32, top_idx [T_loc, k] int32 (global expert ids), top_w [T_loc, k] fp32.
         Returns the layer's output for this rank's tokens, [T_loc, H]."""
+        if self.exchange == "alltoall" and self.world > 1:
+            return self._forward_alltoall(x, top_idx, top_w)
         T_loc, dev = x.shape[0], x.device
         G, k, H, I = self.world, self.k, self.H, self.I
         T = T_loc * G

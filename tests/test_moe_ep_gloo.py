@@ -54,7 +54,7 @@ def _reference_layer(orc, w_gu, w_dn, x, idx, wts, E, k, H, I):
     return out
 
 
-def _worker(rank, world, port, E, k, H, I, T_loc, out_dir):
+def _worker(rank, world, port, E, k, H, I, T_loc, out_dir, exchange="allgather"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -65,13 +65,18 @@ def _worker(rank, world, port, E, k, H, I, T_loc, out_dir):
         gu_rows, dn_rows = 2 * I * E_loc, H * E_loc
         layer = ExpertParallelMoE(torch.from_numpy(w_gu[rank * gu_rows:(rank + 1) * gu_rows].copy()),
                                   torch.from_numpy(w_dn[rank * dn_rows:(rank + 1) * dn_rows].copy()),
-                                  E, k, H, I, _oracle_mm(orc), rank, world)
+                                  E, k, H, I, _oracle_mm(orc), rank, world, exchange=exchange)
         sl = slice(rank * T_loc, (rank + 1) * T_loc)
         out = layer.forward(torch.from_numpy(x[sl].copy()), torch.from_numpy(idx[sl].copy()), torch.from_numpy(wts[sl].copy()))
         want = _reference_layer(orc, w_gu, w_dn, x, idx, wts, E, k, H, I)[sl]
         err = float(np.abs(out.numpy() - want).max() / (np.sqrt((want ** 2).mean()) + 1e-30))
         with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
             f.write(f"{err}\n")
+        if exchange == "alltoall" and world > 1:
+            # a token travels once per destination GPU, not once per expert and not to GPUs that hold none of its experts
+            owners = idx[sl] // E_loc
+            want_rows = sum(len(set(row.tolist())) for row in owners)
+            assert layer.last_dispatch_rows == want_rows, (layer.last_dispatch_rows, want_rows)
     finally:
         dist.destroy_process_group()
 
@@ -81,6 +86,16 @@ def test_expert_parallel_layer(tmp_path, world):
     E, k, H, I, T_loc = 8, 3, 256, 256, 3
     assert row_bytes(T_TYPE, H) == 144
     mp.spawn(_worker, args=(world, _free_port(), E, k, H, I, T_loc, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        err = float((tmp_path / f"r{r}.txt").read_text())
+        assert err < 1e-5, f"rank {r}: max-abs / RMS = {err}"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_layer_token_alltoall(tmp_path, world):
+    """The token all-to-all form of the exchange: deduplicated dispatch, partial sums added in rank order."""
+    E, k, H, I, T_loc = 8, 3, 256, 256, 3
+    mp.spawn(_worker, args=(world, _free_port(), E, k, H, I, T_loc, str(tmp_path), "alltoall"), nprocs=world, join=True)
     for r in range(world):
         err = float((tmp_path / f"r{r}.txt").read_text())
         assert err < 1e-5, f"rank {r}: max-abs / RMS = {err}"
