@@ -57,7 +57,13 @@ enum {
  * (the reference has no device); called from the shim's static initialiser. */
 int  laplace_cuda_init(int device);
 void laplace_cuda_shutdown(void);
+/* Drains the library's own stream, then reads and clears the device status word (time-outs of bounded waits,
+ * bad expert indices). Work enqueued by *_dev calls on a CALLER's stream is not waited for here: synchronise that
+ * stream first, or use laplace_cuda_sync_stream, otherwise a status raised by such work can be missed or be
+ * attributed to a later call. */
 int  laplace_cuda_sync(void);
+/* The same after waiting for `stream` (a cudaStream_t) as well. */
+int  laplace_cuda_sync_stream(void* stream);
 const char* laplace_cuda_last_error(void);
 int  laplace_cuda_sm_count(void);
 
@@ -133,6 +139,9 @@ int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type
  *   x [n_tokens][hidden]; w_gate_up: experts x (2*inter rows of K = hidden), gate rows first;
  *   w_down: experts x (hidden rows of K = inter); top_idx / top_w [n_tokens][top_k];
  *   activation 0 = SwiGLU (silu(gate) * up), 1 = GeGLU (tanh-GELU(gate) * up);
+ *   down_scale (optional, may be NULL): per-expert output scale, indexed like top_idx (by the ids this call
+ *   sees, i.e. local ids on an expert-parallel GPU); the weight of a pair is top_w * down_scale[expert], as in
+ *   src/arch_gemma4.cpp:634-638;
  *   out [n_tokens][hidden] is OVERWRITTEN with the weighted sum over the experts computed here.
  * Negative entries of top_idx are experts that live on another GPU: they contribute nothing, so
  * the per-GPU outputs of an expert-parallel layer add up to the layer's output. h_out (optional,
@@ -140,9 +149,18 @@ int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type
  * pairs untouched). Types as for laplace_cuda_moe_grouped_dev, else LAPLACE_UNSUPPORTED. */
 int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down,
                              uint32_t type_gate_up, uint32_t type_down,
-                             const int* top_idx, const float* top_w,
+                             const int* top_idx, const float* top_w, const float* down_scale,
                              int n_tokens, int top_k, int n_experts_total, int hidden, int inter, int activation,
                              float* out, float* h_out, void* stream);
+
+/* The reference's expert selection (src/arch_gemma4.cpp:547-565) for a batch of tokens, on the device, operation
+ * for operation: softmax over logits [n_tokens][n_experts] (maximum, exponentials summed in index order, division),
+ * top_k times the largest remaining probability (the lowest index wins among equal values), the selected
+ * probabilities divided by their sum. Writes top_idx / top_w [n_tokens][top_k] in selection order - the form
+ * laplace_cuda_moe_ffn_dev takes. The router's own matmul (logits = W_router . x) is an ordinary
+ * laplace_cuda_gemm_dev call for quantized router weights. Device pointers. */
+int laplace_cuda_moe_route_dev(const float* logits, int n_tokens, int n_experts, int top_k,
+                               int* top_idx, float* top_w, void* stream);
 
 /* Exchange helpers of an expert-parallel MoE layer (no reference counterpart): one all-gather moves
  * [x (hidden floats) | expert ids (top_k ints, bit pattern) | weights (top_k floats)] per token.

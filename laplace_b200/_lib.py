@@ -13,6 +13,7 @@ SYMBOLS = {
     "laplace_cuda_init": (_i, [_i]),
     "laplace_cuda_shutdown": (None, []),
     "laplace_cuda_sync": (_i, []),
+    "laplace_cuda_sync_stream": (_i, [_vp]),
     "laplace_cuda_last_error": (C.c_char_p, []),
     "laplace_cuda_sm_count": (_i, []),
     "laplace_cuda_register_weights": (_i, [_vp, _sz]),
@@ -25,7 +26,8 @@ SYMBOLS = {
     "laplace_cuda_gemm_noalloc_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_moe_gemv_dev": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_moe_grouped_dev": (_i, [_vp, _vp, _u32, _vp, _vp, _i, _i, _vp, _i, _i, _vp]),
-    "laplace_cuda_moe_ffn_dev": (_i, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "laplace_cuda_moe_ffn_dev": (_i, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "laplace_cuda_moe_route_dev": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "laplace_cuda_peer_alloc": (_i, [_sz, C.POINTER(_vp), _vp]),
     "laplace_cuda_peer_open": (_i, [_vp, C.POINTER(_vp)]),
     "laplace_cuda_peer_close": (_i, [_vp]),

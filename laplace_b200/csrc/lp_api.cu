@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <chrono>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -50,6 +51,32 @@ Buf g_hx{nullptr, 0, true}, g_hy{nullptr, 0, true};   // pinned host
 
 Context g_ctx;
 
+// LAPLACE_PROF=1, the reference's switch (src/matmul.cpp:355-379: wall time inside the matmuls, reported at process
+// exit): per host-pointer entry point the number of calls, the wall time of the whole call and, inside it, the time
+// spent waiting for the device (copies + kernel), so that a Laplace user sees where a decode step goes without a
+// profiler. Device-pointer entry points only enqueue work and are not timed.
+struct EntryProf { const char* name; long calls = 0; double wall = 0.0, device_wait = 0.0; };
+struct Prof {
+    bool on = std::getenv("LAPLACE_PROF") != nullptr;
+    EntryProf e[3] = {{"gemm"}, {"moe_gemv"}, {"moe_gemv_multi"}};
+    ~Prof() {
+        if (!on) return;
+        for (const EntryProf& p : e)
+            if (p.calls)
+                std::fprintf(stderr, "PROF laplace_cuda_%s: %.3f s over %ld calls (%.1f us per call; %.1f us of it waiting for the GPU)\n",
+                             p.name, p.wall, p.calls, 1e6 * p.wall / p.calls, 1e6 * p.device_wait / p.calls);
+    }
+};
+Prof g_prof;
+struct ProfScope {
+    EntryProf& p;
+    std::chrono::steady_clock::time_point t0;
+    explicit ProfScope(int which) : p(g_prof.e[which]) { if (g_prof.on) t0 = std::chrono::steady_clock::now(); }
+    ~ProfScope() {
+        if (g_prof.on) { p.wall += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); p.calls++; }
+    }
+};
+
 }  // namespace
 
 Context& ctx() { return g_ctx; }
@@ -76,8 +103,14 @@ int require_ready() {
 
 // Drains the stream, then reads and clears the status word. The word lives in
 // mapped pinned host memory, so reading it costs no copy.
-int check_device_status(cudaStream_t st) {
-    cudaError_t e = cudaStreamSynchronize(st);
+int check_device_status(cudaStream_t st, EntryProf* prof = nullptr) {
+    const auto t0 = std::chrono::steady_clock::now();
+    // Decode calls finish within microseconds: poll first (a blocking synchronize costs more than the kernel),
+    // then fall back to the blocking wait.
+    cudaError_t e = cudaErrorNotReady;
+    for (int spin = 0; spin < 20000 && e == cudaErrorNotReady; ++spin) e = cudaStreamQuery(st);
+    if (e == cudaErrorNotReady) e = cudaStreamSynchronize(st);
+    if (prof && g_prof.on) prof->device_wait += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     if (e != cudaSuccess) return cuda_check(e, "stream synchronize");
     const int h = *static_cast<volatile int*>(g_ctx.h_err);
     if (h != DEV_OK) {
@@ -152,6 +185,7 @@ int dispatch_moe_dev(const float* x, const uint8_t* w, uint32_t type, const int*
 int moe_host(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx, int n_experts,
              float* y, int K, int N, int per_expert_x) {
     std::lock_guard<std::mutex> lk(g_mu);
+    ProfScope prof(per_expert_x ? 2 : 1);
     int rc = require_ready();
     if (rc) return rc;
     if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
@@ -180,7 +214,7 @@ int moe_host(const float* x, const uint8_t* w, uint32_t type, const int* expert_
                           static_cast<float*>(g_dy.p), K, N, per_expert_x, st);
     if (rc) return rc;
     cudaMemcpyAsync(g_hy.p, g_dy.p, yb, cudaMemcpyDeviceToHost, st);
-    if ((rc = check_device_status(st))) return rc;
+    if ((rc = check_device_status(st, &prof.p))) return rc;
     std::memcpy(y, g_hy.p, yb);
     return LAPLACE_OK;
 }
@@ -247,6 +281,17 @@ int laplace_cuda_sync(void) {
     return check_device_status(g_ctx.stream);
 }
 
+int laplace_cuda_sync_stream(void* stream) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = require_ready();
+    if (rc) return rc;
+    if (stream) {
+        cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_check(e, "stream synchronize");
+    }
+    return check_device_status(g_ctx.stream);
+}
+
 const char* laplace_cuda_last_error(void) { return g_err; }
 
 int laplace_cuda_sm_count(void) { return g_ctx.ready ? g_ctx.sm_count : 0; }
@@ -307,6 +352,7 @@ void laplace_cuda_nsplit(int N, int rank, int world, int* row_begin, int* row_en
 
 int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N) {
     std::lock_guard<std::mutex> lk(g_mu);
+    ProfScope prof(0);
     int rc = require_ready();
     if (rc) return rc;
     if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
@@ -335,7 +381,7 @@ int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y,
         if (rc == LAPLACE_OK) cudaMemcpyAsync(g_hy.p, g_dy.p, yb, cudaMemcpyDeviceToHost, st);
     }
     if (rc) return rc;
-    if ((rc = check_device_status(st))) return rc;
+    if ((rc = check_device_status(st, &prof.p))) return rc;
     std::memcpy(y, g_hy.p, yb);
     return LAPLACE_OK;
 }
@@ -381,8 +427,8 @@ int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type
 
 int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down,
                              uint32_t type_gate_up, uint32_t type_down, const int* top_idx, const float* top_w,
-                             int n_tokens, int top_k, int n_experts_total, int hidden, int inter, int activation,
-                             float* out, float* h_out, void* stream) {
+                             const float* down_scale, int n_tokens, int top_k, int n_experts_total, int hidden, int inter,
+                             int activation, float* out, float* h_out, void* stream) {
     int rc = require_ready();
     if (rc) return rc;
     if (!block_elems(type_gate_up) || !block_elems(type_down)) return LAPLACE_UNSUPPORTED;
@@ -393,10 +439,20 @@ int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uin
                     n_tokens, top_k, n_experts_total, hidden, inter, activation);
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream;
     if (moe_sa_supports(type_gate_up, hidden, 2 * inter) && moe_sa_supports(type_down, inter, hidden))
-        return launch_moe_ffn_sa(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, n_tokens, top_k, n_experts_total,
-                                 hidden, inter, activation, out, h_out, st);
-    return launch_moe_ffn(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, n_tokens, top_k, n_experts_total,
-                          hidden, inter, activation, out, h_out, st);
+        return launch_moe_ffn_sa(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, down_scale, n_tokens, top_k,
+                                 n_experts_total, hidden, inter, activation, out, h_out, st);
+    return launch_moe_ffn(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, down_scale, n_tokens, top_k,
+                          n_experts_total, hidden, inter, activation, out, h_out, st);
+}
+
+int laplace_cuda_moe_route_dev(const float* logits, int n_tokens, int n_experts, int top_k, int* top_idx, float* top_w,
+                               void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!logits || !top_idx || !top_w) return fail(LAPLACE_ERR_ARG, "moe_route: null pointer");
+    if (n_tokens <= 0 || n_experts <= 0 || top_k <= 0 || top_k > n_experts)
+        return fail(LAPLACE_ERR_ARG, "moe_route: tokens=%d experts=%d top_k=%d", n_tokens, n_experts, top_k);
+    return launch_moe_route(logits, n_tokens, n_experts, top_k, top_idx, top_w, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
 }
 
 int laplace_cuda_moe_pack_dev(const float* x, const int* top_idx, const float* top_w, int n_tokens, int hidden, int top_k,

@@ -99,8 +99,9 @@ bool moe_sa_supports(uint32_t type, int K, int N);
 int  launch_moe_grouped_sa(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
                            int P, int E, float* y, int K, int N, cudaStream_t st);
 int  launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
-                       const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
-                       float* out, float* h_out, cudaStream_t st);
+                       const int* top_idx, const float* top_w, const float* down_scale, int T, int top_k, int E, int H, int I,
+                       int activation, float* out, float* h_out, cudaStream_t st);
+int  launch_moe_route(const float* logits, int T, int E, int top_k, int* top_idx, float* top_w, cudaStream_t st);
 void release_moe_sa_scratch();
 // Expert-grouped matmul over (token, expert) pairs on the tensor cores (lp_moe_grouped.cuh).
 bool moe_grouped_supports(uint32_t type, int K, int N);
@@ -109,8 +110,8 @@ int  launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const i
 void release_moe_grouped_scratch();
 // Fused expert FFN (gate/up matmul, gated activation, down matmul, weighted sum) for a batch of tokens.
 int  launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
-                    const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
-                    float* out, float* h_out, cudaStream_t st);
+                    const int* top_idx, const float* top_w, const float* down_scale, int T, int top_k, int E, int H, int I,
+                    int activation, float* out, float* h_out, cudaStream_t st);
 void release_moe_ffn_scratch();
 int  launch_moe_pack(const float* x, const int* idx, const float* wts, int T, int H, int k, float* packed, cudaStream_t st);
 int  launch_moe_unpack(const float* packed, int T, int H, int k, int first, int count, float* x, int* idx_local, float* wts,

@@ -827,8 +827,10 @@ __global__ void __launch_bounds__(256) moe_act_quant_sa_kernel(const float* __re
 }
 
 // out[t][:] = sum over the token's live pairs, in slot order, of top_w[t][j] * dn[row of pair][:]
+// (the reference's weight of pair j is top_w[j] * down_scale[expert], src/arch_gemma4.cpp:634-638; down_scale may be null)
 __global__ void __launch_bounds__(256) moe_combine_sa_kernel(const float* __restrict__ dn, const int* __restrict__ dst_row,
-                                                             const float* __restrict__ top_w, int T, int top_k, int H,
+                                                             const float* __restrict__ top_w, const int* __restrict__ top_idx,
+                                                             const float* __restrict__ down_scale, int T, int top_k, int H,
                                                              float* __restrict__ out) {
     const int h4 = H / 4;
     const long long total = static_cast<long long>(T) * h4;
@@ -839,7 +841,8 @@ __global__ void __launch_bounds__(256) moe_combine_sa_kernel(const float* __rest
         for (int j = 0; j < top_k; ++j) {
             const int r = __ldg(dst_row + t * top_k + j);
             if (r < 0) continue;
-            const float wgt = __ldg(top_w + t * top_k + j);
+            float wgt = __ldg(top_w + t * top_k + j);
+            if (down_scale) wgt = __fmul_rn(wgt, __ldg(down_scale + __ldg(top_idx + t * top_k + j)));
             const float4 v = __ldg(reinterpret_cast<const float4*>(dn + static_cast<long long>(r) * H) + c);
             acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y);
             acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
@@ -918,8 +921,8 @@ int launch_moe_grouped_sa(const float* x, const uint8_t* w, uint32_t type, const
 }
 
 int launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
-                      const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
-                      float* out, float* h_out, cudaStream_t st) {
+                      const int* top_idx, const float* top_w, const float* down_scale, int T, int top_k, int E, int H, int I,
+                      int activation, float* out, float* h_out, cudaStream_t st) {
     if (!moe_sa_supports(type_gu, H, 2 * I) || !moe_sa_supports(type_dn, I, H)) return LAPLACE_UNSUPPORTED;
     if (I % 32 || H % 4) return fail(LAPLACE_ERR_ARG, "moe_ffn: H=%d I=%d", H, I);
     if ((reinterpret_cast<uintptr_t>(w_gate_up) & 15) || (reinterpret_cast<uintptr_t>(w_down) & 15) ||
@@ -974,10 +977,57 @@ int launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w
     const long long total4 = static_cast<long long>(T) * (H / 4);
     long long blocks = (total4 + 255) / 256;
     if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
-    moe_combine_sa_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(dn, dst_row, top_w, T, top_k, H, out);
+    moe_combine_sa_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(dn, dst_row, top_w, top_idx, down_scale, T, top_k, H, out);
     c.launches++;
     c.last_path = 4;
     return cuda_check(cudaGetLastError(), "moe_combine launch");
+}
+
+
+// ---- router ------------------------------------------------------------------------------------------------
+// The reference's expert selection for one token (src/arch_gemma4.cpp:547-565), operation for operation: softmax
+// over the router logits (maximum, exp(l - max) summed in index order, division), then top_k times the largest
+// remaining probability - the FIRST index wins among equal values, as its strict comparison does - and the selected
+// probabilities renormalised by their sum (added in selection order). One thread per token walks the experts in
+// order, so every fp32 operation happens in the reference's order; with a few hundred experts that is microseconds.
+namespace {
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int T, int E, int top_k,
+                                                        int* __restrict__ top_idx, float* __restrict__ top_w) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const float* l = logits + static_cast<size_t>(t) * E;
+    float maxl = l[0];
+    for (int e = 1; e < E; ++e) if (l[e] > maxl) maxl = l[e];
+    float suml = 0.0f;
+    for (int e = 0; e < E; ++e) suml = __fadd_rn(suml, expf(__fsub_rn(l[e], maxl)));
+    int* ti = top_idx + static_cast<size_t>(t) * top_k;
+    float* tw = top_w + static_cast<size_t>(t) * top_k;
+    float wsum = 0.0f;
+    for (int k = 0; k < top_k; ++k) {
+        int best = -1;
+        float best_p = 0.0f;
+        for (int e = 0; e < E; ++e) {
+            bool taken = false;
+            for (int j = 0; j < k; ++j) taken |= ti[j] == e;
+            // a taken expert's probability has been replaced by -1e30 in the reference
+            const float p = taken ? -1e30f : __fdiv_rn(expf(__fsub_rn(l[e], maxl)), suml);
+            if (best < 0 || p > best_p) { best = e; best_p = p; }
+        }
+        ti[k] = best;
+        tw[k] = best_p;
+        wsum = __fadd_rn(wsum, best_p);
+    }
+    for (int k = 0; k < top_k; ++k) tw[k] = __fdiv_rn(tw[k], wsum);
+}
+
+}  // namespace
+
+int launch_moe_route(const float* logits, int T, int E, int top_k, int* top_idx, float* top_w, cudaStream_t st) {
+    Context& c = ctx();
+    moe_route_kernel<<<(T + 127) / 128, 128, 0, st>>>(logits, T, E, top_k, top_idx, top_w);
+    c.launches++;
+    return cuda_check(cudaGetLastError(), "moe_route launch");
 }
 
 }  // namespace lp

@@ -283,7 +283,8 @@ __global__ void __launch_bounds__(256) moe_act_quant_kernel(const float* __restr
 
 // out[t][:] = sum over the token's live pairs, in slot order, of top_w[t][j] * dn[row of pair][:]
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ dn, const int* __restrict__ dst_row,
-                                                          const float* __restrict__ top_w, int T, int top_k, int H,
+                                                          const float* __restrict__ top_w, const int* __restrict__ top_idx,
+                                                          const float* __restrict__ down_scale, int T, int top_k, int H,
                                                           float* __restrict__ out) {
     const int h4 = H / 4;
     const long long total = static_cast<long long>(T) * h4;
@@ -294,7 +295,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
         for (int j = 0; j < top_k; ++j) {
             const int r = __ldg(dst_row + t * top_k + j);
             if (r < 0) continue;
-            const float wgt = __ldg(top_w + t * top_k + j);
+            float wgt = __ldg(top_w + t * top_k + j);
+            if (down_scale) wgt = __fmul_rn(wgt, __ldg(down_scale + __ldg(top_idx + t * top_k + j)));
             const float4 v = __ldg(reinterpret_cast<const float4*>(dn + static_cast<long long>(r) * H) + c);
             acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y);
             acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
@@ -310,8 +312,8 @@ Scratch g_ffn_scratch;
 void release_moe_ffn_scratch() { g_ffn_scratch.release(); }
 
 int launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
-                   const int* top_idx, const float* top_w, int T, int top_k, int E, int H, int I, int activation,
-                   float* out, float* h_out, cudaStream_t st) {
+                   const int* top_idx, const float* top_w, const float* down_scale, int T, int top_k, int E, int H, int I,
+                   int activation, float* out, float* h_out, cudaStream_t st) {
     if (!moe_grouped_supports(type_gu, H, 2 * I) || !moe_grouped_supports(type_dn, I, H)) return LAPLACE_UNSUPPORTED;
     if (I % 32 || H % 4) return fail(LAPLACE_ERR_ARG, "moe_ffn: H=%d I=%d", H, I);
     if ((reinterpret_cast<uintptr_t>(w_gate_up) & 15) || (reinterpret_cast<uintptr_t>(w_down) & 15) ||
@@ -408,7 +410,7 @@ int launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_do
         const long long total4 = static_cast<long long>(T) * (H / 4);
         long long blocks = (total4 + 255) / 256;
         if (blocks > cap) blocks = cap;
-        moe_combine_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(dn, dst_row, top_w, T, top_k, H, out);
+        moe_combine_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(dn, dst_row, top_w, top_idx, down_scale, T, top_k, H, out);
         c.launches++;
     }
     c.last_path = 4;

@@ -105,7 +105,8 @@ SWIGLU, GEGLU = 0, 1
 
 def moe_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, t_gate_up: int, t_down: int,
             top_idx: torch.Tensor, top_w: torch.Tensor, n_experts_total: int, hidden: int, inter: int,
-            activation: int = SWIGLU, out: torch.Tensor | None = None, h_out: torch.Tensor | None = None) -> torch.Tensor:
+            activation: int = SWIGLU, out: torch.Tensor | None = None, h_out: torch.Tensor | None = None,
+            down_scale: torch.Tensor | None = None) -> torch.Tensor:
     """The fused expert FFN (laplace_cuda_moe_ffn_dev): out[t] = sum over the experts of token t that live here of
     top_w * down(act(gate_up(x[t]))). Raises for types the grouped kernels do not take."""
     L = lib()
@@ -116,10 +117,22 @@ def moe_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, t_ga
     if out is None:
         out = torch.empty((T, hidden), dtype=torch.float32, device=x.device)
     _check(L, L.laplace_cuda_moe_ffn_dev(x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), int(t_gate_up), int(t_down),
-                                         top_idx.data_ptr(), top_w.data_ptr(), T, k, n_experts_total, hidden, inter,
+                                         top_idx.data_ptr(), top_w.data_ptr(),
+                                         down_scale.data_ptr() if down_scale is not None else None, T, k, n_experts_total, hidden, inter,
                                          activation, out.data_ptr(), h_out.data_ptr() if h_out is not None else None,
                                          _stream()))
     return out
+
+
+def moe_route(logits: torch.Tensor, top_k: int):
+    """Softmax, top-k by repeated argmax and renormalisation of router logits [T, E] (laplace_cuda_moe_route_dev)."""
+    L = lib()
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_cuda and logits.is_contiguous()
+    idx = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    _check(L, L.laplace_cuda_moe_route_dev(logits.data_ptr(), T, E, top_k, idx.data_ptr(), wts.data_ptr(), _stream()))
+    return idx, wts
 
 
 def moe_pack(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, packed: torch.Tensor) -> torch.Tensor:
