@@ -119,13 +119,13 @@ int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type,
  *     y[p*N + j] = dot(x[pair_row[p]*K ...], row j of expert pair_expert[p]).
  * pair_row = NULL means pair p reads x row p (the "multi" form: one input per selected expert);
  * for the shared-input form pass pair_row[p] = token of pair p. Pairs may come in any order; they
- * are grouped by expert on the device. Q4_K (K % 256 == 0) and Q6_K (K % 2048 == 0); other
- * types return LAPLACE_UNSUPPORTED and the caller loops laplace_cuda_moe_gemv_dev per token.
+ * are grouped by expert on the device. Q4_0, Q8_0, Q4_K and Q6_K with K % 256 == 0; anything else
+ * returns LAPLACE_UNSUPPORTED and the caller loops laplace_cuda_moe_gemv_dev per token.
  * A negative expert index marks a pair that is not computed here (its y row is left untouched):
  * with experts placed on several GPUs every GPU passes the whole pair list with the experts of
  * the other GPUs set to -1. An index >= n_experts_total also skips the pair and makes the next
- * laplace_cuda_sync() return LAPLACE_ERR_ARG. x, w and every expert (N*rb bytes) must be
- * 16-byte aligned. All pointers are device memory. */
+ * laplace_cuda_sync() return LAPLACE_ERR_ARG. x must be 16-byte aligned, Q4_K weights too (other types: 2 bytes).
+ * All pointers are device memory. */
 int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type,
                                  const int* pair_expert, const int* pair_row,
                                  int n_pairs, int n_experts_total,
@@ -174,7 +174,7 @@ int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, i
                                 int expert_first, int expert_count,
                                 float* x, int* idx_local, float* top_w, void* stream);
 
-/* Prefill GEMM (M > 8; Q4_K with K % 256 == 0, Q6_K with K % 2048 == 0) that allocates nothing. It has no counterpart in
+/* Prefill GEMM (M > 8, K % 256 == 0; Q4_0, Q8_0, Q4_K, Q6_K) that allocates nothing. It has no counterpart in
  * the reference: it exists for hosts that must not touch the CUDA allocator on the request
  * path - serving processes whose own pools (KV cache, activations) already hold all HBM, so
  * that cudaMalloc would fail or fragment them, and latency-bound loops that cannot take the
@@ -183,8 +183,8 @@ int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, i
  * K-split that entry point would choose, else equal to fp32 rounding); the quantized activations go to a
  * 10 MiB array built into the library (held by every GPU that loads it) instead of a cudaMalloc'd buffer.
  *   - LAPLACE_ERR_LIMIT when the call needs more scratch than the array holds: about
- *     4.13 * pad128(M) * K bytes for Q4_K (M = 512, K = 4096: 8.3 MiB), 2.3 * pad128(M) * K + M * K / 8
- *     for Q6_K; LAPLACE_ERR_ARG for shapes that are not the prefill case (decode calls use no scratch).
+ *     4.13 * pad128(M) * K bytes (M = 512, K = 4096: 8.3 MiB), plus the partial sums of a K-split when they fit;
+ *     LAPLACE_ERR_ARG for shapes that are not the prefill case (decode calls use no scratch).
  *   - The first call on a device looks the array's address up (cudaGetSymbolAddress); make
  *     that call before any stream capture begins.
  *   - All calls share the one array and it keeps the last call's contents (what must start

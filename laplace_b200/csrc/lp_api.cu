@@ -150,9 +150,7 @@ int dispatch_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float* y,
     if (K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm: K=%d is not a multiple of %d", K, block_elems(type));
     // Prefill: tensor-core GEMM where one exists for the type.
     if (gemm_sa_supports(type, M, K, N)) return launch_gemm_sa(x, w, type, y, M, K, N, st);
-    if (gemm_tc_supports(type, M, K, N)) return launch_gemm_tc(x, w, type, y, M, K, N, st);
-    // Small M (or a type without a tensor-core kernel yet): one streaming pass
-    // per group of up to 8 activation rows.
+    // Small M (or a K that is not a multiple of 256): one streaming pass per group of up to 8 activation rows.
     // Rows per pass: up to 8, fewer when K is so long that 8 quantized activation rows
     // (~1.45 bytes per value) would leave the weight rings under half of shared memory.
     int per = 8;
@@ -264,11 +262,8 @@ void laplace_cuda_shutdown(void) {
     g_regions.clear();
     g_dx.release(); g_dy.release(); g_dw.release(); g_didx.release(); g_dq.release();
     g_hx.release(); g_hy.release();
-    release_gemm_tc_scratch();
     release_gemm_sa_scratch();
     release_moe_sa_scratch();
-    release_moe_grouped_scratch();
-    release_moe_ffn_scratch();
     cudaFreeHost(g_ctx.h_err);
     cudaStreamDestroy(g_ctx.stream);
     g_ctx = Context{};
@@ -360,7 +355,7 @@ int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y,
     if (M <= 0 || N <= 0 || K <= 0 || K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
     cudaStream_t st = g_ctx.stream;
     const uint8_t* dw = nullptr;
-    if ((rc = weights_on_device(w, static_cast<size_t>(N) * row_bytes(type, K), type, gemm_tc_supports(type, M, K, N), &dw))) return rc;
+    if ((rc = weights_on_device(w, static_cast<size_t>(N) * row_bytes(type, K), type, false, &dw))) return rc;
     const size_t xb = sizeof(float) * static_cast<size_t>(M) * K, yb = sizeof(float) * static_cast<size_t>(M) * N;
     if ((rc = g_hx.ensure(xb)) || (rc = g_hy.ensure(yb)) || (rc = g_dx.ensure(xb)) || (rc = g_dy.ensure(yb))) return rc;
     std::memcpy(g_hx.p, x, xb);
@@ -421,8 +416,7 @@ int laplace_cuda_moe_grouped_dev(const float* x, const uint8_t* w, uint32_t type
     if (n_pairs <= 0 || n_experts_total <= 0 || N <= 0 || K <= 0 || K % block_elems(type))
         return fail(LAPLACE_ERR_ARG, "moe_grouped: pairs=%d experts=%d K=%d N=%d", n_pairs, n_experts_total, K, N);
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream;
-    if (moe_sa_supports(type, K, N)) return launch_moe_grouped_sa(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N, st);
-    return launch_moe_grouped(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N, st);
+    return launch_moe_grouped_sa(x, w, type, pair_expert, pair_row, n_pairs, n_experts_total, y, K, N, st);
 }
 
 int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down,
@@ -438,11 +432,8 @@ int laplace_cuda_moe_ffn_dev(const float* x, const uint8_t* w_gate_up, const uin
         return fail(LAPLACE_ERR_ARG, "moe_ffn: tokens=%d top_k=%d experts=%d hidden=%d inter=%d activation=%d",
                     n_tokens, top_k, n_experts_total, hidden, inter, activation);
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream;
-    if (moe_sa_supports(type_gate_up, hidden, 2 * inter) && moe_sa_supports(type_down, inter, hidden))
-        return launch_moe_ffn_sa(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, down_scale, n_tokens, top_k,
-                                 n_experts_total, hidden, inter, activation, out, h_out, st);
-    return launch_moe_ffn(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, down_scale, n_tokens, top_k,
-                          n_experts_total, hidden, inter, activation, out, h_out, st);
+    return launch_moe_ffn_sa(x, w_gate_up, w_down, type_gate_up, type_down, top_idx, top_w, down_scale, n_tokens, top_k,
+                             n_experts_total, hidden, inter, activation, out, h_out, st);
 }
 
 int laplace_cuda_moe_route_dev(const float* logits, int n_tokens, int n_experts, int top_k, int* top_idx, float* top_w,

@@ -85,16 +85,15 @@ struct PeerOut {
 int launch_gemv_stream(const GemvArgs& a, cudaStream_t st);
 int launch_allgather_wait(const PeerOut& po, cudaStream_t st);
 
-// Tensor-core prefill GEMM (lp_gemm_tc.cu). Uses library-owned scratch for the quantized activations.
-bool gemm_tc_supports(uint32_t type, int M, int K, int N);
-int  launch_gemm_tc(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st);
-void release_gemm_tc_scratch();
-// Tensor-core prefill GEMM with the activation scales folded into the operand (lp_gemm_sa.cu): Q4_K.
+// Tensor-core prefill GEMM with the activation scales folded into the operand (lp_gemm_sa.cu): Q4_0, Q8_0, Q4_K, Q6_K
+// with M > 8 and K % 256 == 0. Uses library-owned scratch for the quantized activations, or the caller's.
 bool gemm_sa_supports(uint32_t type, int M, int K, int N);
 int  launch_gemm_sa(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st);
 int  launch_gemm_sa_prealloc(uint8_t* scratch, size_t cap, const float* x, const uint8_t* w, uint32_t type, float* y,
                              int M, int K, int N, cudaStream_t st);
 void release_gemm_sa_scratch();
+// Expert-grouped matmul over (token, expert) pairs and the fused expert FFN (gate/up matmul, gated activation, down
+// matmul, weighted sum) for a batch of tokens, on the same kernels.
 bool moe_sa_supports(uint32_t type, int K, int N);
 int  launch_moe_grouped_sa(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
                            int P, int E, float* y, int K, int N, cudaStream_t st);
@@ -103,16 +102,6 @@ int  launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* 
                        int activation, float* out, float* h_out, cudaStream_t st);
 int  launch_moe_route(const float* logits, int T, int E, int top_k, int* top_idx, float* top_w, cudaStream_t st);
 void release_moe_sa_scratch();
-// Expert-grouped matmul over (token, expert) pairs on the tensor cores (lp_moe_grouped.cuh).
-bool moe_grouped_supports(uint32_t type, int K, int N);
-int  launch_moe_grouped(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
-                        int P, int E, float* y, int K, int N, cudaStream_t st);
-void release_moe_grouped_scratch();
-// Fused expert FFN (gate/up matmul, gated activation, down matmul, weighted sum) for a batch of tokens.
-int  launch_moe_ffn(const float* x, const uint8_t* w_gate_up, const uint8_t* w_down, uint32_t type_gu, uint32_t type_dn,
-                    const int* top_idx, const float* top_w, const float* down_scale, int T, int top_k, int E, int H, int I,
-                    int activation, float* out, float* h_out, cudaStream_t st);
-void release_moe_ffn_scratch();
 int  launch_moe_pack(const float* x, const int* idx, const float* wts, int T, int H, int k, float* packed, cudaStream_t st);
 int  launch_moe_unpack(const float* packed, int T, int H, int k, int first, int count, float* x, int* idx_local, float* wts,
                        cudaStream_t st);

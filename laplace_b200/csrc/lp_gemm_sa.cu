@@ -77,6 +77,8 @@ static_assert(OFF_RAW % 128 == 0 && RAW_TILE % 128 == 0 && OFF_G % 128 == 0, "TM
 static_assert(OFF_A % 1024 == 0 && A_TILE % 1024 == 0 && W_TILE % 1024 == 0, "swizzled tiles are 1024-byte aligned");
 
 struct SaParams {
+    const uint8_t* w;          // packed weights (the two-piece weight types copy rows by address)
+    uint32_t     rb;           // bytes per weight row
     float*       y;            // [rows of y][N]
     const float* inv_s;        // [operand rows] 2^-e_m
     int*         err;
@@ -416,6 +418,404 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
     }
 }
 
+// ---- the same kernel for weight types whose operand needs two fp16 pieces: Q4_0, Q8_0, Q6_K ----------------------
+// (replaces gemm_int<dot_row_q4_0_int_neon / q8_0 / q6_k> of Laplace src/matmul_simd.cpp:143-182, 285-342 for large M.)
+// A drain group is 256 values: a Q6_K super-block, or eight consecutive 32-value blocks of Q4_0 / Q8_0 (K % 256 == 0).
+//   Q6_K        weight value sc * (q6 - 32), up to +-4096: split exactly into H = 32 * ((u >> 5) - 128) and L = u & 31 with
+//               u = value + 4096 (both exact in fp16); group scale t = d of the super-block.
+//   Q8_0, Q4_0  every block has its own fp16 scale d_b, so the operand carries (d_b / t) * q with t = max |d_b| of the
+//               group: ratio = d_b / t in fp32, cut into fp16 pieces r1 + r2 (22 bits), and per value
+//               hi = rn(r1 * q), lo = rn(r2 * q + (r1 * q - hi)) - the inner difference is exact (one fused
+//               multiply-add). A group whose blocks share one scale has ratio 1: the operand is the integer q itself.
+// Both weight pieces meet the stacked activation pieces: two MMA instructions per 16-value step, D += Wh . [hi | lo] and
+// D += Wl . [hi | lo]; the drain adds y += t * (F_hi + F_lo) once per group. No min term in these types (Q4_0's offset
+// -8 is part of the operand value nibble - 8). Weight rows are only 2-byte aligned in general (34-byte and 210-byte
+// blocks), so the packed rows arrive by one plain bulk copy per row from the 16-byte boundary below the group's first
+// byte, and the converters skip the difference.
+namespace w2 {
+
+constexpr int STAGES = 2;
+constexpr int RAW_TILE_MAX = TW * 288;             // 36 KB: Q8_0 rows of 272 bytes + alignment slop
+constexpr int TABN2 = 4;
+template <uint32_t TYPE> struct Geo;
+template <> struct Geo<LAPLACE_TYPE_Q4_0> { static constexpr int GROUP_BYTES = 8 * Q4_0_BYTES, PITCH = 160; };
+template <> struct Geo<LAPLACE_TYPE_Q8_0> { static constexpr int GROUP_BYTES = 8 * Q8_0_BYTES, PITCH = 288; };
+template <> struct Geo<LAPLACE_TYPE_Q6_K> { static constexpr int GROUP_BYTES = Q6_K_BYTES, PITCH = 224; };
+
+constexpr uint32_t OFF_WH = 0;
+constexpr uint32_t OFF_WL = OFF_WH + STAGES * W_TILE;
+constexpr uint32_t OFF_A = OFF_WL + STAGES * W_TILE;
+constexpr uint32_t OFF_RAW = OFF_A + STAGES * A_TILE;
+constexpr uint32_t OFF_TAB = OFF_RAW + RAW_STAGES * RAW_TILE_MAX;
+constexpr uint32_t OFF_BAR = OFF_TAB + TABN2 * TW * 4;
+constexpr uint32_t BAR_FULL_A = OFF_BAR, BAR_FULL_W = BAR_FULL_A + 8 * STAGES, BAR_EMPTY = BAR_FULL_W + 8 * STAGES,
+                   BAR_RAW_FULL = BAR_EMPTY + 8 * STAGES, BAR_RAW_EMPTY = BAR_RAW_FULL + 8 * RAW_STAGES,
+                   BAR_TMEM_FULL = BAR_RAW_EMPTY + 8 * RAW_STAGES, BAR_TMEM_EMPTY = BAR_TMEM_FULL + 16,
+                   BAR_TAB_EMPTY = BAR_TMEM_EMPTY + 16, OFF_TMEM_PTR = BAR_TAB_EMPTY + 8 * TABN2, OFF_ABORT = OFF_TMEM_PTR + 8;
+constexpr uint32_t SMEM_BYTES = OFF_ABORT + 8 + 1024;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+static_assert(OFF_A % 1024 == 0 && OFF_RAW % 128 == 0, "tile alignment");
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+// hi / lo pieces of (r1 + r2) * x for a pair of exact small integers x
+__device__ __forceinline__ void two_piece(__half2 r1, __half2 r2, __half2 x, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __hmul2(r1, x);
+    hi = h2_bits(h);
+    lo = h2_bits(__hfma2(r2, x, __hfma2(r1, x, __hneg2(h))));
+}
+// fp16 pieces of a ratio in [-1, 1]
+__device__ __forceinline__ void ratio_pieces(float d, float t, __half2& r1, __half2& r2) {
+    const float ratio = t > 0.0f ? __fdiv_rn(d, t) : 0.0f;
+    const __half a = __float2half_rn(ratio);
+    r1 = __half2half2(a);
+    r2 = __half2half2(__float2half_rn(ratio - __half2float(a)));
+}
+
+// Where group `sb` of weight row `grow` starts, and how far that is above the 16-byte boundary the row's copy starts at.
+template <uint32_t TYPE>
+__device__ __forceinline__ const uint8_t* group_src(const SaParams& p, long long grow, int sb, uint32_t& mis) {
+    const uint8_t* src = p.w + grow * static_cast<long long>(p.rb) + static_cast<long long>(sb) * Geo<TYPE>::GROUP_BYTES;
+    mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15u);
+    return src - mis;
+}
+
+template <uint32_t TYPE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
+    using G = Geo<TYPE>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (sbase - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_ABORT);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(sbase + BAR_FULL_A + 8 * s, 1);
+            mbar_init(sbase + BAR_FULL_W + 8 * s, 4);
+            mbar_init(sbase + BAR_EMPTY + 8 * s, 1);
+        }
+        for (int q = 0; q < RAW_STAGES; ++q) {
+            mbar_init(sbase + BAR_RAW_FULL + 8 * q, 1);
+            mbar_init(sbase + BAR_RAW_EMPTY + 8 * q, 4);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(sbase + BAR_TMEM_FULL + 8 * t, 1);
+            mbar_init(sbase + BAR_TMEM_EMPTY + 8 * t, 8);
+        }
+        for (int t = 0; t < TABN2; ++t) mbar_init(sbase + BAR_TAB_EMPTY + 8 * t, 8);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(sbase + OFF_TMEM_PTR), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
+    const int n_tiles = tile_count(p);
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer: activation pieces ----------------
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const TileRef tr = tile_ref(p, tile);
+                const int bk = box_bucket(tr.nt);
+                const uint32_t piece = static_cast<uint32_t>(16 << bk) * 128u;
+                for (int kc = tr.sb0 * 4; kc < tr.sb1 * 4; ++kc, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_or_abort<false>(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, 2 * piece);
+                    tma_load_2d(sbase + OFF_A + s * A_TILE, &maps.a[bk], kc * BKC, tr.m0, sbase + BAR_FULL_A + 8 * s);
+                    tma_load_2d(sbase + OFF_A + s * A_TILE + piece, &maps.a[bk], kc * BKC, p.m_pad + tr.m0, sbase + BAR_FULL_A + 8 * s);
+                }
+            }
+            if (!ok) {
+                for (int k = 0; k < STAGES; ++k) {
+                    const int v = it - 1 - k;
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_FULL_A + 8 * (v % STAGES), (v / STAGES) & 1);
+                }
+            }
+        } else if (warp == 3) {
+            // ---------------- packed weights: one bulk copy per row and group, four rows per lane ----------------
+            int sbc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const TileRef tr = tile_ref(p, tile);
+                for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
+                    const int q = sbc % RAW_STAGES;
+                    bool w_ok = true;
+                    if (lane == 0) w_ok = wait_or_abort<false>(sbase + BAR_RAW_EMPTY + 8 * q, ((sbc / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY);
+                    if (!__shfl_sync(0xffffffffu, w_ok, 0)) { ok = false; break; }
+                    const uint8_t* src[4];
+                    uint32_t bytes[4], total = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = 4 * lane + i;
+                        uint32_t mis = 0;
+                        src[i] = group_src<TYPE>(p, static_cast<long long>(tr.wrow0) + tr.n0 + r, sb, mis);
+                        bytes[i] = tr.n0 + r < p.N ? ((mis + G::GROUP_BYTES + 15u) & ~15u) : 0u;       // rows past N: nothing to copy
+                        total += bytes[i];
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                    if (lane == 0) mbar_expect_tx(sbase + BAR_RAW_FULL + 8 * q, total);
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (bytes[i]) bulk_g2s(sbase + OFF_RAW + q * RAW_TILE_MAX + (4 * lane + i) * G::PITCH, src[i], bytes[i], sbase + BAR_RAW_FULL + 8 * q);
+                }
+            }
+            if (!ok && lane == 0) {
+                for (int k = 0; k < RAW_STAGES; ++k) {
+                    const int v = sbc - 1 - k;
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_RAW_FULL + 8 * (v % RAW_STAGES), (v / RAW_STAGES) & 1);
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------- MMA issue: two instructions per 16-value step (weight pieces Wh, Wl) ----------------
+            int it = 0, sbc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const TileRef tr = tile_ref(p, tile);
+                const uint32_t idesc = idesc_f16_m128((16 << box_bucket(tr.nt)) + ((tr.nt + 15) & ~15));
+                for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
+                    const int b = sbc & 1;
+                    if (!wait_or_abort<true>(sbase + BAR_TMEM_EMPTY + 8 * b, ((sbc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                    fence_after();
+                    const uint32_t f_tmem = tmem_base + b * 256;
+                    for (int c = 0; c < 4; ++c, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!wait_or_abort<true>(sbase + BAR_FULL_A + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                            !wait_or_abort<true>(sbase + BAR_FULL_W + 8 * s, ph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                        fence_after();
+                        const uint64_t hdesc = smem_desc_sw128(sbase + OFF_WH + s * W_TILE);
+                        const uint64_t ldesc = smem_desc_sw128(sbase + OFF_WL + s * W_TILE);
+                        const uint64_t adesc = smem_desc_sw128(sbase + OFF_A + s * A_TILE);
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const uint64_t off = static_cast<uint64_t>(ks * 2);
+                            mma_f16(f_tmem, hdesc + off, adesc + off, idesc, (c | ks) != 0);
+                            mma_f16(f_tmem, ldesc + off, adesc + off, idesc, 1);
+                        }
+                        commit(sbase + BAR_EMPTY + 8 * s);
+                    }
+                    if (!ok) break;
+                    commit(sbase + BAR_TMEM_FULL + 8 * b);
+                }
+            }
+        }
+    } else if (warp < 8) {
+        // ---------------- converters: thread r owns weight row n0 + r (they keep the 128 registers of the launch) ----------------
+        const int r = threadIdx.x - 128;
+        const __half2 k1152 = __half2half2(__float2half_rn(1152.f));
+        int it = 0, sbc = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            const TileRef tr = tile_ref(p, tile);
+            const bool live = tr.n0 + r < p.N;
+            for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
+                const int q = sbc % RAW_STAGES, slot = sbc % TABN2;
+                uint32_t mis = 0;
+                group_src<TYPE>(p, static_cast<long long>(tr.wrow0) + tr.n0 + r, sb, mis);
+                const uint32_t raw = sbase + OFF_RAW + q * RAW_TILE_MAX + r * G::PITCH + mis;      // byte 0 of this row's group (2-byte aligned)
+                if (!wait_or_abort<false>(sbase + BAR_RAW_FULL + 8 * q, (sbc / RAW_STAGES) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
+                    !wait_or_abort<false>(sbase + BAR_TAB_EMPTY + 8 * slot, ((sbc / TABN2) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                // group scale t and (Q4_0 / Q8_0) the blocks' own scales
+                float t = 0.0f, dblk[8];
+                if constexpr (TYPE == LAPLACE_TYPE_Q6_K) {
+                    t = live ? half_bits_to_float(lds16(raw + 208)) : 0.0f;
+                } else {
+                    constexpr int BB = TYPE == LAPLACE_TYPE_Q8_0 ? Q8_0_BYTES : Q4_0_BYTES;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        dblk[b] = live ? half_bits_to_float(lds16(raw + b * BB)) : 0.0f;
+                        t = fmaxf(t, fabsf(dblk[b]));
+                    }
+                }
+                reinterpret_cast<float*>(smem + OFF_TAB)[slot * TW + r] = t;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c, ++it) {
+                    const int s = it % STAGES;
+                    uint32_t hw[32], lw[32];                 // the row's 64 operand values of this chunk, two pieces
+                    if (!live) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) hw[i] = lw[i] = 0u;
+                    } else if constexpr (TYPE == LAPLACE_TYPE_Q8_0) {
+#pragma unroll
+                        for (int bb = 0; bb < 2; ++bb) {
+                            __half2 r1, r2;
+                            ratio_pieces(dblk[2 * c + bb], t, r1, r2);
+                            uint32_t w8[8];
+                            {
+                                uint32_t a4[4], b4[4];
+                                lds16B_align2(raw + (2 * c + bb) * Q8_0_BYTES + 2, a4);
+                                lds16B_align2(raw + (2 * c + bb) * Q8_0_BYTES + 18, b4);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) { w8[i] = a4[i]; w8[4 + i] = b4[i]; }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                // bytes + 128 under an fp16 exponent of 2^10: (1024 + 128 + q) - 1152 = q, exactly
+                                const uint32_t u = w8[i] ^ 0x80808080u;
+                                const __half2 x02 = __hsub2(bits_h2(prmt(u, 0x64646464u, 0x4240u)), k1152);
+                                const __half2 x13 = __hsub2(bits_h2(prmt(u, 0x64646464u, 0x4341u)), k1152);
+                                two_piece(r1, r2, x02, hw[16 * bb + 2 * i], lw[16 * bb + 2 * i]);
+                                two_piece(r1, r2, x13, hw[16 * bb + 2 * i + 1], lw[16 * bb + 2 * i + 1]);
+                            }
+                        }
+                    } else if constexpr (TYPE == LAPLACE_TYPE_Q4_0) {
+                        const __half2 k1032 = __half2half2(__float2half_rn(1032.f)), k16th = __half2half2(__float2half_rn(0.0625f)),
+                                      km72 = __half2half2(__float2half_rn(-72.f));
+#pragma unroll
+                        for (int bb = 0; bb < 2; ++bb) {
+                            __half2 r1, r2;
+                            ratio_pieces(dblk[2 * c + bb], t, r1, r2);
+                            uint32_t w4[4];
+                            lds16B_align2(raw + (2 * c + bb) * Q4_0_BYTES + 2, w4);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                // element l = low nibble of byte l, element l + 16 = high nibble; value = nibble - 8
+                                const uint32_t w = w4[i], sh = w >> 8;
+                                const __half2 l02 = __hsub2(bits_h2((w & 0x000f000fu) | 0x64006400u), k1032);
+                                const __half2 l13 = __hsub2(bits_h2((sh & 0x000f000fu) | 0x64006400u), k1032);
+                                const __half2 h02 = __hfma2(bits_h2((w & 0x00f000f0u) | 0x64006400u), k16th, km72);      // (1024 + 16 n) / 16 - 72
+                                const __half2 h13 = __hfma2(bits_h2((sh & 0x00f000f0u) | 0x64006400u), k16th, km72);
+                                two_piece(r1, r2, l02, hw[16 * bb + 2 * i], lw[16 * bb + 2 * i]);
+                                two_piece(r1, r2, l13, hw[16 * bb + 2 * i + 1], lw[16 * bb + 2 * i + 1]);
+                                two_piece(r1, r2, h02, hw[16 * bb + 8 + 2 * i], lw[16 * bb + 8 + 2 * i]);
+                                two_piece(r1, r2, h13, hw[16 * bb + 8 + 2 * i + 1], lw[16 * bb + 8 + 2 * i + 1]);
+                            }
+                        }
+                    } else {
+                        // Q6_K (Laplace src/kernels.h:46-54, src/matmul.cpp:180-195): chunk c = half h, nibble side nib;
+                        // value v of the chunk: 4 bits from ql[64 h + v] (low or high nibble), 2 bits from
+                        // qh[32 h + (v & 31)] at shift 2 * (2 nib + (v >> 5)), scale sc[8 h + 4 nib + (v >> 4)]
+                        const int h = c >> 1, nib = c & 1;
+                        const __half2 hoff = __half2half2(__float2half_rn(-36864.f)), loff = __half2half2(__float2half_rn(-1024.f));
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; ++j4) {                 // 16 values share a scale
+                            uint32_t ql4[4], qh4[4];
+                            lds16B_align2(raw + 64 * h + 16 * j4, ql4);
+                            lds16B_align2(raw + 128 + 32 * h + 16 * (j4 & 1), qh4);
+                            const int sc = lds_s8(raw + 192 + 8 * h + 4 * nib + j4);
+                            const int hshift = 2 * (2 * nib + (j4 >> 1));
+                            const uint32_t cc = static_cast<uint32_t>(4096 - 32 * sc) * 0x00010001u;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t q6 = ((ql4[i] >> (4 * nib)) & 0x0f0f0f0fu) | (((qh4[i] >> hshift) << 4) & 0x30303030u);
+                                const uint32_t e02 = q6 & 0x00ff00ffu, e13 = (q6 >> 8) & 0x00ff00ffu;
+                                // both 16-bit lanes: u = sc * (q6 - 32) + 4096 in [0, 8192]; the 32-bit product cannot borrow
+                                const uint32_t u02 = e02 * static_cast<uint32_t>(sc) + cc, u13 = e13 * static_cast<uint32_t>(sc) + cc;
+                                // (v | 0x7800) is fp16(32768 + 32 v), (v | 0x6400) is fp16(1024 + v)
+                                hw[8 * j4 + 2 * i] = h2_bits(__hadd2(bits_h2(((u02 >> 5) & 0x01ff01ffu) | 0x78007800u), hoff));
+                                hw[8 * j4 + 2 * i + 1] = h2_bits(__hadd2(bits_h2(((u13 >> 5) & 0x01ff01ffu) | 0x78007800u), hoff));
+                                lw[8 * j4 + 2 * i] = h2_bits(__hadd2(bits_h2((u02 & 0x001f001fu) | 0x64006400u), loff));
+                                lw[8 * j4 + 2 * i + 1] = h2_bits(__hadd2(bits_h2((u13 & 0x001f001fu) | 0x64006400u), loff));
+                            }
+                        }
+                    }
+                    if (!wait_or_abort<false>(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    uint8_t* hrow = smem + OFF_WH + s * W_TILE + r * 128;
+                    uint8_t* lrow = smem + OFF_WL + s * W_TILE + r * 128;
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) {
+                        const uint32_t off = static_cast<uint32_t>(jj ^ (r & 7)) << 4;
+                        *reinterpret_cast<uint4*>(hrow + off) = make_uint4(hw[4 * jj], hw[4 * jj + 1], hw[4 * jj + 2], hw[4 * jj + 3]);
+                        *reinterpret_cast<uint4*>(lrow + off) = make_uint4(lw[4 * jj], lw[4 * jj + 1], lw[4 * jj + 2], lw[4 * jj + 3]);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sbase + BAR_FULL_W + 8 * s);
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sbase + BAR_RAW_EMPTY + 8 * q);
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");       // 4 x 40 + 4 x 128 + 8 x 168 <= 16 x 128
+        // ---------------- drain: y += t * (F_hi + F_lo) once per group ----------------
+        const int e8 = warp - 8;
+        const int quad = e8 & 3, half = e8 >> 2;
+        const uint32_t t_lane = static_cast<uint32_t>(quad * 32) << 16;
+        const int wr = quad * 32 + lane;
+        int sbc = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            const TileRef tr = tile_ref(p, tile);
+            const int box = 16 << box_bucket(tr.nt);
+            float2 acc[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) acc[c] = make_float2(0.f, 0.f);
+            for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
+                const int b = sbc & 1, slot = sbc % TABN2;
+                if (!wait_or_abort<false>(sbase + BAR_TMEM_FULL + 8 * b, (sbc >> 1) & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
+                fence_after();
+                const float tt = reinterpret_cast<const float*>(smem + OFF_TAB)[slot * TW + wr];
+                const float2 t2 = make_float2(tt, tt);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (half * 64 + h * 32 < tr.nt) {
+                        float fh[32], fl[32];
+                        ld32(tmem_base + t_lane + b * 256 + half * 64 + h * 32, fh);
+                        ld32(tmem_base + t_lane + b * 256 + box + half * 64 + h * 32, fl);
+                        wait_ld();
+#pragma unroll
+                        for (int c2 = 0; c2 < 16; ++c2)
+                            acc[h * 16 + c2] = __ffma2_rn(t2, __fadd2_rn(make_float2(fh[2 * c2], fh[2 * c2 + 1]), make_float2(fl[2 * c2], fl[2 * c2 + 1])),
+                                                          acc[h * 16 + c2]);
+                    }
+                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * b);
+                    mbar_arrive(sbase + BAR_TAB_EMPTY + 8 * slot);
+                }
+            }
+            if (!ok) break;
+            const int n = tr.n0 + wr;
+            float* ybase = p.ksplit > 1 ? p.y_part + static_cast<size_t>(tr.ks) * p.M * p.N : p.y;
+            if (n < p.N) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const int col = half * 64 + c;
+                    if (col < tr.nt) {
+                        const int row = tr.m0 + col;
+                        int orow = p.out_row ? __ldg(p.out_row + row) : row;
+                        if (p.out_identity && orow >= 0) orow = row;
+                        const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                        if (orow >= 0) ybase[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
+                    }
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace w2
+
+
 // ---- activation quantizer ------------------------------------------------------------------
 // One CTA per activation row. The int8 values q and the block scales d are the reference's (Laplace
 // src/matmul_simd.cpp:348-410: d = amax / 127, q = rne(x * (1 / d)), sums from the unclamped integers); what is
@@ -560,7 +960,7 @@ SaOperand carve_operand(uint8_t*& s, size_t m_pad, int K) {
 }
 
 struct SaLaunch {
-    const uint8_t* w; float* y; int M, K, N;
+    const uint8_t* w; uint32_t type; float* y; int M, K, N;
     long long w_rows;            // rows of the (stacked) weight matrix
     SaOperand op;
     const int4* tile_tab; const int* n_tiles_dev; const int* out_row; int out_identity;
@@ -579,11 +979,16 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
                          static_cast<uint64_t>(K / 16) * 4, 16, 8u << bk, CU_TENSOR_MAP_SWIZZLE_NONE, "block sums"))
             return LAPLACE_ERR_CUDA;
     }
-    const uint64_t rb = row_bytes(LAPLACE_TYPE_Q4_K, K);
-    if (!make_map_2d(&maps.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, rb, static_cast<uint64_t>(L.w_rows), rb, Q4_K_BYTES, TW,
-                     CU_TENSOR_MAP_SWIZZLE_NONE, "weights"))
-        return LAPLACE_ERR_CUDA;
+    const uint64_t rb = row_bytes(L.type, K);
+    if (L.type == LAPLACE_TYPE_Q4_K) {
+        if (!make_map_2d(&maps.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, L.w, rb, static_cast<uint64_t>(L.w_rows), rb, Q4_K_BYTES, TW,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, "weights"))
+            return LAPLACE_ERR_CUDA;
+    } else {
+        maps.w = maps.a[0];      // not used by the two-piece kernels (they copy weight rows by address)
+    }
     SaParams p{};
+    p.w = L.w; p.rb = static_cast<uint32_t>(rb);
     p.y = L.y; p.inv_s = L.op.inv_s; p.err = c.d_err;
     p.M = L.M; p.N = L.N; p.K = K; p.m_pad = L.op.m_pad;
     p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n;
@@ -592,10 +997,19 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_sa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(w2::SMEM_BYTES));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(w2::SMEM_BYTES));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(w2::SMEM_BYTES));
         if (e != cudaSuccess) return cuda_check(e, "cudaFuncSetAttribute gemm_sa");
         configured = true;
     }
-    gemm_q4k_sa_kernel<<<L.grid, THREADS, SMEM_BYTES, st>>>(maps, p);
+    switch (L.type) {
+        case LAPLACE_TYPE_Q4_K: gemm_q4k_sa_kernel<<<L.grid, THREADS, SMEM_BYTES, st>>>(maps, p); break;
+        case LAPLACE_TYPE_Q4_0: w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p); break;
+        case LAPLACE_TYPE_Q8_0: w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p); break;
+        case LAPLACE_TYPE_Q6_K: w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p); break;
+        default: return LAPLACE_UNSUPPORTED;
+    }
     c.launches++;
     c.last_path = 2;
     return cuda_check(cudaGetLastError(), "gemm_sa launch");
@@ -627,7 +1041,9 @@ SplitPlan plan_split(int M, int K, int N, bool allow) {
 void release_gemm_sa_scratch() { g_scratch.release(); }
 
 bool gemm_sa_supports(uint32_t type, int M, int K, int N) {
-    return type == LAPLACE_TYPE_Q4_K && M > 8 && N > 0 && K > 0 && K % 256 == 0;
+    // drain groups are 256 values for every type (a super-block, or eight 32-value blocks)
+    return (type == LAPLACE_TYPE_Q4_K || type == LAPLACE_TYPE_Q6_K || type == LAPLACE_TYPE_Q4_0 || type == LAPLACE_TYPE_Q8_0) &&
+           M > 8 && N > 0 && K > 0 && K % 256 == 0;
 }
 
 namespace {
@@ -652,13 +1068,14 @@ SaPlan plan_sa(int M, int K, int N, bool allow_split) {
 
 int check_args(const float* x, const uint8_t* w, uint32_t type, int M, int K, int N) {
     if (!gemm_sa_supports(type, M, K, N)) return LAPLACE_UNSUPPORTED;
-    if (reinterpret_cast<uintptr_t>(w) & 15) return fail(LAPLACE_ERR_ARG, "gemm: weights must be 16-byte aligned on the device");
+    if (reinterpret_cast<uintptr_t>(w) & (type == LAPLACE_TYPE_Q4_K ? 15 : 1))
+        return fail(LAPLACE_ERR_ARG, "gemm: weights must be 16-byte (Q4_K) / 2-byte aligned on the device");
     if (reinterpret_cast<uintptr_t>(x) & 15) return fail(LAPLACE_ERR_ARG, "gemm: x not 16-byte aligned");
     return LAPLACE_OK;
 }
 
 // Quantizes x into `scratch` (device memory of at least pl.total() bytes, 256-byte aligned) and runs the kernel.
-int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const uint8_t* w, float* y, int M, int K, int N,
+int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N,
                        cudaStream_t st) {
     Context& c = ctx();
     int rc;
@@ -668,7 +1085,7 @@ int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const
     c.launches++;
     if ((rc = cuda_check(cudaGetLastError(), "quantize_sa launch"))) return rc;
     SaLaunch L{};
-    L.w = w; L.y = y; L.M = M; L.K = K; L.N = N; L.w_rows = N; L.op = op;
+    L.w = w; L.type = type; L.y = y; L.M = M; L.K = K; L.N = N; L.w_rows = N; L.op = op;
     L.tiles_m = pl.tiles_m; L.tiles_n = pl.tiles_n;
     L.ksplit = pl.sp.ksplit; L.sb_per = pl.sp.sb_per;
     L.y_part = pl.sp.ksplit > 1 ? reinterpret_cast<float*>(s) : nullptr;
@@ -699,7 +1116,7 @@ int launch_gemm_sa(const float* x, const uint8_t* w, uint32_t type, float* y, in
     if (rc) return rc;
     const SaPlan pl = plan_sa(M, K, N, can_split(y, M, N));
     if ((rc = g_scratch.ensure(pl.total(), st))) return rc;
-    return gemm_sa_on_scratch(static_cast<uint8_t*>(g_scratch.p), pl, x, w, y, M, K, N, st);
+    return gemm_sa_on_scratch(static_cast<uint8_t*>(g_scratch.p), pl, x, w, type, y, M, K, N, st);
 }
 
 // The same call on scratch memory the caller owns (`cap` bytes at `scratch`, 256-byte aligned); nothing is
@@ -713,7 +1130,7 @@ int launch_gemm_sa_prealloc(uint8_t* scratch, size_t cap, const float* x, const 
     if (pl.total() > cap) pl = plan_sa(M, K, N, false);
     if (pl.total() > cap)
         return fail(LAPLACE_ERR_LIMIT, "gemm: M=%d K=%d needs %zu bytes of scratch, the caller's area holds %zu", M, K, pl.total(), cap);
-    return gemm_sa_on_scratch(scratch, pl, x, w, y, M, K, N, st);
+    return gemm_sa_on_scratch(scratch, pl, x, w, type, y, M, K, N, st);
 }
 
 
@@ -888,10 +1305,8 @@ bool moe_sa_supports(uint32_t type, int K, int N) { return gemm_sa_supports(type
 int launch_moe_grouped_sa(const float* x, const uint8_t* w, uint32_t type, const int* pair_expert, const int* pair_row,
                           int P, int E, float* y, int K, int N, cudaStream_t st) {
     if (!moe_sa_supports(type, K, N)) return LAPLACE_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
-        return fail(LAPLACE_ERR_ARG, "moe_grouped: x and w must be 16-byte aligned on the device");
-    if ((static_cast<size_t>(N) * row_bytes(type, K)) % 16)
-        return fail(LAPLACE_ERR_ARG, "moe_grouped: expert stride is not a 16-byte multiple");
+    if ((reinterpret_cast<uintptr_t>(w) & (type == LAPLACE_TYPE_Q4_K ? 15 : 1)) || (reinterpret_cast<uintptr_t>(x) & 15))
+        return fail(LAPLACE_ERR_ARG, "moe_grouped: x (16 bytes) or w (16 bytes for Q4_K, else 2) is misaligned on the device");
     Context& c = ctx();
     const int tiles_n = (N + TW - 1) / TW;
     const GroupBounds gb = group_bounds(P, E);
@@ -912,7 +1327,7 @@ int launch_moe_grouped_sa(const float* x, const uint8_t* w, uint32_t type, const
     c.launches++;
     if ((rc = cuda_check(cudaGetLastError(), "moe quantize launch"))) return rc;
     SaLaunch L{};
-    L.w = w; L.y = y; L.M = P; L.K = K; L.N = N; L.w_rows = static_cast<long long>(E) * N; L.op = op;
+    L.w = w; L.type = type; L.y = y; L.M = P; L.K = K; L.N = N; L.w_rows = static_cast<long long>(E) * N; L.op = op;
     L.tile_tab = tab; L.n_tiles_dev = n_tiles; L.out_row = out_row;
     L.tiles_m = 1; L.tiles_n = tiles_n; L.grid = grid_for_tiles(gb.groups * tiles_n);
     rc = run_sa_kernel(L, st);
@@ -925,11 +1340,10 @@ int launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w
                       int activation, float* out, float* h_out, cudaStream_t st) {
     if (!moe_sa_supports(type_gu, H, 2 * I) || !moe_sa_supports(type_dn, I, H)) return LAPLACE_UNSUPPORTED;
     if (I % 32 || H % 4) return fail(LAPLACE_ERR_ARG, "moe_ffn: H=%d I=%d", H, I);
-    if ((reinterpret_cast<uintptr_t>(w_gate_up) & 15) || (reinterpret_cast<uintptr_t>(w_down) & 15) ||
+    if ((reinterpret_cast<uintptr_t>(w_gate_up) & (type_gu == LAPLACE_TYPE_Q4_K ? 15 : 1)) ||
+        (reinterpret_cast<uintptr_t>(w_down) & (type_dn == LAPLACE_TYPE_Q4_K ? 15 : 1)) ||
         (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
-        return fail(LAPLACE_ERR_ARG, "moe_ffn: x, out and the weights must be 16-byte aligned on the device");
-    if ((static_cast<size_t>(2 * I) * row_bytes(type_gu, H)) % 16 || (static_cast<size_t>(H) * row_bytes(type_dn, I)) % 16)
-        return fail(LAPLACE_ERR_ARG, "moe_ffn: expert stride is not a 16-byte multiple");
+        return fail(LAPLACE_ERR_ARG, "moe_ffn: x, out (16 bytes) or the weights (16 bytes for Q4_K, else 2) are misaligned on the device");
     Context& c = ctx();
     const int P = T * top_k;
     const int tiles_n1 = (2 * I + TW - 1) / TW, tiles_n2 = (H + TW - 1) / TW;
@@ -959,7 +1373,7 @@ int launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w
     if ((rc = cuda_check(cudaGetLastError(), "moe quantize launch"))) return rc;
 
     SaLaunch L{};
-    L.w = w_gate_up; L.y = gu; L.M = P; L.K = H; L.N = 2 * I; L.w_rows = static_cast<long long>(E) * 2 * I; L.op = op1;
+    L.w = w_gate_up; L.type = type_gu; L.y = gu; L.M = P; L.K = H; L.N = 2 * I; L.w_rows = static_cast<long long>(E) * 2 * I; L.op = op1;
     L.tile_tab = tab1; L.n_tiles_dev = n_tiles1; L.out_row = out_row; L.out_identity = 1;      // gu stays in operand-row order
     L.tiles_m = 1; L.tiles_n = tiles_n1; L.grid = grid_for_tiles(gb.groups * tiles_n1);
     if ((rc = run_sa_kernel(L, st))) return rc;
@@ -969,7 +1383,7 @@ int launch_moe_ffn_sa(const float* x, const uint8_t* w_gate_up, const uint8_t* w
     if ((rc = cuda_check(cudaGetLastError(), "moe_act_quant launch"))) return rc;
 
     SaLaunch L2{};
-    L2.w = w_down; L2.y = dn; L2.M = P; L2.K = I; L2.N = H; L2.w_rows = static_cast<long long>(E) * H; L2.op = op2;
+    L2.w = w_down; L2.type = type_dn; L2.y = dn; L2.M = P; L2.K = I; L2.N = H; L2.w_rows = static_cast<long long>(E) * H; L2.op = op2;
     L2.tile_tab = tab2; L2.n_tiles_dev = n_tiles2; L2.out_row = out_row; L2.out_identity = 1;
     L2.tiles_m = 1; L2.tiles_n = tiles_n2; L2.grid = grid_for_tiles(gb.groups * tiles_n2);
     if ((rc = run_sa_kernel(L2, st))) return rc;
@@ -1030,4 +1444,112 @@ int launch_moe_route(const float* logits, int T, int E, int top_k, int* top_idx,
     return cuda_check(cudaGetLastError(), "moe_route launch");
 }
 
+
+// ---- exchange helpers of the expert-parallel layer ---------------------------------------
+// One all-gather moves [x | expert ids | weights] per token. pack builds a rank's send rows,
+// unpack splits the gathered rows and turns global expert ids into local ones (-1 = another GPU's).
+namespace {
+
+__global__ void moe_pack_kernel(const float* __restrict__ x, const int* __restrict__ idx, const float* __restrict__ wts,
+                                int T, int H, int k, float* __restrict__ packed) {
+    const int stride = H + 2 * k;
+    const long long total = static_cast<long long>(T) * stride;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / stride), c = static_cast<int>(i - static_cast<long long>(t) * stride);
+        float v;
+        if (c < H) v = x[static_cast<long long>(t) * H + c];
+        else if (c < H + k) v = __int_as_float(idx[t * k + (c - H)]);
+        else v = wts[t * k + (c - H - k)];
+        packed[i] = v;
+    }
+}
+
+__global__ void moe_unpack_kernel(const float* __restrict__ packed, int T, int H, int k, int first, int count,
+                                  float* __restrict__ x, int* __restrict__ idx_local, float* __restrict__ wts) {
+    const int stride = H + 2 * k;
+    const long long total = static_cast<long long>(T) * stride;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / stride), c = static_cast<int>(i - static_cast<long long>(t) * stride);
+        const float v = packed[i];
+        if (c < H) x[static_cast<long long>(t) * H + c] = v;
+        else if (c < H + k) {
+            const int e = __float_as_int(v) - first;
+            idx_local[t * k + (c - H)] = (e >= 0 && e < count) ? e : -1;
+        } else wts[t * k + (c - H - k)] = v;
+    }
+}
+
+}  // namespace
+
+int launch_moe_pack(const float* x, const int* idx, const float* wts, int T, int H, int k, float* packed, cudaStream_t st) {
+    Context& c = ctx();
+    const long long total = static_cast<long long>(T) * (H + 2 * k);
+    long long blocks = (total + 255) / 256;
+    if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
+    moe_pack_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(x, idx, wts, T, H, k, packed);
+    c.launches++;
+    return cuda_check(cudaGetLastError(), "moe_pack launch");
+}
+
+int launch_moe_unpack(const float* packed, int T, int H, int k, int first, int count, float* x, int* idx_local, float* wts,
+                      cudaStream_t st) {
+    Context& c = ctx();
+    const long long total = static_cast<long long>(T) * (H + 2 * k);
+    long long blocks = (total + 255) / 256;
+    if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
+    moe_unpack_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), 256, 0, st>>>(packed, T, H, k, first, count, x, idx_local, wts);
+    c.launches++;
+    return cuda_check(cudaGetLastError(), "moe_unpack launch");
+}
+
+// ---- the entry point that allocates nothing -------------------------------------------
+// Some hosts of this library must not (or cannot) call the CUDA allocator on the request
+// path: a serving process that has handed all free HBM to its own pools (KV cache,
+// activations), so that cudaMalloc would fail or fragment them, and latency-bound loops that
+// cannot take the allocator's locks or the implicit device synchronisation that comes with
+// cudaFree when a buffer has to grow. For them the scratch of the prefill GEMM
+// (the quantized activations) lives in a fixed array inside the library image instead of a
+// growable cudaMalloc'd buffer.
+//
+// The array is part of every context that loads the library (NOALLOC_SCRATCH_BYTES of HBM
+// per GPU until the process exits). In host code its name is only a handle; the device
+// address comes from cudaGetSymbolAddress, asked once per device with that device current.
+constexpr size_t NOALLOC_SCRATCH_BYTES = 10u << 20;    // 10 MiB: e.g. M = 512, K = 4096 needs 8.3 MiB
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+namespace {
+uint8_t* g_noalloc_ptr = nullptr;     // device address of g_noalloc_scratch on g_noalloc_dev
+int      g_noalloc_dev = -1;
+}  // namespace
+
 }  // namespace lp
+
+extern "C" int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t type, float* y,
+                                             int M, int K, int N, void* stream) {
+    using namespace lp;
+    Context& c = ctx();
+    if (!c.ready) return fail(LAPLACE_ERR_STATE, "laplace_cuda_init has not been called (or found no GPU)");
+    if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm_noalloc: null pointer");
+    if (!gemm_sa_supports(type, M, K, N))
+        return fail(LAPLACE_ERR_ARG, "gemm_noalloc: only the prefill shapes are served here (M > 8, K %% 256 == 0, Q4_0 / Q8_0 / Q4_K / "
+                                     "Q6_K); decode calls (M <= 8) use no scratch at all, call laplace_cuda_gemm_dev");
+    if (g_noalloc_dev != c.device) {
+        // first call on this device: resolve the array's device address (the library is bound to c.device,
+        // make sure it is the current one for the lookup)
+        int cur = -1;
+        cudaError_t e = cudaGetDevice(&cur);
+        if (e == cudaSuccess && cur != c.device) e = cudaSetDevice(c.device);
+        void* ptr = nullptr;
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e == cudaSuccess && cur >= 0 && cur != c.device) e = cudaSetDevice(cur);
+        if (e != cudaSuccess || !ptr) return cuda_check(e == cudaSuccess ? cudaErrorInvalidSymbol : e, "cudaGetSymbolAddress(scratch)");
+        g_noalloc_ptr = static_cast<uint8_t*>(ptr);
+        g_noalloc_dev = c.device;
+    }
+    // the same K-split as laplace_cuda_gemm_dev (hence bit-identical results) whenever its partial results fit the
+    // array too; otherwise no split (results then agree to fp32 rounding)
+    return launch_gemm_sa_prealloc(g_noalloc_ptr, NOALLOC_SCRATCH_BYTES, x, w, type, y, M, K, N,
+                                   stream ? static_cast<cudaStream_t>(stream) : c.stream);
+}

@@ -133,8 +133,7 @@ def test_block_sums_of_the_timed_kernels_bit_exact(oracle, t, M):
         w, x1, sc = synth.single_live_block(t, K, N, 3000 + live, live)
         x = np.concatenate([x1 * np.float32(2.0 ** -(m % 5)) * (-1) ** m for m in range(M)])     # still exact in Q8
         y, path = run_dev(t, x, w, M, K, N)
-        if M <= 8 or t in (GGMLType.Q4_K, GGMLType.Q6_K):
-            assert path == (1 if M <= 8 else 2)
+        assert path == (1 if M <= 8 else 2)
         want = _expected_from_blocksums(oracle, t, w, x, sc, K, N, live)
         assert np.array_equal(y, want), f"{t.name} M={M} live block {live}: {np.abs(y - want).max()}"
 

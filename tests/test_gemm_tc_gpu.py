@@ -58,13 +58,28 @@ def test_prefill_through_host_entry_point(oracle):
 
 
 @pytest.mark.parametrize("t", [GGMLType.Q4_0, GGMLType.Q8_0, GGMLType.Q6_K])
-def test_other_types_large_m(oracle, t):
-    """Types without a tensor-core kernel run as repeated 8-row streaming passes: still exact."""
-    M, K, N = 20, 512, 40
-    w = synth.weights(t, K, N, seed=81, how="affine")
+@pytest.mark.parametrize("how", ["random", "ref", "affine"])
+@pytest.mark.parametrize("M,K,N", [(20, 512, 40), (512, 4096, 4096), (130, 768, 129), (96, 2816, 200), (64, 14336, 136)])
+def test_other_types_large_m(oracle, t, how, M, K, N):
+    """Q4_0, Q8_0 and Q6_K (any K that is a multiple of 256) on the tensor cores: weight operand in two fp16 pieces."""
+    if (M, K, N) == (512, 4096, 4096) and how != "affine":
+        pytest.skip("one packing is enough at the large shape")
+    w = synth.weights(t, K, N, seed=81, how=how)
     x = synth.normal_f32(82, (M, K))
-    y, _ = run_dev(t, x, w, M, K, N)
-    check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"{t.name} M=20")
+    y, path = run_dev(t, x, w, M, K, N)
+    assert path == 2, "the tensor-core kernel did not run"
+    check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"{t.name} {how} M={M} K={K} N={N}")
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q4_0, GGMLType.Q8_0])
+def test_block_quants_with_other_k_run_as_streaming_passes(oracle, t):
+    """K that is not a multiple of 256 (legal for the 32-value block types) keeps the streaming kernel: still exact."""
+    M, K, N = 20, 544, 40
+    w = synth.weights(t, K, N, seed=83, how="affine")
+    x = synth.normal_f32(84, (M, K))
+    y, path = run_dev(t, x, w, M, K, N)
+    assert path == 1
+    check_close(y, oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"{t.name} K=544")
 
 
 @pytest.mark.parametrize("how", ["random", "ref", "affine"])

@@ -26,7 +26,8 @@ def _host_activation(gu, inter, activation):
 
 @pytest.mark.parametrize("activation", [0, 1])
 @pytest.mark.parametrize("t_gu,t_dn,H,I", [(GGMLType.Q4_K, GGMLType.Q4_K, 512, 256), (GGMLType.Q4_K, GGMLType.Q4_K, 2048, 768),
-                                           (GGMLType.Q6_K, GGMLType.Q4_K, 2048, 256)])
+                                           (GGMLType.Q6_K, GGMLType.Q4_K, 2048, 256), (GGMLType.Q8_0, GGMLType.Q4_0, 512, 256),
+                                           (GGMLType.Q4_K, GGMLType.Q6_K, 768, 512)])
 def test_fused_ffn_stage_by_stage(oracle, activation, t_gu, t_dn, H, I):
     import torch
     from laplace_b200 import device
@@ -80,11 +81,13 @@ def test_partial_sums_over_expert_shards_add_up(oracle):
     assert np.abs(got - want).max() <= 1e-5 * np.sqrt((want ** 2).mean()) * 10
 
 
-def test_unsupported_type_is_reported():
+def test_unsupported_shape_is_reported():
+    """Hidden / expert widths that are not multiples of 256 have no grouped kernel: the call says so (return value 1)
+    and the caller loops the expert-indexed GEMV per token, as the reference does."""
     import torch
     from laplace_b200 import device
     from laplace_b200.matmul import LaplaceCudaError
-    t, E, k, T, H, I = GGMLType.Q8_0, 2, 1, 2, 256, 256
+    t, E, k, T, H, I = GGMLType.Q8_0, 2, 1, 2, 256, 160
     w1 = device.upload_weights(synth.weights(t, H, E * 2 * I, seed=620, how="random"))
     w2 = device.upload_weights(synth.weights(t, I, E * H, seed=621, how="random"))
     x = torch.zeros((T, H), dtype=torch.float32, device="cuda")
