@@ -90,15 +90,28 @@ def test_grouped_equals_per_token_calls_on_device(oracle):
     assert np.allclose(y, ref, rtol=1e-4, atol=1e-4)
 
 
-def test_other_types_fall_back_to_expert_indexed_gemv(oracle):
-    t, K, N, E, T, top_k = GGMLType.Q8_0, 256, 64, 6, 5, 2
+@pytest.mark.parametrize("t", [GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.Q6_K])
+def test_other_types_run_grouped(oracle, t):
+    K, N, E, T, top_k = 512, 136, 6, 21, 2
+    w = synth.weights(t, K, N * E, seed=345, how="random")
+    x = synth.normal_f32(346, (T, K))
+    top = _routing(347, T, E, top_k)
+    y, path = _run(t, x, w, top.reshape(-1), np.repeat(np.arange(T, dtype=np.int32), top_k), E, K, N)
+    assert path == 3
+    ref = np.concatenate([oracle.moe_gemv(x[tok], w, t, top[tok], K, N, multi=False, mode=1) for tok in range(T)])
+    check_close(y, ref, f"grouped {t.name}")
+
+
+def test_other_k_falls_back_to_expert_indexed_gemv(oracle):
+    """K that is not a multiple of 256: no grouped kernel, the Python mirror loops the expert-indexed GEMV."""
+    t, K, N, E, T, top_k = GGMLType.Q8_0, 160, 64, 6, 5, 2
     w = synth.weights(t, K, N * E, seed=340, how="random")
     x = synth.normal_f32(341, (T, K))
     top = _routing(342, T, E, top_k)
     y, path = _run(t, x, w, top.reshape(-1), np.repeat(np.arange(T, dtype=np.int32), top_k), E, K, N)
     assert path == 1
     ref = np.concatenate([oracle.moe_gemv(x[tok], w, t, top[tok], K, N, multi=False, mode=1) for tok in range(T)])
-    check_close(y, ref, "grouped fallback Q8_0")
+    check_close(y, ref, "grouped fallback Q8_0, K=160")
 
 
 def test_bad_expert_index_is_reported():
