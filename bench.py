@@ -483,6 +483,44 @@ def decode_leg(device, synth, torch):
         del g
         out.append({"type": name, "M": M, "K": K, "N": N, "us": round(us, 2), "weight_gbs": round(wbytes / us / 1e3, 1)})
         del ws
+    # several matrices that share x in ONE launch (laplace_cuda_gemm_multi_dev), with the RMSNorm of x in the prologue:
+    # the reference's rmsnorm + matmul_rows(gate) + matmul_rows(up), and rmsnorm + q + k + v (src/arch_llama.cpp:475-501)
+    for label, Ns in (("gate+up", (14336, 14336)), ("q+k+v", (4096, 1024, 1024))):
+        t, M, K = 12, 1, 4096
+        wbytes = sum(Ns) * (K // 256) * 144
+        n_copies = max(2, min(24, -(-(160 << 20) // wbytes)))
+        sets = []
+        for c in range(n_copies):
+            sets.append([device.upload_weights(np.roll(synth.weights(t, K, n, seed=1700 + i, how="random"), 16 * c, axis=0)) for i, n in enumerate(Ns)])
+        x = torch.from_numpy(synth.normal_f32(1601, (M, K))).cuda()
+        nw = torch.ones(K, dtype=torch.float32, device="cuda")
+        for c in range(n_copies):
+            device.gemm_multi(x, sets[c], t, M, K, Ns, norm_weight=nw, eps=1e-5)
+        torch.cuda.synchronize()
+        iters = 40
+        g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        keep = []
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                for i in range(iters):
+                    keep.append(device.gemm_multi(x, sets[i % n_copies], t, M, K, Ns, norm_weight=nw, eps=1e-5))
+        torch.cuda.current_stream().wait_stream(st)
+        g.replay()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        us = best / iters * 1e3
+        del g, keep, sets
+        out.append({"type": "Q4_K", "M": M, "K": K, "N": list(Ns), "matrices_in_one_launch": label, "rmsnorm_fused": True,
+                    "us": round(us, 2), "weight_gbs": round(wbytes / us / 1e3, 1)})
     device.sync()
     return out
 

@@ -111,6 +111,17 @@ int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type,
                               const int* expert_idx, int n_experts,
                               float* y, int K, int N, int per_expert_x, void* stream);
 
+/* Several weight matrices of one type and one K against the SAME activation rows in one launch, with an optional
+ * RMSNorm in front: what the reference does as  ops::rmsnorm(x, w_norm, x_norm)  followed by one matmul_rows call per
+ * matrix on x_norm (src/ops.cpp:34-74; src/arch_llama.cpp:475-501: q, k, v after the attention norm, gate and up
+ * after the FFN norm - it quantizes x_norm again for every matrix). Here x is normalised (norm_weight != NULL:
+ * x_norm = x * 1/sqrt(mean(x^2) + norm_eps) * norm_weight, fp32) and quantized ONCE inside the kernel's prologue and
+ * every matrix streams past it: y_i[m*N_i + j] = dot(quantize(x_norm[m]), row j of matrix i). x_norm_out (optional)
+ * receives the normalised rows [M][K]. M <= 8 (decode); 1..8 matrices. Device pointers. */
+typedef struct { const uint8_t* w; float* y; int N; } laplace_cuda_matrix;
+int laplace_cuda_gemm_multi_dev(const float* x, const float* norm_weight, float norm_eps, float* x_norm_out,
+                                const laplace_cuda_matrix* mats, int n_mats, uint32_t type, int M, int K, void* stream);
+
 /* Expert-grouped matmul for a batch of tokens. The reference runs a mixture-of-experts layer
  * token by token: one fused_moe_gemm_idx call per token for gate/up (src/matmul.h:36-44,
  * src/arch_gemma4.cpp:604) and one fused_moe_gemm_multi call for down (src/matmul.h:46-54,

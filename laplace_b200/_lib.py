@@ -23,6 +23,7 @@ SYMBOLS = {
     "laplace_cuda_moe_gemv": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i]),
     "laplace_cuda_moe_gemv_multi": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i]),
     "laplace_cuda_gemm_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
+    "laplace_cuda_gemm_multi_dev": (_i, [_vp, _vp, C.c_float, _vp, _vp, _i, _u32, _i, _i, _vp]),
     "laplace_cuda_gemm_noalloc_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_moe_gemv_dev": (_i, [_vp, _vp, _u32, _vp, _i, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_moe_grouped_dev": (_i, [_vp, _vp, _u32, _vp, _vp, _i, _i, _vp, _i, _i, _vp]),
@@ -42,6 +43,13 @@ SYMBOLS = {
     "laplace_cuda_last_path": (_i, []),
     "laplace_cuda_launch_count": (C.c_longlong, [_i]),
 }
+
+
+
+class Matrix(C.Structure):
+    """laplace_cuda_matrix: one weight matrix of a multi-matrix call (device pointers)."""
+    _fields_ = [("w", C.c_void_p), ("y", C.c_void_p), ("N", C.c_int)]
+
 
 _lib = None
 

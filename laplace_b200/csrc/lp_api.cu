@@ -398,6 +398,23 @@ int laplace_cuda_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float
     return dispatch_gemm_dev(x, w, type, y, M, K, N, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
 }
 
+int laplace_cuda_gemm_multi_dev(const float* x, const float* norm_weight, float norm_eps, float* x_norm_out,
+                                const laplace_cuda_matrix* mats, int n_mats, uint32_t type, int M, int K, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    if (!x || !mats || n_mats <= 0 || n_mats > 8) return fail(LAPLACE_ERR_ARG, "gemm_multi: null pointer or %d matrices (1..8)", n_mats);
+    if (M <= 0 || K <= 0 || K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm_multi: M=%d K=%d", M, K);
+    if (M > 8) return fail(LAPLACE_ERR_ARG, "gemm_multi: M=%d: this entry serves decode (M <= 8); for prefill call laplace_cuda_gemm_dev per matrix", M);
+    const uint8_t* ws[8]; float* ys[8]; int ns[8];
+    for (int i = 0; i < n_mats; ++i) { ws[i] = mats[i].w; ys[i] = mats[i].y; ns[i] = mats[i].N; }
+    GemvArgs a{};
+    a.x = x; a.type = type; a.M = M; a.K = K; a.n_seg = 1;
+    a.n_mats = n_mats; a.mat_w = ws; a.mat_y = ys; a.mat_n = ns;
+    a.norm_w = norm_weight; a.norm_eps = norm_eps; a.x_norm_out = x_norm_out;
+    return launch_gemv_stream(a, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
 int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx,
                               int n_experts, float* y, int K, int N, int per_expert_x, void* stream) {
     int rc = require_ready();

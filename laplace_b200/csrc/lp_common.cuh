@@ -68,6 +68,15 @@ struct GemvArgs {
     int            n_seg;        // 1, or the number of selected experts
     int            per_seg_x;    // 0: all segments read rows [0,M); 1: segment s reads row s (M == 1)
     const struct PeerOut* peers; // nullptr, or: results go to every GPU's buffer instead of y (fused all-gather)
+    // several matrices of the same type and K that share x (w, y, N above are then unused)
+    int            n_mats;
+    const uint8_t* const* mat_w;
+    float* const*  mat_y;
+    const int*     mat_n;
+    // optional RMSNorm of x in front of the quantizer: x_norm = x * inv_rms * norm_w
+    const float*   norm_w;
+    float          norm_eps;
+    float*         x_norm_out;
 };
 // Fused all-gather of a row-split matmul: every GPU stores its slice of the result straight into
 // every GPU's full-width buffer through peer-mapped pointers, then raises a per-source step flag.

@@ -37,6 +37,7 @@ namespace lp {
 namespace {
 
 constexpr int MAX_SLOTS = 4;
+constexpr int MAX_MATS = 8;
 constexpr int PRODUCER_WARPS = 4;   // a lane issues a bulk copy in ~100 cycles; four warps issue in parallel
 constexpr int REC_BYTES = 176;   // activation record per 128 values: 128 int8, d[4], sum[4], 16 pad
                                  // (44 words: consecutive lanes fall in distinct bank groups)
@@ -62,6 +63,16 @@ struct KParams {
     uint32_t       isum_row_stride; // bytes between rows of the int16 half-sums (Q6_K only, else 0)
     uint32_t       off_isum, off_ring;
     int            rows_q, rows_r;  // CTA b owns rows_q (+1 if b < rows_r) rows
+    // several matrices that share x (same type and K): global row g belongs to matrix i with mat_end[i-1] <= g < mat_end[i]
+    int            n_mats;          // 0: one matrix (w, y, N)
+    const uint8_t* mat_w[MAX_MATS];
+    float*         mat_y[MAX_MATS];
+    int            mat_end[MAX_MATS];
+    int            mat_n[MAX_MATS];
+    // optional RMSNorm of x in front of the quantizer (Laplace src/ops.cpp:34-74): x_norm = x * inv * norm_w
+    const float*   norm_w;
+    float          norm_eps;
+    float*         x_norm_out;      // optional: the normalised rows, written by CTA 0
     PeerOut        peers;           // peers.world == 0: results go to y
     uint32_t       off_stage;       // fused all-gather: this CTA's results are staged here, [M][stage_ld] floats
     int            stage_ld;
@@ -71,8 +82,9 @@ struct KParams {
 // one warp writes the CTA's contiguous column range to every GPU in 128-byte coalesced stores.
 // `row` counts result rows, `col` the column inside this GPU's slice, `cta_col0` the CTA's first column.
 template <bool PEERS>
-__device__ __forceinline__ void store_result(const KParams& p, uint8_t* smem, int cta_col0, size_t row, int col, float v) {
-    if (!PEERS || p.peers.world == 0) p.y[row * p.N + col] = v;
+__device__ __forceinline__ void store_result(const KParams& p, uint8_t* smem, int cta_col0, size_t row, int col, float v, int mat = 0) {
+    if (p.n_mats) p.mat_y[mat][row * p.mat_n[mat] + col] = v;
+    else if (!PEERS || p.peers.world == 0) p.y[row * p.N + col] = v;
     else reinterpret_cast<float*>(smem + p.off_stage)[row * p.stage_ld + (col - cta_col0)] = v;
 }
 
@@ -317,35 +329,42 @@ template <> struct Traits<LAPLACE_TYPE_Q6_K> {
 // rows of one segment, or one K-slice of one row. Producer lane w and consumer
 // warp w walk the same sequence of units over w's contiguous range of rows.
 struct Unit {
-    long long src_off;   // byte offset from p.w of the first byte to copy
+    const uint8_t* src;  // first byte to copy
     uint32_t  len;       // bytes the unit needs
-    int       seg, j, nrows, slice;
+    int       seg, j, nrows, slice, mat;
 };
 struct Walker {
     int g, g_end, slice;
     __device__ bool next(const KParams& p, Unit& u) {
         if (g >= g_end) return false;
-        int seg = 0, j = g;
+        int seg = 0, j = g, mat = 0, n_here = p.N;
         long long rowidx = g;
+        const uint8_t* base = p.w;
         if (p.expert_idx) {
             seg = g / p.N;
             j = g - seg * p.N;
             rowidx = static_cast<long long>(p.expert_idx[seg]) * p.N + j;
+        } else if (p.n_mats) {
+            while (g >= p.mat_end[mat]) ++mat;
+            j = g - (mat ? p.mat_end[mat - 1] : 0);
+            rowidx = j;
+            base = p.mat_w[mat];
+            n_here = p.mat_n[mat];
         }
-        u.seg = seg; u.j = j; u.slice = slice;
+        u.seg = seg; u.j = j; u.slice = slice; u.mat = mat;
         if (p.n_slices > 1) {
             const uint32_t off = static_cast<uint32_t>(slice) * p.slice_bytes;
             u.nrows = 1;
             u.len = (p.rb - off) < p.slice_bytes ? (p.rb - off) : p.slice_bytes;
-            u.src_off = rowidx * p.rb + off;
+            u.src = base + rowidx * p.rb + off;
             if (++slice == p.n_slices) { slice = 0; ++g; }
         } else {
             int n = p.rows_per_unit;
             if (n > g_end - g) n = g_end - g;
-            if (n > p.N - j) n = p.N - j;              // a copy never crosses into another expert
+            if (n > n_here - j) n = n_here - j;        // a copy never crosses into another expert or matrix
             u.nrows = n;
             u.len = static_cast<uint32_t>(n) * p.rb;
-            u.src_off = rowidx * p.rb;
+            u.src = base + rowidx * p.rb;
             g += n;
         }
         return true;
@@ -426,7 +445,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
             if (have) {
                 const int slot = ui % p.n_slots, round = ui / p.n_slots;
                 if (round == 0 || mbar_try_wait(bar_empty(w, slot), (round - 1) & 1)) {
-                    const uint8_t* src = p.w + un.src_off;
+                    const uint8_t* src = un.src;
                     const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src) & 15u);
                     const uint32_t bytes = (mis + un.len + 15u) & ~15u;
                     mbar_expect_tx(bar_full(w, slot), bytes);
@@ -483,14 +502,55 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         constexpr int GROUPS = WARPS * 4;
         const int grp = threadIdx.x >> 3, t8 = threadIdx.x & 7;
         const int nblk = p.act_rows * bpr;
-        auto load_x = [&](int b) -> float4 {
-            if (b >= nblk) return make_float4(0.f, 0.f, 0.f, 0.f);
-            const int m = b / bpr, kb = b - m * bpr;
-            return __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8);
-        };
         // Tell the producers first: they need ~100 cycles from here to their
         // first copy, the loads below are issued within a few.
         asm volatile("bar.arrive 2, %0;" :: "r"((WARPS + PW) * 32) : "memory");
+        // Optional RMSNorm in front of the quantizer (Laplace src/ops.cpp:34-74: inv = 1 / sqrt(mean(x^2) + eps),
+        // x_norm = x * inv * w, the two multiplies in that order). Every CTA needs every row, so every CTA computes
+        // the row sums itself: per-thread partial sums, shuffles, one table of per-warp sums in the (not yet used)
+        // activation area, added in warp order.
+        float inv_row[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) inv_row[m] = 1.0f;
+        if (p.norm_w) {
+            float* red = reinterpret_cast<float*>(smem + OFF_ACT);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float part = 0.f;
+                if (m < p.act_rows)
+                    for (int i = threadIdx.x; i < p.K / 4; i += WARPS * 32) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K) + i);
+                        part = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, part))));
+                    }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                if (lane == 0) red[warp * M + m] = part;
+            }
+            named_bar_sync(3, WARPS * 32);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float ms = 0.f;
+                for (int w = 0; w < WARPS; ++w) ms += red[w * M + m];
+                inv_row[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ms, static_cast<float>(p.K)), p.norm_eps)));
+            }
+            named_bar_sync(3, WARPS * 32);            // the table has been read: the area may take the quantized rows
+        }
+        auto load_x = [&](int b) -> float4 {
+            if (b >= nblk) return make_float4(0.f, 0.f, 0.f, 0.f);
+            const int m = b / bpr, kb = b - m * bpr;
+            float4 v = __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8);
+            if (p.norm_w) {
+                float inv = inv_row[0];
+#pragma unroll
+                for (int mm = 1; mm < M; ++mm) inv = m == mm ? inv_row[mm] : inv;
+                const float4 w = __ldg(reinterpret_cast<const float4*>(p.norm_w + kb * 32) + t8);
+                v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x); v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
+                v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z); v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
+                if (p.x_norm_out && blockIdx.x == 0)
+                    reinterpret_cast<float4*>(p.x_norm_out + static_cast<size_t>(m) * p.K + kb * 32)[t8] = v;
+            }
+            return v;
+        };
         float4 nxt = load_x(grp), nxt2 = load_x(grp + GROUPS);                   // two rounds ahead
         // whole warps iterate together so the 8-lane shuffles stay converged
         for (int base = 0; base < nblk; base += GROUPS) {
@@ -574,11 +634,11 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                     b.y += __shfl_xor_sync(0xffffffffu, b.y, o);
                 }
                 if (lane == 0) {
-                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x);
-                    store_result<PEERS>(p, smem, g0, m0, un.j + r + 1, b.x);
+                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x, un.mat);
+                    store_result<PEERS>(p, smem, g0, m0, un.j + r + 1, b.x, un.mat);
                     if (m1 != m0) {
-                        store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y);
-                        store_result<PEERS>(p, smem, g0, m1, un.j + r + 1, b.y);
+                        store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y, un.mat);
+                        store_result<PEERS>(p, smem, g0, m1, un.j + r + 1, b.y, un.mat);
                     }
                 }
             }
@@ -595,8 +655,8 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                     a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
                 }
                 if (lane == 0) {
-                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x);
-                    if (m1 != m0) store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y);
+                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x, un.mat);
+                    if (m1 != m0) store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y, un.mat);
                 }
             }
             __syncwarp();
@@ -626,7 +686,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                     a0 += __shfl_xor_sync(0xffffffffu, a0, o);
                     a1 += __shfl_xor_sync(0xffffffffu, a1, o);
                 }
-                if (lane == 0) { store_result<PEERS>(p, smem, g0, 0, un.j + r, a0); store_result<PEERS>(p, smem, g0, 0, un.j + r + 1, a1); }
+                if (lane == 0) { store_result<PEERS>(p, smem, g0, 0, un.j + r, a0, un.mat); store_result<PEERS>(p, smem, g0, 0, un.j + r + 1, a1, un.mat); }
             }
             if (r < un.nrows) {
                 float a0 = 0.f;
@@ -637,7 +697,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-                if (lane == 0) store_result<PEERS>(p, smem, g0, 0, un.j + r, a0);
+                if (lane == 0) store_result<PEERS>(p, smem, g0, 0, un.j + r, a0, un.mat);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(grp, slot));                  // slot may be refilled
@@ -650,7 +710,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
             peer_poll();
-            const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.w + un.src_off) & 15u);
+            const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(un.src) & 15u);
             const int arow = p.per_seg_x ? un.seg : 0;
             const uint32_t act = act0 + arow * p.act_row_stride, isum = isum0 + arow * p.isum_row_stride;
             const int i0 = un.slice * p.slice_items;
@@ -666,7 +726,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                         float a = acc[m];
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                        if (lane == 0) store_result<PEERS>(p, smem, g0, static_cast<size_t>(un.seg) * M + m, un.j + r, a);
+                        if (lane == 0) store_result<PEERS>(p, smem, g0, static_cast<size_t>(un.seg) * M + m, un.j + r, a, un.mat);
                         acc[m] = 0.f;
                     }
                 }
@@ -801,16 +861,30 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     const int epb = block_elems(a.type);
     if (!epb) return LAPLACE_UNSUPPORTED;
     if (a.K <= 0 || a.K % epb) return fail(LAPLACE_ERR_ARG, "gemv: K=%d is not a multiple of %d", a.K, epb);
-    if (a.N <= 0 || a.n_seg <= 0) return fail(LAPLACE_ERR_ARG, "gemv: N=%d n_seg=%d", a.N, a.n_seg);
-    if (reinterpret_cast<uintptr_t>(a.w) & 1) return fail(LAPLACE_ERR_ARG, "gemv: weight pointer not 2-byte aligned");
+    if (a.n_mats < 0 || a.n_mats > MAX_MATS) return fail(LAPLACE_ERR_ARG, "gemv: %d matrices (at most %d share one launch)", a.n_mats, MAX_MATS);
+    if (a.n_mats && (a.expert_idx || a.peers || a.n_seg != 1)) return fail(LAPLACE_ERR_ARG, "gemv: several matrices take neither expert indices nor the fused all-gather");
+    if (!a.n_mats && (a.N <= 0 || a.n_seg <= 0)) return fail(LAPLACE_ERR_ARG, "gemv: N=%d n_seg=%d", a.N, a.n_seg);
     if (reinterpret_cast<uintptr_t>(a.x) & 15) return fail(LAPLACE_ERR_ARG, "gemv: x not 16-byte aligned");
-    if (a.type == LAPLACE_TYPE_Q4_K && (reinterpret_cast<uintptr_t>(a.w) & 15))
+    if (a.norm_w && ((reinterpret_cast<uintptr_t>(a.norm_w) & 15) || (a.x_norm_out && (reinterpret_cast<uintptr_t>(a.x_norm_out) & 15)) || a.per_seg_x))
+        return fail(LAPLACE_ERR_ARG, "gemv: the norm weights (and the optional output) must be 16-byte aligned, one shared x");
+    uintptr_t w_bits = reinterpret_cast<uintptr_t>(a.w);
+    long long total_rows_in = static_cast<long long>(a.n_seg) * a.N;
+    if (a.n_mats) {
+        w_bits = 0;
+        total_rows_in = 0;
+        for (int i = 0; i < a.n_mats; ++i) {
+            if (!a.mat_w[i] || !a.mat_y[i] || a.mat_n[i] <= 0) return fail(LAPLACE_ERR_ARG, "gemv: matrix %d: null pointer or no rows", i);
+            w_bits |= reinterpret_cast<uintptr_t>(a.mat_w[i]);
+            total_rows_in += a.mat_n[i];
+        }
+    }
+    if (w_bits & 1) return fail(LAPLACE_ERR_ARG, "gemv: weight pointer not 2-byte aligned");
+    if (a.type == LAPLACE_TYPE_Q4_K && (w_bits & 15))
         return fail(LAPLACE_ERR_ARG, "gemv: Q4_K weights must be 16-byte aligned on the device");
 
     // Register-resident activations (see the kernel): Q4_K, one activation row,
     // a plain matrix whose 16-byte-aligned rows hold at most 32 items.
-    const bool resident = a.type == LAPLACE_TYPE_Q4_K && !a.expert_idx && a.K <= 4096 &&
-                          (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
+    const bool resident = a.type == LAPLACE_TYPE_Q4_K && !a.expert_idx && a.K <= 4096 && (w_bits & 15) == 0;
     // consumer warps, and how many of them share one ring (resident path with M > 1: ceil(M / 2))
     // one activation row, rows of 8 KB and more (K = 14336): fewer consumer warps, so that a warp's ring slot
     // holds a K-slice of a few KB (small bulk copies are issue-bound)
@@ -824,6 +898,13 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
         p.peers = *a.peers;
     }
     p.K = a.K; p.N = a.N; p.n_seg = a.n_seg; p.per_seg_x = a.per_seg_x;
+    p.n_mats = a.n_mats;
+    for (int i = 0, end = 0; i < a.n_mats; ++i) {
+        end += a.mat_n[i];
+        p.mat_w[i] = a.mat_w[i]; p.mat_y[i] = a.mat_y[i]; p.mat_n[i] = a.mat_n[i]; p.mat_end[i] = end;
+    }
+    if (a.n_mats) p.N = static_cast<int>(total_rows_in);      // for the planning below: rows of all matrices
+    p.norm_w = a.norm_w; p.norm_eps = a.norm_eps; p.x_norm_out = a.x_norm_out;
     p.act_rows = a.per_seg_x ? a.n_seg : a.M;
     p.rb = static_cast<uint32_t>(row_bytes(a.type, a.K));
     p.act_row_stride = static_cast<uint32_t>((a.K + 127) / 128) * REC_BYTES;
@@ -855,7 +936,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     if (p.off_ring + static_cast<size_t>(warps) * 2 * 256 > budget)
         return fail(LAPLACE_ERR_LIMIT, "gemv: M=%d K=%d: the quantized activations do not fit shared memory", a.M, a.K);
     const size_t per_warp = ((budget - p.off_ring) / warps) & ~size_t(15);
-    const bool aligned_rows = (p.rb % 16 == 0) && ((reinterpret_cast<uintptr_t>(a.w) & 15) == 0) &&
+    const bool aligned_rows = (p.rb % 16 == 0) && ((w_bits & 15) == 0) &&
                               (a.type == LAPLACE_TYPE_Q4_K);          // the others read 4 bytes ahead
     const uint32_t slack = aligned_rows ? 0u : 32u;
     const uint32_t unit_bytes = bpb * unit_blocks;
@@ -894,7 +975,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     if (resident && (p.n_slices != 1 || slack != 0))
         return fail(LAPLACE_ERR_STATE, "gemv: internal planning error (resident path needs whole aligned rows)");
 
-    const long long total_rows = static_cast<long long>(a.n_seg) * a.N;
+    const long long total_rows = total_rows_in;
     if (total_rows >= (1LL << 31)) return fail(LAPLACE_ERR_LIMIT, "gemv: more than 2^31 weight rows");
     const long long want = (total_rows + warps * p.rows_per_unit - 1) / (warps * p.rows_per_unit);
     int grid = c.sm_count;

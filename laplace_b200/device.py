@@ -58,6 +58,20 @@ def gemm(x: torch.Tensor, w: torch.Tensor, t: int, M: int, K: int, N: int, y: to
     return y
 
 
+def gemm_multi(x: torch.Tensor, ws, t: int, M: int, K: int, Ns, norm_weight: torch.Tensor | None = None, eps: float = 0.0,
+               want_x_norm: bool = False):
+    """Several matrices of one type against the same (optionally RMS-normalised) activation rows in one launch
+    (laplace_cuda_gemm_multi_dev). Returns the list of outputs, and the normalised rows when asked for."""
+    L = lib()
+    assert x.dtype == torch.float32 and x.is_cuda and x.is_contiguous() and len(ws) == len(Ns)
+    ys = [torch.empty((M, n), dtype=torch.float32, device=x.device) for n in Ns]
+    mats = (_lib.Matrix * len(ws))(*[_lib.Matrix(w.data_ptr(), y.data_ptr(), int(n)) for w, y, n in zip(ws, ys, Ns)])
+    xn = torch.empty((M, K), dtype=torch.float32, device=x.device) if want_x_norm else None
+    _check(L, L.laplace_cuda_gemm_multi_dev(x.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
+                                            xn.data_ptr() if xn is not None else None, mats, len(ws), int(t), M, K, _stream()))
+    return (ys, xn) if want_x_norm else ys
+
+
 def moe_gemv(x: torch.Tensor, w: torch.Tensor, t: int, expert_idx: torch.Tensor, K: int, N: int,
              per_expert_x: bool, y: torch.Tensor | None = None) -> torch.Tensor:
     L = lib()

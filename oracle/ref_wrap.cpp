@@ -9,6 +9,7 @@
 
 #include "fp16.h"
 #include "matmul.h"
+#include "ops.h"
 #include "tensor.h"
 #include "threadpool.h"
 
@@ -27,6 +28,11 @@ static Tensor view(const uint8_t* w, uint32_t type, int K, int N, int n_experts)
 }
 
 extern "C" {
+
+// src/ops.cpp:34-74, 128-176 (scalar branches on an x86 host)
+void ref_rmsnorm_rows(const float* x, const float* w, float* y, int rows, int cols, float eps) { ops::rmsnorm_rows(x, w, y, rows, cols, eps); }
+void ref_swiglu(const float* gate, const float* up, float* out, int n) { ops::swiglu(gate, up, out, n); }
+void ref_geglu(const float* gate, const float* up, float* out, int n) { ops::geglu(gate, up, out, n); }
 
 void ref_set_threads(int t) { ThreadPool::get().set_threads(t); }
 int  ref_threads() { return ThreadPool::get().threads(); }

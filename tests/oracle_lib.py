@@ -121,6 +121,22 @@ class Oracle:
         return x, w
 
 
+def rmsnorm_rows_np(x, w, eps):
+    """Restatement of the reference's scalar rmsnorm (src/ops.cpp:69-73): ms summed in index order in fp32,
+    inv = 1 / sqrt(ms / n + eps), y = x * inv * w (two fp32 multiplies in that order)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    y = np.zeros_like(x)
+    n = x.shape[1]
+    for r in range(x.shape[0]):
+        ms = np.float32(0.0)
+        for v in x[r]:
+            ms = np.float32(ms + np.float32(v * v))
+        inv = np.float32(1.0) / np.sqrt(np.float32(ms / np.float32(n)) + np.float32(eps), dtype=np.float32)
+        y[r] = (x[r] * inv).astype(np.float32) * w
+    return y
+
+
 class Reference:
     """The reference's own scalar matmul, when oracle/_ref was built (needs the reference checkout)."""
 
@@ -142,6 +158,16 @@ class Reference:
         L.ref_fp16_to_fp32.argtypes = [C.c_uint16]
         L.ref_fp32_to_fp16.restype = C.c_uint16
         L.ref_fp32_to_fp16.argtypes = [C.c_float]
+        if hasattr(L, "ref_rmsnorm_rows"):
+            L.ref_rmsnorm_rows.argtypes = [_vp, _vp, _vp, _i, _i, C.c_float]
+
+    def rmsnorm_rows(self, x, w, eps) -> np.ndarray:
+        """ops::rmsnorm_rows of the reference build (src/ops.cpp:34-80)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        y = np.zeros_like(x)
+        self.lib.ref_rmsnorm_rows(_ptr(x), _ptr(w), _ptr(y), x.shape[0], x.shape[1], float(eps))
+        return y
 
     def set_threads(self, t: int) -> int:
         self.lib.ref_set_threads(t)
