@@ -105,11 +105,7 @@ int require_ready() {
 // mapped pinned host memory, so reading it costs no copy.
 int check_device_status(cudaStream_t st, EntryProf* prof = nullptr) {
     const auto t0 = std::chrono::steady_clock::now();
-    // Decode calls finish within microseconds: poll first (a blocking synchronize costs more than the kernel),
-    // then fall back to the blocking wait.
-    cudaError_t e = cudaErrorNotReady;
-    for (int spin = 0; spin < 20000 && e == cudaErrorNotReady; ++spin) e = cudaStreamQuery(st);
-    if (e == cudaErrorNotReady) e = cudaStreamSynchronize(st);
+    cudaError_t e = cudaStreamSynchronize(st);
     if (prof && g_prof.on) prof->device_wait += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     if (e != cudaSuccess) return cuda_check(e, "stream synchronize");
     const int h = *static_cast<volatile int*>(g_ctx.h_err);

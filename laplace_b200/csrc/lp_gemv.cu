@@ -81,9 +81,10 @@ struct KParams {
 // Result store: to y, or (fused all-gather) into this CTA's staging area in shared memory, from where
 // one warp writes the CTA's contiguous column range to every GPU in 128-byte coalesced stores.
 // `row` counts result rows, `col` the column inside this GPU's slice, `cta_col0` the CTA's first column.
-template <bool PEERS>
+// EXT: the instantiation that serves several matrices and the RMSNorm prologue; the plain one carries none of that code.
+template <bool PEERS, bool EXT>
 __device__ __forceinline__ void store_result(const KParams& p, uint8_t* smem, int cta_col0, size_t row, int col, float v, int mat = 0) {
-    if (p.n_mats) p.mat_y[mat][row * p.mat_n[mat] + col] = v;
+    if (EXT && p.n_mats) p.mat_y[mat][row * p.mat_n[mat] + col] = v;
     else if (!PEERS || p.peers.world == 0) p.y[row * p.N + col] = v;
     else reinterpret_cast<float*>(smem + p.off_stage)[row * p.stage_ld + (col - cta_col0)] = v;
 }
@@ -335,6 +336,7 @@ struct Unit {
 };
 struct Walker {
     int g, g_end, slice;
+    template <bool EXT>
     __device__ bool next(const KParams& p, Unit& u) {
         if (g >= g_end) return false;
         int seg = 0, j = g, mat = 0, n_here = p.N;
@@ -344,7 +346,7 @@ struct Walker {
             seg = g / p.N;
             j = g - seg * p.N;
             rowidx = static_cast<long long>(p.expert_idx[seg]) * p.N + j;
-        } else if (p.n_mats) {
+        } else if (EXT && p.n_mats) {
             while (g >= p.mat_end[mat]) ++mat;
             j = g - (mat ? p.mat_end[mat - 1] : 0);
             rowidx = j;
@@ -386,7 +388,7 @@ struct Walker {
 // shares one ring: every warp of the group meets every weight row of the group
 // with its own two rows of x, so shared memory serves each weight row G times
 // instead of each activation row once per weight row.
-template <uint32_t TYPE, int M, int WARPS, bool RESIDENT, int PW = PRODUCER_WARPS, bool PEERS = true>
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT, int PW = PRODUCER_WARPS, bool PEERS = true, bool EXT = false>
 __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const KParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -431,7 +433,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         Walker wk = walker_of(serving ? w : 0);
         if (!serving) wk.g_end = wk.g;
         Unit un;
-        bool have = wk.next(p, un);
+        bool have = wk.template next<EXT>(p, un);
         int ui = 0;
         uint32_t idle = 0;
         bool gave_up = false;
@@ -452,7 +454,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                     bulk_g2s(ring + slot * p.slot_bytes, src - mis, bytes, bar_full(w, slot));
                     ++ui;
                     issued = true;
-                    have = wk.next(p, un);
+                    have = wk.template next<EXT>(p, un);
                 }
             }
             if (__any_sync(0xffffffffu, issued)) {
@@ -505,26 +507,45 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         // Tell the producers first: they need ~100 cycles from here to their
         // first copy, the loads below are issued within a few.
         asm volatile("bar.arrive 2, %0;" :: "r"((WARPS + PW) * 32) : "memory");
+        auto load_raw = [&](int b) -> float4 {
+            if (b >= nblk) return make_float4(0.f, 0.f, 0.f, 0.f);
+            const int m = b / bpr, kb = b - m * bpr;
+            return __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8);
+        };
+        auto load_w = [&](int b) -> float4 {                 // the norm weights of block b, fetched as early as x
+            if (!(EXT && p.norm_w) || b >= nblk) return make_float4(0.f, 0.f, 0.f, 0.f);
+            return __ldg(reinterpret_cast<const float4*>(p.norm_w + (b % bpr) * 32) + t8);
+        };
+        float4 nxt = load_raw(grp), nxt2 = load_raw(grp + GROUPS);                   // two rounds ahead
+        float4 wnxt = load_w(grp), wnxt2 = load_w(grp + GROUPS);
         // Optional RMSNorm in front of the quantizer (Laplace src/ops.cpp:34-74: inv = 1 / sqrt(mean(x^2) + eps),
         // x_norm = x * inv * w, the two multiplies in that order). Every CTA needs every row, so every CTA computes
-        // the row sums itself: per-thread partial sums, shuffles, one table of per-warp sums in the (not yet used)
-        // activation area, added in warp order.
+        // the row sums itself, from the very values its threads are about to quantize (each 32-value block belongs
+        // to one 8-lane group, so every element is counted once): per-thread partial sums, shuffles, one table of
+        // per-warp sums in the (not yet used) activation area, added in warp order.
         float inv_row[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) inv_row[m] = 1.0f;
-        if (p.norm_w) {
+        if (EXT && p.norm_w) {
+            float part[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) part[m] = 0.f;
+            auto add_sq = [&](const float4& v, int b) {
+                const float sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+                const int mrow = b < nblk ? b / bpr : 0;
+#pragma unroll
+                for (int m = 0; m < M; ++m) part[m] += m == mrow ? sq : 0.f;          // values past the end are zeros
+            };
+            add_sq(nxt, grp);
+            add_sq(nxt2, grp + GROUPS);
+            for (int b = grp + 2 * GROUPS; b < nblk; b += GROUPS) add_sq(load_raw(b), b);      // read again by the loop below
             float* red = reinterpret_cast<float*>(smem + OFF_ACT);
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                float part = 0.f;
-                if (m < p.act_rows)
-                    for (int i = threadIdx.x; i < p.K / 4; i += WARPS * 32) {
-                        const float4 v = __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K) + i);
-                        part = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, part))));
-                    }
+                float s = part[m];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-                if (lane == 0) red[warp * M + m] = part;
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (lane == 0) red[warp * M + m] = s;
             }
             named_bar_sync(3, WARPS * 32);
 #pragma unroll
@@ -535,15 +556,13 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
             }
             named_bar_sync(3, WARPS * 32);            // the table has been read: the area may take the quantized rows
         }
-        auto load_x = [&](int b) -> float4 {
-            if (b >= nblk) return make_float4(0.f, 0.f, 0.f, 0.f);
-            const int m = b / bpr, kb = b - m * bpr;
-            float4 v = __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8);
-            if (p.norm_w) {
+        // x as the quantizer sees it
+        auto finish_x = [&](float4 v, const float4& w, int b) -> float4 {
+            if (EXT && p.norm_w && b < nblk) {
+                const int m = b / bpr, kb = b - m * bpr;
                 float inv = inv_row[0];
 #pragma unroll
                 for (int mm = 1; mm < M; ++mm) inv = m == mm ? inv_row[mm] : inv;
-                const float4 w = __ldg(reinterpret_cast<const float4*>(p.norm_w + kb * 32) + t8);
                 v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x); v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
                 v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z); v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
                 if (p.x_norm_out && blockIdx.x == 0)
@@ -551,15 +570,15 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
             }
             return v;
         };
-        float4 nxt = load_x(grp), nxt2 = load_x(grp + GROUPS);                   // two rounds ahead
         // whole warps iterate together so the 8-lane shuffles stay converged
         for (int base = 0; base < nblk; base += GROUPS) {
             const int b = base + grp;
             const bool live = b < nblk;
             const int m = live ? b / bpr : 0, kb = live ? b - m * bpr : 0;
-            const float4 v = nxt;
+            const float4 v = finish_x(nxt, wnxt, b);
             nxt = nxt2;
-            nxt2 = load_x(b + 2 * GROUPS);
+            nxt2 = load_raw(b + 2 * GROUPS);
+            if (EXT) { wnxt = wnxt2; wnxt2 = load_w(b + 2 * GROUPS); }
             uint32_t packed; int hs;
             const float d = quantize_block_8lanes(v, packed, hs);
             const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
@@ -611,7 +630,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
             q4k_load_act(act0 + m0 * p.act_row_stride + lane * REC_BYTES, x0);
             q4k_load_act(act0 + m1 * p.act_row_stride + lane * REC_BYTES, x1);
         }
-        for (; wk.next(p, un); ++u) {
+        for (; wk.template next<EXT>(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
             peer_poll();
@@ -634,11 +653,11 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                     b.y += __shfl_xor_sync(0xffffffffu, b.y, o);
                 }
                 if (lane == 0) {
-                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x, un.mat);
-                    store_result<PEERS>(p, smem, g0, m0, un.j + r + 1, b.x, un.mat);
+                    store_result<PEERS, EXT>(p, smem, g0, m0, un.j + r, a.x, un.mat);
+                    store_result<PEERS, EXT>(p, smem, g0, m0, un.j + r + 1, b.x, un.mat);
                     if (m1 != m0) {
-                        store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y, un.mat);
-                        store_result<PEERS>(p, smem, g0, m1, un.j + r + 1, b.y, un.mat);
+                        store_result<PEERS, EXT>(p, smem, g0, m1, un.j + r, a.y, un.mat);
+                        store_result<PEERS, EXT>(p, smem, g0, m1, un.j + r + 1, b.y, un.mat);
                     }
                 }
             }
@@ -655,8 +674,8 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                     a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
                 }
                 if (lane == 0) {
-                    store_result<PEERS>(p, smem, g0, m0, un.j + r, a.x, un.mat);
-                    if (m1 != m0) store_result<PEERS>(p, smem, g0, m1, un.j + r, a.y, un.mat);
+                    store_result<PEERS, EXT>(p, smem, g0, m0, un.j + r, a.x, un.mat);
+                    if (m1 != m0) store_result<PEERS, EXT>(p, smem, g0, m1, un.j + r, a.y, un.mat);
                 }
             }
             __syncwarp();
@@ -666,7 +685,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         Q4KAct xr;
         const bool has_item = lane < n_items;
         if (has_item) q4k_load_act(act0 + lane * REC_BYTES, xr);
-        for (; wk.next(p, un); ++u) {
+        for (; wk.template next<EXT>(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
             peer_poll();
@@ -686,7 +705,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                     a0 += __shfl_xor_sync(0xffffffffu, a0, o);
                     a1 += __shfl_xor_sync(0xffffffffu, a1, o);
                 }
-                if (lane == 0) { store_result<PEERS>(p, smem, g0, 0, un.j + r, a0, un.mat); store_result<PEERS>(p, smem, g0, 0, un.j + r + 1, a1, un.mat); }
+                if (lane == 0) { store_result<PEERS, EXT>(p, smem, g0, 0, un.j + r, a0, un.mat); store_result<PEERS, EXT>(p, smem, g0, 0, un.j + r + 1, a1, un.mat); }
             }
             if (r < un.nrows) {
                 float a0 = 0.f;
@@ -697,7 +716,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-                if (lane == 0) store_result<PEERS>(p, smem, g0, 0, un.j + r, a0, un.mat);
+                if (lane == 0) store_result<PEERS, EXT>(p, smem, g0, 0, un.j + r, a0, un.mat);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(grp, slot));                  // slot may be refilled
@@ -706,7 +725,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         float acc[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m] = 0.f;
-        for (; wk.next(p, un); ++u) {
+        for (; wk.template next<EXT>(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
             peer_poll();
@@ -726,7 +745,7 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
                         float a = acc[m];
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                        if (lane == 0) store_result<PEERS>(p, smem, g0, static_cast<size_t>(un.seg) * M + m, un.j + r, a, un.mat);
+                        if (lane == 0) store_result<PEERS, EXT>(p, smem, g0, static_cast<size_t>(un.seg) * M + m, un.j + r, a, un.mat);
                         acc[m] = 0.f;
                     }
                 }
@@ -796,12 +815,12 @@ __global__ void allgather_wait_kernel(PeerOut po, int* err) {
     report_status(err, DEV_TIMEOUT_PEER);
 }
 
-template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false, int PW = PRODUCER_WARPS, bool PEERS = true>
+template <uint32_t TYPE, int M, int WARPS, bool RESIDENT = false, int PW = PRODUCER_WARPS, bool PEERS = true, bool EXT = false>
 cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     // The opt-in shared-memory size is raised once per instantiation (not on
     // every launch, so launches stay legal inside a stream capture).
     static bool configured = false;
-    auto k = gemv_stream_kernel<TYPE, M, WARPS, RESIDENT, PW, PEERS>;
+    auto k = gemv_stream_kernel<TYPE, M, WARPS, RESIDENT, PW, PEERS, EXT>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(ctx().smem_optin));
@@ -828,26 +847,28 @@ cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st
 constexpr int RESIDENT_PRODUCER_WARPS = 2;  // 448 threads per CTA leave 146 registers per thread: two weight rows in flight
 constexpr int RESIDENT_WARPS = 12;      // consumer warps of the register-resident path with M > 1: splits into groups of 1, 2, 3 or 4
 
-template <uint32_t TYPE>
+template <uint32_t TYPE, bool EXT>
 cudaError_t launch_typed(int M, bool resident, bool long_rows, const KParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+    // EXT (several matrices / RMSNorm prologue) never meets the fused all-gather, so it is built without that code
+    constexpr bool PE = !EXT;
     switch (M) {
         case 1:
             if constexpr (TYPE == LAPLACE_TYPE_Q4_K) {
                 // the common case (results to y) gets a kernel without the fused all-gather's code
-                if (resident) return p.peers.world ? launch_one<TYPE, 1, 16, true>(p, grid, smem, st)
-                                                   : launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, false>(p, grid, smem, st);
+                if (resident) return (PE && p.peers.world) ? launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st)
+                                                           : launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, false, EXT>(p, grid, smem, st);
             }
-            if (long_rows) return launch_one<TYPE, 1, 16>(p, grid, smem, st);
-            return launch_one<TYPE, 1, 24>(p, grid, smem, st);
+            if (long_rows) return launch_one<TYPE, 1, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+            return launch_one<TYPE, 1, 24, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
 #define LP_RESIDENT_CASE(m) \
-        if constexpr (TYPE == LAPLACE_TYPE_Q4_K) { if (resident) return launch_one<TYPE, m, RESIDENT_WARPS, true, RESIDENT_PRODUCER_WARPS>(p, grid, smem, st); }
-        case 2: LP_RESIDENT_CASE(2) return launch_one<TYPE, 2, 24>(p, grid, smem, st);
-        case 3: LP_RESIDENT_CASE(3) return launch_one<TYPE, 3, 16>(p, grid, smem, st);
-        case 4: LP_RESIDENT_CASE(4) return launch_one<TYPE, 4, 16>(p, grid, smem, st);
-        case 5: LP_RESIDENT_CASE(5) return launch_one<TYPE, 5, 16>(p, grid, smem, st);
-        case 6: LP_RESIDENT_CASE(6) return launch_one<TYPE, 6, 16>(p, grid, smem, st);
-        case 7: LP_RESIDENT_CASE(7) return launch_one<TYPE, 7, 16>(p, grid, smem, st);
-        case 8: LP_RESIDENT_CASE(8) return launch_one<TYPE, 8, 16>(p, grid, smem, st);
+        if constexpr (TYPE == LAPLACE_TYPE_Q4_K) { if (resident) return launch_one<TYPE, m, RESIDENT_WARPS, true, RESIDENT_PRODUCER_WARPS, PE, EXT>(p, grid, smem, st); }
+        case 2: LP_RESIDENT_CASE(2) return launch_one<TYPE, 2, 24, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+        case 3: LP_RESIDENT_CASE(3) return launch_one<TYPE, 3, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+        case 4: LP_RESIDENT_CASE(4) return launch_one<TYPE, 4, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+        case 5: LP_RESIDENT_CASE(5) return launch_one<TYPE, 5, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+        case 6: LP_RESIDENT_CASE(6) return launch_one<TYPE, 6, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+        case 7: LP_RESIDENT_CASE(7) return launch_one<TYPE, 7, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+        case 8: LP_RESIDENT_CASE(8) return launch_one<TYPE, 8, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
 #undef LP_RESIDENT_CASE
         default: return cudaErrorInvalidValue;
     }
@@ -985,13 +1006,18 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     if (a.peers && p.rows_q + 1 > p.stage_ld) return fail(LAPLACE_ERR_STATE, "gemv: internal planning error (staging area too small)");
 
     cudaError_t e;
+    const bool ext = a.n_mats > 0 || a.norm_w != nullptr;
     switch (a.type) {
         case LAPLACE_TYPE_Q4_K:
-            e = launch_typed<LAPLACE_TYPE_Q4_K>(a.M, resident, long_rows, p, dim3(grid), smem, st);
+            e = ext ? launch_typed<LAPLACE_TYPE_Q4_K, true>(a.M, resident, long_rows, p, dim3(grid), smem, st)
+                    : launch_typed<LAPLACE_TYPE_Q4_K, false>(a.M, resident, long_rows, p, dim3(grid), smem, st);
             break;
-        case LAPLACE_TYPE_Q6_K: e = launch_typed<LAPLACE_TYPE_Q6_K>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
-        case LAPLACE_TYPE_Q4_0: e = launch_typed<LAPLACE_TYPE_Q4_0>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
-        case LAPLACE_TYPE_Q8_0: e = launch_typed<LAPLACE_TYPE_Q8_0>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q6_K: e = ext ? launch_typed<LAPLACE_TYPE_Q6_K, true>(a.M, false, long_rows, p, dim3(grid), smem, st)
+                                        : launch_typed<LAPLACE_TYPE_Q6_K, false>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q4_0: e = ext ? launch_typed<LAPLACE_TYPE_Q4_0, true>(a.M, false, long_rows, p, dim3(grid), smem, st)
+                                        : launch_typed<LAPLACE_TYPE_Q4_0, false>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q8_0: e = ext ? launch_typed<LAPLACE_TYPE_Q8_0, true>(a.M, false, long_rows, p, dim3(grid), smem, st)
+                                        : launch_typed<LAPLACE_TYPE_Q8_0, false>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
         default: return LAPLACE_UNSUPPORTED;
     }
     c.launches++;
