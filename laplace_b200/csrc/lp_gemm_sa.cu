@@ -91,28 +91,46 @@ struct SaParams {
     const int*   n_tiles_dev;
     const int*   out_row;
     int          out_identity; // 1: a live operand row r is written to row r of y
-    // split-K (dense tiling with few output tiles): ksplit CTAs share an output tile, each takes sb_per super-blocks
-    // and writes its partial result to y_part[slice][M][N]; a second kernel adds the slices in a fixed order
-    int          ksplit, sb_per;
+    // Balanced split of a dense call: the work is the list of (output tile, super-block) units in tile order, and CTA c
+    // takes units [c * units / grid, (c + 1) * units / grid). A tile whose units fall to more than one CTA is written as
+    // partial results (slot 2c for the piece that continues a tile, 2c + 1 for the piece that begins one; a slot holds
+    // [TT tokens][TW rows] floats) which a second kernel adds up in k order. 0 units: whole tiles, dealt round-robin.
+    long long    sk_units;
     float*       y_part;
 };
 
-struct TileRef { int m0, n0, wrow0, nt, sb0, sb1, ks; };     // nt = tokens of the tile
-__device__ __forceinline__ TileRef tile_ref(const SaParams& p, int tile) {
+struct TileRef { int m0, n0, wrow0, nt, sb0, sb1, part; };     // nt = tokens of the tile; part = slot of a partial result or -1
+// The pieces of work of one CTA, in the order every role of the CTA walks them.
+struct Segments { int n; long long u0, u1; };
+__host__ __device__ __forceinline__ long long sk_start(long long units, int grid, int c) { return units * c / grid; }
+__device__ __forceinline__ Segments segments(const SaParams& p) {
+    if (p.tile_tab || p.sk_units == 0) {
+        const int n_tiles = p.tile_tab ? __ldg(p.n_tiles_dev) : p.tiles_m * p.tiles_n;
+        const int b = static_cast<int>(blockIdx.x), g = static_cast<int>(gridDim.x);
+        return {b < n_tiles ? (n_tiles - b + g - 1) / g : 0, 0, 0};
+    }
+    const int nsb = p.K / 256;
+    const long long u0 = sk_start(p.sk_units, gridDim.x, blockIdx.x), u1 = sk_start(p.sk_units, gridDim.x, blockIdx.x + 1);
+    return {u1 > u0 ? static_cast<int>((u1 - 1) / nsb - u0 / nsb) + 1 : 0, u0, u1};
+}
+__device__ __forceinline__ TileRef seg_ref(const SaParams& p, const Segments& sg, int i) {
     const int nsb = p.K / 256;
     if (p.tile_tab) {
-        const int4 t = __ldg(p.tile_tab + tile);
-        return {t.x, t.y, t.z, t.w, 0, nsb, 0};
+        const int4 t = __ldg(p.tile_tab + blockIdx.x + i * gridDim.x);
+        return {t.x, t.y, t.z, t.w, 0, nsb, -1};
     }
-    const int out_tiles = p.tiles_m * p.tiles_n;
-    const int ks = tile / out_tiles, t = tile - ks * out_tiles;
-    const int sb0 = ks * p.sb_per;
-    const int sb1 = sb0 + p.sb_per < nsb ? sb0 + p.sb_per : nsb;
+    int t, sb0 = 0, sb1 = nsb;
+    if (p.sk_units == 0) {
+        t = blockIdx.x + i * gridDim.x;
+    } else {
+        const int t_first = static_cast<int>(sg.u0 / nsb), t_last = static_cast<int>((sg.u1 - 1) / nsb);
+        t = t_first + i;
+        if (i == 0) sb0 = static_cast<int>(sg.u0 - static_cast<long long>(t_first) * nsb);
+        if (t == t_last) sb1 = static_cast<int>(sg.u1 - 1 - static_cast<long long>(t_last) * nsb) + 1;
+    }
     const int m0 = (t % p.tiles_m) * TT;
-    return {m0, (t / p.tiles_m) * TW, 0, p.M - m0 < TT ? p.M - m0 : TT, sb0, sb1, ks};
-}
-__device__ __forceinline__ int tile_count(const SaParams& p) {
-    return p.tile_tab ? __ldg(p.n_tiles_dev) : p.tiles_m * p.tiles_n * p.ksplit;
+    const int part = (sb0 > 0 || sb1 < nsb) ? 2 * static_cast<int>(blockIdx.x) + (sb0 == 0 ? 1 : 0) : -1;
+    return {m0, (t / p.tiles_m) * TW, 0, p.M - m0 < TT ? p.M - m0 : TT, sb0, sb1, part};
 }
 // Activation boxes come in four heights (16, 32, 64, 128 rows); a tile uses the smallest that holds its tokens.
 // In shared memory and in TMEM the lo piece follows the hi piece at a distance of one box height.
@@ -134,7 +152,7 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(sbase + BAR_FULL_A + 8 * s, 1);
+            mbar_init(sbase + BAR_FULL_A + 8 * s, 2);        // one arrive per activation piece
             mbar_init(sbase + BAR_FULL_W + 8 * s, 4);        // one arrive per converter warp
             mbar_init(sbase + BAR_EMPTY + 8 * s, 1);         // tcgen05.commit
         }
@@ -162,27 +180,29 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
-    const int n_tiles = tile_count(p);
+    const Segments sg = segments(p);
 
     // Counters every role advances in the same order:
     //   it   64-k chunk counter, main-ring stage = it % STAGES
     //   sbc  super-block counter: accumulator = sbc & 1, raw slot = sbc % RAW_STAGES, table / g slot = sbc % TABN
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-        if (warp == 0 && lane == 0) {
-            // ---------------- TMA producer: activation pieces ----------------
+        if ((warp == 0 || warp == 2) && lane == 0) {
+            // ---------------- TMA producers: warp 0 copies the hi piece of the activations, warp 2 the lo piece.
+            // (The copies one thread issues are served one after the other at some 20 bytes per clock; the copies of
+            // two threads run side by side.) ----------------
+            const int pc = warp >> 1;
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const TileRef tr = tile_ref(p, tile);
+            for (int seg = 0; ok && seg < sg.n; ++seg) {
+                const TileRef tr = seg_ref(p, sg, seg);
                 const int bk = box_bucket(tr.nt);
                 const uint32_t piece = static_cast<uint32_t>(16 << bk) * 128u;
                 for (int kc = tr.sb0 * 4; kc < tr.sb1 * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort<false>(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, 2 * piece);
-                    tma_load_2d(sbase + OFF_A + s * A_TILE, &maps.a[bk], kc * BKC, tr.m0, sbase + BAR_FULL_A + 8 * s);
-                    tma_load_2d(sbase + OFF_A + s * A_TILE + piece, &maps.a[bk], kc * BKC, p.m_pad + tr.m0, sbase + BAR_FULL_A + 8 * s);
+                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, piece);
+                    tma_load_2d(sbase + OFF_A + s * A_TILE + pc * piece, &maps.a[bk], kc * BKC, pc * p.m_pad + tr.m0, sbase + BAR_FULL_A + 8 * s);
                 }
             }
             if (!ok) {
@@ -197,8 +217,8 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             // and, per super-block, the tile of activation block sums ----------------
             int sbc = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const TileRef tr = tile_ref(p, tile);
+            for (int seg = 0; ok && seg < sg.n; ++seg) {
+                const TileRef tr = seg_ref(p, sg, seg);
                 const int bk = box_bucket(tr.nt);
                 for (int sb = tr.sb0; sb < tr.sb1; ++sb, ++sbc) {
                     const int q = sbc % RAW_STAGES, slot = sbc % TABN;
@@ -226,8 +246,8 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             // 115 cycles however small it is, so one wide instruction beats two narrow ones.) ----------------
             int it = 0, sbc = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const TileRef tr = tile_ref(p, tile);
+            for (int seg = 0; ok && seg < sg.n; ++seg) {
+                const TileRef tr = seg_ref(p, sg, seg);
                 const uint32_t idesc = idesc_f16_m128((16 << box_bucket(tr.nt)) + ((tr.nt + 15) & ~15));
                 for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
                     const int b = sbc & 1;
@@ -260,8 +280,8 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
         const int r = threadIdx.x - 128;
         int it = 0, sbc = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const TileRef tr = tile_ref(p, tile);
+        for (int seg = 0; ok && seg < sg.n; ++seg) {
+            const TileRef tr = seg_ref(p, sg, seg);
             for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
                 const int q = sbc % RAW_STAGES, slot = sbc % TABN;
                 const uint32_t raw = sbase + OFF_RAW + q * RAW_TILE + r * Q4_K_BYTES;      // this row's 144 bytes
@@ -336,8 +356,8 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
         const int wr = quad * 32 + lane;                 // weight row inside the tile
         int sbc = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const TileRef tr = tile_ref(p, tile);
+        for (int seg = 0; ok && seg < sg.n; ++seg) {
+            const TileRef tr = seg_ref(p, sg, seg);
             const int box = 16 << box_bucket(tr.nt);
             float2 acc[32];
 #pragma unroll
@@ -394,8 +414,16 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             if (!ok) break;
             // y[token][n] = 2^-e_token * acc: for a fixed token the warp's 32 lanes write 32 consecutive floats
             const int n = tr.n0 + wr;
-            float* ybase = p.ksplit > 1 ? p.y_part + static_cast<size_t>(tr.ks) * p.M * p.N : p.y;
-            if (n < p.N) {
+            if (tr.part >= 0) {
+                // a piece of a tile: [token][weight row] into the piece's slot
+                float* part = p.y_part + static_cast<size_t>(tr.part) * (TT * TW);
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const int col = half * 64 + c;
+                    const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                    if (col < tr.nt) part[col * TW + wr] = v * __ldg(p.inv_s + tr.m0 + col);
+                }
+            } else if (n < p.N) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int col = half * 64 + c;
@@ -404,7 +432,7 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         int orow = p.out_row ? __ldg(p.out_row + row) : row;
                         if (p.out_identity && orow >= 0) orow = row;
                         const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-                        if (orow >= 0) ybase[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
+                        if (orow >= 0) p.y[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
                     }
                 }
             }
@@ -497,7 +525,7 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(sbase + BAR_FULL_A + 8 * s, 1);
+            mbar_init(sbase + BAR_FULL_A + 8 * s, 2);
             mbar_init(sbase + BAR_FULL_W + 8 * s, 4);
             mbar_init(sbase + BAR_EMPTY + 8 * s, 1);
         }
@@ -522,24 +550,24 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + OFF_TMEM_PTR);
-    const int n_tiles = tile_count(p);
+    const Segments sg = segments(p);
 
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-        if (warp == 0 && lane == 0) {
-            // ---------------- TMA producer: activation pieces ----------------
+        if ((warp == 0 || warp == 2) && lane == 0) {
+            // ---------------- TMA producers: warp 0 copies the hi piece of the activations, warp 2 the lo piece ----------------
+            const int pc = warp >> 1;
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const TileRef tr = tile_ref(p, tile);
+            for (int seg = 0; ok && seg < sg.n; ++seg) {
+                const TileRef tr = seg_ref(p, sg, seg);
                 const int bk = box_bucket(tr.nt);
                 const uint32_t piece = static_cast<uint32_t>(16 << bk) * 128u;
                 for (int kc = tr.sb0 * 4; kc < tr.sb1 * 4; ++kc, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort<false>(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, 2 * piece);
-                    tma_load_2d(sbase + OFF_A + s * A_TILE, &maps.a[bk], kc * BKC, tr.m0, sbase + BAR_FULL_A + 8 * s);
-                    tma_load_2d(sbase + OFF_A + s * A_TILE + piece, &maps.a[bk], kc * BKC, p.m_pad + tr.m0, sbase + BAR_FULL_A + 8 * s);
+                    mbar_expect_tx(sbase + BAR_FULL_A + 8 * s, piece);
+                    tma_load_2d(sbase + OFF_A + s * A_TILE + pc * piece, &maps.a[bk], kc * BKC, pc * p.m_pad + tr.m0, sbase + BAR_FULL_A + 8 * s);
                 }
             }
             if (!ok) {
@@ -552,8 +580,8 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             // ---------------- packed weights: one bulk copy per row and group, four rows per lane ----------------
             int sbc = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const TileRef tr = tile_ref(p, tile);
+            for (int seg = 0; ok && seg < sg.n; ++seg) {
+                const TileRef tr = seg_ref(p, sg, seg);
                 for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
                     const int q = sbc % RAW_STAGES;
                     bool w_ok = true;
@@ -588,8 +616,8 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             // ---------------- MMA issue: two instructions per 16-value step (weight pieces Wh, Wl) ----------------
             int it = 0, sbc = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const TileRef tr = tile_ref(p, tile);
+            for (int seg = 0; ok && seg < sg.n; ++seg) {
+                const TileRef tr = seg_ref(p, sg, seg);
                 const uint32_t idesc = idesc_f16_m128((16 << box_bucket(tr.nt)) + ((tr.nt + 15) & ~15));
                 for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
                     const int b = sbc & 1;
@@ -624,8 +652,18 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
         const __half2 k1152 = __half2half2(__float2half_rn(1152.f));
         int it = 0, sbc = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const TileRef tr = tile_ref(p, tile);
+        // A finished operand chunk is handed to the MMA thread one chunk late: the fence that makes the stores visible
+        // to the tensor core waits for them to land, which takes about as long as converting the next chunk.
+        int pend = -1;
+        auto publish = [&]() {
+            if (pend < 0) return;
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sbase + BAR_FULL_W + 8 * pend);
+            pend = -1;
+        };
+        for (int seg = 0; ok && seg < sg.n; ++seg) {
+            const TileRef tr = seg_ref(p, sg, seg);
             const bool live = tr.n0 + r < p.N;
             for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
                 const int q = sbc % RAW_STAGES, slot = sbc % TABN2;
@@ -729,6 +767,7 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         }
                     }
                     if (!wait_or_abort<false>(sbase + BAR_EMPTY + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    publish();                    // the previous chunk
                     uint8_t* hrow = smem + OFF_WH + s * W_TILE + r * 128;
                     uint8_t* lrow = smem + OFF_WL + s * W_TILE + r * 128;
 #pragma unroll
@@ -737,15 +776,14 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         *reinterpret_cast<uint4*>(hrow + off) = make_uint4(hw[4 * jj], hw[4 * jj + 1], hw[4 * jj + 2], hw[4 * jj + 3]);
                         *reinterpret_cast<uint4*>(lrow + off) = make_uint4(lw[4 * jj], lw[4 * jj + 1], lw[4 * jj + 2], lw[4 * jj + 3]);
                     }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(sbase + BAR_FULL_W + 8 * s);
+                    pend = s;
                 }
                 if (!ok) break;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sbase + BAR_RAW_EMPTY + 8 * q);
             }
         }
+        if (ok) publish();
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");       // 4 x 40 + 4 x 128 + 8 x 168 <= 16 x 128
         // ---------------- drain: y += t * (F_hi + F_lo) once per group ----------------
@@ -755,8 +793,8 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
         const int wr = quad * 32 + lane;
         int sbc = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const TileRef tr = tile_ref(p, tile);
+        for (int seg = 0; ok && seg < sg.n; ++seg) {
+            const TileRef tr = seg_ref(p, sg, seg);
             const int box = 16 << box_bucket(tr.nt);
             float2 acc[32];
 #pragma unroll
@@ -789,8 +827,16 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             }
             if (!ok) break;
             const int n = tr.n0 + wr;
-            float* ybase = p.ksplit > 1 ? p.y_part + static_cast<size_t>(tr.ks) * p.M * p.N : p.y;
-            if (n < p.N) {
+            if (tr.part >= 0) {
+                // a piece of a tile: [token][weight row] into the piece's slot
+                float* part = p.y_part + static_cast<size_t>(tr.part) * (TT * TW);
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const int col = half * 64 + c;
+                    const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                    if (col < tr.nt) part[col * TW + wr] = v * __ldg(p.inv_s + tr.m0 + col);
+                }
+            } else if (n < p.N) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int col = half * 64 + c;
@@ -799,7 +845,7 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         int orow = p.out_row ? __ldg(p.out_row + row) : row;
                         if (p.out_identity && orow >= 0) orow = row;
                         const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-                        if (orow >= 0) ybase[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
+                        if (orow >= 0) p.y[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
                     }
                 }
             }
@@ -899,17 +945,42 @@ __global__ void __launch_bounds__(256) quantize_sa_kernel(const float* __restric
                     op.g + static_cast<size_t>(m >> 1) * (K / 16), m & 1, op.inv_s + m);
 }
 
-// y = sum of the k-slices' partial results, slices added in index order.
-__global__ void __launch_bounds__(256) splitk_reduce_sa_kernel(const float4* __restrict__ part, long long n4, int ksplit,
-                                                               float4* __restrict__ y) {
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        float4 a = __ldg(part + i);
-        for (int k = 1; k < ksplit; ++k) {
-            const float4 b = __ldg(part + static_cast<long long>(k) * n4 + i);
-            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+// Adds up the pieces of every output tile that the balanced split cut, in k order, and writes the tile to y.
+// Block (t, j) handles 16 tokens of output tile t; a tile one CTA computed whole is already in y.
+__global__ void __launch_bounds__(256) sk_fixup_kernel(const float* __restrict__ part, long long units, int grid, int nsb, int tiles_m,
+                                                       int M, int N, float* __restrict__ y) {
+    const int t = blockIdx.x;
+    const long long ua = static_cast<long long>(t) * nsb, ub = ua + nsb - 1;
+    // the CTA that holds unit u is the largest c with sk_start(c) <= u
+    auto owner = [&](long long u) {
+        int c = static_cast<int>(((u + 1) * grid + units - 1) / units) - 1;
+        c = c < 0 ? 0 : c >= grid ? grid - 1 : c;
+        while (c + 1 < grid && sk_start(units, grid, c + 1) <= u) ++c;
+        while (c > 0 && sk_start(units, grid, c) > u) --c;
+        return c;
+    };
+    const int ca = owner(ua), cb = owner(ub);
+    if (ca == cb) return;
+    const int m0 = (t % tiles_m) * TT, n0 = (t / tiles_m) * TW;
+    const int nt = M - m0 < TT ? M - m0 : TT;
+    const int wr = threadIdx.x & (TW - 1);
+    const int col0 = blockIdx.y * 16 + (threadIdx.x >> 7);          // this thread: tokens col0, col0 + 2, ..., col0 + 14
+    if (n0 + wr >= N || col0 >= nt) return;
+    float a[8];
+    for (int c = ca; c <= cb; ++c) {
+        const int slot = 2 * c + (c == ca ? 1 : 0);        // CTA ca holds the tile's first unit: its piece begins the tile
+        const float* src = part + static_cast<size_t>(slot) * (TT * TW) + wr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = col0 + 2 * j;
+            const float v = col < nt ? __ldg(src + col * TW) : 0.f;
+            a[j] = c == ca ? v : a[j] + v;
         }
-        y[i] = a;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int col = col0 + 2 * j;
+        if (col < nt) y[static_cast<size_t>(m0 + col) * N + n0 + wr] = a[j];
     }
 }
 
@@ -965,7 +1036,7 @@ struct SaLaunch {
     SaOperand op;
     const int4* tile_tab; const int* n_tiles_dev; const int* out_row; int out_identity;
     int tiles_m, tiles_n, grid;
-    int ksplit, sb_per; float* y_part;
+    long long sk_units; float* y_part;
 };
 
 int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
@@ -993,7 +1064,7 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
     p.M = L.M; p.N = L.N; p.K = K; p.m_pad = L.op.m_pad;
     p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n;
     p.tile_tab = L.tile_tab; p.n_tiles_dev = L.n_tiles_dev; p.out_row = L.out_row; p.out_identity = L.out_identity;
-    p.ksplit = L.ksplit > 1 ? L.ksplit : 1; p.sb_per = L.ksplit > 1 ? L.sb_per : K / 256; p.y_part = L.y_part;
+    p.sk_units = L.sk_units; p.y_part = L.y_part;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_sa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
@@ -1015,24 +1086,24 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
     return cuda_check(cudaGetLastError(), "gemm_sa launch");
 }
 
-// Split-K plan for a dense call with few output tiles: up to four CTAs share a tile, each over a multiple of four
-// super-blocks (one G operand group).
-struct SplitPlan { int ksplit, sb_per; };
+// Balanced split of a dense call (see SaParams::sk_units). With at least as many output tiles as SMs every SM gets the
+// same number of super-blocks; with fewer tiles a CTA takes no less than three super-blocks (about 4 us of work), so
+// that a small call is not cut into pieces that cost more to add up than they save.
+struct SplitPlan { int grid; long long units; };
 SplitPlan plan_split(int M, int K, int N, bool allow) {
     const int nsb = K / 256, tiles = ((M + TT - 1) / TT) * ((N + TW - 1) / TW), sms = ctx().sm_count;
-    SplitPlan s{1, nsb};
-    if (!allow || nsb < 8 || tiles * 2 > sms) return s;
-    double best = static_cast<double>((tiles + sms - 1) / sms) * nsb;
-    for (int want = 2; want <= 4; ++want) {
-        int per = (nsb + want - 1) / want;
-        per = (per + 3) & ~3;
-        const int ks = (nsb + per - 1) / per;
-        if (ks < 2) continue;
-        const double waves = static_cast<double>((static_cast<long long>(tiles) * ks + sms - 1) / sms);
-        // cost in super-blocks of one tile (~1.2 us each); the reduction moves (slices + 1) x M x N floats
-        const double cost = waves * per + static_cast<double>(ks + 1) * M * N * 4.0 / 6.0e6 / 1.2 + 0.5;
-        if (cost < best * 0.97) { best = cost; s.ksplit = ks; s.sb_per = per; }
-    }
+    SplitPlan s{tiles < sms ? tiles : sms, 0};
+    if (!allow || tiles % sms == 0) return s;
+    const long long units = static_cast<long long>(tiles) * nsb;
+    long long grid = tiles >= sms ? sms : units / 3;
+    if (grid > sms) grid = sms;
+    if (grid < 2) return s;
+    // the longest CTA's work, in super-blocks, with whole tiles and with the split; adding up the pieces is one more
+    // launch, worth about three super-blocks
+    const long long whole = static_cast<long long>((tiles + sms - 1) / sms) * nsb, split = (units + grid - 1) / grid;
+    if (whole - split < 3) return s;
+    s.grid = static_cast<int>(grid);
+    s.units = units;
     return s;
 }
 
@@ -1062,7 +1133,7 @@ SaPlan plan_sa(int M, int K, int N, bool allow_split) {
     pl.m_pad = static_cast<size_t>(pl.tiles_m) * TT;
     pl.sp = plan_split(M, K, N, allow_split);
     pl.op_bytes = operand_bytes(pl.m_pad, K).total();
-    pl.part_bytes = pl.sp.ksplit > 1 ? align256(static_cast<size_t>(pl.sp.ksplit) * M * N * sizeof(float)) : 0;
+    pl.part_bytes = pl.sp.units ? align256(static_cast<size_t>(2 * pl.sp.grid) * TT * TW * sizeof(float)) : 0;
     return pl;
 }
 
@@ -1087,46 +1158,37 @@ int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const
     SaLaunch L{};
     L.w = w; L.type = type; L.y = y; L.M = M; L.K = K; L.N = N; L.w_rows = N; L.op = op;
     L.tiles_m = pl.tiles_m; L.tiles_n = pl.tiles_n;
-    L.ksplit = pl.sp.ksplit; L.sb_per = pl.sp.sb_per;
-    L.y_part = pl.sp.ksplit > 1 ? reinterpret_cast<float*>(s) : nullptr;
-    const int n_tiles = pl.tiles_m * pl.tiles_n * pl.sp.ksplit;
-    L.grid = n_tiles < c.sm_count ? n_tiles : c.sm_count;
+    L.sk_units = pl.sp.units;
+    L.y_part = pl.sp.units ? reinterpret_cast<float*>(s) : nullptr;
+    L.grid = pl.sp.grid;
     if ((rc = run_sa_kernel(L, st))) return rc;
-    if (pl.sp.ksplit > 1) {
-        const long long n4 = static_cast<long long>(M) * N / 4;
-        long long blocks = (n4 + 255) / 256;
-        if (blocks > static_cast<long long>(c.sm_count) * 8) blocks = static_cast<long long>(c.sm_count) * 8;
-        splitk_reduce_sa_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(reinterpret_cast<const float4*>(L.y_part), n4, pl.sp.ksplit,
-                                                                        reinterpret_cast<float4*>(y));
+    if (pl.sp.units) {
+        sk_fixup_kernel<<<dim3(pl.tiles_m * pl.tiles_n, TT / 16), 256, 0, st>>>(L.y_part, pl.sp.units, pl.sp.grid, K / 256, pl.tiles_m, M, N, y);
         c.launches++;
-        return cuda_check(cudaGetLastError(), "splitk_reduce launch");
+        return cuda_check(cudaGetLastError(), "sk_fixup launch");
     }
     return LAPLACE_OK;
 }
 
-// split-K only when its partial results can be added up with vector loads
-bool can_split(const float* y, int M, int N) {
-    return (static_cast<long long>(M) * N) % 4 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
-}
 
 }  // namespace
 
 int launch_gemm_sa(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st) {
     int rc = check_args(x, w, type, M, K, N);
     if (rc) return rc;
-    const SaPlan pl = plan_sa(M, K, N, can_split(y, M, N));
+    const SaPlan pl = plan_sa(M, K, N, true);
     if ((rc = g_scratch.ensure(pl.total(), st))) return rc;
     return gemm_sa_on_scratch(static_cast<uint8_t*>(g_scratch.p), pl, x, w, type, y, M, K, N, st);
 }
 
 // The same call on scratch memory the caller owns (`cap` bytes at `scratch`, 256-byte aligned); nothing is
-// allocated. The K-split of launch_gemm_sa is kept when its partial results fit too (the result is then
-// bit-identical to launch_gemm_sa's), otherwise the call runs unsplit.
+// allocated. The balanced split of launch_gemm_sa is kept when its partial results fit too (the result is then
+// bit-identical to launch_gemm_sa's), otherwise the call runs on whole tiles.
 int launch_gemm_sa_prealloc(uint8_t* scratch, size_t cap, const float* x, const uint8_t* w, uint32_t type, float* y,
                             int M, int K, int N, cudaStream_t st) {
     int rc = check_args(x, w, type, M, K, N);
     if (rc) return rc;
-    SaPlan pl = plan_sa(M, K, N, can_split(y, M, N));
+    SaPlan pl = plan_sa(M, K, N, true);
     if (pl.total() > cap) pl = plan_sa(M, K, N, false);
     if (pl.total() > cap)
         return fail(LAPLACE_ERR_LIMIT, "gemm: M=%d K=%d needs %zu bytes of scratch, the caller's area holds %zu", M, K, pl.total(), cap);
