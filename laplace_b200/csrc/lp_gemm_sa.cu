@@ -54,32 +54,26 @@ constexpr int RAW_STAGES = 2;
 constexpr int RAW_TILE = TW * Q4_K_BYTES;          // 18 KB
 constexpr int W_TILE = TW * BKC * 2;               // 16 KB: 128 rows of 64 fp16
 constexpr int A_TILE = 2 * TT * BKC * 2;           // 32 KB: the hi rows, then the lo rows
-constexpr int TABN = 4;                            // ring of per-super-block tables of the rows' d
-constexpr int MINN = 3;                            // ring of min-term operands, one slot per super-block
-constexpr int W2_TILE = TW * 32;                   // 4 KB: per weight row 16 fp16, the pieces of -dmin * mn_j
-constexpr int G_TILE = 2 * TT * 32;                // 8 KB: per token 16 fp16 (g_j / 32 twice), hi rows then lo rows
-constexpr int MIN_SLOT = W2_TILE + G_TILE;
+constexpr int TABN = 4;                            // ring of per-super-block weight-scale tables and g tiles
+constexpr int TAB_ROW = 12;                        // floats per weight row: d, -dmin*mn[0..7], 3 unused
+constexpr int G_TILE = (TT / 2) * 16 * 4;          // 4 KB: per token pair 8 x (g[even token], g[odd token])
 constexpr int THREADS = 512;
-constexpr uint32_t TMEM_COLS = 512;                // F (hi | lo, 256 columns) and F2, the min term of the whole tile (256 columns)
-constexpr uint32_t TM_F2 = 256;
+constexpr uint32_t TMEM_COLS = 512;                // two accumulators of 256 columns (hi | lo)
 
 constexpr uint32_t OFF_W = 0;
 constexpr uint32_t OFF_A = OFF_W + STAGES * W_TILE;
 constexpr uint32_t OFF_RAW = OFF_A + STAGES * A_TILE;
-constexpr uint32_t OFF_MIN = OFF_RAW + RAW_STAGES * RAW_TILE;
-constexpr uint32_t OFF_TAB = OFF_MIN + MINN * MIN_SLOT;
-constexpr uint32_t OFF_BAR = OFF_TAB + TABN * TW * 4;
+constexpr uint32_t OFF_TAB = OFF_RAW + RAW_STAGES * RAW_TILE;
+constexpr uint32_t OFF_G = OFF_TAB + TABN * TW * TAB_ROW * 4;
+constexpr uint32_t OFF_BAR = OFF_G + TABN * G_TILE;
 constexpr uint32_t BAR_FULL_A = OFF_BAR, BAR_FULL_W = BAR_FULL_A + 8 * STAGES, BAR_EMPTY = BAR_FULL_W + 8 * STAGES,
                    BAR_RAW_FULL = BAR_EMPTY + 8 * STAGES, BAR_RAW_EMPTY = BAR_RAW_FULL + 8 * RAW_STAGES,
-                   BAR_TMEM_FULL = BAR_RAW_EMPTY + 8 * RAW_STAGES, BAR_TMEM_EMPTY = BAR_TMEM_FULL + 8,
-                   BAR_F2_FULL = BAR_TMEM_EMPTY + 8, BAR_F2_EMPTY = BAR_F2_FULL + 8,
-                   BAR_G_FULL = BAR_F2_EMPTY + 8, BAR_W2_FULL = BAR_G_FULL + 8 * MINN, BAR_MIN_EMPTY = BAR_W2_FULL + 8 * MINN,
-                   BAR_TAB_EMPTY = BAR_MIN_EMPTY + 8 * MINN,
+                   BAR_TMEM_FULL = BAR_RAW_EMPTY + 8 * RAW_STAGES, BAR_TMEM_EMPTY = BAR_TMEM_FULL + 16,
+                   BAR_G_FULL = BAR_TMEM_EMPTY + 16, BAR_TAB_EMPTY = BAR_G_FULL + 8 * TABN,
                    OFF_TMEM_PTR = BAR_TAB_EMPTY + 8 * TABN, OFF_ABORT = OFF_TMEM_PTR + 8;
 constexpr uint32_t SMEM_BYTES = OFF_ABORT + 8 + 1024;       // + slack for the 1024-byte alignment
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
-static_assert(OFF_RAW % 128 == 0 && RAW_TILE % 128 == 0, "TMA destinations are 128-byte aligned");
-static_assert(OFF_MIN % 256 == 0 && MIN_SLOT % 256 == 0 && W2_TILE % 256 == 0, "the 32-byte swizzle repeats every 256 bytes");
+static_assert(OFF_RAW % 128 == 0 && RAW_TILE % 128 == 0 && OFF_G % 128 == 0, "TMA destinations are 128-byte aligned");
 static_assert(OFF_A % 1024 == 0 && A_TILE % 1024 == 0 && W_TILE % 1024 == 0, "swizzled tiles are 1024-byte aligned");
 
 struct SaParams {
@@ -144,7 +138,7 @@ __device__ __forceinline__ int box_bucket(int nt) { return nt <= 16 ? 0 : nt <= 
 
 struct SaMaps {
     CUtensorMap a[4];      // activation pieces, [2 * m_pad][K] fp16, boxes of 64 k x {16, 32, 64, 128} rows, 128-byte swizzle
-    CUtensorMap g[4];      // block-sum pieces, [2 * m_pad][K/256 * 16] fp16, boxes of 16 x {16, 32, 64, 128} rows, 32-byte swizzle
+    CUtensorMap g[4];      // block sums, [m_pad / 2][K/256 * 16] fp32, boxes of 16 x {8, 16, 32, 64} token pairs
     CUtensorMap w;         // packed weights as bytes, rows of K/256 * 144 bytes, boxes of 144 bytes x 128 rows
 };
 
@@ -166,16 +160,14 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             mbar_init(sbase + BAR_RAW_FULL + 8 * q, 1);
             mbar_init(sbase + BAR_RAW_EMPTY + 8 * q, 4);
         }
-        mbar_init(sbase + BAR_TMEM_FULL, 1);                 // tcgen05.commit
-        mbar_init(sbase + BAR_TMEM_EMPTY, 8);                // one arrive per drain warp
-        mbar_init(sbase + BAR_F2_FULL, 1);
-        mbar_init(sbase + BAR_F2_EMPTY, 8);
-        for (int t = 0; t < MINN; ++t) {
-            mbar_init(sbase + BAR_G_FULL + 8 * t, 1);
-            mbar_init(sbase + BAR_W2_FULL + 8 * t, 4);       // one arrive per converter warp
-            mbar_init(sbase + BAR_MIN_EMPTY + 8 * t, 1);     // tcgen05.commit
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(sbase + BAR_TMEM_FULL + 8 * t, 1);     // tcgen05.commit
+            mbar_init(sbase + BAR_TMEM_EMPTY + 8 * t, 8);    // one arrive per drain warp
         }
-        for (int t = 0; t < TABN; ++t) mbar_init(sbase + BAR_TAB_EMPTY + 8 * t, 8);
+        for (int t = 0; t < TABN; ++t) {
+            mbar_init(sbase + BAR_G_FULL + 8 * t, 1);
+            mbar_init(sbase + BAR_TAB_EMPTY + 8 * t, 8);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -229,16 +221,13 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                 const TileRef tr = seg_ref(p, sg, seg);
                 const int bk = box_bucket(tr.nt);
                 for (int sb = tr.sb0; sb < tr.sb1; ++sb, ++sbc) {
-                    const int q = sbc % RAW_STAGES, slot = sbc % MINN;
+                    const int q = sbc % RAW_STAGES, slot = sbc % TABN;
                     if (!wait_or_abort<false>(sbase + BAR_RAW_EMPTY + 8 * q, ((sbc / RAW_STAGES) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                     mbar_expect_tx(sbase + BAR_RAW_FULL + 8 * q, RAW_TILE);
                     tma_load_2d(sbase + OFF_RAW + q * RAW_TILE, &maps.w, sb * Q4_K_BYTES, tr.wrow0 + tr.n0, sbase + BAR_RAW_FULL + 8 * q);
-                    if (!wait_or_abort<false>(sbase + BAR_MIN_EMPTY + 8 * slot, ((sbc / MINN) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-                    const uint32_t gpiece = static_cast<uint32_t>(16 << bk) * 32u;
-                    const uint32_t gdst = sbase + OFF_MIN + slot * MIN_SLOT + W2_TILE;
-                    mbar_expect_tx(sbase + BAR_G_FULL + 8 * slot, 2 * gpiece);
-                    tma_load_2d(gdst, &maps.g[bk], sb * 16, tr.m0, sbase + BAR_G_FULL + 8 * slot);
-                    tma_load_2d(gdst + gpiece, &maps.g[bk], sb * 16, p.m_pad + tr.m0, sbase + BAR_G_FULL + 8 * slot);
+                    if (!wait_or_abort<false>(sbase + BAR_TAB_EMPTY + 8 * slot, ((sbc / TABN) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                    mbar_expect_tx(sbase + BAR_G_FULL + 8 * slot, static_cast<uint32_t>(8 << bk) * 64u);
+                    tma_load_2d(sbase + OFF_G + slot * G_TILE, &maps.g[bk], sb * 16, tr.m0 >> 1, sbase + BAR_G_FULL + 8 * slot);
                 }
             }
             if (!ok) {
@@ -246,24 +235,25 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                     const int v = sbc - 1 - k;
                     if (v >= 0) mbar_wait_bounded(sbase + BAR_RAW_FULL + 8 * (v % RAW_STAGES), (v / RAW_STAGES) & 1);
                 }
-                for (int k = 0; k < MINN; ++k) {
+                for (int k = 0; k < TABN; ++k) {
                     const int v = sbc - 1 - k;
-                    if (v >= 0) mbar_wait_bounded(sbase + BAR_G_FULL + 8 * (v % MINN), (v / MINN) & 1);
+                    if (v >= 0) mbar_wait_bounded(sbase + BAR_G_FULL + 8 * (v % TABN), (v / TABN) & 1);
                 }
             }
         } else if (warp == 1 && lane == 0) {
             // ---------------- MMA issue: per 16-value step one instruction over the stacked pieces, D columns
             // [0, nt) = weights x hi, [box, box + nt) = weights x lo. (One thread issues an instruction roughly every
-            // 115 cycles however small it is, so one wide instruction beats two narrow ones.) After a super-block's
-            // sixteen instructions one more adds its min term to F2: A = pieces of -dmin * mn_j, B = pieces of g_j. ----------------
+            // 115 cycles however small it is, so one wide instruction beats two narrow ones.) ----------------
             int it = 0, sbc = 0;
             bool ok = true;
             for (int seg = 0; ok && seg < sg.n; ++seg) {
                 const TileRef tr = seg_ref(p, sg, seg);
                 const uint32_t idesc = idesc_f16_m128((16 << box_bucket(tr.nt)) + ((tr.nt + 15) & ~15));
                 for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
-                    if (!wait_or_abort<true>(sbase + BAR_TMEM_EMPTY, (sbc & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
+                    const int b = sbc & 1;
+                    if (!wait_or_abort<true>(sbase + BAR_TMEM_EMPTY + 8 * b, ((sbc >> 1) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
                     fence_after();
+                    const uint32_t f_tmem = tmem_base + b * 256;
                     for (int c = 0; c < 4; ++c, ++it) {
                         const int s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
@@ -275,23 +265,12 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
                             const uint64_t off = static_cast<uint64_t>(ks * 2);      // 32 bytes >> 4 inside the swizzle row
-                            mma_f16(tmem_base, wdesc + off, adesc + off, idesc, (c | ks) != 0);
+                            mma_f16(f_tmem, wdesc + off, adesc + off, idesc, (c | ks) != 0);
                         }
                         commit(sbase + BAR_EMPTY + 8 * s);                  // operands consumed -> producers
                     }
                     if (!ok) break;
-                    commit(sbase + BAR_TMEM_FULL);                          // the super-block's products are complete -> drain
-                    // the min term, while the drain empties F
-                    const int slot = sbc % MINN;
-                    const uint32_t mph = (sbc / MINN) & 1;
-                    if (!wait_or_abort<true>(sbase + BAR_G_FULL + 8 * slot, mph, abort_flag, p.err, DEV_TIMEOUT_FULL) ||
-                        !wait_or_abort<true>(sbase + BAR_W2_FULL + 8 * slot, mph, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
-                    if (sb == tr.sb0 && !wait_or_abort<true>(sbase + BAR_F2_EMPTY, (seg & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_TMEM)) { ok = false; break; }
-                    fence_after();
-                    mma_f16(tmem_base + TM_F2, smem_desc_sw32(sbase + OFF_MIN + slot * MIN_SLOT), smem_desc_sw32(sbase + OFF_MIN + slot * MIN_SLOT + W2_TILE),
-                            idesc, sb != tr.sb0);
-                    commit(sbase + BAR_MIN_EMPTY + 8 * slot);
-                    if (sb == tr.sb1 - 1) commit(sbase + BAR_F2_FULL);      // the tile's (piece's) min term is complete
+                    commit(sbase + BAR_TMEM_FULL + 8 * b);                  // the super-block's products are complete -> drain
                 }
             }
         }
@@ -312,33 +291,16 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                 const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, mn_lo = hdr.z & 0x3f3f3f3fu;
                 const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
                 const uint32_t mn_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
-                const int mslot = sbc % MINN;
-                if (!wait_or_abort<false>(sbase + BAR_TAB_EMPTY + 8 * slot, ((sbc / TABN) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY) ||
-                    !wait_or_abort<false>(sbase + BAR_MIN_EMPTY + 8 * mslot, ((sbc / MINN) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+                if (!wait_or_abort<false>(sbase + BAR_TAB_EMPTY + 8 * slot, ((sbc / TABN) & 1) ^ 1, abort_flag, p.err, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
                 {
-                    // the row's d for the drain, and the min-term operand: -dmin * mn_j (at most 17 significant bits,
-                    // formed exactly in fp32 as the reference forms dmin * m) cut into two fp16 pieces, (hi_j, lo_j) for
-                    // j = 0..7. Needs |dmin * mn_j| < 65504; GGUF's dmin is a fraction of the weights' range.
-                    reinterpret_cast<float*>(smem + OFF_TAB)[slot * TW + r] = half_bits_to_float(hdr.x);
-                    const float ndmin = -half_bits_to_float(hdr.x >> 16);
-                    uint32_t w2[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint32_t mn = ((j < 4 ? mn_lo : mn_hi) >> (8 * (j & 3))) & 0xff;
-                        const float v = ndmin * static_cast<float>(mn);
-                        const __half vh = __float2half_rn(v);
-                        const __half vl = __float2half_rn(v - __half2float(vh));
-                        const __half2 pr = __halves2half2(vh, vl);
-                        w2[j] = *reinterpret_cast<const uint32_t*>(&pr);
-                    }
-                    // row r of a K-major tile with 32-byte rows and the 32-byte swizzle: 16-byte chunk c sits at c ^ bit 2 of r
-                    uint8_t* w2row = smem + OFF_MIN + mslot * MIN_SLOT + r * 32;
-                    const uint32_t sw = static_cast<uint32_t>((r >> 2) & 1) << 4;
-                    *reinterpret_cast<uint4*>(w2row + (0u ^ sw)) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
-                    *reinterpret_cast<uint4*>(w2row + (16u ^ sw)) = make_uint4(w2[4], w2[5], w2[6], w2[7]);
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(sbase + BAR_W2_FULL + 8 * mslot);
+                    // the row's scales for the drain: d, and -dmin * mn_j (exact in fp32, as the reference forms them)
+                    const float d = half_bits_to_float(hdr.x), ndmin = -half_bits_to_float(hdr.x >> 16);
+                    float4* trow = reinterpret_cast<float4*>(smem + OFF_TAB + (slot * TW + r) * (TAB_ROW * 4));
+                    trow[0] = make_float4(d, ndmin * static_cast<float>(mn_lo & 0xff), ndmin * static_cast<float>((mn_lo >> 8) & 0xff),
+                                          ndmin * static_cast<float>((mn_lo >> 16) & 0xff));
+                    trow[1] = make_float4(ndmin * static_cast<float>(mn_lo >> 24), ndmin * static_cast<float>(mn_hi & 0xff),
+                                          ndmin * static_cast<float>((mn_hi >> 8) & 0xff), ndmin * static_cast<float>((mn_hi >> 16) & 0xff));
+                    trow[2] = make_float4(ndmin * static_cast<float>(mn_hi >> 24), 0.f, 0.f, 0.f);
                 }
 #pragma unroll
                 for (int c = 0; c < 4; ++c, ++it) {
@@ -385,8 +347,9 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ---------------- drain: lane = weight row (output column), 64 token columns per warp ----------------
-        // Once per super-block: y += d * (F_hi + F_lo), two token columns per packed instruction; once per tile (or
-        // piece of a tile): y += 32 * (F2_hi + F2_lo), the min term.
+        // Once per super-block: y += d * (F_hi + F_lo) + sum_j (-dmin mn_j) * g_j, two token columns per packed
+        // instruction. The min term is the reference's own fp32 arithmetic (src/matmul_simd.cpp:263-279:
+        // acc_min += (dmin * m) * sum_x), not a tensor-core product.
         const int e8 = warp - 8;
         const int quad = e8 & 3, half = e8 >> 2;
         const uint32_t t_lane = static_cast<uint32_t>(quad * 32) << 16;
@@ -399,48 +362,55 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             float2 acc[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) acc[c] = make_float2(0.f, 0.f);
-            // adds scale * (hi + lo) of 256 accumulator columns at `cols`; `release` is raised once the warp's columns are in registers
-            auto take = [&](uint32_t cols, float scale, uint32_t release) {
-                const float2 dd = make_float2(scale, scale);
+            for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
+                const int b = sbc & 1, slot = sbc % TABN;
+                if (!wait_or_abort<false>(sbase + BAR_TMEM_FULL + 8 * b, (sbc >> 1) & 1, abort_flag, p.err, DEV_TIMEOUT_MMA) ||
+                    !wait_or_abort<false>(sbase + BAR_G_FULL + 8 * slot, (sbc / TABN) & 1, abort_flag, p.err, DEV_TIMEOUT_FULL)) { ok = false; break; }
+                fence_after();
+                const uint32_t trow = sbase + OFF_TAB + (slot * TW + wr) * (TAB_ROW * 4);
+                const uint4 t0 = lds128(trow), t1 = lds128(trow + 16);
+                const float dm8 = __uint_as_float(lds32(trow + 32));
+                const float2 dd = make_float2(__uint_as_float(t0.x), __uint_as_float(t0.x));
+                const float dm[8] = {__uint_as_float(t0.y), __uint_as_float(t0.z), __uint_as_float(t0.w), __uint_as_float(t1.x),
+                                     __uint_as_float(t1.y), __uint_as_float(t1.z), __uint_as_float(t1.w), dm8};
+                const uint32_t gbase = sbase + OFF_G + slot * G_TILE + half * 32 * 64;      // this warp's 32 token pairs
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (half * 64 + h * 32 < tr.nt) {                  // warp-uniform: columns past the tile's tokens hold nothing
                         float fh[32], fl[32];
-                        ld32(tmem_base + t_lane + cols + half * 64 + h * 32, fh);
-                        ld32(tmem_base + t_lane + cols + box + half * 64 + h * 32, fl);
+                        ld32(tmem_base + t_lane + b * 256 + half * 64 + h * 32, fh);
+                        ld32(tmem_base + t_lane + b * 256 + box + half * 64 + h * 32, fl);
                         wait_ld();
                         if (h == 1 || half * 64 + 32 >= tr.nt) {
                             // the accumulator is in registers: the MMA may overwrite it
                             fence_before();
                             __syncwarp();
-                            if (lane == 0) mbar_arrive(release);
+                            if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * b);
                         }
 #pragma unroll
-                        for (int c2 = 0; c2 < 16; ++c2)
-                            acc[h * 16 + c2] = __ffma2_rn(dd, __fadd2_rn(make_float2(fh[2 * c2], fh[2 * c2 + 1]), make_float2(fl[2 * c2], fl[2 * c2 + 1])),
-                                                          acc[h * 16 + c2]);
+                        for (int c2 = 0; c2 < 16; ++c2) {
+                            const int cp = h * 16 + c2;                // token pair of this warp
+                            float2 a = acc[cp];
+                            a = __ffma2_rn(dd, __fadd2_rn(make_float2(fh[2 * c2], fh[2 * c2 + 1]), make_float2(fl[2 * c2], fl[2 * c2 + 1])), a);
+#pragma unroll
+                            for (int jq = 0; jq < 4; ++jq) {
+                                const uint4 gv = lds128(gbase + cp * 64 + jq * 16);      // (g_j[even], g_j[odd], g_j+1[even], g_j+1[odd])
+                                a = __ffma2_rn(make_float2(dm[2 * jq], dm[2 * jq]), make_float2(__uint_as_float(gv.x), __uint_as_float(gv.y)), a);
+                                a = __ffma2_rn(make_float2(dm[2 * jq + 1], dm[2 * jq + 1]), make_float2(__uint_as_float(gv.z), __uint_as_float(gv.w)), a);
+                            }
+                            acc[cp] = a;
+                        }
                     } else if (h == 0) {
                         // nothing to read for this warp: release the accumulator at once
                         fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(release);
+                        if (lane == 0) mbar_arrive(sbase + BAR_TMEM_EMPTY + 8 * b);
                     }
                 }
-            };
-            for (int sb = tr.sb0; sb < tr.sb1 && ok; ++sb, ++sbc) {
-                const int slot = sbc % TABN;
-                if (!wait_or_abort<false>(sbase + BAR_TMEM_FULL, sbc & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
-                fence_after();
-                const float d = reinterpret_cast<const float*>(smem + OFF_TAB)[slot * TW + wr];
-                take(0, d, sbase + BAR_TMEM_EMPTY);
-                // the table entry has been read: the converters may reuse it
+                // the table entry and the g tile have been read: the converters and the copy engine may reuse them
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sbase + BAR_TAB_EMPTY + 8 * slot);
             }
-            if (!ok) break;
-            if (!wait_or_abort<false>(sbase + BAR_F2_FULL, seg & 1, abort_flag, p.err, DEV_TIMEOUT_MMA)) { ok = false; break; }
-            fence_after();
-            take(TM_F2, 32.0f, sbase + BAR_F2_EMPTY);            // the g operand is g / 32 (see the quantizer)
             if (!ok) break;
             // y[token][n] = 2^-e_token * acc: for a fixed token the warp's 32 lanes write 32 consecutive floats
             const int n = tr.n0 + wr;
@@ -898,15 +868,14 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
 // written is the tensor-core operand built from them:
 //   hi, lo [k]      fp16 pieces of 2^e * (d * q[k]), e chosen so that the row's largest |x| lands in [2^13, 2^14);
 //                   within every four consecutive k the order is (0, 2, 1, 3), like the weight operand
-//   g_hi, g_lo [2b], [2b+1]   fp16 pieces of 2^e * (d * integer sum of block b) / 32 - the reference's ActQ8::sum, scaled
-//                   like the row; / 32 keeps a block of 32 equal values inside fp16's range - each piece stored twice:
-//                   the min-term operand of the weights has two columns per block (pieces of -dmin * mn)
+//   g               fp32 2^e * (d * integer sum) per block - the reference's ActQ8::sum, scaled like the row -
+//                   stored per PAIR of rows: g_pair[16 sb + 2 j + (row & 1)] for block 8 sb + j
 //   inv_s           2^-e
 // `load(b, t8)` returns values 4 t8 .. 4 t8 + 3 of block b of the row. The row is read twice (maximum, then
 // quantization); the second read hits L1 / L2.
 template <class Load>
 __device__ __forceinline__ void quantize_row_sa(Load load, int K, __half* __restrict__ hi_row, __half* __restrict__ lo_row,
-                                                __half* __restrict__ g_hi, __half* __restrict__ g_lo, float* __restrict__ inv_s) {
+                                                float* __restrict__ g_pair, int odd, float* __restrict__ inv_s) {
     __shared__ float red[8];
     const int bpr = K / 32, grp = threadIdx.x >> 3, t8 = threadIdx.x & 7, groups = blockDim.x >> 3;
     float amax = 0.f;
@@ -956,18 +925,14 @@ __device__ __forceinline__ void quantize_row_sa(Load load, int K, __half* __rest
         if (t8 == 0) {
             const short slo = static_cast<short>(hs), shi = static_cast<short>(hs_hi);
             const float sum = __fmul_rn(d, static_cast<float>(static_cast<int>(slo) + static_cast<int>(shi)));
-            const float g = __fmul_rn(__fmul_rn(sum, s), 0.03125f);
-            const __half gh = __float2half_rn(g);
-            const __half gl = __float2half_rn(g - __half2float(gh));
-            reinterpret_cast<__half2*>(g_hi)[b] = __halves2half2(gh, gh);
-            reinterpret_cast<__half2*>(g_lo)[b] = __halves2half2(gl, gl);
+            g_pair[2 * b + odd] = __fmul_rn(sum, s);          // element 16 (b / 8) + 2 (b % 8) + odd
         }
     }
 }
 
 struct SaOperand {          // operand buffers of one matmul
     __half* a;              // [2][m_pad][K]: hi rows, then lo rows
-    __half* g;              // [2][m_pad][K / 16]: block-sum pieces, hi rows, then lo rows
+    float*  g;              // [m_pad / 2][K / 16]: block sums of a pair of rows, interleaved
     float*  inv_s;          // [m_pad]
     int     m_pad;
 };
@@ -977,7 +942,7 @@ __global__ void __launch_bounds__(256) quantize_sa_kernel(const float* __restric
     const float* xr = x + static_cast<size_t>(m) * K;
     quantize_row_sa([&](int b, int t8) { return __ldg(reinterpret_cast<const float4*>(xr + b * 32) + t8); }, K,
                     op.a + static_cast<size_t>(m) * K, op.a + (static_cast<size_t>(op.m_pad) + m) * K,
-                    op.g + static_cast<size_t>(m) * (K / 16), op.g + (static_cast<size_t>(op.m_pad) + m) * (K / 16), op.inv_s + m);
+                    op.g + static_cast<size_t>(m >> 1) * (K / 16), m & 1, op.inv_s + m);
 }
 
 // Adds up the pieces of every output tile that the balanced split cut, in k order, and writes the tile to y.
@@ -1053,13 +1018,13 @@ Scratch g_scratch;
 
 struct OperandBytes { size_t a, g, s; size_t total() const { return a + g + s; } };
 OperandBytes operand_bytes(size_t m_pad, int K) {
-    return {align256(2 * m_pad * K * sizeof(__half)), align256(2 * m_pad * (K / 16) * sizeof(__half)), align256(m_pad * sizeof(float))};
+    return {align256(2 * m_pad * K * sizeof(__half)), align256(m_pad / 2 * (K / 16) * sizeof(float)), align256(m_pad * sizeof(float))};
 }
 SaOperand carve_operand(uint8_t*& s, size_t m_pad, int K) {
     const OperandBytes ob = operand_bytes(m_pad, K);
     SaOperand op;
     op.a = reinterpret_cast<__half*>(s);      s += ob.a;
-    op.g = reinterpret_cast<__half*>(s);      s += ob.g;
+    op.g = reinterpret_cast<float*>(s);       s += ob.g;
     op.inv_s = reinterpret_cast<float*>(s);   s += ob.s;
     op.m_pad = static_cast<int>(m_pad);
     return op;
@@ -1081,8 +1046,8 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
     for (int bk = 0; bk < 4; ++bk) {
         if (!make_map_2d(&maps.a[bk], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, L.op.a, static_cast<uint64_t>(K), 2ull * L.op.m_pad,
                          static_cast<uint64_t>(K) * 2, BKC, 16u << bk, CU_TENSOR_MAP_SWIZZLE_128B, "activations") ||
-            !make_map_2d(&maps.g[bk], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, L.op.g, static_cast<uint64_t>(K / 16), 2ull * L.op.m_pad,
-                         static_cast<uint64_t>(K / 16) * 2, 16, 16u << bk, CU_TENSOR_MAP_SWIZZLE_32B, "block sums"))
+            !make_map_2d(&maps.g[bk], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, L.op.g, static_cast<uint64_t>(K / 16), static_cast<uint64_t>(L.op.m_pad / 2),
+                         static_cast<uint64_t>(K / 16) * 4, 16, 8u << bk, CU_TENSOR_MAP_SWIZZLE_NONE, "block sums"))
             return LAPLACE_ERR_CUDA;
     }
     const uint64_t rb = row_bytes(L.type, K);
@@ -1308,7 +1273,7 @@ __global__ void __launch_bounds__(256) quantize_sa_mapped_kernel(const float* __
     const float* xr = x + static_cast<size_t>(src_rows ? __ldg(src_rows + p) : p / src_div) * K;
     quantize_row_sa([&](int b, int t8) { return __ldg(reinterpret_cast<const float4*>(xr + b * 32) + t8); }, K,
                     op.a + static_cast<size_t>(dr) * K, op.a + (static_cast<size_t>(op.m_pad) + dr) * K,
-                    op.g + static_cast<size_t>(dr) * (K / 16), op.g + (static_cast<size_t>(op.m_pad) + dr) * (K / 16), op.inv_s + dr);
+                    op.g + static_cast<size_t>(dr >> 1) * (K / 16), dr & 1, op.inv_s + dr);
 }
 
 __device__ __forceinline__ float act_swiglu(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
@@ -1337,7 +1302,7 @@ __global__ void __launch_bounds__(256) moe_act_quant_sa_kernel(const float* __re
         for (int i = threadIdx.x; i < I / 4; i += blockDim.x)
             reinterpret_cast<float4*>(h_out + static_cast<size_t>(p) * I)[i] = load(i >> 3, i & 7);
     quantize_row_sa(load, I, op.a + static_cast<size_t>(r) * I, op.a + (static_cast<size_t>(op.m_pad) + r) * I,
-                    op.g + static_cast<size_t>(r) * (I / 16), op.g + (static_cast<size_t>(op.m_pad) + r) * (I / 16), op.inv_s + r);
+                    op.g + static_cast<size_t>(r >> 1) * (I / 16), r & 1, op.inv_s + r);
 }
 
 // out[t][:] = sum over the token's live pairs, in slot order, of top_w[t][j] * dn[row of pair][:]

@@ -64,16 +64,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     d |= static_cast<uint64_t>(2) << 61;                        // SWIZZLE_128B
     return d;
 }
-// K-major, 32-byte-swizzled operand tile: rows of 32 bytes (16 fp16: one MMA step), 8-row groups 256 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw32(uint32_t addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);
-    d |= static_cast<uint64_t>(1) << 16;
-    d |= static_cast<uint64_t>(256 >> 4) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(6) << 61;                        // SWIZZLE_32B
-    return d;
-}
 // kind::f16 instruction descriptor: D fp32, A and B fp16, both K-major, M = 128 rows of A, n rows of B.
 __device__ __forceinline__ uint32_t idesc_f16_m128(int n) {
     return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);

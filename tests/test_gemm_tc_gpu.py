@@ -135,8 +135,7 @@ def test_prefill_special_rows(oracle, t, K):
     keep = np.ones(M, dtype=bool)
     keep[7] = False
     check_close(y[keep], ref[keep], f"{t.name} prefill with special rows")
-    # one live block: the main and the min term (each carried in two fp16 pieces, 2^-22) cancel in part
-    assert np.allclose(y[11], ref[11], rtol=1e-5, atol=0.0), np.abs(y[11] / ref[11] - 1).max()
+    assert np.allclose(y[11], ref[11], rtol=2e-6, atol=0.0)
 
 
 def test_scratch_growth_is_refused_during_stream_capture(oracle):
