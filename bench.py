@@ -361,8 +361,8 @@ def gpu_arm(args):
         assert np.array_equal(yh, y_loc[last].cpu().numpy()), "host-pointer result differs from the device-pointer result"
         lb.matmul_unregister_weights(region)
     prefill = prefill_leg(device, synth, torch, rank, world, dist) if not args.no_prefill else None
-    moe = moe_leg(device, synth, torch, dist, rank, world, steps=16, warmup=3, repeats=8, e2e=False) if not args.no_prefill else None
-    decode = decode_leg(device, synth, torch) if (world == 1 and not args.no_prefill) else None
+    moe = moe_leg(device, synth, torch, dist, rank, world, steps=16, warmup=3, repeats=8, e2e=False) if not (args.no_prefill or args.no_moe) else None
+    decode = decode_leg(device, synth, torch) if (world == 1 and not (args.no_prefill or args.no_shapes)) else None
     clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
@@ -827,7 +827,9 @@ def main():
     ap.add_argument("--repeats", type=int, default=0, help="timed repeats of the K-step region (0: until ~1.5 s have passed)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-pointer leg (for short profiler runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for short profiler runs)")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 prefill leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the M=512 prefill leg (and the MoE and decode-shape legs)")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MoE leg of the default line (for short profiler runs)")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the decode-shape table of the default line (for short profiler runs)")
     ap.add_argument("--no-graph", action="store_true", help="N>1 only: launch the steps eagerly instead of replaying a CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N>1, gemv workload: how the output slices are combined")
