@@ -345,6 +345,8 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
             }
         }
     } else {
+        // (register budget of the CTA: 4 x 40 + 4 x 104 + 8 x 184 <= 16 x 128 per lane; a sum above what the CTA was
+        // launched with would leave setmaxnreg.inc waiting for registers that never come)
         asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ---------------- drain: lane = weight row (output column), 64 token columns per warp ----------------
         // Once per super-block: y += d * (F_hi + F_lo) + sum_j (-dmin mn_j) * g_j, two token columns per packed
