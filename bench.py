@@ -249,7 +249,7 @@ def gpu_arm(args):
         for c in range(1, min(N_COPIES, warmup)):
             assert np.array_equal(np.roll(y0, c * 16, axis=-1), y_loc[c].cpu().numpy()), "rotated weight copies disagree"
     else:
-        y_all = pg.slot(warmup & 1).clone()              # step numbers start at 1: warm-up step `warmup` is the last one
+        y_all = pg.slot(warmup).clone()              # step numbers start at 1: warm-up step `warmup` is the last one
         for c in range(N_COPIES):                        # y_loc is still needed by the host-pointer leg's check
             device.gemm(x, copies[c], TYPE_Q4_K, M_ROWS, K_DIM, n_loc, y=y_loc[c])
         device.sync()

@@ -212,16 +212,17 @@ int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t typ
  * (flag [rank] of every GPU raised to the step number) by the NEXT gemm_allgather kernel's
  * prologue, or by laplace_cuda_allgather_wait_dev, which closes a chain of steps: it announces the
  * current step and waits (bounded) until all `world` flags of this GPU have reached it; the full y
- * of step s is then in slot (s & 1) of this GPU's buffer; consumers of y run after that call. A kernel
- * stores step s only after it has seen every GPU's announcement of step s - 1 (made when that GPU's
- * step-s kernel starts, i.e. when nothing on it reads the slot about to be overwritten any more),
- * which is what makes two slots enough. Replaces "GEMV + ncclAllGather" for decode, where the
+ * of step s is then in slot (s & 3) of this GPU's buffer; consumers of y run after that call. A kernel
+ * stores step s (over the slices of step s - 4) only after it has seen every GPU's flag at s - 3 or more: a
+ * GPU raises its flag to s' - 1 when its step-s' kernel starts, i.e. when everything it enqueued before that
+ * kernel - the readers of steps up to s' - 2 - has finished. Four slots keep that check off a step's critical
+ * path. Replaces "GEMV + ncclAllGather" for decode, where the
  * collective's latency is 2-3x the kernel.
  *
  * Memory: each GPU allocates one buffer with laplace_cuda_peer_alloc (zeroed; returns a 64-byte
  * IPC handle to pass to the other processes by any host channel) and opens the others' with
  * laplace_cuda_peer_open. Layout is up to the caller; the calls take pointers:
- *   peer_y[r]     GPU r's result area, float [2][M][n_total]
+ *   peer_y[r]     GPU r's result area, float [4][M][n_total]
  *   peer_flags[r] GPU r's flag array, int [world]
  *   step_counter  this GPU's int, done_counter this GPU's unsigned (both start at 0)
  * Steps are counted on the device, so the calls can be replayed from a CUDA graph. Every GPU must

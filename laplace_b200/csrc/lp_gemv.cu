@@ -389,7 +389,7 @@ struct Walker {
 // with its own two rows of x, so shared memory serves each weight row G times
 // instead of each activation row once per weight row.
 template <uint32_t TYPE, int M, int WARPS, bool RESIDENT, int PW = PRODUCER_WARPS, bool PEERS = true, bool EXT = false>
-__global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const KParams p) {
+__global__ void __launch_bounds__((WARPS + PW + (PEERS ? 1 : 0)) * 32, 1) gemv_stream_kernel(const KParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -414,6 +414,67 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
     auto bar_empty = [&](int w, int slot) { return sbase + w * 64 + 32 + 8 * slot; };
     auto ring_of = [&](int w) { return sbase + p.off_ring + w * (p.n_slots * p.slot_bytes); };
 
+    if (PEERS && warp == WARPS + PW) {
+        // ------------------------------ fused all-gather: its own warp -----------------------------
+        // Everything the exchange needs besides the results themselves happens here, beside the warps that stream:
+        // reading the step counter, announcing the previous step (a system-scope fence), watching the other GPUs'
+        // flags, advancing the counter, and at the end the coalesced stores of this CTA's column range into every
+        // GPU's buffer. (Done by consumer warp 0, these steps lengthened every launch by almost 3 us.)
+        if (!p.peers.world) return;
+        asm volatile("griddepcontrol.wait;" ::: "memory");     // the previous launch's stores and counter update are complete
+        const bool chained = p.peers.step_ctr != nullptr;
+        // This launch is step (counter + 1); its results go to slot (step & 3) of every buffer.
+        int prev = 0;
+        if (chained) {
+            prev = *reinterpret_cast<volatile const int*>(p.peers.step_ctr);
+            if (lane == 0) {
+                asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" :: "l"(p.peers.done_ctr) : "memory");   // "this CTA has read the counter"
+                // The previous launch's slices are complete (grid dependency), so one thread of the grid announces
+                // them: flag [rank] of every GPU is raised to the previous step.
+                if (blockIdx.x == gridDim.x - 1) {
+                    __threadfence_system();
+                    for (int r = 0; r < p.peers.world; ++r)
+                        asm volatile("st.relaxed.sys.global.s32 [%0], %1;" :: "l"(p.peers.flags[r] + p.peers.rank), "r"(prev) : "memory");
+                }
+            }
+        }
+        const size_t slot_off = chained ? static_cast<size_t>((prev + 1) & 3) * static_cast<size_t>(p.n_seg) * M * p.peers.ld : 0;
+        // This step overwrites slot (s & 3), i.e. the slices of step s - 4. A GPU raises its flag to s' - 1 when
+        // its step-s' kernel starts, and everything it enqueued before that kernel - the readers of steps up to
+        // s' - 2 among them - has finished by then (stream order). So a flag of s - 3 or more says that GPU is done
+        // reading step s - 4. Lane r watches GPU r; the GPUs run within a step or two of one another, so the flags
+        // have normally been there for a long time.
+        bool seen = !(chained && lane < p.peers.world);
+        bool bumped = !(chained && blockIdx.x == 0 && lane == 0);
+        for (uint32_t it = 0; it < (1u << 21); ++it) {
+            if (!seen) {
+                int v;
+                asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.peers.flags[p.peers.rank] + lane) : "memory");
+                seen = v - (prev - 2) >= 0;
+            }
+            if (!bumped && *reinterpret_cast<volatile unsigned*>(p.peers.done_ctr) == gridDim.x) {
+                // every CTA of this launch has read the old value: one thread of the grid advances the step counter
+                *reinterpret_cast<volatile unsigned*>(p.peers.done_ctr) = 0u;
+                *reinterpret_cast<volatile int*>(p.peers.step_ctr) = prev + 1;
+                bumped = true;
+            }
+            if (__all_sync(0xffffffffu, seen && bumped)) break;
+            if (it > 64) __nanosleep(100);
+        }
+        if (!(seen && bumped)) report_status(p.err, DEV_TIMEOUT_PEER);
+        named_bar_sync(3, (WARPS + 1) * 32);                    // all consumer warps of this CTA have staged their results
+        // No fence follows the stores: they are complete when the grid is, and the NEXT launch (or the closing wait
+        // kernel) announces them.
+        const float* stage = reinterpret_cast<const float*>(smem + p.off_stage);
+        for (int m = 0; m < M; ++m) {
+            const size_t at = slot_off + static_cast<size_t>(m) * p.peers.ld + p.peers.col0 + g0;
+            for (int i = lane; i < cta_rows; i += 32) {
+                const float v = stage[m * p.stage_ld + i];
+                for (int r = 0; r < p.peers.world; ++r) p.peers.y[r][at + i] = v;
+            }
+        }
+        return;
+    }
     if (warp >= WARPS) {
         // ------------------------------ producer warps -----------------------------
         constexpr int PER = (GROUPS + PW - 1) / PW;   // ring groups served per producer warp
@@ -480,23 +541,6 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
     // -------------------------------- consumer warps --------------------------------
     // x may be produced, and y read, by the kernel before this one in the stream.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // Fused all-gather: this launch is step (counter + 1); its results go to slot (step & 1) of every buffer.
-    // The previous launch's slices are complete now (grid dependency), so one thread of the grid announces
-    // them: flag [rank] of every GPU is raised to the previous step. Nothing else in the kernel waits for that.
-    size_t peer_slot_off = 0;
-    int peer_prev = 0;
-    if (PEERS && p.peers.world && p.peers.step_ctr) {
-        peer_prev = *reinterpret_cast<volatile const int*>(p.peers.step_ctr);
-        peer_slot_off = static_cast<size_t>((peer_prev + 1) & 1) * static_cast<size_t>(p.n_seg) * M * p.peers.ld;
-        if (threadIdx.x == 0) {
-            asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" :: "l"(p.peers.done_ctr) : "memory");   // "this CTA has read the counter"
-            if (blockIdx.x == gridDim.x - 1) {
-                __threadfence_system();
-                for (int r = 0; r < p.peers.world; ++r)
-                    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" :: "l"(p.peers.flags[r] + p.peers.rank), "r"(peer_prev) : "memory");
-            }
-        }
-    }
     // (1) quantize the activations into shared memory while the rings fill. Each
     // group of 8 lanes owns 32-value blocks grp, grp + GROUPS, ...
     {
@@ -600,17 +644,6 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         named_bar_sync(1, (WARPS + PW) * 32);      // all consumers + the producer's arrive
     }
 
-    // Fused all-gather: lanes 0 .. world-1 of warp 0 look at the other GPUs' flags for the previous step now and
-    // then while the warp streams (relaxed loads whose latency nobody waits for); see the sending phase below.
-    bool peer_seen = !(PEERS && p.peers.world && p.peers.step_ctr && warp == 0 && lane < p.peers.world);
-    int peer_pending = peer_prev - 1;                      // value of the load issued by the previous poll
-    auto peer_poll = [&]() {
-        if (PEERS && !peer_seen) {
-            peer_seen = peer_pending - peer_prev >= 0;     // the previous poll's load has long returned
-            if (!peer_seen)
-                asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(peer_pending) : "l"(p.peers.flags[p.peers.rank] + lane) : "memory");
-        }
-    };
     // (2) stream this warp's (group's) units
     const int grp = warp / G, sub = warp - grp * G;
     Walker wk = walker_of(grp);
@@ -633,7 +666,6 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         for (; wk.template next<EXT>(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
-            peer_poll();
             const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
             int r = 0;
             for (; r + 2 <= un.nrows; r += 2) {                   // two weight rows at a time: independent chains
@@ -688,7 +720,6 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         for (; wk.template next<EXT>(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
-            peer_poll();
             const uint32_t base = ring + slot * p.slot_bytes;     // rows are 16-byte aligned here
             int r = 0;
             for (; r + 2 <= un.nrows; r += 2) {                   // two rows at a time: independent chains
@@ -728,7 +759,6 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         for (; wk.template next<EXT>(p, un); ++u) {
             const int slot = u % p.n_slots;
             if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
-            peer_poll();
             const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(un.src) & 15u);
             const int arow = p.per_seg_x ? un.seg : 0;
             const uint32_t act = act0 + arow * p.act_row_stride, isum = isum0 + arow * p.isum_row_stride;
@@ -755,43 +785,8 @@ __global__ void __launch_bounds__((WARPS + PW) * 32, 1) gemv_stream_kernel(const
         }
     }
     if (!ok && lane == 0) report_status(p.err, DEV_TIMEOUT_FULL);   // the producer drains the copies
-    if (PEERS && p.peers.world) {
-        // Fused all-gather, sending: the CTA's results are staged in shared memory; warp 0 writes the CTA's
-        // contiguous column range to every GPU in coalesced stores. No fence follows: the stores are
-        // complete when the grid is, and the NEXT launch (or the closing wait kernel) announces them.
-        named_bar_sync(3, WARPS * 32);                          // all consumer warps of this CTA have staged their results
-        if (warp == 0) {
-            // Before this step's slices go out, the previous step must be complete HERE: every GPU stores
-            // step s only after it has seen all of step s - 1, which is what makes two slots enough.
-            // Every GPU announces step s - 1 when its step-s kernel starts, i.e. when nothing on it reads the slot
-            // that step s is about to overwrite any more. Seeing that flag (a control dependency: the stores below
-            // do not start before the loads have returned) is what makes two slots enough. Normally all flags
-            // have been seen by the polls above.
-            for (uint32_t it = 0; it < (1u << 21) && !peer_seen; ++it) {
-                peer_poll();
-                if (!peer_seen && it > 64) __nanosleep(100);
-            }
-            if (!peer_seen) report_status(p.err, DEV_TIMEOUT_PEER);
-            __syncwarp();
-            const float* stage = reinterpret_cast<const float*>(smem + p.off_stage);
-            for (int m = 0; m < M; ++m) {
-                const size_t at = peer_slot_off + static_cast<size_t>(m) * p.peers.ld + p.peers.col0 + g0;
-                for (int i = lane; i < cta_rows; i += 32) {
-                    const float v = stage[m * p.stage_ld + i];
-                    for (int r = 0; r < p.peers.world; ++r) p.peers.y[r][at + i] = v;
-                }
-            }
-            // one thread of the grid advances the step counter, once every CTA has read the old value
-            if (blockIdx.x == 0 && lane == 0 && p.peers.step_ctr) {
-                bool all_read = false;
-                for (uint32_t it = 0; it < (1u << 21) && !all_read; ++it)
-                    all_read = *reinterpret_cast<volatile unsigned*>(p.peers.done_ctr) == gridDim.x;
-                if (!all_read) report_status(p.err, DEV_TIMEOUT_PEER);
-                *reinterpret_cast<volatile unsigned*>(p.peers.done_ctr) = 0u;
-                *reinterpret_cast<volatile int*>(p.peers.step_ctr) = peer_prev + 1;
-            }
-        }
-    }
+    // Fused all-gather: the results are staged in shared memory; the all-gather warp sends them.
+    if (PEERS && p.peers.world) asm volatile("bar.arrive 3, %0;" :: "r"((WARPS + 1) * 32) : "memory");
     // Let the next kernel in the stream start launching as this grid's SMs free up.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
@@ -833,7 +828,7 @@ cudaError_t launch_one(const KParams& p, dim3 grid, size_t smem, cudaStream_t st
     // x and the writes of y after that kernel's completion.
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3((WARPS + PW) * 32);
+    cfg.blockDim = dim3((WARPS + PW + (PEERS ? 1 : 0)) * 32);      // the fused all-gather has a warp of its own
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];

@@ -85,7 +85,7 @@ class PeerGather:
     def __init__(self, lib, shards: RowShards, M: int, group=None):
         self.L, self.sh, self.M, self.group = lib, shards, int(M), group
         world, rank, N = shards.world, shards.rank, shards.N
-        self.y_bytes = (2 * self.M * N * 4 + 255) & ~255
+        self.y_bytes = (4 * self.M * N * 4 + 255) & ~255      # four result slots
         self.total = self.y_bytes + 512                       # + flags[world] (256 B) + step / done counters (256 B)
         ptr = C.c_void_p()
         handle = (C.c_ubyte * 64)()
@@ -118,7 +118,7 @@ class PeerGather:
             raise RuntimeError(f"laplace_cuda error {rc}: {self.L.laplace_cuda_last_error().decode()}")
 
     def gemm(self, x: torch.Tensor, w: torch.Tensor, t: int, K: int, stream: int) -> None:
-        """Enqueues this rank's slice of y = W x; results land in slot (step & 1) of every rank's buffer."""
+        """Enqueues this rank's slice of y = W x; results land in slot (step & 3) of every rank's buffer."""
         sh = self.sh
         self._check(self.L.laplace_cuda_gemm_allgather_dev(x.data_ptr(), w.data_ptr(), int(t), self.peer_y, self.peer_flags,
                                                           self.step_ctr, self.done_ctr, sh.rank, sh.world, sh.begin, sh.N,
@@ -131,8 +131,8 @@ class PeerGather:
         self._check(self.L.laplace_cuda_allgather_wait_dev(self.peer_flags, self.step_ctr, self.sh.rank, self.sh.world, stream))
 
     def slot(self, which: int) -> torch.Tensor:
-        """Slot `which` (0 or 1) of this rank's result buffer as a [M, N] tensor; step s lands in slot s & 1."""
-        mem = _DevMem(self.own + (which & 1) * self.M * self.sh.N * 4, (self.M, self.sh.N), "<f4")
+        """Slot `which & 3` of this rank's result buffer as a [M, N] tensor; step s (counted from 1) lands in slot s & 3."""
+        mem = _DevMem(self.own + (which & 3) * self.M * self.sh.N * 4, (self.M, self.sh.N), "<f4")
         return torch.as_tensor(mem, device="cuda")
 
     def close(self) -> None:
