@@ -204,6 +204,45 @@ int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, i
 int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t type,
                                   float* y, int M, int K, int N, void* stream);
 
+/* ---- GGUF file -> HBM ------------------------------------------------------------------
+ * Replaces, for a GPU box, what GGUFContext::open (src/gguf.cpp:217-335) plus matmul_register_weights
+ * (src/matmul.h:26, src/main.cpp:705) do on the host: the file is mapped and its header, metadata and tensor
+ * table are parsed (GGUF v2 / v3); laplace_cuda_gguf_upload then copies, straight from the mapping, the part of
+ * every tensor that rank `rank` of `world` GPUs works on:
+ *   kind 2  stacked expert tensors (3 dims and more, dims = [K, rows, experts]): whole experts,
+ *           expert e on GPU e / ceil(experts / world)
+ *   kind 1  matrices (2 dims, at least 256 rows): the rows of laplace_cuda_nsplit(rows, rank, world)
+ *   kind 0  everything else, and every tensor named in `replicate` (e.g. the token embedding, which is read
+ *           by row index): the whole tensor
+ * Blocks keep the on-disk format, which is the matmul kernels' wire format (src/tensor.h:130-163). Opening and
+ * the tensor / metadata queries need no GPU; the upload needs laplace_cuda_init. The handle owns the mapping
+ * and one device allocation; `dev` pointers stay valid until laplace_cuda_gguf_close. */
+typedef struct laplace_cuda_gguf laplace_cuda_gguf;
+typedef struct {
+    const char*        name;
+    uint32_t           type;             /* ggml type id */
+    uint32_t           n_dims;
+    unsigned long long dims[4];          /* innermost first, as in the file; unused dims are 1 */
+    int                kind;             /* 0 whole tensor, 1 rows [row_begin, row_end), 2 experts [expert_begin, expert_end) */
+    unsigned long long row_begin, row_end;
+    unsigned long long expert_begin, expert_end;
+    unsigned long long file_offset;      /* of this rank's part */
+    unsigned long long bytes;            /* of this rank's part */
+    const void*        host;             /* the part inside the mapping */
+    void*              dev;              /* the part in HBM; NULL before laplace_cuda_gguf_upload */
+} laplace_cuda_gguf_tensor_info;
+int  laplace_cuda_gguf_open(const char* path, int rank, int world, const char* const* replicate, int n_replicate,
+                            laplace_cuda_gguf** out);
+int  laplace_cuda_gguf_upload(laplace_cuda_gguf* g);
+int  laplace_cuda_gguf_tensor_count(const laplace_cuda_gguf* g);
+/* By name when `name` is not NULL (LAPLACE_UNSUPPORTED = 1 when the file has no such tensor), else by index. */
+int  laplace_cuda_gguf_tensor(const laplace_cuda_gguf* g, int index, const char* name, laplace_cuda_gguf_tensor_info* info);
+/* Scalar metadata (general.alignment, llama.block_count, ...): 1 when the key is absent or of another kind. */
+int  laplace_cuda_gguf_meta_u64(const laplace_cuda_gguf* g, const char* key, unsigned long long* value);
+int  laplace_cuda_gguf_meta_f64(const laplace_cuda_gguf* g, const char* key, double* value);
+const char* laplace_cuda_gguf_meta_str(const laplace_cuda_gguf* g, const char* key);
+void laplace_cuda_gguf_close(laplace_cuda_gguf* g);
+
 /* ---- fused all-gather for the row-split (tensor-parallel) decode matmul ---------------
  * No reference counterpart (the reference is single-device). With a weight matrix split
  * along N over `world` GPUs, every GPU's GEMV stores its slice of y straight into EVERY

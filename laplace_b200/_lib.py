@@ -40,10 +40,26 @@ SYMBOLS = {
     "laplace_cuda_quantize_act_dev": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "laplace_cuda_debug_blocksums_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_debug_tensor_peak": (_i, [_i, C.POINTER(C.c_double)]),
+    "laplace_cuda_gguf_open": (_i, [C.c_char_p, _i, _i, C.POINTER(C.c_char_p), _i, C.POINTER(_vp)]),
+    "laplace_cuda_gguf_upload": (_i, [_vp]),
+    "laplace_cuda_gguf_tensor_count": (_i, [_vp]),
+    "laplace_cuda_gguf_tensor": (_i, [_vp, _i, C.c_char_p, _vp]),
+    "laplace_cuda_gguf_meta_u64": (_i, [_vp, C.c_char_p, C.POINTER(C.c_ulonglong)]),
+    "laplace_cuda_gguf_meta_f64": (_i, [_vp, C.c_char_p, C.POINTER(C.c_double)]),
+    "laplace_cuda_gguf_meta_str": (C.c_char_p, [_vp, C.c_char_p]),
+    "laplace_cuda_gguf_close": (None, [_vp]),
     "laplace_cuda_last_path": (_i, []),
     "laplace_cuda_launch_count": (C.c_longlong, [_i]),
 }
 
+
+
+class GgufTensorInfo(C.Structure):
+    """laplace_cuda_gguf_tensor_info."""
+    _fields_ = [("name", C.c_char_p), ("type", C.c_uint32), ("n_dims", C.c_uint32), ("dims", C.c_ulonglong * 4),
+                ("kind", C.c_int), ("row_begin", C.c_ulonglong), ("row_end", C.c_ulonglong),
+                ("expert_begin", C.c_ulonglong), ("expert_end", C.c_ulonglong), ("file_offset", C.c_ulonglong),
+                ("bytes", C.c_ulonglong), ("host", C.c_void_p), ("dev", C.c_void_p)]
 
 
 class Matrix(C.Structure):

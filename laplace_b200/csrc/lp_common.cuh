@@ -82,7 +82,7 @@ struct GemvArgs {
 // every GPU's full-width buffer through peer-mapped pointers, then raises a per-source step flag.
 constexpr int MAX_PEERS = 8;
 struct PeerOut {
-    float*    y[MAX_PEERS];      // every GPU's result buffer: [2 slots][M][ld], slot = step & 1
+    float*    y[MAX_PEERS];      // every GPU's result buffer: [4 slots][M][ld], slot = step & 3
     int*      flags[MAX_PEERS];  // every GPU's flag array [world]; GPU r writes entry r of each
     int*      step_ctr;          // this GPU's step counter; nullptr = no step protocol at all: the results are only
                                  // staged and written, coalesced, to y[0] (used for output in host-mapped memory)
