@@ -204,6 +204,26 @@ int laplace_cuda_moe_unpack_dev(const float* packed, int n_tokens, int hidden, i
 int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t type,
                                   float* y, int M, int K, int N, void* stream);
 
+/* ---- weight types without an int8 kernel, dequantize(), LM head ---------------------------
+ * laplace_cuda_gemm and laplace_cuda_gemm_dev also take F32 (0), F16 (1), BF16 (30), Q5_0 (6), Q2_K (10),
+ * Q3_K (11) and Q5_K (13) weights. For those the reference has no int8 kernel on this kind of host and computes
+ * y[m][j] = dot_row_<type>(x[m], row j) with fp32 activations (gemm_fallback, src/matmul.cpp:336-352); so does the
+ * library (activations are NOT quantized for these types). K must be a multiple of the type's block (16 for the
+ * plain types).
+ *
+ * laplace_cuda_dequantize_dev replaces dequantize(const Tensor&, float* dst, int n) (src/matmul.cpp:504-675) for
+ * every type above plus Q4_0 / Q8_0 / Q4_K / Q6_K, bit for bit (the reference's expressions, separate roundings);
+ * n = number of values, a multiple of the block size. laplace_cuda_embed_rows_dev is the token-embedding lookup of
+ * src/model.cpp:366-378: dst[m] = dequantize(row tokens[m]) * scale (scale = the model's embedding scale, 1 for most);
+ * a token id outside [0, vocab) is reported through laplace_cuda_sync like a bad expert index.
+ * laplace_cuda_lm_head_dev replaces matmul_lm_head (src/matmul.cpp:439-444) followed by the optional logit
+ * soft-cap of src/model.cpp:399-406 (softcap > 0: y = tanh(y / softcap) * softcap). */
+int laplace_cuda_dequantize_dev(const uint8_t* w, uint32_t type, float* dst, long long n, void* stream);
+int laplace_cuda_embed_rows_dev(const uint8_t* w, uint32_t type, const int* tokens, int M, int H, long long vocab, float scale,
+                                float* dst, void* stream);
+int laplace_cuda_lm_head_dev(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, float softcap,
+                             void* stream);
+
 /* ---- GGUF file -> HBM ------------------------------------------------------------------
  * Replaces, for a GPU box, what GGUFContext::open (src/gguf.cpp:217-335) plus matmul_register_weights
  * (src/matmul.h:26, src/main.cpp:705) do on the host: the file is mapped and its header, metadata and tensor

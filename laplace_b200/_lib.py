@@ -40,6 +40,9 @@ SYMBOLS = {
     "laplace_cuda_quantize_act_dev": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "laplace_cuda_debug_blocksums_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _vp]),
     "laplace_cuda_debug_tensor_peak": (_i, [_i, C.POINTER(C.c_double)]),
+    "laplace_cuda_dequantize_dev": (_i, [_vp, _u32, _vp, C.c_longlong, _vp]),
+    "laplace_cuda_embed_rows_dev": (_i, [_vp, _u32, _vp, _i, _i, C.c_longlong, C.c_float, _vp, _vp]),
+    "laplace_cuda_lm_head_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, C.c_float, _vp]),
     "laplace_cuda_gguf_open": (_i, [C.c_char_p, _i, _i, C.POINTER(C.c_char_p), _i, C.POINTER(_vp)]),
     "laplace_cuda_gguf_upload": (_i, [_vp]),
     "laplace_cuda_gguf_tensor_count": (_i, [_vp]),

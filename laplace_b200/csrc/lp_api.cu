@@ -140,6 +140,11 @@ int weights_on_device(const uint8_t* w, size_t bytes, uint32_t type, bool need_a
 
 int dispatch_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N,
                       cudaStream_t st) {
+    if (f32act_type(type)) {
+        // no int8 kernel in the reference for this type: fp32 activations against dequantized rows (its scalar path)
+        if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return fail(LAPLACE_ERR_ARG, "gemm: null pointer or M=%d K=%d N=%d", M, K, N);
+        return launch_gemm_f32act(x, w, type, y, M, K, N, st);
+    }
     if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
     if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm: null pointer");
     if (M <= 0 || N <= 0 || K <= 0) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
@@ -346,19 +351,20 @@ int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y,
     ProfScope prof(0);
     int rc = require_ready();
     if (rc) return rc;
-    if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
+    const bool other = f32act_type(type);
+    if (!other && !block_elems(type)) return LAPLACE_UNSUPPORTED;
     if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm: null pointer");
-    if (M <= 0 || N <= 0 || K <= 0 || K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
+    if (M <= 0 || N <= 0 || K <= 0 || K % (other ? any_block_elems(type) : block_elems(type))) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
     cudaStream_t st = g_ctx.stream;
     const uint8_t* dw = nullptr;
-    if ((rc = weights_on_device(w, static_cast<size_t>(N) * row_bytes(type, K), type, false, &dw))) return rc;
+    if ((rc = weights_on_device(w, static_cast<size_t>(N) * (other ? any_row_bytes(type, K) : row_bytes(type, K)), type, type == 0, &dw))) return rc;
     const size_t xb = sizeof(float) * static_cast<size_t>(M) * K, yb = sizeof(float) * static_cast<size_t>(M) * N;
     if ((rc = g_hx.ensure(xb)) || (rc = g_hy.ensure(yb)) || (rc = g_dx.ensure(xb)) || (rc = g_dy.ensure(yb))) return rc;
     std::memcpy(g_hx.p, x, xb);
     cudaMemcpyAsync(g_dx.p, g_hx.p, xb, cudaMemcpyHostToDevice, st);
     // Decode calls: the kernel writes y straight into the pinned host buffer (which the device can address) in
     // coalesced stores from its epilogue, so no device-to-host copy has to be queued behind it.
-    const bool direct = M <= 8 && static_cast<size_t>(M) * (static_cast<size_t>(N) / g_ctx.sm_count + 256) * sizeof(float) < 40 * 1024;
+    const bool direct = !other && M <= 8 && static_cast<size_t>(M) * (static_cast<size_t>(N) / g_ctx.sm_count + 256) * sizeof(float) < 40 * 1024;
     if (direct) {
         PeerOut po{};
         po.y[0] = static_cast<float*>(g_hy.p);
@@ -392,6 +398,29 @@ int laplace_cuda_gemm_dev(const float* x, const uint8_t* w, uint32_t type, float
     int rc = require_ready();
     if (rc) return rc;
     return dispatch_gemm_dev(x, w, type, y, M, K, N, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_dequantize_dev(const uint8_t* w, uint32_t type, float* dst, long long n, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    return launch_dequantize(w, type, dst, n, 1.0f, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_embed_rows_dev(const uint8_t* w, uint32_t type, const int* tokens, int M, int H, long long vocab, float scale,
+                                float* dst, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    return launch_embed_rows(w, type, tokens, M, H, vocab, scale, dst, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_lm_head_dev(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, float softcap,
+                             void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream;
+    if ((rc = dispatch_gemm_dev(x, w, type, y, M, K, N, st))) return rc;
+    if (softcap > 0.0f) return launch_softcap(y, static_cast<long long>(M) * N, softcap, st);
+    return LAPLACE_OK;
 }
 
 int laplace_cuda_gemm_multi_dev(const float* x, const float* norm_weight, float norm_eps, float* x_norm_out,

@@ -92,6 +92,16 @@ struct PeerOut {
     int       col0;              // first column of this GPU's slice
 };
 int launch_gemv_stream(const GemvArgs& a, cudaStream_t st);
+// weight types served with fp32 activations (the reference's scalar path), dequantize() and friends (lp_types.cu)
+bool   f32act_type(uint32_t type);
+bool   dequant_type(uint32_t type);
+size_t any_row_bytes(uint32_t type, long long K);
+int    any_block_elems(uint32_t type);
+int launch_gemm_f32act(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st);
+int launch_dequantize(const uint8_t* w, uint32_t type, float* dst, long long n, float scale, cudaStream_t st);
+int launch_embed_rows(const uint8_t* w, uint32_t type, const int* tokens, int M, int H, long long vocab, float scale, float* dst,
+                      cudaStream_t st);
+int launch_softcap(float* y, long long n, float cap, cudaStream_t st);
 int launch_allgather_wait(const PeerOut& po, cudaStream_t st);
 
 // Tensor-core prefill GEMM with the activation scales folded into the operand (lp_gemm_sa.cu): Q4_0, Q8_0, Q4_K, Q6_K

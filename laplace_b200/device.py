@@ -10,7 +10,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .ggml import blocksums_per_row, row_bytes
+from .ggml import any_row_bytes, blocksums_per_row, row_bytes
 from .matmul import LaplaceCudaError, _check
 
 _ready_on = None
@@ -51,7 +51,7 @@ def upload_weights(w: np.ndarray) -> torch.Tensor:
 def gemm(x: torch.Tensor, w: torch.Tensor, t: int, M: int, K: int, N: int, y: torch.Tensor | None = None) -> torch.Tensor:
     L = lib()
     assert x.dtype == torch.float32 and x.is_cuda and x.is_contiguous() and x.numel() >= M * K
-    assert w.dtype == torch.uint8 and w.is_cuda and w.numel() >= N * row_bytes(t, K)
+    assert w.dtype == torch.uint8 and w.is_cuda and w.numel() >= N * any_row_bytes(t, K)
     if y is None:
         y = torch.empty((M, N), dtype=torch.float32, device=x.device)
     _check(L, L.laplace_cuda_gemm_dev(x.data_ptr(), w.data_ptr(), int(t), y.data_ptr(), M, K, N, _stream()))
@@ -188,6 +188,31 @@ def debug_blocksums(x: torch.Tensor, w: torch.Tensor, t: int, M: int, K: int, N:
     out = torch.empty((M, N, blocksums_per_row(t, K)), dtype=torch.int32, device=x.device)
     _check(L, L.laplace_cuda_debug_blocksums_dev(x.data_ptr(), w.data_ptr(), int(t), out.data_ptr(), M, K, N, _stream()))
     return out
+
+
+def dequantize(w: torch.Tensor, t: int, n: int) -> torch.Tensor:
+    """dequantize(w, dst, n) of src/matmul.cpp:504 on device blocks."""
+    dst = torch.empty(n, dtype=torch.float32, device=w.device)
+    L = lib()
+    _check(L, L.laplace_cuda_dequantize_dev(w.data_ptr(), int(t), dst.data_ptr(), n, _stream()))
+    return dst
+
+
+def embed_rows(w: torch.Tensor, t: int, tokens: torch.Tensor, H: int, vocab: int, scale: float = 1.0) -> torch.Tensor:
+    """Token-embedding lookup (src/model.cpp:366-378): rows tokens[m] of the table, dequantized, times scale."""
+    M = tokens.numel()
+    dst = torch.empty((M, H), dtype=torch.float32, device=w.device)
+    L = lib()
+    _check(L, L.laplace_cuda_embed_rows_dev(w.data_ptr(), int(t), tokens.data_ptr(), M, H, vocab, float(scale), dst.data_ptr(), _stream()))
+    return dst
+
+
+def lm_head(x: torch.Tensor, w: torch.Tensor, t: int, M: int, K: int, N: int, softcap: float = 0.0) -> torch.Tensor:
+    """matmul_lm_head (src/matmul.cpp:439) plus the optional logit soft-cap (src/model.cpp:399-406)."""
+    y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    L = lib()
+    _check(L, L.laplace_cuda_lm_head_dev(x.data_ptr(), w.data_ptr(), int(t), y.data_ptr(), M, K, N, float(softcap), _stream()))
+    return y
 
 
 def sync() -> None:

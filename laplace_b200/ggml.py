@@ -14,7 +14,10 @@ class GGMLType(enum.IntEnum):
     Q4_0 = 2
     Q5_0 = 6
     Q8_0 = 8
+    Q2_K = 10
+    Q3_K = 11
     Q4_K = 12
+    Q5_K = 13
     Q6_K = 14
     BF16 = 30
 
@@ -26,7 +29,19 @@ _GEOM = {
     GGMLType.Q6_K: (256, 210),
 }
 
-SUPPORTED = tuple(_GEOM)
+SUPPORTED = tuple(_GEOM)          # the types with an int8 path (Q8 activations)
+
+# every type the library takes: the four above, and those served with fp32 activations / dequantized only
+# (elements and bytes per block, Laplace src/tensor.h:41-100)
+ALL_GEOM = dict(_GEOM)
+ALL_GEOM.update({GGMLType.F32: (1, 4), GGMLType.F16: (1, 2), GGMLType.BF16: (1, 2), GGMLType.Q5_0: (32, 22),
+                 GGMLType.Q2_K: (256, 84), GGMLType.Q3_K: (256, 110), GGMLType.Q5_K: (256, 176)})
+F32_ACTIVATION_TYPES = (GGMLType.F32, GGMLType.F16, GGMLType.BF16, GGMLType.Q5_0, GGMLType.Q2_K, GGMLType.Q3_K, GGMLType.Q5_K)
+
+
+def any_row_bytes(t: int, K: int) -> int:
+    e, b = ALL_GEOM[GGMLType(t)]
+    return K // e * b
 
 
 def block_elems(t: int) -> int:

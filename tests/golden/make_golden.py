@@ -1,4 +1,4 @@
-"""Regenerates tests/golden/hotpath_golden.npz. Run where the reference checkout is present:
+"""Regenerates tests/golden/hotpath_golden.npz, lossless_golden.npz and other_types_golden.npz. Run where the reference checkout is present:
 
     make -C oracle all ref && python tests/golden/make_golden.py
 
@@ -72,6 +72,7 @@ def main():
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes")
     lossless(r)
+    other_types(r)
 
 
 # Reference-build outputs for activations that Q8 represents exactly (tests.synth.lossless_q8_activations): with
@@ -94,6 +95,23 @@ def lossless(r):
         out[f"l{i}_meta"] = np.array([t, M, K, N, ws, xs], dtype=np.int64)
         out[f"l{i}_ref_y"] = r.matmul_rows(x, w, t, M, K, N)
     path = Path(__file__).with_name("lossless_golden.npz")
+    np.savez_compressed(path, **out)
+    print(path, path.stat().st_size, "bytes")
+
+
+# Reference-build outputs for the weight types outside the int8 path and for dequantize() of every type
+# (other_types_golden.npz): weight bytes, dequantized values, and matmul_rows (scalar path, fp32 activations).
+def other_types(r):
+    K, N, M = 512, 24, 3
+    out = {"K": np.array(K), "x": synth.normal_f32(8801, (M, K))}
+    for t in (0, 1, 30, 6, 10, 11, 13, 2, 8, 12, 14):
+        w = synth.other_type_weights(t, K, N, seed=8810 + t) if t in (0, 1, 30, 6, 10, 11, 13) else synth.weights(t, K, N, seed=8810 + t, how="random")
+        w = np.ascontiguousarray(w)
+        out[f"w_{t}"] = w
+        out[f"deq_{t}"] = r.dequantize(w, t, N * K)
+        if t in (0, 1, 30, 6, 10, 11, 13):
+            out[f"y_{t}"] = r.matmul_rows(out["x"], w, t, M, K, N)
+    path = Path(__file__).with_name("other_types_golden.npz")
     np.savez_compressed(path, **out)
     print(path, path.stat().st_size, "bytes")
 

@@ -352,3 +352,30 @@ def single_live_block(t: int, K: int, N: int, seed: int, live: int):
     scales[:, 8 * half + 2 * gq + 1] = live_sc[:, 1]
     blk[:, sb, 192:208] = scales.view(np.uint8)
     return w, x, live_sc.astype(np.float32)
+
+
+# ---- weight types that are served with fp32 activations / only dequantized (F32, F16, BF16, Q5_0, Q2_K, Q3_K, Q5_K)
+_OTHER_GEOM = {0: (1, 4), 1: (1, 2), 30: (1, 2), 6: (32, 22), 10: (256, 84), 11: (256, 110), 13: (256, 176)}
+_OTHER_SCALE_FIELDS = {6: (0,), 10: (80, 82), 11: (108,), 13: (0, 2)}        # byte offsets of the fp16 scales in a block
+
+
+def other_type_weights(t: int, K: int, N: int, seed: int) -> np.ndarray:
+    """[N, row_bytes] uint8: random blocks of a type outside the int8 path, fp16 scale fields set to small positive
+    values (random bytes there would be NaNs and infinities), plain types filled with N(0, 0.02^2) values."""
+    t = int(t)
+    g = rng(seed)
+    if t in (0, 1, 30):
+        v = (g.standard_normal((N, K)) * 0.02).astype(np.float32)
+        if t == 0:
+            return v.view(np.uint8).reshape(N, K * 4)
+        if t == 1:
+            return v.astype(np.float16).view(np.uint8).reshape(N, K * 2)
+        return (v.view(np.uint32) >> 16).astype(np.uint16).view(np.uint8).reshape(N, K * 2)
+    e, b = _OTHER_GEOM[t]
+    nb = K // e
+    w = g.integers(0, 256, size=(N, nb, b), dtype=np.uint8)
+    for off in _OTHER_SCALE_FIELDS[t]:
+        d = (g.uniform(0.001, 0.05, size=(N, nb))).astype(np.float16).view(np.uint16)
+        w[:, :, off] = (d & 0xFF).astype(np.uint8)
+        w[:, :, off + 1] = (d >> 8).astype(np.uint8)
+    return w.reshape(N, nb * b)
