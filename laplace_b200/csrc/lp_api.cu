@@ -354,6 +354,8 @@ int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type, float* y,
     const bool other = f32act_type(type);
     if (!other && !block_elems(type)) return LAPLACE_UNSUPPORTED;
     if (!x || !w || !y) return fail(LAPLACE_ERR_ARG, "gemm: null pointer");
+    // F32 / F16 / BF16 rows are walked 16 values at a time; another K is left to the caller's scalar path
+    if (other && (type == 0 || type == 1 || type == 30) && K > 0 && K % 16) return LAPLACE_UNSUPPORTED;
     if (M <= 0 || N <= 0 || K <= 0 || K % (other ? any_block_elems(type) : block_elems(type))) return fail(LAPLACE_ERR_ARG, "gemm: M=%d K=%d N=%d", M, K, N);
     cudaStream_t st = g_ctx.stream;
     const uint8_t* dw = nullptr;

@@ -278,7 +278,10 @@ int any_block_elems(uint32_t type) {
 int launch_gemm_f32act(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, cudaStream_t st) {
     if (!f32act_type(type)) return LAPLACE_UNSUPPORTED;
     const Geo g = geo_of(type);
-    if (K % g.elems) return fail(LAPLACE_ERR_ARG, "gemm: K=%d is not a multiple of %d for type %u", K, g.elems, type);
+    if (K % g.elems) {
+        if (type == T_F32 || type == T_F16 || type == T_BF16) return LAPLACE_UNSUPPORTED;      // rows are walked 16 values at a time
+        return fail(LAPLACE_ERR_ARG, "gemm: K=%d is not a multiple of %d for type %u", K, g.elems, type);
+    }
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & (type == T_F32 ? 15 : 1)))
         return fail(LAPLACE_ERR_ARG, "gemm: x must be 16-byte aligned, weights 2-byte (F32: 16-byte) aligned");
     Context& c = ctx();

@@ -86,6 +86,7 @@ def matmul_unregister_weights(base: np.ndarray) -> None:
 def matmul_rows(x: np.ndarray, w: Tensor, y: np.ndarray, M: int, K: int, N: int) -> None:
     """``matmul_rows`` (src/matmul.cpp:408-433): y[m*N+j] = dot(x[m], row j of w)."""
     lib = _ensure_init()
+    x = np.ascontiguousarray(x, dtype=np.float32) if not (isinstance(x, np.ndarray) and x.flags.c_contiguous) else x
     _f32(x, M * K, "x")
     _f32(y, M * N, "y")
     d = _u8(w, N * row_bytes(w.type, K)) if int(w.type) in (2, 8, 12, 14) else w.data

@@ -142,8 +142,11 @@ def test_unsupported_type_and_bad_args():
     y = np.zeros((1, 4), dtype=np.float32)
     w = np.zeros((4, 2048), dtype=np.uint8)
     with pytest.raises(lb.LaplaceCudaError) as e:
-        lb.matmul_rows(x, lb.Tensor(GGMLType.F32, w), y, 1, 512, 4)
+        lb.matmul_rows(x, lb.Tensor(3, w), y, 1, 512, 4)          # Q4_1: no kernel in the reference either
     assert e.value.code == 1                   # "not handled": the reference would fall back to scalar
+    with pytest.raises(lb.LaplaceCudaError) as e:
+        lb.matmul_rows(x[:, :500], lb.Tensor(GGMLType.F32, w), y, 1, 500, 4)      # plain rows are walked 16 values at a time
+    assert e.value.code == 1
     # K not a multiple of the block: rejected by the library itself (device-pointer call)
     import torch
     from laplace_b200 import device
