@@ -57,14 +57,28 @@ __device__ __forceinline__ void decode16(uint32_t type, const uint8_t* __restric
             for (int i = 0; i < 4; ++i) { const float4 t = __ldg(p + i); v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w; }
             break;
         }
-        case T_F16: {
+        case T_F16: case T_BF16: {
+            // 32 bytes; two 16-byte loads when the group is 16-byte aligned (rows of K % 16 == 0 values at an aligned base)
+            uint32_t wds[8];
+            if ((reinterpret_cast<uintptr_t>(b) & 15) == 0) {
+                const uint4 a = __ldg(reinterpret_cast<const uint4*>(b)), c = __ldg(reinterpret_cast<const uint4*>(b) + 1);
+                wds[0] = a.x; wds[1] = a.y; wds[2] = a.z; wds[3] = a.w; wds[4] = c.x; wds[5] = c.y; wds[6] = c.z; wds[7] = c.w;
+            } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = h16(b + 2 * i);
-            break;
-        }
-        case T_BF16: {
+                for (int i = 0; i < 8; ++i)
+                    wds[i] = static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(b + 4 * i)) |
+                             (static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(b + 4 * i + 2)) << 16);
+            }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(b + 2 * i)) << 16);
+            for (int i = 0; i < 8; ++i) {
+                if (type == T_F16) {
+                    v[2 * i] = __half2float(__ushort_as_half(static_cast<unsigned short>(wds[i] & 0xffffu)));
+                    v[2 * i + 1] = __half2float(__ushort_as_half(static_cast<unsigned short>(wds[i] >> 16)));
+                } else {
+                    v[2 * i] = __uint_as_float(wds[i] << 16);
+                    v[2 * i + 1] = __uint_as_float(wds[i] & 0xffff0000u);
+                }
+            }
             break;
         }
         case T_Q4_0: {
