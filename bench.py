@@ -533,7 +533,7 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
     (BASELINE.json configs[3]); q/k/v/o/gate/up are Q4_K, down is Q6_K. Reported beside the headline.
     With more than one GPU every projection is split along N (laplace_cuda_nsplit) and the [512, N/G] slices are
     all-gathered with NCCL inside the timed region; times are the maximum over ranks."""
-    from laplace_b200.shard import RowShards
+    from laplace_b200.shard import PeerGather, RowShards
     M = 512
     projs = [("q", 12, 4096, 4096), ("k", 12, 4096, 1024), ("v", 12, 4096, 1024), ("o", 12, 4096, 4096),
              ("gate", 12, 4096, 14336), ("up", 12, 4096, 14336), ("down", 14, 14336, 4096)]
@@ -550,15 +550,25 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
         w = device.upload_weights(w_loc_np)
         y = torch.empty((M, sh.n_loc), dtype=torch.float32, device="cuda")
         y_full = torch.empty((M, N), dtype=torch.float32, device="cuda") if world > 1 else None
+        # N > 1: the GEMM's drain stores this rank's slice into every rank's [M, N] buffer (peer stores), one closing
+        # kernel announces the step and waits for the others; kernel + NCCL all-gather is the cross-check
+        pg = PeerGather(L, sh, M) if world > 1 else None
 
         def run():
-            device.gemm(xs[K], w, t, M, K, sh.n_loc, y=y)
             if world > 1:
-                sh.gather(y, y_full)
+                assert pg.gemm_peers(xs[K], w, t, K, device._stream())
+                pg.step_wait(device._stream())
+            else:
+                device.gemm(xs[K], w, t, M, K, sh.n_loc, y=y)
 
         for _ in range(3):
             run()
         path = L.laplace_cuda_last_path()
+        if world > 1:
+            device.gemm(xs[K], w, t, M, K, sh.n_loc, y=y)
+            sh.gather(y, y_full)
+            torch.cuda.synchronize()
+            assert torch.equal(pg.slot(0), y_full), f"prefill {name}: peer-store result differs from kernel + NCCL all-gather"
         iters = 10 if path == 2 else 3
         torch.cuda.synchronize()
         # parity gate on the tensors that are timed (this rank's slice)
@@ -595,6 +605,8 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
         total_ms += ms
         total_ops += ops
         del w
+        if pg is not None:
+            pg.close()
     device.sync()
     peak_bf16 = 1628.3
     p = ROOT / "MEASURED_PEAKS.json"
@@ -610,7 +622,7 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
     assert L.laplace_cuda_debug_tensor_peak(0, _C.byref(peak_f16)) == 0, L.laplace_cuda_last_error()
     layer_tops = total_ops / total_ms / 1e9
     return {"workload": "Llama-3-8B decoder layer, 7 projections, M=512 tokens (223.34 Gop)" +
-                        ("" if world == 1 else f", N-split over {world} GPUs + NCCL all-gather of the [512, N/{world}] slices"),
+                        ("" if world == 1 else f", N-split over {world} GPUs, every GEMM storing its [512, N/{world}] slice into all GPUs' buffers (peer stores) + one closing wait kernel"),
             "ms_per_layer": total_ms,
             "tops": total_ops / total_ms / 1e9, "q4k_only_tops": q4k_ops / q4k_ms / 1e9,
             "roofline": {"bound": "tensor", "achieved": layer_tops / world, "peak": peak_i8.value, "unit": "Top/s (per GPU)",

@@ -224,6 +224,19 @@ int laplace_cuda_embed_rows_dev(const uint8_t* w, uint32_t type, const int* toke
 int laplace_cuda_lm_head_dev(const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N, float softcap,
                              void* stream);
 
+/* ---- row-split prefill: the GEMM stores into every GPU's buffer --------------------------
+ * laplace_cuda_gemm_peers_dev is laplace_cuda_gemm_dev for M > 8 over a weight matrix split along N: this GPU's
+ * n_local columns of y go, from the kernel's own drain, to every GPU's row-major [M][n_total] buffer at column
+ * row_begin (plain stores to peer-mapped memory allocated with laplace_cuda_peer_alloc; no collective, no copy
+ * afterwards). LAPLACE_UNSUPPORTED for shapes the tensor-core kernels do not take (M <= 8, K not a multiple of 256).
+ * The stores are complete when the call's kernels are; laplace_cuda_allgather_step_wait_dev, enqueued next, advances
+ * this GPU's step counter, announces the step to every GPU and waits (bounded) until every GPU has announced it:
+ * after it, all slices are in this GPU's buffer. Every gemm_peers call must be followed by that call before its
+ * buffers are read or written again on any GPU. */
+int laplace_cuda_gemm_peers_dev(const float* x, const uint8_t* w, uint32_t type, float* const* peer_y, int world,
+                                int row_begin, int n_total, int M, int K, int n_local, void* stream);
+int laplace_cuda_allgather_step_wait_dev(int* const* peer_flags, int* step_counter, int rank, int world, void* stream);
+
 /* ---- GGUF file -> HBM ------------------------------------------------------------------
  * Replaces, for a GPU box, what GGUFContext::open (src/gguf.cpp:217-335) plus matmul_register_weights
  * (src/matmul.h:26, src/main.cpp:705) do on the host: the file is mapped and its header, metadata and tensor

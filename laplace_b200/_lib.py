@@ -35,6 +35,8 @@ SYMBOLS = {
     "laplace_cuda_peer_free": (_i, [_vp]),
     "laplace_cuda_gemm_allgather_dev": (_i, [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "laplace_cuda_allgather_wait_dev": (_i, [_vp, _vp, _i, _i, _vp]),
+    "laplace_cuda_gemm_peers_dev": (_i, [_vp, _vp, _u32, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "laplace_cuda_allgather_step_wait_dev": (_i, [_vp, _vp, _i, _i, _vp]),
     "laplace_cuda_moe_pack_dev": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "laplace_cuda_moe_unpack_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "laplace_cuda_quantize_act_dev": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -574,6 +574,37 @@ int laplace_cuda_gemm_allgather_dev(const float* x, const uint8_t* w, uint32_t t
     return launch_gemv_stream(a, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
 }
 
+int laplace_cuda_gemm_peers_dev(const float* x, const uint8_t* w, uint32_t type, float* const* peer_y, int world,
+                                int row_begin, int n_total, int M, int K, int n_local, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!x || !w || !peer_y) return fail(LAPLACE_ERR_ARG, "gemm_peers: null pointer");
+    if (world < 1 || world > MAX_PEERS || M < 1 || n_local <= 0 || K <= 0 || row_begin < 0 || row_begin + n_local > n_total)
+        return fail(LAPLACE_ERR_ARG, "gemm_peers: world=%d M=%d K=%d rows [%d,%d) of %d", world, M, K, row_begin, row_begin + n_local, n_total);
+    if (!gemm_sa_supports(type, M, K, n_local)) return LAPLACE_UNSUPPORTED;
+    PeerOut po{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_y[r]) return fail(LAPLACE_ERR_ARG, "gemm_peers: null peer pointer %d", r);
+        po.y[r] = peer_y[r];
+    }
+    po.world = world; po.ld = n_total; po.col0 = row_begin;
+    return launch_gemm_sa_peers(x, w, type, po, M, K, n_local, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+}
+
+int laplace_cuda_allgather_step_wait_dev(int* const* peer_flags, int* step_counter, int rank, int world, void* stream) {
+    int rc = require_ready();
+    if (rc) return rc;
+    if (!peer_flags || !step_counter || world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return fail(LAPLACE_ERR_ARG, "allgather_step_wait: bad argument");
+    PeerOut po{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_flags[r]) return fail(LAPLACE_ERR_ARG, "allgather_step_wait: null peer pointer %d", r);
+        po.flags[r] = peer_flags[r];
+    }
+    po.step_ctr = step_counter; po.world = world; po.rank = rank;
+    return launch_allgather_wait(po, stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream, true);
+}
+
 int laplace_cuda_allgather_wait_dev(int* const* peer_flags, int* step_counter, int rank, int world, void* stream) {
     int rc = require_ready();
     if (rc) return rc;

@@ -102,7 +102,8 @@ int launch_dequantize(const uint8_t* w, uint32_t type, float* dst, long long n, 
 int launch_embed_rows(const uint8_t* w, uint32_t type, const int* tokens, int M, int H, long long vocab, float scale, float* dst,
                       cudaStream_t st);
 int launch_softcap(float* y, long long n, float cap, cudaStream_t st);
-int launch_allgather_wait(const PeerOut& po, cudaStream_t st);
+int launch_allgather_wait(const PeerOut& po, cudaStream_t st, bool advance = false);
+int launch_gemm_sa_peers(const float* x, const uint8_t* w, uint32_t type, const PeerOut& po, int M, int K, int N, cudaStream_t st);
 
 // Tensor-core prefill GEMM with the activation scales folded into the operand (lp_gemm_sa.cu): Q4_0, Q8_0, Q4_K, Q6_K
 // with M > 8 and K % 256 == 0. Uses library-owned scratch for the quantized activations, or the caller's.

@@ -97,6 +97,10 @@ struct SaParams {
     // [TT tokens][TW rows] floats) which a second kernel adds up in k order. 0 units: whole tiles, dealt round-robin.
     long long    sk_units;
     float*       y_part;
+    // Row-split over several GPUs: the tile goes to row-major [M][peer_ld] buffers of EVERY GPU at column peer_col0 + n
+    // (plain stores to peer-mapped memory; complete when the grid is) instead of to y. 0 peers: y.
+    float*       peer_y[MAX_PEERS];
+    int          n_peers, peer_ld, peer_col0;
 };
 
 struct TileRef { int m0, n0, wrow0, nt, sb0, sb1, part; };     // nt = tokens of the tile; part = slot of a partial result or -1
@@ -434,7 +438,15 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         int orow = p.out_row ? __ldg(p.out_row + row) : row;
                         if (p.out_identity && orow >= 0) orow = row;
                         const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-                        if (orow >= 0) p.y[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
+                        if (orow >= 0) {
+                            const float out = v * __ldg(p.inv_s + row);
+                            if (p.n_peers == 0) {
+                                p.y[static_cast<size_t>(orow) * p.N + n] = out;
+                            } else {
+                                const size_t at = static_cast<size_t>(orow) * p.peer_ld + p.peer_col0 + n;
+                                for (int r = 0; r < p.n_peers; ++r) p.peer_y[r][at] = out;
+                            }
+                        }
                     }
                 }
             }
@@ -847,7 +859,15 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                         int orow = p.out_row ? __ldg(p.out_row + row) : row;
                         if (p.out_identity && orow >= 0) orow = row;
                         const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-                        if (orow >= 0) p.y[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
+                        if (orow >= 0) {
+                            const float out = v * __ldg(p.inv_s + row);
+                            if (p.n_peers == 0) {
+                                p.y[static_cast<size_t>(orow) * p.N + n] = out;
+                            } else {
+                                const size_t at = static_cast<size_t>(orow) * p.peer_ld + p.peer_col0 + n;
+                                for (int r = 0; r < p.n_peers; ++r) p.peer_y[r][at] = out;
+                            }
+                        }
                     }
                 }
             }
@@ -949,8 +969,9 @@ __global__ void __launch_bounds__(256) quantize_sa_kernel(const float* __restric
 
 // Adds up the pieces of every output tile that the balanced split cut, in k order, and writes the tile to y.
 // Block (t, j) handles 16 tokens of output tile t; a tile one CTA computed whole is already in y.
+struct FixupOut { float* y; float* peer_y[MAX_PEERS]; int n_peers, peer_ld, peer_col0; };
 __global__ void __launch_bounds__(256) sk_fixup_kernel(const float* __restrict__ part, long long units, int grid, int nsb, int tiles_m,
-                                                       int M, int N, float* __restrict__ y) {
+                                                       int M, int N, const FixupOut out) {
     const int t = blockIdx.x;
     const long long ua = static_cast<long long>(t) * nsb, ub = ua + nsb - 1;
     // the CTA that holds unit u is the largest c with sk_start(c) <= u
@@ -982,7 +1003,14 @@ __global__ void __launch_bounds__(256) sk_fixup_kernel(const float* __restrict__
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int col = col0 + 2 * j;
-        if (col < nt) y[static_cast<size_t>(m0 + col) * N + n0 + wr] = a[j];
+        if (col < nt) {
+            if (out.n_peers == 0) {
+                out.y[static_cast<size_t>(m0 + col) * N + n0 + wr] = a[j];
+            } else {
+                const size_t at = static_cast<size_t>(m0 + col) * out.peer_ld + out.peer_col0 + n0 + wr;
+                for (int r = 0; r < out.n_peers; ++r) out.peer_y[r][at] = a[j];
+            }
+        }
     }
 }
 
@@ -1039,6 +1067,7 @@ struct SaLaunch {
     const int4* tile_tab; const int* n_tiles_dev; const int* out_row; int out_identity;
     int tiles_m, tiles_n, grid;
     long long sk_units; float* y_part;
+    const PeerOut* peers;        // nullptr, or: the result goes to every GPU's buffer
 };
 
 int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
@@ -1067,6 +1096,10 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
     p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n;
     p.tile_tab = L.tile_tab; p.n_tiles_dev = L.n_tiles_dev; p.out_row = L.out_row; p.out_identity = L.out_identity;
     p.sk_units = L.sk_units; p.y_part = L.y_part;
+    if (L.peers) {
+        for (int r = 0; r < L.peers->world; ++r) p.peer_y[r] = L.peers->y[r];
+        p.n_peers = L.peers->world; p.peer_ld = L.peers->ld; p.peer_col0 = L.peers->col0;
+    }
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_q4k_sa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
@@ -1149,7 +1182,7 @@ int check_args(const float* x, const uint8_t* w, uint32_t type, int M, int K, in
 
 // Quantizes x into `scratch` (device memory of at least pl.total() bytes, 256-byte aligned) and runs the kernel.
 int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const uint8_t* w, uint32_t type, float* y, int M, int K, int N,
-                       cudaStream_t st) {
+                       cudaStream_t st, const PeerOut* peers = nullptr) {
     Context& c = ctx();
     int rc;
     uint8_t* s = scratch;
@@ -1161,11 +1194,18 @@ int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const
     L.w = w; L.type = type; L.y = y; L.M = M; L.K = K; L.N = N; L.w_rows = N; L.op = op;
     L.tiles_m = pl.tiles_m; L.tiles_n = pl.tiles_n;
     L.sk_units = pl.sp.units;
+    L.peers = peers;
     L.y_part = pl.sp.units ? reinterpret_cast<float*>(s) : nullptr;
     L.grid = pl.sp.grid;
     if ((rc = run_sa_kernel(L, st))) return rc;
     if (pl.sp.units) {
-        sk_fixup_kernel<<<dim3(pl.tiles_m * pl.tiles_n, TT / 16), 256, 0, st>>>(L.y_part, pl.sp.units, pl.sp.grid, K / 256, pl.tiles_m, M, N, y);
+        FixupOut fo{};
+        fo.y = y;
+        if (peers) {
+            for (int r = 0; r < peers->world; ++r) fo.peer_y[r] = peers->y[r];
+            fo.n_peers = peers->world; fo.peer_ld = peers->ld; fo.peer_col0 = peers->col0;
+        }
+        sk_fixup_kernel<<<dim3(pl.tiles_m * pl.tiles_n, TT / 16), 256, 0, st>>>(L.y_part, pl.sp.units, pl.sp.grid, K / 256, pl.tiles_m, M, N, fo);
         c.launches++;
         return cuda_check(cudaGetLastError(), "sk_fixup launch");
     }
@@ -1181,6 +1221,17 @@ int launch_gemm_sa(const float* x, const uint8_t* w, uint32_t type, float* y, in
     const SaPlan pl = plan_sa(M, K, N, true);
     if ((rc = g_scratch.ensure(pl.total(), st))) return rc;
     return gemm_sa_on_scratch(static_cast<uint8_t*>(g_scratch.p), pl, x, w, type, y, M, K, N, st);
+}
+
+// The same call for a row-split matrix: this GPU's N columns of the result go to every GPU's [M][ld] buffer at column col0
+// (see SaParams::peer_y). The stores are complete when the launched kernels are; announcing them to the other GPUs is
+// the caller's next step (laplace_cuda_allgather_step_wait_dev).
+int launch_gemm_sa_peers(const float* x, const uint8_t* w, uint32_t type, const PeerOut& po, int M, int K, int N, cudaStream_t st) {
+    int rc = check_args(x, w, type, M, K, N);
+    if (rc) return rc;
+    const SaPlan pl = plan_sa(M, K, N, true);
+    if ((rc = g_scratch.ensure(pl.total(), st))) return rc;
+    return gemm_sa_on_scratch(static_cast<uint8_t*>(g_scratch.p), pl, x, w, type, nullptr, M, K, N, st, &po);
 }
 
 // The same call on scratch memory the caller owns (`cap` bytes at `scratch`, 256-byte aligned); nothing is

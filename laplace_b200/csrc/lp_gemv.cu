@@ -795,10 +795,17 @@ __global__ void __launch_bounds__((WARPS + PW + (PEERS ? 1 : 0)) * 32, 1) gemv_s
 // since this kernel runs after the GEMV that stored them) to every GPU, then waits (bounded) until every
 // source's flag has reached this GPU's step: all slices of the step are in this GPU's buffer.
 // One warp; lane r talks to GPU r.
-__global__ void allgather_wait_kernel(PeerOut po, int* err) {
+// advance = 1: the step being closed is a NEW one whose slices were stored by kernels that do not run the step protocol
+// themselves (the prefill GEMM with peer stores): the counter is advanced here first.
+__global__ void allgather_wait_kernel(PeerOut po, int* err, int advance) {
     const int r = threadIdx.x;
+    int step = 0;
+    if (r == 0) {
+        step = *reinterpret_cast<volatile const int*>(po.step_ctr) + advance;
+        if (advance) *reinterpret_cast<volatile int*>(po.step_ctr) = step;
+    }
+    step = __shfl_sync(0xffffffffu, step, 0);
     if (r >= po.world) return;
-    const int step = *reinterpret_cast<volatile const int*>(po.step_ctr);
     __threadfence_system();
     asm volatile("st.relaxed.sys.global.s32 [%0], %1;" :: "l"(po.flags[r] + po.rank), "r"(step) : "memory");
     for (uint32_t it = 0; it < (1u << 21); ++it) {
@@ -1020,10 +1027,10 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     return cuda_check(e, "gemv_stream launch");
 }
 
-int launch_allgather_wait(const PeerOut& po, cudaStream_t st) {
+int launch_allgather_wait(const PeerOut& po, cudaStream_t st, bool advance) {
     Context& c = ctx();
     if (po.world < 1 || po.world > MAX_PEERS) return fail(LAPLACE_ERR_ARG, "allgather_wait: %d peers", po.world);
-    allgather_wait_kernel<<<1, 32, 0, st>>>(po, c.d_err);
+    allgather_wait_kernel<<<1, 32, 0, st>>>(po, c.d_err, advance ? 1 : 0);
     c.launches++;
     return cuda_check(cudaGetLastError(), "allgather_wait launch");
 }

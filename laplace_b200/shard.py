@@ -130,6 +130,22 @@ class PeerGather:
         (bounded) wait for all ranks' slices."""
         self._check(self.L.laplace_cuda_allgather_wait_dev(self.peer_flags, self.step_ctr, self.sh.rank, self.sh.world, stream))
 
+    def gemm_peers(self, x: torch.Tensor, w: torch.Tensor, t: int, K: int, stream: int) -> bool:
+        """Prefill (M > 8): this rank's slice of y = W x goes to slot 0 of every rank's buffer from the GEMM's own drain
+        (laplace_cuda_gemm_peers_dev). False when the tensor-core kernels do not take the shape (nothing was enqueued).
+        Must be followed by step_wait before the buffers are read or written again."""
+        sh = self.sh
+        rc = self.L.laplace_cuda_gemm_peers_dev(x.data_ptr(), w.data_ptr(), int(t), self.peer_y, sh.world, sh.begin, sh.N,
+                                                self.M, K, sh.n_loc, stream)
+        if rc == 1:
+            return False
+        self._check(rc)
+        return True
+
+    def step_wait(self, stream: int) -> None:
+        """Advances this rank's step, announces it to every rank and enqueues the (bounded) wait for all ranks' slices."""
+        self._check(self.L.laplace_cuda_allgather_step_wait_dev(self.peer_flags, self.step_ctr, self.sh.rank, self.sh.world, stream))
+
     def slot(self, which: int) -> torch.Tensor:
         """Slot `which & 3` of this rank's result buffer as a [M, N] tensor; step s (counted from 1) lands in slot s & 3."""
         mem = _DevMem(self.own + (which & 3) * self.M * self.sh.N * 4, (self.M, self.sh.N), "<f4")

@@ -47,6 +47,25 @@ def _worker(rank, world, port, out_dir):
                 device.sync()
                 ok = ok and bool(torch.equal(pg.slot(step), want))
         pg.close()
+    # prefill: the GEMM's drain stores every rank's slice into every rank's buffer; bit-identical to one GPU computing
+    # the whole matrix (an N-split does not change any dot's summation... per tile; compared at the tests' tolerance)
+    for t, M, K, N in [(GGMLType.Q4_K, 200, 1024, 1024), (GGMLType.Q6_K, 72, 2048, 400), (GGMLType.Q4_K, 512, 4096, 4096)]:
+        w = synth.weights(t, K, N, seed=830 + M, how="random")
+        sh = RowShards(L, N, rank, world)
+        w_loc = device.upload_weights(np.ascontiguousarray(sh.slice_rows(w)))
+        w_all = device.upload_weights(w)
+        pg = PeerGather(L, sh, M)
+        for rep in range(2):
+            x = torch.from_numpy(synth.normal_f32(840 + rep, (M, K))).cuda()
+            ok = ok and pg.gemm_peers(x, w_loc, t, K, device._stream())
+            pg.step_wait(device._stream())
+            device.sync()
+            want = device.gemm(x, w_all, t, M, K, N)
+            device.sync()
+            got = pg.slot(0)
+            rel = float((got - want).norm() / want.norm())
+            ok = ok and rel <= 1e-5
+        pg.close()
     with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
         f.write("1" if ok else "0")
     dist.barrier()

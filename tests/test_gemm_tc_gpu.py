@@ -170,3 +170,24 @@ def test_scratch_growth_is_refused_during_stream_capture(oracle):
         g2.replay()
     device.sync()
     check_close(y.cpu().numpy(), oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), "captured prefill call")
+
+
+def test_peer_store_form_on_one_gpu(oracle):
+    """laplace_cuda_gemm_peers_dev with a world of one: the drain (and the fix-up of tiles the balanced split cut) writes
+    into the rank's own peer buffer; the closing kernel advances and announces the step."""
+    import torch
+    from laplace_b200 import device
+    from laplace_b200.shard import PeerGather, RowShards
+    L = device.lib()
+    for t, M, K, N in ((GGMLType.Q4_K, 200, 1024, 1160), (GGMLType.Q6_K, 40, 2048, 136), (GGMLType.Q4_K, 512, 4096, 1024)):
+        w = synth.weights(t, K, N, seed=2300 + M, how="random")
+        x = synth.normal_f32(2301 + M, (M, K))
+        pg = PeerGather(L, RowShards(L, N, 0, 1), M)
+        try:
+            for rep in range(2):
+                assert pg.gemm_peers(torch.from_numpy(x).cuda(), device.upload_weights(w), t, K, device._stream())
+                pg.step_wait(device._stream())
+                device.sync()
+                check_close(pg.slot(0).cpu().numpy(), oracle.gemm(x, w, t, M, K, N, mode=1, threads=THREADS), f"peer-store GEMM {t.name} {M}x{K}x{N}")
+        finally:
+            pg.close()
