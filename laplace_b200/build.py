@@ -17,7 +17,7 @@ CSRC = PKG / "csrc"
 ROOT = PKG.parent
 LIB = PKG / "liblaplace_cuda.so"
 
-SOURCES = ["lp_api.cu", "lp_gemv.cu", "lp_quantize.cu", "lp_gemm_sa.cu", "lp_peak.cu", "lp_gguf.cu", "lp_types.cu"]
+SOURCES = ["lp_api.cu", "lp_gemv.cu", "lp_quantize.cu", "lp_gemm_sa.cu", "lp_peak.cu", "lp_gguf.cu", "lp_types.cu", "lp_gemv_mma.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -92,6 +92,7 @@ struct PeerOut {
     int       col0;              // first column of this GPU's slice
 };
 int launch_gemv_stream(const GemvArgs& a, cudaStream_t st);
+int launch_gemv_mma_q4k(const float* x, const uint8_t* w, float* y, int M, int K, int N, cudaStream_t st);
 // weight types served with fp32 activations (the reference's scalar path), dequantize() and friends (lp_types.cu)
 bool   f32act_type(uint32_t type);
 bool   dequant_type(uint32_t type);
