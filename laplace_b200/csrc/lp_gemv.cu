@@ -905,9 +905,10 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     if (a.type == LAPLACE_TYPE_Q4_K && (w_bits & 15))
         return fail(LAPLACE_ERR_ARG, "gemv: Q4_K weights must be 16-byte aligned on the device");
 
-    // 5..8 activation rows against a plain Q4_K matrix: the integer block sums on mma.sync (lp_gemv_mma.cu; measured
-    // 20.8 us against 25-31.5 us of the dp4a kernel at 4096 x 14336; below five rows the dp4a kernel is the faster one)
-    if (a.type == LAPLACE_TYPE_Q4_K && a.M >= 5 && !a.expert_idx && !a.peers && !a.n_mats && !a.norm_w && a.n_seg == 1 && a.K % 256 == 0) {
+    // 3..8 activation rows against a plain Q4_K matrix: the integer block sums on mma.sync (lp_gemv_mma.cu; measured
+    // 15.1 us whatever the row count against 16.7 / 18.2 / 31.5 us of the dp4a kernel at 3 / 4 / 8 rows, 4096 x 14336; with
+    // two rows the dp4a kernel's 11.4 us win)
+    if (a.type == LAPLACE_TYPE_Q4_K && a.M >= 3 && !a.expert_idx && !a.peers && !a.n_mats && !a.norm_w && a.n_seg == 1 && a.K % 256 == 0) {
         const int rc = launch_gemv_mma_q4k(a.x, a.w, a.y, a.M, a.K, a.N, st);
         if (rc != LAPLACE_UNSUPPORTED) return rc;
     }

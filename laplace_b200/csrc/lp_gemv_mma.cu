@@ -1,4 +1,4 @@
-// lp_gemv_mma.cu - decode GEMV for 5..8 activation rows (the kernel takes 2..8), Q4_K weights: the integer block sums on the warp-level
+// lp_gemv_mma.cu - decode GEMV for 3..8 activation rows (the kernel takes 2..8), Q4_K weights: the integer block sums on the warp-level
 // int8 tensor-core instruction.
 //
 // gemm_int<dot_row_q4_k_int_neon> (Laplace src/matmul_simd.cpp:226-283, 432-455) with a handful of activation rows
@@ -10,17 +10,20 @@
 //   - one persistent CTA per SM: a producer warp copies groups of 16 weight rows (whole rows for K <= 4096, 16
 //     super-blocks of every row otherwise) into a ring of shared-memory slots, one bulk copy per row, rows staggered by
 //     16 bytes so that the fragment loads below meet no bank conflicts;
-//   - the activations are quantized once per CTA into shared memory exactly as the reference does (ActQ8: d = amax /
-//     127 in fp32, q = rne(x * (1 / d)), sums from the unclamped integers);
+//   - the activations are quantized ONCE per call by a small kernel exactly as the reference does (ActQ8: d = amax /
+//     127 in fp32, q = rne(x * (1 / d)), sums from the unclamped integers) into an image of the shared-memory layout
+//     in device memory, which every CTA then fetches with two bulk copies (quantizing all rows in every CTA cost 3.4 to
+//     8.3 us per launch: two IEEE divisions per block, 148 times over);
 //   - sixteen consumer warps share every 16-row group, each taking every sixteenth super-block: A fragment = masked nibbles
 //     (u8), B fragment = activations (s8), C = the sixteen-by-eight integer block sums, bit for bit the reference's;
 //     the fp32 scale chain follows in the reference's order ((d * sc) * d_x) * U and (dmin * m) * sum_x;
 //   - the warps' partial results of a group meet in shared memory and are added in warp order.
 // Every wait is bounded; a wait that gives up raises the status word and the CTA drains its copies and leaves.
-// Measured at 4096 x 14336: 16.8-17.2 us for 2-4 rows, 20.8 us for 5-8 (dp4a kernel: 11.3 / 18.1 / 31.5 us at 2 / 4 / 8
-// rows). Where the time goes (ablations): every CTA quantizing all rows costs 3.4 us (<= 4 rows) to 8.3 us (8 rows),
-// streaming without arithmetic 8 us, the arithmetic adds 5.6 us that the streaming does not hide - a warp has one
-// super-block per 16-row group between a barrier wait and a CTA-wide hand-over, too little to cover latencies.
+// Measured at 4096 x 14336: 15.1-15.2 us for any row count (quantizer launch included), against 11.4 / 16.7 / 18.2 / 31.5 us
+// of the dp4a kernel at 2 / 3 / 4 / 8 rows. History of the figure: 20.8-21.7 us with every CTA quantizing all rows itself
+// (3.4 us at <= 4 rows, 8.3 us at 8) and with each block's loads, MMA, shuffles and fp32 chain issued one after the other
+// (the arithmetic then added 5.6 us that the 8 us of streaming did not hide); 17.2 us before the consumer warps went from
+// eight to sixteen.
 #include "lp_common.cuh"
 
 namespace lp {
@@ -44,12 +47,43 @@ struct MmaParams {
     uint32_t       rb;             // bytes per weight row
     uint32_t       act_stride;     // bytes per quantized activation row in shared memory (K + 16)
     uint32_t       off_act, off_ds, off_part, off_ring;
+    const uint8_t* act_img;        // [8][act_stride] int8 then [K / 32][8] (d, d * sum): written by quantize_rows_kernel
+    uint32_t       act_bytes, ds_bytes;
 };
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+constexpr int MAX_K = 16384;
+// The quantized activations of the call in flight (one per device; calls on different streams would race for it).
+__device__ __align__(128) uint8_t g_act_img[MAXM * (MAX_K + 16) + (MAX_K / 32) * MAXM * 8];
+
+// int8 values [8][K + 16] (rows M..7 zero) and per block and row (d, d * sum), 8 lanes per 32-value block.
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restrict__ x, int M, int K, uint32_t act_stride,
+                                                            uint8_t* __restrict__ img) {
+    const int bpr = K >> 5, nblk = MAXM * bpr;
+    uint8_t* ds = img + MAXM * act_stride;
+    const int t8 = threadIdx.x & 7;
+    for (int base = blockIdx.x * 32; base < nblk; base += gridDim.x * 32) {      // whole warps iterate together
+        const int b = base + (threadIdx.x >> 3);
+        const bool inside = b < nblk;
+        const int m = inside ? b / bpr : 0, kb = inside ? b - m * bpr : 0;
+        const bool live = inside && m < M;
+        const float4 v = live ? __ldg(reinterpret_cast<const float4*>(x + static_cast<size_t>(m) * K + kb * 32) + t8) : make_float4(0.f, 0.f, 0.f, 0.f);
+        uint32_t packed; int hs;
+        const float d = quantize_block_8lanes(v, packed, hs);
+        const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
+        if (inside) {
+            *reinterpret_cast<uint32_t*>(img + m * act_stride + kb * 32 + t8 * 4) = live ? packed : 0u;
+            if (t8 == 0) {
+                const int isum = static_cast<int>(static_cast<short>(hs)) + static_cast<int>(static_cast<short>(hs_hi));
+                *reinterpret_cast<float2*>(ds + (static_cast<size_t>(kb) * MAXM + m) * 8) = live ? make_float2(d, d * static_cast<float>(isum)) : make_float2(0.f, 0.f);
+            }
+        }
+    }
 }
 
 __global__ void __launch_bounds__(THREADS, 1) gemv_mma_q4k_kernel(const MmaParams p) {
@@ -64,9 +98,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_q4k_kernel(const MmaParam
     const int n_units = (g_end - g_begin) * n_slices;
     auto bar_full = [&](int s) { return sbase + 8 * s; };
     auto bar_empty = [&](int s) { return sbase + 64 + 8 * s; };
+    const uint32_t bar_act = sbase + 48;                   // full barriers use 0..31, empty barriers 64..95
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.n_slots; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), CW); }
+        mbar_init(bar_act, 1);
         fence_barrier_init();
     }
     __syncthreads();
@@ -111,55 +147,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_q4k_kernel(const MmaParam
     // x may be produced, and y read, by the kernel before this one in the stream (the weights are not, so the producer
     // starts at once)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // (1) quantize the activation rows into shared memory: int8 values [m][K] and per block and row (d, d * sum)
-    {
-        const int bpr = p.K >> 5, nblk = p.M * bpr;
-        const int grp = threadIdx.x >> 3, t8 = threadIdx.x & 7;
-        constexpr int GROUPS8 = CW * 4;
-        constexpr int PF = 8;                                       // loads in flight per thread
-        // Every CTA reads all of x. Each starts at another block, so that at any moment the 148 CTAs ask the L2 for
-        // different lines instead of all for the same ones.
-        const int span = (nblk + PF * GROUPS8 - 1) / (PF * GROUPS8) * (PF * GROUPS8);
-        const int shift = static_cast<int>((static_cast<long long>(blockIdx.x) * span) / gridDim.x) & ~7;
-        auto rot = [&](int i) { int b = i + shift; return b >= span ? b - span : b; };
-        for (int base0 = 0; base0 < nblk; base0 += PF * GROUPS8) {  // whole warps iterate together
-            float4 v[PF];
-#pragma unroll
-            for (int i = 0; i < PF; ++i) {
-                const int b = rot(base0 + i * GROUPS8 + grp);
-                const int m = b < nblk ? b / bpr : 0, kb = b < nblk ? b - m * bpr : 0;
-                v[i] = b < nblk ? __ldg(reinterpret_cast<const float4*>(p.x + static_cast<size_t>(m) * p.K + kb * 32) + t8)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int i = 0; i < PF; ++i) {
-                const int b = rot(base0 + i * GROUPS8 + grp);
-                const bool live = b < nblk;
-                const int m = live ? b / bpr : 0, kb = live ? b - m * bpr : 0;
-                uint32_t packed; int hs;
-                const float d = quantize_block_8lanes(v[i], packed, hs);
-                const int hs_hi = __shfl_down_sync(0xffffffffu, hs, 4);
-                if (live) {
-                    *reinterpret_cast<uint32_t*>(smem + p.off_act + m * p.act_stride + kb * 32 + t8 * 4) = packed;
-                    if (t8 == 0) {
-                        const int isum = static_cast<int>(static_cast<short>(hs)) + static_cast<int>(static_cast<short>(hs_hi));
-                        *reinterpret_cast<float2*>(smem + p.off_ds + (static_cast<size_t>(kb) * MAXM + m) * 8) =
-                            make_float2(d, d * static_cast<float>(isum));
-                    }
-                }
-            }
-        }
-        // rows M..7 of the B operand are zeros, their scales too
-        for (int i = threadIdx.x; i < (MAXM - p.M) * (p.K / 4); i += CW * 32) {
-            const int m = p.M + i / (p.K / 4), k4 = i % (p.K / 4);
-            *reinterpret_cast<uint32_t*>(smem + p.off_act + m * p.act_stride + k4 * 4) = 0u;
-        }
-        for (int i = threadIdx.x; i < (MAXM - p.M) * bpr; i += CW * 32) {
-            const int m = p.M + i / bpr, kb = i % bpr;
-            *reinterpret_cast<float2*>(smem + p.off_ds + (static_cast<size_t>(kb) * MAXM + m) * 8) = make_float2(0.f, 0.f);
-        }
-        named_bar_sync(1, CW * 32);
+    // (1) the quantized activation rows (written by quantize_rows_kernel, the launch before this one) into shared memory
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(bar_act, p.act_bytes + p.ds_bytes);
+        bulk_g2s(sbase + p.off_act, p.act_img, p.act_bytes, bar_act);
+        bulk_g2s(sbase + p.off_ds, p.act_img + p.act_bytes, p.ds_bytes, bar_act);
     }
+    if (!mbar_wait_bounded(bar_act, 0)) { if (lane == 0) report_status(p.err, DEV_TIMEOUT_FULL); return; }
 
     // (2) the units. Fragment coordinates of this lane: weight rows gq and gq + 8 of the group, activation rows
     // 2 tq and 2 tq + 1 (C), activation row gq (B), k bytes 4 tq .. 4 tq + 3 and 16 + 4 tq .. (A and B).
@@ -189,35 +183,45 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_q4k_kernel(const MmaParam
                 dsc[r][1] = d * static_cast<float>((b_hi & 0xF) | ((b_lo >> 6) << 4));
                 dmn[r][1] = dmin * static_cast<float>((b_hi >> 4) | ((b_mid >> 6) << 4));
             }
+            // The super-block in phases - every load, then the eight MMAs, then shuffles and the fp32 chain - so that each
+            // kind of latency is paid once per super-block, not once per block.
+            uint32_t wa[8], wb[8], bq[16];
+            uint4 ds[8];
 #pragma unroll
             for (int jb = 0; jb < 4; ++jb) {                        // 64-value chunk: low nibbles, then high nibbles
-                const uint32_t wa0 = lds32(blk_a + 16 + 32 * jb + 4 * tq), wa1 = lds32(blk_a + 32 + 32 * jb + 4 * tq);
-                const uint32_t wb0 = lds32(blk_b + 16 + 32 * jb + 4 * tq), wb1 = lds32(blk_b + 32 + 32 * jb + 4 * tq);
+                wa[2 * jb] = lds32(blk_a + 16 + 32 * jb + 4 * tq); wa[2 * jb + 1] = lds32(blk_a + 32 + 32 * jb + 4 * tq);
+                wb[2 * jb] = lds32(blk_b + 16 + 32 * jb + 4 * tq); wb[2 * jb + 1] = lds32(blk_b + 32 + 32 * jb + 4 * tq);
+            }
 #pragma unroll
-                for (int hi = 0; hi < 2; ++hi) {
-                    const int j = 2 * jb + hi;                      // sub-block of the super-block
-                    const int bx = sb * 8 + j;                      // activation block
-                    const uint32_t a[4] = {(wa0 >> (4 * hi)) & 0x0f0f0f0fu, (wb0 >> (4 * hi)) & 0x0f0f0f0fu,
-                                           (wa1 >> (4 * hi)) & 0x0f0f0f0fu, (wb1 >> (4 * hi)) & 0x0f0f0f0fu};
-                    const uint32_t act = sbase + p.off_act + gq * p.act_stride + bx * 32 + 4 * tq;
-                    const uint32_t b0 = lds32(act), b1 = lds32(act + 16);
-                    int c[4];
-                    mma_u8s8(c, a, b0, b1);
-                    // the block's weight scales live in lane (gq, j & 3), first or second value
-                    const int src = (lane & ~3) | (j & 3);
-                    const float sa = __shfl_sync(0xffffffffu, dsc[0][j >> 2], src), sb_ = __shfl_sync(0xffffffffu, dsc[1][j >> 2], src);
-                    const float ma = __shfl_sync(0xffffffffu, dmn[0][j >> 2], src), mb = __shfl_sync(0xffffffffu, dmn[1][j >> 2], src);
-                    const uint4 ds = lds128(sbase + p.off_ds + (static_cast<uint32_t>(bx) * MAXM + 2 * tq) * 8);      // (d, sum) of rows 2 tq, 2 tq + 1
-                    const float d0 = __uint_as_float(ds.x), s0 = __uint_as_float(ds.y), d1 = __uint_as_float(ds.z), s1 = __uint_as_float(ds.w);
-                    acc[0] = fmaf(sa * d0, static_cast<float>(c[0]), acc[0]);
-                    acc[1] = fmaf(sa * d1, static_cast<float>(c[1]), acc[1]);
-                    acc[2] = fmaf(sb_ * d0, static_cast<float>(c[2]), acc[2]);
-                    acc[3] = fmaf(sb_ * d1, static_cast<float>(c[3]), acc[3]);
-                    accm[0] = fmaf(ma, s0, accm[0]);
-                    accm[1] = fmaf(ma, s1, accm[1]);
-                    accm[2] = fmaf(mb, s0, accm[2]);
-                    accm[3] = fmaf(mb, s1, accm[3]);
-                }
+            for (int j = 0; j < 8; ++j) {
+                const int bx = sb * 8 + j;                          // activation block
+                const uint32_t act = sbase + p.off_act + gq * p.act_stride + bx * 32 + 4 * tq;
+                bq[2 * j] = lds32(act); bq[2 * j + 1] = lds32(act + 16);
+                ds[j] = lds128(sbase + p.off_ds + (static_cast<uint32_t>(bx) * MAXM + 2 * tq) * 8);      // (d, sum) of rows 2 tq, 2 tq + 1
+            }
+            int c[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {                           // sub-block j: chunk j / 2, low or high nibbles
+                const int jb = j >> 1, hi = j & 1;
+                const uint32_t a[4] = {(wa[2 * jb] >> (4 * hi)) & 0x0f0f0f0fu, (wb[2 * jb] >> (4 * hi)) & 0x0f0f0f0fu,
+                                       (wa[2 * jb + 1] >> (4 * hi)) & 0x0f0f0f0fu, (wb[2 * jb + 1] >> (4 * hi)) & 0x0f0f0f0fu};
+                mma_u8s8(c[j], a, bq[2 * j], bq[2 * j + 1]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                // the block's weight scales live in lane (gq, j & 3), first or second value
+                const int src = (lane & ~3) | (j & 3);
+                const float sa = __shfl_sync(0xffffffffu, dsc[0][j >> 2], src), sb_ = __shfl_sync(0xffffffffu, dsc[1][j >> 2], src);
+                const float ma = __shfl_sync(0xffffffffu, dmn[0][j >> 2], src), mb = __shfl_sync(0xffffffffu, dmn[1][j >> 2], src);
+                const float d0 = __uint_as_float(ds[j].x), s0 = __uint_as_float(ds[j].y), d1 = __uint_as_float(ds[j].z), s1 = __uint_as_float(ds[j].w);
+                acc[0] = fmaf(sa * d0, static_cast<float>(c[j][0]), acc[0]);
+                acc[1] = fmaf(sa * d1, static_cast<float>(c[j][1]), acc[1]);
+                acc[2] = fmaf(sb_ * d0, static_cast<float>(c[j][2]), acc[2]);
+                acc[3] = fmaf(sb_ * d1, static_cast<float>(c[j][3]), acc[3]);
+                accm[0] = fmaf(ma, s0, accm[0]);
+                accm[1] = fmaf(ma, s1, accm[1]);
+                accm[2] = fmaf(mb, s0, accm[2]);
+                accm[3] = fmaf(mb, s1, accm[3]);
             }
         }
         __syncwarp();
@@ -254,7 +258,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_q4k_kernel(const MmaParam
 // (the caller falls back to the dp4a kernel).
 int launch_gemv_mma_q4k(const float* x, const uint8_t* w, float* y, int M, int K, int N, cudaStream_t st) {
     Context& c = ctx();
-    if (M < 2 || M > MAXM || K <= 0 || K % 256 || N <= 0) return LAPLACE_UNSUPPORTED;
+    if (M < 2 || M > MAXM || K <= 0 || K % 256 || K > MAX_K || N <= 0) return LAPLACE_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return LAPLACE_UNSUPPORTED;
     MmaParams p{};
     p.x = x; p.w = w; p.y = y; p.err = c.d_err; p.M = M; p.K = K; p.N = N;
@@ -277,6 +281,25 @@ int launch_gemv_mma_q4k(const float* x, const uint8_t* w, float* y, int M, int K
         cudaError_t e = cudaFuncSetAttribute(gemv_mma_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(c.smem_optin));
         if (e != cudaSuccess) return cuda_check(e, "cudaFuncSetAttribute gemv_mma");
         configured = true;
+    }
+    static uint8_t* img_of[64] = {};                         // the array's address on every device this process has used
+    if (c.device < 0 || c.device >= 64) return LAPLACE_UNSUPPORTED;
+    if (!img_of[c.device]) {
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&img_of[c.device]), g_act_img);
+        if (e != cudaSuccess) { img_of[c.device] = nullptr; return cuda_check(e, "cudaGetSymbolAddress g_act_img"); }
+    }
+    uint8_t* img = img_of[c.device];
+    p.act_img = img;
+    p.act_bytes = MAXM * p.act_stride;
+    p.ds_bytes = static_cast<uint32_t>(K / 32) * MAXM * 8;
+    {
+        const int nblk = MAXM * (K / 32);
+        int qgrid = (nblk + 31) / 32;
+        if (qgrid > 2 * c.sm_count) qgrid = 2 * c.sm_count;
+        quantize_rows_kernel<<<qgrid, 256, 0, st>>>(x, M, K, p.act_stride, img);
+        c.launches++;
+        const int rc = cuda_check(cudaGetLastError(), "quantize_rows launch");
+        if (rc) return rc;
     }
     const int groups = (N + GROUP - 1) / GROUP;
     const int grid = groups < c.sm_count ? groups : c.sm_count;
