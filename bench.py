@@ -328,6 +328,36 @@ def gpu_arm(args):
         repeats += 1
     launches_eager = L.laplace_cuda_launch_count(0)
     device.sync()
+    # N > 1, fused form: the figure above is pipelined throughput (one closing wait per chain of steps). In a
+    # tensor-parallel decode the y of a step feeds the next one, so every step needs its wait: the same steps with the
+    # closing kernel after each of them, reported beside the headline as the latency of a dependent step.
+    dependent_us = None
+    if fused:
+        n_dep = min(steps, 128)
+        gdep = torch.cuda.CUDAGraph()
+        s2 = torch.cuda.Stream()
+        s2.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s2):
+            with torch.cuda.graph(gdep, stream=s2):
+                for i in range(n_dep):
+                    step(i)
+                    finish()
+        torch.cuda.current_stream().wait_stream(s2)
+        gdep.replay()
+        dep = []
+        for _ in range(5):
+            barrier()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            gdep.replay()
+            ev1.record()
+            barrier()
+            t = torch.tensor([ev0.elapsed_time(ev1)], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dep.append(float(t.item()))
+        dependent_us = statistics.median(dep) / n_dep * 1e3
+        del gdep
+        device.sync()
     ms_total = statistics.median(times)
     ms_step = ms_total / steps
     value = WEIGHT_BYTES / (ms_step * 1e-3) / 1e9
@@ -384,6 +414,10 @@ def gpu_arm(args):
                     "how": "laplace_cuda_gemm with host x and y, synchronous, weights registered (resident) as at model load"},
             "parity": parity,
             **({"note": gather_note} if gather_note else {}),
+            **({"dependent_step": {"us_per_step": dependent_us, "value_gbs": WEIGHT_BYTES / dependent_us / 1e3,
+                                   "how": "the same steps with the closing wait kernel after EVERY step (the y of a step is complete on "
+                                          "every GPU before the next step starts); `value` above is the pipelined figure with one wait per chain"}}
+               if dependent_us else {}),
             "gpu_launches": (steps + 1 if fused else steps) if use_graph else int(launches_eager // max(repeats, 1)),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved if achieved else value / world, "peak": peak, "unit": "GB/s",

@@ -83,6 +83,14 @@ int laplace_cuda_unregister_weights(const void* base);
  * reference is single-device). */
 void laplace_cuda_nsplit(int N, int rank, int world, int* row_begin, int* row_end);
 
+/* Scratch memory and CUDA graphs. laplace_cuda_gemm_dev (more than 8 activation rows), laplace_cuda_moe_grouped_dev,
+ * laplace_cuda_moe_ffn_dev and laplace_cuda_gemm_peers_dev keep their quantized operands in scratch buffers that grow to
+ * the largest call seen. A buffer that was handed to a launch is never freed before laplace_cuda_shutdown (a captured
+ * graph may hold its address), but growing calls the allocator, which is illegal while the call's stream is being
+ * captured: such a call returns LAPLACE_ERR_STATE and leaves the capture valid. Make every call shape once before
+ * capturing it. Calls that share a scratch buffer must not overlap on the GPU (one stream, or the caller's own
+ * ordering). laplace_cuda_gemm_dev with 3 to 8 rows of Q4_K uses a fixed array inside the library in the same way. */
+
 /* ---- the three back-end entry points (host pointers) -------------------- */
 
 /* Replaces kernels::gemm_fn (src/kernels.h:97), implemented in the reference
