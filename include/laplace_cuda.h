@@ -125,7 +125,9 @@ int laplace_cuda_moe_gemv_dev(const float* x, const uint8_t* w, uint32_t type,
  * after the FFN norm - it quantizes x_norm again for every matrix). Here x is normalised (norm_weight != NULL:
  * x_norm = x * 1/sqrt(mean(x^2) + norm_eps) * norm_weight, fp32) and quantized ONCE inside the kernel's prologue and
  * every matrix streams past it: y_i[m*N_i + j] = dot(quantize(x_norm[m]), row j of matrix i). x_norm_out (optional)
- * receives the normalised rows [M][K]. M <= 8 (decode); 1..8 matrices. Device pointers. */
+ * receives the normalised rows [M][K]. 1..8 matrices. Device pointers. With M <= 8 (decode) everything is one launch;
+ * with more rows (prefill; K a multiple of 256) one quantizer launch normalises and quantizes the rows once and every
+ * matrix then runs as a tensor-core GEMM on that shared operand. */
 typedef struct { const uint8_t* w; float* y; int N; } laplace_cuda_matrix;
 int laplace_cuda_gemm_multi_dev(const float* x, const float* norm_weight, float norm_eps, float* x_norm_out,
                                 const laplace_cuda_matrix* mats, int n_mats, uint32_t type, int M, int K, void* stream);

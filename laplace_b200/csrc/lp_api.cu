@@ -432,9 +432,18 @@ int laplace_cuda_gemm_multi_dev(const float* x, const float* norm_weight, float 
     if (!block_elems(type)) return LAPLACE_UNSUPPORTED;
     if (!x || !mats || n_mats <= 0 || n_mats > 8) return fail(LAPLACE_ERR_ARG, "gemm_multi: null pointer or %d matrices (1..8)", n_mats);
     if (M <= 0 || K <= 0 || K % block_elems(type)) return fail(LAPLACE_ERR_ARG, "gemm_multi: M=%d K=%d", M, K);
-    if (M > 8) return fail(LAPLACE_ERR_ARG, "gemm_multi: M=%d: this entry serves decode (M <= 8); for prefill call laplace_cuda_gemm_dev per matrix", M);
     const uint8_t* ws[8]; float* ys[8]; int ns[8];
     for (int i = 0; i < n_mats; ++i) { ws[i] = mats[i].w; ys[i] = mats[i].y; ns[i] = mats[i].N; }
+    if (M > 8) {
+        // prefill: one (normalising) quantizer launch, then the tensor-core GEMM per matrix on the shared operand
+        for (int i = 0; i < n_mats; ++i) {
+            if (!ws[i] || !ys[i] || ns[i] <= 0) return fail(LAPLACE_ERR_ARG, "gemm_multi: matrix %d: null pointer or no rows", i);
+            if (!gemm_sa_supports(type, M, K, ns[i]))
+                return fail(LAPLACE_ERR_ARG, "gemm_multi: M=%d K=%d: prefill calls need K to be a multiple of 256", M, K);
+        }
+        return launch_gemm_sa_multi(x, norm_weight, norm_eps, x_norm_out, ws, ys, ns, n_mats, type, M, K,
+                                    stream ? static_cast<cudaStream_t>(stream) : g_ctx.stream);
+    }
     GemvArgs a{};
     a.x = x; a.type = type; a.M = M; a.K = K; a.n_seg = 1;
     a.n_mats = n_mats; a.mat_w = ws; a.mat_y = ys; a.mat_n = ns;

@@ -104,6 +104,8 @@ int launch_embed_rows(const uint8_t* w, uint32_t type, const int* tokens, int M,
                       cudaStream_t st);
 int launch_softcap(float* y, long long n, float cap, cudaStream_t st);
 int launch_allgather_wait(const PeerOut& po, cudaStream_t st, bool advance = false);
+int launch_gemm_sa_multi(const float* x, const float* norm_w, float eps, float* x_norm_out, const uint8_t* const* ws, float* const* ys,
+                         const int* ns, int n_mats, uint32_t type, int M, int K, cudaStream_t st);
 int launch_gemm_sa_peers(const float* x, const uint8_t* w, uint32_t type, const PeerOut& po, int M, int K, int N, cudaStream_t st);
 
 // Tensor-core prefill GEMM with the activation scales folded into the operand (lp_gemm_sa.cu): Q4_0, Q8_0, Q4_K, Q6_K

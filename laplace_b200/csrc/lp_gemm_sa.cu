@@ -967,6 +967,44 @@ __global__ void __launch_bounds__(256) quantize_sa_kernel(const float* __restric
                     op.g + static_cast<size_t>(m >> 1) * (K / 16), m & 1, op.inv_s + m);
 }
 
+// The same with the RMSNorm of the row in front (Laplace src/ops.cpp:34-74: inv = 1 / sqrt(mean(x^2) + eps),
+// x_norm = (x * inv) * w), for prefill calls whose matrices share one normalised input (src/arch_llama.cpp:475-499).
+__global__ void __launch_bounds__(256) quantize_sa_norm_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps,
+                                                               float* __restrict__ x_norm_out, int K, SaOperand op) {
+    __shared__ float red[8];
+    __shared__ float s_inv;
+    const int m = blockIdx.x;
+    const float* xr = x + static_cast<size_t>(m) * K;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(xr) + i);
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+        s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, static_cast<float>(K)), eps)));
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    auto load = [&](int b, int t8) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(xr + b * 32) + t8);
+        const float4 w = __ldg(reinterpret_cast<const float4*>(norm_w + b * 32) + t8);
+        return make_float4(__fmul_rn(__fmul_rn(v.x, inv), w.x), __fmul_rn(__fmul_rn(v.y, inv), w.y),
+                           __fmul_rn(__fmul_rn(v.z, inv), w.z), __fmul_rn(__fmul_rn(v.w, inv), w.w));
+    };
+    if (x_norm_out)
+        for (int i = threadIdx.x; i < K / 4; i += blockDim.x)
+            reinterpret_cast<float4*>(x_norm_out + static_cast<size_t>(m) * K)[i] = load(i >> 3, i & 7);
+    __syncthreads();                  // quantize_row_sa reuses a shared array of its own for the row maximum
+    quantize_row_sa(load, K, op.a + static_cast<size_t>(m) * K, op.a + (static_cast<size_t>(op.m_pad) + m) * K,
+                    op.g + static_cast<size_t>(m >> 1) * (K / 16), m & 1, op.inv_s + m);
+}
+
 // Adds up the pieces of every output tile that the balanced split cut, in k order, and writes the tile to y.
 // Block (t, j) handles 16 tokens of output tile t; a tile one CTA computed whole is already in y.
 struct FixupOut { float* y; float* peer_y[MAX_PEERS]; int n_peers, peer_ld, peer_col0; };
@@ -1187,9 +1225,11 @@ int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const
     int rc;
     uint8_t* s = scratch;
     const SaOperand op = carve_operand(s, pl.m_pad, K);
-    quantize_sa_kernel<<<M, 256, 0, st>>>(x, K, op);
-    c.launches++;
-    if ((rc = cuda_check(cudaGetLastError(), "quantize_sa launch"))) return rc;
+    if (x) {                          // nullptr: the operand is in place already (several matrices share one input)
+        quantize_sa_kernel<<<M, 256, 0, st>>>(x, K, op);
+        c.launches++;
+        if ((rc = cuda_check(cudaGetLastError(), "quantize_sa launch"))) return rc;
+    }
     SaLaunch L{};
     L.w = w; L.type = type; L.y = y; L.M = M; L.K = K; L.N = N; L.w_rows = N; L.op = op;
     L.tiles_m = pl.tiles_m; L.tiles_n = pl.tiles_n;
@@ -1221,6 +1261,34 @@ int launch_gemm_sa(const float* x, const uint8_t* w, uint32_t type, float* y, in
     const SaPlan pl = plan_sa(M, K, N, true);
     if ((rc = g_scratch.ensure(pl.total(), st))) return rc;
     return gemm_sa_on_scratch(static_cast<uint8_t*>(g_scratch.p), pl, x, w, type, y, M, K, N, st);
+}
+
+// Several matrices of one type and K against the same input rows (q / k / v, gate / up of src/arch_llama.cpp:475-499): the
+// input is normalised (optional) and quantized once, then every matrix runs on that operand.
+int launch_gemm_sa_multi(const float* x, const float* norm_w, float eps, float* x_norm_out, const uint8_t* const* ws, float* const* ys,
+                         const int* ns, int n_mats, uint32_t type, int M, int K, cudaStream_t st) {
+    int rc;
+    size_t need = 0;
+    for (int i = 0; i < n_mats; ++i) {
+        if ((rc = check_args(x, ws[i], type, M, K, ns[i]))) return rc;
+        const size_t t = plan_sa(M, K, ns[i], true).total();
+        need = t > need ? t : need;
+    }
+    if (norm_w && ((reinterpret_cast<uintptr_t>(norm_w) & 15) || (x_norm_out && (reinterpret_cast<uintptr_t>(x_norm_out) & 15))))
+        return fail(LAPLACE_ERR_ARG, "gemm_multi: the norm weights (and the optional output) must be 16-byte aligned");
+    if ((rc = g_scratch.ensure(need, st))) return rc;
+    uint8_t* scratch = static_cast<uint8_t*>(g_scratch.p);
+    {
+        uint8_t* s = scratch;
+        const SaOperand op = carve_operand(s, plan_sa(M, K, ns[0], true).m_pad, K);
+        if (norm_w) quantize_sa_norm_kernel<<<M, 256, 0, st>>>(x, norm_w, eps, x_norm_out, K, op);
+        else quantize_sa_kernel<<<M, 256, 0, st>>>(x, K, op);
+        ctx().launches++;
+        if ((rc = cuda_check(cudaGetLastError(), "quantize_sa launch"))) return rc;
+    }
+    for (int i = 0; i < n_mats; ++i)
+        if ((rc = gemm_sa_on_scratch(scratch, plan_sa(M, K, ns[i], true), nullptr, ws[i], type, ys[i], M, K, ns[i], st))) return rc;
+    return LAPLACE_OK;
 }
 
 // The same call for a row-split matrix: this GPU's N columns of the result go to every GPU's [M][ld] buffer at column col0

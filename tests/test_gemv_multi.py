@@ -45,7 +45,42 @@ def test_multi_matrix_gemv(oracle, t, M, K, Ns, norm):
     for y, w, n in zip(ys, ws, Ns):
         mass = oracle.gemm(x_in, w, t, M, K, n, mode=2)
         check_close(y.cpu().numpy(), oracle.gemm(x_in, w, t, M, K, n, mode=1), f"multi {t.name} M={M} K={K} N={n} norm={norm}", mass)
-        # and bit-identical to a single-matrix call on the same activations
+        # and bit-identical to a single-matrix call on the same activations (the same kernel), except where the single
+        # call takes another kernel (Q4_K with 3..8 rows runs on mma.sync tiles: another fp32 summation order)
+        single = device.gemm(torch.from_numpy(np.ascontiguousarray(x_in)).cuda(), device.upload_weights(w), t, M, K, n)
+        device.sync()
+        if t == GGMLType.Q4_K and 3 <= M <= 8 and K % 256 == 0:
+            check_close(single.cpu().numpy(), y.cpu().numpy().astype(np.float64), "single (mma kernel) vs multi (dp4a kernel)", mass)
+        else:
+            assert np.array_equal(single.cpu().numpy(), y.cpu().numpy())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("t,M,K,Ns", [(GGMLType.Q4_K, 64, 1024, (256, 136, 128)), (GGMLType.Q6_K, 40, 2048, (200, 128)),
+                                      (GGMLType.Q4_K, 512, 4096, (1024, 1024))])
+@pytest.mark.parametrize("norm", [False, True])
+def test_multi_matrix_prefill(oracle, t, M, K, Ns, norm):
+    """More than 8 rows: one (normalising) quantizer launch, then one tensor-core GEMM per matrix on the shared operand."""
+    import os
+    import torch
+    from laplace_b200 import device
+    ws = [synth.weights(t, K, n, seed=180 + i, how="affine") for i, n in enumerate(Ns)]
+    x = synth.normal_f32(190, (M, K)) * np.float32(2.5)
+    nw = (1.0 + 0.1 * synth.normal_f32(191, (K,))).astype(np.float32)
+    wd = [device.upload_weights(w) for w in ws]
+    if norm:
+        ys, xn = device.gemm_multi(torch.from_numpy(x).cuda(), wd, t, M, K, Ns, norm_weight=torch.from_numpy(nw).cuda(), eps=1e-5, want_x_norm=True)
+        device.sync()
+        xn = xn.cpu().numpy()
+        assert np.allclose(xn, rmsnorm_rows_np(x, nw, 1e-5), rtol=2e-6, atol=0.0)
+        x_in = xn
+    else:
+        ys = device.gemm_multi(torch.from_numpy(x).cuda(), wd, t, M, K, Ns)
+        device.sync()
+        x_in = x
+    assert device.lib().laplace_cuda_last_path() == 2
+    for y, w, n in zip(ys, ws, Ns):
+        check_close(y.cpu().numpy(), oracle.gemm(x_in, w, t, M, K, n, mode=1, threads=os.cpu_count() or 1), f"multi prefill {t.name} M={M} K={K} N={n} norm={norm}")
         single = device.gemm(torch.from_numpy(np.ascontiguousarray(x_in)).cuda(), device.upload_weights(w), t, M, K, n)
         device.sync()
         assert np.array_equal(single.cpu().numpy(), y.cpu().numpy())
