@@ -480,17 +480,18 @@ def decode_leg(device, synth, torch):
     (best of 5 replays)."""
     shapes = [("Q4_0", 2, 1, 4096, 4096), ("Q4_K", 12, 1, 4096, 4096), ("Q4_K", 12, 1, 4096, 1024),
               ("Q6_K", 14, 1, 14336, 4096), ("Q6_K", 14, 1, 4096, 14336), ("Q8_0", 8, 1, 4096, 14336),
+              ("Q5_0", 6, 1, 4096, 14336),
               ("Q4_K", 12, 2, 4096, 14336), ("Q4_K", 12, 4, 4096, 14336), ("Q4_K", 12, 8, 4096, 14336),
               # types the reference serves with fp32 activations (its scalar path): an F16 LM head of 32,000 rows and
               # one Q5_K matrix
               ("F16", 1, 1, 4096, 32000), ("Q5_K", 13, 1, 4096, 14336)]
-    geom = {2: (32, 18), 8: (32, 34), 12: (256, 144), 14: (256, 210), 1: (1, 2), 13: (256, 176)}
+    geom = {2: (32, 18), 6: (32, 22), 8: (32, 34), 12: (256, 144), 14: (256, 210), 1: (1, 2), 13: (256, 176)}
     out = []
     for name, t, M, K, N in shapes:
         eb, bb = geom[t]
         wbytes = N * (K // eb) * bb
         n_copies = max(2, min(24, -(-(160 << 20) // wbytes)))
-        base = synth.weights(t, K, N, seed=1500 + t + N, how="random") if t in (2, 8, 12, 14) else synth.other_type_weights(t, K, N, seed=1500 + t + N)
+        base = synth.weights(t, K, N, seed=1500 + t + N, how="random") if t in (2, 6, 8, 12, 14) else synth.other_type_weights(t, K, N, seed=1500 + t + N)
         ws = [device.upload_weights(np.roll(base, 16 * i, axis=0)) for i in range(n_copies)]
         x = torch.from_numpy(synth.normal_f32(1600 + M, (M, K))).cuda()
         y = torch.empty((M, N), dtype=torch.float32, device="cuda")

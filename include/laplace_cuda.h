@@ -36,6 +36,7 @@ extern "C" {
 
 /* GGML type ids, src/tensor.h:11-34 */
 #define LAPLACE_TYPE_Q4_0 2u
+#define LAPLACE_TYPE_Q5_0 6u
 #define LAPLACE_TYPE_Q8_0 8u
 #define LAPLACE_TYPE_Q4_K 12u
 #define LAPLACE_TYPE_Q6_K 14u
@@ -215,14 +216,14 @@ int laplace_cuda_gemm_noalloc_dev(const float* x, const uint8_t* w, uint32_t typ
                                   float* y, int M, int K, int N, void* stream);
 
 /* ---- weight types without an int8 kernel, dequantize(), LM head ---------------------------
- * laplace_cuda_gemm and laplace_cuda_gemm_dev also take F32 (0), F16 (1), BF16 (30), Q5_0 (6), Q2_K (10),
- * Q3_K (11) and Q5_K (13) weights. For those the reference has no int8 kernel on this kind of host and computes
+ * laplace_cuda_gemm and laplace_cuda_gemm_dev also take F32 (0), F16 (1), BF16 (30), Q2_K (10), Q3_K (11) and
+ * Q5_K (13) weights. For those the reference has no int8 kernel and computes
  * y[m][j] = dot_row_<type>(x[m], row j) with fp32 activations (gemm_fallback, src/matmul.cpp:336-352); so does the
  * library (activations are NOT quantized for these types). K must be a multiple of the type's block (16 for the
  * plain types).
  *
  * laplace_cuda_dequantize_dev replaces dequantize(const Tensor&, float* dst, int n) (src/matmul.cpp:504-675) for
- * every type above plus Q4_0 / Q8_0 / Q4_K / Q6_K, bit for bit (the reference's expressions, separate roundings);
+ * every type above plus Q4_0 / Q5_0 / Q8_0 / Q4_K / Q6_K, bit for bit (the reference's expressions, separate roundings);
  * n = number of values, a multiple of the block size. laplace_cuda_embed_rows_dev is the token-embedding lookup of
  * src/model.cpp:366-378: dst[m] = dequantize(row tokens[m]) * scale (scale = the model's embedding scale, 1 for most);
  * a token id outside [0, vocab) is reported through laplace_cuda_sync like a bad expert index.
@@ -330,7 +331,7 @@ int laplace_cuda_quantize_act_dev(const float* x, int M, int K,
                                   void* stream);
 
 /* Exact integer block sums, for parity tests on small shapes:
- * out[(m*N+j)*per_row + b], per_row = K/32 (Q8_0, Q4_0, Q4_K) or K/16 (Q6_K);
+ * out[(m*N+j)*per_row + b], per_row = K/32 (Q8_0, Q4_0, Q5_0, Q4_K) or K/16 (Q6_K);
  * same definition as the per-block accumulations of
  * src/matmul_simd.cpp:143-342. Device pointers. */
 int laplace_cuda_debug_blocksums_dev(const float* x, const uint8_t* w, uint32_t type,

@@ -11,13 +11,14 @@ namespace lp {
 
 // ---- block geometry (Laplace src/kernels.h:21-54, src/tensor.h:41-100) ------
 constexpr int Q4_0_BYTES = 18;
+constexpr int Q5_0_BYTES = 22;
 constexpr int Q8_0_BYTES = 34;
 constexpr int Q4_K_BYTES = 144;
 constexpr int Q6_K_BYTES = 210;
 
 __host__ __device__ inline int block_elems(uint32_t type) {
     switch (type) {
-        case LAPLACE_TYPE_Q4_0: case LAPLACE_TYPE_Q8_0: return 32;
+        case LAPLACE_TYPE_Q4_0: case LAPLACE_TYPE_Q5_0: case LAPLACE_TYPE_Q8_0: return 32;
         case LAPLACE_TYPE_Q4_K: case LAPLACE_TYPE_Q6_K: return 256;
         default: return 0;
     }
@@ -25,6 +26,7 @@ __host__ __device__ inline int block_elems(uint32_t type) {
 __host__ __device__ inline int block_bytes(uint32_t type) {
     switch (type) {
         case LAPLACE_TYPE_Q4_0: return Q4_0_BYTES;
+        case LAPLACE_TYPE_Q5_0: return Q5_0_BYTES;
         case LAPLACE_TYPE_Q8_0: return Q8_0_BYTES;
         case LAPLACE_TYPE_Q4_K: return Q4_K_BYTES;
         case LAPLACE_TYPE_Q6_K: return Q6_K_BYTES;

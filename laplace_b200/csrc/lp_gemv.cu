@@ -1,5 +1,5 @@
 // lp_gemv.cu - decode-time streaming GEMV (1..8 activation rows) for Q4_0,
-// Q8_0, Q4_K and Q6_K weights, with the activation quantizer fused into the
+// Q5_0, Q8_0, Q4_K and Q6_K weights, with the activation quantizer fused into the
 // prologue. Replaces the row loop + dot kernels of Laplace's NEON back-end
 // (src/matmul_simd.cpp:143-342, 348-455, 506-544) for small M.
 //
@@ -245,6 +245,45 @@ template <> struct Traits<LAPLACE_TYPE_Q4_0> {
             }
             const int u = ul + (uh >> 4);
             acc[m] = fmaf(d * dx, static_cast<float>(u), acc[m]) - d * 8.0f * sx;
+        }
+    }
+};
+
+// Q5_0: item = one 22-byte block: fp16 d, 32 fifth bits (bit l of the little-endian word belongs to value l), 16
+// bytes of nibbles packed as in Q4_0. The signed weight is (nibble | bit << 4) - 16; since 0 <= nibble <= 15 that
+// is the byte nibble | (bit ? 0x00 : 0xF0), built four values at a time: the four bits are spread to one per byte
+// by a multiply (x * 0x00204081 puts bit i at position 8i), inverted, and multiplied by 0xF0, which stays
+// inside each byte (Laplace src/matmul_simd.cpp:184-224).
+template <> struct Traits<LAPLACE_TYPE_Q5_0> {
+    static constexpr int ITEMS_PER_BLOCK = 1;
+    __device__ static __forceinline__ uint32_t sign_fill(uint32_t four_bits) {
+        return (((four_bits * 0x00204081u) & 0x01010101u) ^ 0x01010101u) * 0xF0u;
+    }
+    template <int M>
+    __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
+                                float (&acc)[M]) {
+        const uint32_t blk = row + i * Q5_0_BYTES;
+        const float d = half_bits_to_float(lds16(blk));
+        const uint32_t qh = lds16(blk + 2) | (lds16(blk + 4) << 16);
+        uint32_t wq[4];
+        lds16B_align2(blk + 6, wq);
+        uint32_t wl[4], wh[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            wl[t] = (wq[t] & 0x0f0f0f0fu) | sign_fill((qh >> (4 * t)) & 15u);
+            wh[t] = ((wq[t] >> 4) & 0x0f0f0f0fu) | sign_fill((qh >> (16 + 4 * t)) & 15u);
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const uint32_t q = act_q(act + m * astride, i);
+            const uint4 x0 = lds128(q), x1 = lds128(q + 16);
+            const float dx = __uint_as_float(lds32(act_d(act + m * astride, i)));
+            int ua = 0, ub = 0;
+            ua = dp4a_ss(wl[0], x0.x, ua); ub = dp4a_ss(wl[1], x0.y, ub);
+            ua = dp4a_ss(wl[2], x0.z, ua); ub = dp4a_ss(wl[3], x0.w, ub);
+            ua = dp4a_ss(wh[0], x1.x, ua); ub = dp4a_ss(wh[1], x1.y, ub);
+            ua = dp4a_ss(wh[2], x1.z, ua); ub = dp4a_ss(wh[3], x1.w, ub);
+            acc[m] = fmaf(d * dx, static_cast<float>(ua + ub), acc[m]);
         }
     }
 };
@@ -949,7 +988,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     // is not 16-byte aligned (<= 15 bytes in front) and the 4-byte read-ahead
     // of the unaligned loads. Slice boundaries sit on multiples of 8 blocks
     // (any super-block for Q4_K) so they are 16-byte aligned within the row.
-    const int unit_blocks = a.type == LAPLACE_TYPE_Q4_K ? 1 : 8;   // 8 x 210, 8 x 18, 8 x 34 are multiples of 16
+    const int unit_blocks = a.type == LAPLACE_TYPE_Q4_K ? 1 : 8;   // 8 x 210, 8 x 18, 8 x 22, 8 x 34 are multiples of 16
     const int items_per_block = a.type == LAPLACE_TYPE_Q4_K ? 2 : (a.type == LAPLACE_TYPE_Q6_K ? 4 : 1);
     const uint32_t bpb = static_cast<uint32_t>(block_bytes(a.type));
     const int n_blocks = a.K / epb;
@@ -1025,6 +1064,8 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
                                         : launch_typed<LAPLACE_TYPE_Q6_K, false>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
         case LAPLACE_TYPE_Q4_0: e = ext ? launch_typed<LAPLACE_TYPE_Q4_0, true>(a.M, false, long_rows, p, dim3(grid), smem, st)
                                         : launch_typed<LAPLACE_TYPE_Q4_0, false>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
+        case LAPLACE_TYPE_Q5_0: e = ext ? launch_typed<LAPLACE_TYPE_Q5_0, true>(a.M, false, long_rows, p, dim3(grid), smem, st)
+                                        : launch_typed<LAPLACE_TYPE_Q5_0, false>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
         case LAPLACE_TYPE_Q8_0: e = ext ? launch_typed<LAPLACE_TYPE_Q8_0, true>(a.M, false, long_rows, p, dim3(grid), smem, st)
                                         : launch_typed<LAPLACE_TYPE_Q8_0, false>(a.M, false, long_rows, p, dim3(grid), smem, st); break;
         default: return LAPLACE_UNSUPPORTED;

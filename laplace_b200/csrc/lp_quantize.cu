@@ -43,7 +43,8 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const float* __restri
 // Integer weight value of element k of a row, written straight from the block
 // layouts (Laplace src/kernels.h:21-54, src/matmul.cpp:84-198) without any of
 // the word-level unpacking the fast kernels use. Q4_0 / Q4_K give the unsigned
-// nibble, Q8_0 the signed byte, Q6_K the 6-bit value minus 32.
+// nibble, Q8_0 the signed byte, Q5_0 the 5-bit value minus 16, Q6_K the 6-bit
+// value minus 32.
 __device__ int weight_value(uint32_t type, const uint8_t* row, int k) {
     switch (type) {
         case LAPLACE_TYPE_Q4_0: {
@@ -51,6 +52,13 @@ __device__ int weight_value(uint32_t type, const uint8_t* row, int k) {
             const int l = k & 31;
             const int byte = blk[2 + (l & 15)];
             return l < 16 ? (byte & 15) : (byte >> 4);
+        }
+        case LAPLACE_TYPE_Q5_0: {
+            const uint8_t* blk = row + (k >> 5) * Q5_0_BYTES;
+            const int l = k & 31;
+            const int byte = blk[6 + (l & 15)];
+            const int bit = (blk[2 + (l >> 3)] >> (l & 7)) & 1;           // qh is little-endian: bit l of the 32
+            return ((l < 16 ? (byte & 15) : (byte >> 4)) | (bit << 4)) - 16;
         }
         case LAPLACE_TYPE_Q8_0: {
             const uint8_t* blk = row + (k >> 5) * Q8_0_BYTES;

@@ -1,7 +1,7 @@
 // lp_types.cu - the weight types that have no int8 kernel in the reference, and dequantize() on the device.
 //
-// Laplace serves Q4_0 / Q8_0 / Q4_K / Q6_K (and Q5_0) matmuls through its int8 back-end and everything else -
-// F32, F16, BF16, Q5_0 on other hosts, Q2_K, Q3_K, Q5_K - through the scalar path with fp32 activations
+// Laplace serves Q4_0 / Q5_0 / Q8_0 / Q4_K / Q6_K matmuls through its int8 back-end and everything else -
+// F32, F16, BF16, Q2_K, Q3_K, Q5_K - through the scalar path with fp32 activations
 // (gemm_fallback, src/matmul.cpp:336-352: y[m][j] = dot_row_<type>(x[m], row j)). dequantize() (src/matmul.cpp:504-675)
 // turns blocks into floats for token-embedding lookups (src/model.cpp:366-378). Here:
 //   dequantize_kernel        every type, 16 values per thread, the reference's expressions with separate roundings
@@ -277,7 +277,7 @@ cudaError_t launch_f32act(const float* x, const uint8_t* w, uint32_t type, float
 }  // namespace
 
 bool f32act_type(uint32_t type) {
-    return type == T_F32 || type == T_F16 || type == T_BF16 || type == T_Q5_0 || type == T_Q2_K || type == T_Q3_K || type == T_Q5_K;
+    return type == T_F32 || type == T_F16 || type == T_BF16 || type == T_Q2_K || type == T_Q3_K || type == T_Q5_K;
 }
 bool dequant_type(uint32_t type) { return geo_of(type).elems != 0; }
 size_t any_row_bytes(uint32_t type, long long K) {

@@ -6,8 +6,8 @@
 // arch_*.cpp, laplace_moe.cpp and matmul.cpp compile and link unchanged. A
 // return value of `false` keeps the reference's contract (kernels.h:94-96):
 // "this back-end does not handle the call, fall back to the scalar path" -
-// that happens only for weight types the library does not take (it takes Q4_0 / Q8_0 / Q4_K / Q6_K on the int8 path
-// and F32 / F16 / BF16 / Q5_0 / Q2_K / Q3_K / Q5_K with fp32 activations, as the scalar path computes them). An
+// that happens only for weight types the library does not take (it takes Q4_0 / Q5_0 / Q8_0 / Q4_K / Q6_K on the int8 path
+// and F32 / F16 / BF16 / Q2_K / Q3_K / Q5_K with fp32 activations, as the scalar path computes them). An
 // error from the CUDA library (a failed CUDA call, a device-side timeout, a bad
 // argument) is NOT turned into a fall-back: the scalar path computes with fp32
 // activations, i.e. different numbers, so the process prints the error and aborts.

@@ -1,4 +1,4 @@
-"""GGML type ids and block geometry of the four weight formats on this path.
+"""GGML type ids and block geometry of the weight formats on this path.
 
 Values follow Laplace ``src/tensor.h:11-34`` (ids) and ``src/tensor.h:41-100`` /
 ``src/kernels.h:21-54`` (bytes and elements per block).
@@ -24,6 +24,7 @@ class GGMLType(enum.IntEnum):
 
 _GEOM = {
     GGMLType.Q4_0: (32, 18),
+    GGMLType.Q5_0: (32, 22),
     GGMLType.Q8_0: (32, 34),
     GGMLType.Q4_K: (256, 144),
     GGMLType.Q6_K: (256, 210),
@@ -31,12 +32,12 @@ _GEOM = {
 
 SUPPORTED = tuple(_GEOM)          # the types with an int8 path (Q8 activations)
 
-# every type the library takes: the four above, and those served with fp32 activations / dequantized only
+# every type the library takes: those above, and those served with fp32 activations / dequantized only
 # (elements and bytes per block, Laplace src/tensor.h:41-100)
 ALL_GEOM = dict(_GEOM)
-ALL_GEOM.update({GGMLType.F32: (1, 4), GGMLType.F16: (1, 2), GGMLType.BF16: (1, 2), GGMLType.Q5_0: (32, 22),
+ALL_GEOM.update({GGMLType.F32: (1, 4), GGMLType.F16: (1, 2), GGMLType.BF16: (1, 2),
                  GGMLType.Q2_K: (256, 84), GGMLType.Q3_K: (256, 110), GGMLType.Q5_K: (256, 176)})
-F32_ACTIVATION_TYPES = (GGMLType.F32, GGMLType.F16, GGMLType.BF16, GGMLType.Q5_0, GGMLType.Q2_K, GGMLType.Q3_K, GGMLType.Q5_K)
+F32_ACTIVATION_TYPES = (GGMLType.F32, GGMLType.F16, GGMLType.BF16, GGMLType.Q2_K, GGMLType.Q3_K, GGMLType.Q5_K)
 
 
 def any_row_bytes(t: int, K: int) -> int:

@@ -89,7 +89,7 @@ def matmul_rows(x: np.ndarray, w: Tensor, y: np.ndarray, M: int, K: int, N: int)
     x = np.ascontiguousarray(x, dtype=np.float32) if not (isinstance(x, np.ndarray) and x.flags.c_contiguous) else x
     _f32(x, M * K, "x")
     _f32(y, M * N, "y")
-    d = _u8(w, N * row_bytes(w.type, K)) if int(w.type) in (2, 8, 12, 14) else w.data
+    d = _u8(w, N * row_bytes(w.type, K)) if int(w.type) in (2, 6, 8, 12, 14) else w.data
     _check(lib, lib.laplace_cuda_gemm(x.ctypes.data, d.ctypes.data, int(w.type), y.ctypes.data, M, K, N))
 
 

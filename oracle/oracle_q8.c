@@ -66,11 +66,11 @@ uint16_t lpo_fp32_to_fp16(float val) {
 /* -------------------------------------------------------------- layouts */
 
 /* src/kernels.h:21-54 (sizes), src/tensor.h:41-100 */
-enum { Q4_0_BYTES = 18, Q8_0_BYTES = 34, Q4_K_BYTES = 144, Q6_K_BYTES = 210 };
+enum { Q4_0_BYTES = 18, Q5_0_BYTES = 22, Q8_0_BYTES = 34, Q4_K_BYTES = 144, Q6_K_BYTES = 210 };
 
 int lpo_block_elems(uint32_t type) {
     switch (type) {
-        case LPO_Q4_0: case LPO_Q8_0: return 32;
+        case LPO_Q4_0: case LPO_Q5_0: case LPO_Q8_0: return 32;
         case LPO_Q4_K: case LPO_Q6_K: return 256;
         default: return 0;
     }
@@ -79,6 +79,7 @@ int lpo_block_elems(uint32_t type) {
 static size_t block_bytes(uint32_t type) {
     switch (type) {
         case LPO_Q4_0: return Q4_0_BYTES;
+        case LPO_Q5_0: return Q5_0_BYTES;
         case LPO_Q8_0: return Q8_0_BYTES;
         case LPO_Q4_K: return Q4_K_BYTES;
         case LPO_Q6_K: return Q6_K_BYTES;
@@ -251,6 +252,42 @@ static double dot_q4_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode,
     return mode == LPO_MODE_F64 ? acc64 : (double)(hsum4(acc) - acc_offset);
 }
 
+/* ----------------------------------------------------------------- Q5_0 */
+
+/* The 32 signed weights of one 22-byte block: nibble | fifth bit << 4, minus 16
+ * (src/matmul_simd.cpp:196-214; qh bit l belongs to element l). */
+static inline void q5_0_weights(const uint8_t* blk, int8_t w[32]) {
+    uint32_t qh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24);
+    for (int l = 0; l < 16; l++) {
+        w[l]      = (int8_t)((int)((blk[6 + l] & 0x0f) | (((qh >> l) & 1u) << 4)) - 16);
+        w[l + 16] = (int8_t)((int)((blk[6 + l] >> 4)   | (((qh >> (l + 16)) & 1u) << 4)) - 16);
+    }
+}
+
+/* src/matmul_simd.cpp:184-224 - one accumulator, the two halves fma'd in turn. */
+static double dot_q5_0(const lpo_actq8* xa, const uint8_t* row, int K, int mode, int32_t* sums) {
+    float  acc[4] = {0, 0, 0, 0};
+    double acc64 = 0.0, mass = 0.0;
+    for (int b = 0; b < K / 32; b++) {
+        const uint8_t* blk = row + (size_t)b * Q5_0_BYTES;
+        float dw = lpo_fp16_to_fp32(rd16(blk));
+        int8_t w[32];
+        q5_0_weights(blk, w);
+        int32_t p0[4], p1[4];
+        dot16_ss(w, xa[b].qs, p0);
+        dot16_ss(w + 16, xa[b].qs + 16, p1);
+        if (sums) sums[b] = sum4(p0) + sum4(p1);
+        float scale = dw * xa[b].d;
+        fma_lanes(acc, scale, p0);
+        fma_lanes(acc, scale, p1);
+        double term = (double)dw * (double)xa[b].d * (double)(sum4(p0) + sum4(p1));
+        acc64 += term;
+        mass += fabs(term);
+    }
+    if (mode == LPO_MODE_MASS) return mass;
+    return mode == LPO_MODE_F64 ? acc64 : (double)hsum4(acc);
+}
+
 /* ----------------------------------------------------------------- Q4_K */
 
 /* src/matmul_simd.cpp:226-283 */
@@ -344,6 +381,7 @@ static double dot_any(uint32_t type, const lpo_actq8* xa, const uint8_t* row, in
     switch (type) {
         case LPO_Q8_0: return dot_q8_0(xa, row, K, mode, sums);
         case LPO_Q4_0: return dot_q4_0(xa, row, K, mode, sums);
+        case LPO_Q5_0: return dot_q5_0(xa, row, K, mode, sums);
         case LPO_Q4_K: return dot_q4_k(xa, row, K, mode, sums);
         case LPO_Q6_K: return dot_q6_k(xa, row, K, mode, sums);
         default: return 0.0;
@@ -503,6 +541,19 @@ float lpo_dot_scalar(uint32_t type, const float* x, const uint8_t* row, int K) {
             }
             acc += lpo_fp16_to_fp32(rd16(blk)) * sum;
         }
+    } else if (type == LPO_Q5_0) {                    /* src/matmul.cpp:102-121 */
+        for (int b = 0; b < K / 32; b++) {
+            const uint8_t* blk = row + (size_t)b * Q5_0_BYTES;
+            const float*   xb  = x + b * 32;
+            int8_t w[32];
+            q5_0_weights(blk, w);
+            float sum = 0.0f;
+            for (int l = 0; l < 16; l++) {
+                sum += xb[l]      * (float)w[l];
+                sum += xb[l + 16] * (float)w[l + 16];
+            }
+            acc += lpo_fp16_to_fp32(rd16(blk)) * sum;
+        }
     } else if (type == LPO_Q8_0) {
         for (int b = 0; b < K / 32; b++) {
             const uint8_t* blk = row + (size_t)b * Q8_0_BYTES;
@@ -588,6 +639,14 @@ int lpo_dequantize(uint32_t type, const uint8_t* w, float* dst, size_t n) {
                 dst[i + l + 16] = d * ((blk[2 + l] >> 4) - 8);
             }
         }
+    } else if (type == LPO_Q5_0) {                    /* src/matmul.cpp:532-545 */
+        for (size_t i = 0; i < n; i += 32) {
+            const uint8_t* blk = w + (i / 32) * Q5_0_BYTES;
+            float d = lpo_fp16_to_fp32(rd16(blk));
+            int8_t q[32];
+            q5_0_weights(blk, q);
+            for (int l = 0; l < 32; l++) dst[i + l] = d * (float)q[l];
+        }
     } else if (type == LPO_Q8_0) {
         for (size_t i = 0; i < n; i += 32) {
             const uint8_t* blk = w + (i / 32) * Q8_0_BYTES;
@@ -664,7 +723,7 @@ void lpo_testgen_x(uint32_t type, int K, float* x) {
  * (seeds 17 / 19 / 23 / 29), N * K / block_elems blocks in memory order. */
 int lpo_testgen_weights(uint32_t type, int K, int N, uint8_t* out) {
     int epb = lpo_block_elems(type);
-    if (!epb) return 1;
+    if (!epb || type == LPO_Q5_0) return 1;          /* that test has no Q5_0 case */
     size_t nblk = (size_t)N * (size_t)(K / epb);
     xs32 r;
     switch (type) {

@@ -10,6 +10,7 @@
  *   src/matmul_simd.cpp:348-410  quantize_act_q8_neon
  *   src/matmul_simd.cpp:143-160  dot_row_q8_0_int_neon
  *   src/matmul_simd.cpp:162-182  dot_row_q4_0_int_neon
+ *   src/matmul_simd.cpp:184-224  dot_row_q5_0_int_neon
  *   src/matmul_simd.cpp:226-283  dot_row_q4_k_int_neon
  *   src/matmul_simd.cpp:285-342  dot_row_q6_k_int_neon
  *   src/matmul_simd.cpp:432-455  gemm_int row loop
@@ -39,7 +40,7 @@ extern "C" {
 #endif
 
 /* GGML type ids used on this path (src/tensor.h:11-34). */
-enum { LPO_Q4_0 = 2, LPO_Q8_0 = 8, LPO_Q4_K = 12, LPO_Q6_K = 14 };
+enum { LPO_Q4_0 = 2, LPO_Q5_0 = 6, LPO_Q8_0 = 8, LPO_Q4_K = 12, LPO_Q6_K = 14 };
 
 /* Same 44-byte layout as the reference's private ActQ8. */
 typedef struct {
@@ -71,12 +72,12 @@ void lpo_quantize_rows(const float* x, int M, int K, lpo_actq8* out);
 /* One weight row against one quantized activation row. */
 double lpo_dot(uint32_t type, const lpo_actq8* xa, const uint8_t* row, int K, int mode);
 
-/* Integer block sums of one row. Q8_0/Q4_0/Q4_K: K/32 values; Q6_K: K/16 values.
+/* Integer block sums of one row. Q8_0/Q4_0/Q5_0/Q4_K: K/32 values; Q6_K: K/16 values.
  * Returns how many were written. */
 int lpo_row_blocksums(uint32_t type, const lpo_actq8* xa, const uint8_t* row, int K, int32_t* out);
 
 /* y[m*N+j] for all m<M, j<N. threads<=1 runs serially. Returns 0, or 1 when
- * the type is not one of the four. */
+ * the type is not one of the five. */
 int lpo_gemm(const float* x, const uint8_t* w, uint32_t type, float* y,
              int M, int K, int N, int mode, int threads);
 int lpo_moe_gemv(const float* x, const uint8_t* w, uint32_t type, const int* expert_idx,

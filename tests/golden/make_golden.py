@@ -84,6 +84,7 @@ LOSSLESS_CASES = [  # (type, M, K, N, weight seed, activation seed)
     (14, 1, 4096, 512, 9604, 9704), (12, 8, 4096, 512, 9605, 9705), (12, 64, 2048, 256, 9606, 9706),
     (14, 64, 2048, 256, 9607, 9707), (2, 40, 1024, 128, 9608, 9708), (8, 40, 1024, 128, 9609, 9709),
     (12, 1, 14336, 128, 9610, 9710), (14, 1, 14336, 128, 9611, 9711),
+    (6, 1, 4096, 512, 9612, 9712), (6, 40, 1024, 128, 9613, 9713),
 ]
 
 

@@ -122,6 +122,19 @@ def pack_ref_q4_0(w: np.ndarray) -> np.ndarray:
     return out.reshape(b.shape[0], -1)
 
 
+def pack_ref_q5_0(w: np.ndarray) -> np.ndarray:
+    """tests/test_metal.cpp:36-50: d = amax / 16, q = roundf(x / d + 16); low four bits in the nibbles, bit 4 in qh."""
+    b = _blocks(w, 32)
+    _, d, inv = _amax_d(b, 16)
+    q = _roundf(b * inv[..., None] + np.float32(16)).astype(np.int64)
+    out = np.zeros(b.shape[:2] + (22,), dtype=np.uint8)
+    out[..., 0:2] = f32_to_f16_bits(d)[..., None].view(np.uint8).reshape(b.shape[:2] + (2,))
+    qh = (((q >> 4) & 1) << np.arange(32, dtype=np.int64)).sum(axis=-1).astype(np.uint32)
+    out[..., 2:6] = qh[..., None].view(np.uint8).reshape(b.shape[:2] + (4,))
+    out[..., 6:] = ((q[..., :16] & 0xF) | ((q[..., 16:] & 0xF) << 4)).astype(np.uint8)
+    return out.reshape(b.shape[0], -1)
+
+
 def pack_ref_q8_0(w: np.ndarray) -> np.ndarray:
     """tests/test_metal.cpp:51-60."""
     b = _blocks(w, 32)
@@ -198,6 +211,18 @@ def pack_affine_q4_0(w: np.ndarray) -> np.ndarray:
     return out.reshape(b.shape[0], -1)
 
 
+def pack_affine_q5_0(w: np.ndarray) -> np.ndarray:
+    b = _blocks(w, 32)
+    bits, d = _h(np.abs(b).max(axis=-1) / np.float32(15))
+    q = np.clip(np.rint(_safe_div(b, d[..., None])) + 16, 0, 31).astype(np.int64)
+    out = np.zeros(b.shape[:2] + (22,), dtype=np.uint8)
+    _put16(out, 0, bits)
+    qh = ((q >> 4) << np.arange(32, dtype=np.int64)).sum(axis=-1).astype(np.uint32)
+    out[..., 2:6] = qh[..., None].view(np.uint8).reshape(b.shape[:2] + (4,))
+    out[..., 6:] = ((q[..., :16] & 0xF) | ((q[..., 16:] & 0xF) << 4)).astype(np.uint8)
+    return out.reshape(b.shape[0], -1)
+
+
 def pack_affine_q8_0(w: np.ndarray) -> np.ndarray:
     b = _blocks(w, 32)
     bits, d = _h(np.abs(b).max(axis=-1) / np.float32(127))
@@ -253,9 +278,9 @@ def pack_affine_q6_K(w: np.ndarray) -> np.ndarray:
     return out.reshape(b.shape[0], -1)
 
 
-PACK_REF = {GGMLType.Q4_0: pack_ref_q4_0, GGMLType.Q8_0: pack_ref_q8_0,
+PACK_REF = {GGMLType.Q4_0: pack_ref_q4_0, GGMLType.Q5_0: pack_ref_q5_0, GGMLType.Q8_0: pack_ref_q8_0,
             GGMLType.Q4_K: pack_ref_q4_K, GGMLType.Q6_K: pack_ref_q6_K}
-PACK_AFFINE = {GGMLType.Q4_0: pack_affine_q4_0, GGMLType.Q8_0: pack_affine_q8_0,
+PACK_AFFINE = {GGMLType.Q4_0: pack_affine_q4_0, GGMLType.Q5_0: pack_affine_q5_0, GGMLType.Q8_0: pack_affine_q8_0,
                GGMLType.Q4_K: pack_affine_q4_K, GGMLType.Q6_K: pack_affine_q6_K}
 
 
@@ -268,13 +293,13 @@ def random_blocks(t: int, K: int, N: int, seed: int) -> np.ndarray:
     g = rng(seed)
     rb = row_bytes(t, K)
     raw = g.integers(0, 256, size=(N, rb), dtype=np.uint8)
-    bb = {GGMLType.Q4_0: 18, GGMLType.Q8_0: 34, GGMLType.Q4_K: 144, GGMLType.Q6_K: 210}[t]
+    bb = {GGMLType.Q4_0: 18, GGMLType.Q5_0: 22, GGMLType.Q8_0: 34, GGMLType.Q4_K: 144, GGMLType.Q6_K: 210}[t]
     blk = raw.reshape(N, rb // bb, bb)
 
     def scale():
         return (0.005 + 0.065 * g.random(blk.shape[:2], dtype=np.float32)).astype(np.float16).view(np.uint16)
 
-    if t in (GGMLType.Q4_0, GGMLType.Q8_0):
+    if t in (GGMLType.Q4_0, GGMLType.Q5_0, GGMLType.Q8_0):
         _put16(blk, 0, scale())
     elif t == GGMLType.Q4_K:
         _put16(blk, 0, scale())
@@ -322,8 +347,8 @@ def single_live_block(t: int, K: int, N: int, seed: int, live: int):
     q[int(g.integers(0, 32))] = 127.0
     x[0, live * 32:(live + 1) * 32] = q * np.float32(0.125)
     one = np.frombuffer(np.float16(1.0).tobytes(), dtype=np.uint8)
-    if t in (GGMLType.Q4_0, GGMLType.Q8_0):
-        bb = 18 if t == GGMLType.Q4_0 else 34
+    if t in (GGMLType.Q4_0, GGMLType.Q5_0, GGMLType.Q8_0):
+        bb = {GGMLType.Q4_0: 18, GGMLType.Q5_0: 22, GGMLType.Q8_0: 34}[t]
         blk = w.reshape(N, rb // bb, bb)
         blk[:, :, 0:2] = 0
         blk[:, live, 0:2] = one

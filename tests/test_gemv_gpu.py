@@ -11,7 +11,7 @@ from laplace_b200.ggml import GGMLType
 
 pytestmark = pytest.mark.gpu
 
-TYPES = [GGMLType.Q4_0, GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q6_K]
+TYPES = [GGMLType.Q4_0, GGMLType.Q5_0, GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q6_K]
 
 
 from tests.parity import check_close  # noqa: E402
@@ -67,7 +67,7 @@ def test_long_rows_are_sliced(oracle, t):
 def test_blocksums_bit_exact(oracle, t):
     import torch
     from laplace_b200 import device
-    M, K, N = 3, 768 if t in (GGMLType.Q4_0, GGMLType.Q8_0) else 1024, 19
+    M, K, N = 3, 1024 if t in (GGMLType.Q4_K, GGMLType.Q6_K) else 768, 19
     w = synth.weights(t, K, N, seed=700 + int(t), how="random")
     x = synth.normal_f32(800, (M, K))
     out = device.debug_blocksums(torch.from_numpy(x).cuda(), device.upload_weights(w), t, M, K, N)

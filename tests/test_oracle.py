@@ -8,7 +8,8 @@ from tests import synth
 from laplace_b200.ggml import GGMLType, blocksums_per_row, row_bytes
 from tests.oracle_lib import ACTQ8, Reference
 
-TYPES = [GGMLType.Q4_0, GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q6_K]
+TYPES = [GGMLType.Q4_0, GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q6_K]      # the types the reference's test_matmul builds
+INT8_TYPES = TYPES + [GGMLType.Q5_0]                                      # every type with an int8 kernel there
 
 
 def almost_equal(a, b, rel, abs_tol):
@@ -111,7 +112,7 @@ def test_golden_vectors(oracle, golden_dir):
 
 
 @pytest.mark.skipif(not Reference.available(), reason="oracle/_ref not built (no reference checkout here)")
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", INT8_TYPES)
 def test_against_reference_build_live(oracle, t):
     """Dequantizers bit-equal to the reference's compiled code; one-hot activations make Q8 lossless,
     so the int8 path must then reproduce single dequantized weights."""
@@ -148,7 +149,7 @@ def test_quantizer_known_answers(oracle):
     assert np.isnan(b["d"]) and not b["qs"].any()       # NaN amax -> id = 0 -> every q = 0
 
 
-@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("t", INT8_TYPES)
 def test_blocksums_rebuild_the_dot(oracle, t):
     """Scaling the integer block sums by the block scales reproduces the float64 dot."""
     M, K, N = 2, 512, 5
@@ -164,7 +165,7 @@ def test_blocksums_rebuild_the_dot(oracle, t):
         for j in range(N):
             row = w[j]
             acc = 0.0
-            if t in (GGMLType.Q4_0, GGMLType.Q8_0):
+            if t in (GGMLType.Q4_0, GGMLType.Q5_0, GGMLType.Q8_0):
                 bb = rb // (K // 32)
                 for b in range(K // 32):
                     dw = f16(int(row[b * bb]), int(row[b * bb + 1]))

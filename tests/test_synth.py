@@ -6,7 +6,7 @@ import pytest
 from tests import synth
 from laplace_b200.ggml import GGMLType, row_bytes
 
-TYPES = [GGMLType.Q4_0, GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q6_K]
+TYPES = [GGMLType.Q4_0, GGMLType.Q5_0, GGMLType.Q8_0, GGMLType.Q4_K, GGMLType.Q6_K]
 
 
 def test_lcg_matches_a_plain_loop():
@@ -30,7 +30,7 @@ def test_shapes_and_determinism(t, how):
 
 def test_affine_packers_approximate_their_input(oracle):
     w = synth.normal_f32(8, (6, 1024), 0.02)
-    for t, tol in ((GGMLType.Q4_0, 0.15), (GGMLType.Q8_0, 0.01), (GGMLType.Q4_K, 0.12), (GGMLType.Q6_K, 0.04)):
+    for t, tol in ((GGMLType.Q4_0, 0.15), (GGMLType.Q5_0, 0.08), (GGMLType.Q8_0, 0.01), (GGMLType.Q4_K, 0.12), (GGMLType.Q6_K, 0.04)):
         deq = oracle.dequantize(synth.PACK_AFFINE[t](w), t, w.size).reshape(w.shape)
         assert np.linalg.norm(deq - w) / np.linalg.norm(w) < tol, t
 
