@@ -97,11 +97,13 @@ struct SaParams {
     // [TT tokens][TW rows] floats) which a second kernel adds up in k order. 0 units: whole tiles, dealt round-robin.
     long long    sk_units;
     float*       y_part;
-    // Row-split over several GPUs: the tile goes to row-major [M][peer_ld] buffers of EVERY GPU at column peer_col0 + n
-    // (plain stores to peer-mapped memory; complete when the grid is) instead of to y. 0 peers: y.
-    float*       peer_y[MAX_PEERS];
-    int          n_peers, peer_ld, peer_col0;
 };
+
+// Row-split over several GPUs: the tile goes to row-major [M][ld] buffers of EVERY GPU at column col0 + n (plain stores
+// to peer-mapped memory; complete when the grid is) instead of to SaParams::y. A kernel parameter of its own that only
+// the PEERS instantiations carry, so that the one-GPU kernels keep their parameter block and code as they were.
+template <bool PEERS> struct SaPeers {};
+template <> struct SaPeers<true> { float* y[MAX_PEERS]; int n, ld, col0; };
 
 struct TileRef { int m0, n0, wrow0, nt, sb0, sb1, part; };     // nt = tokens of the tile; part = slot of a partial result or -1
 // The pieces of work of one CTA, in the order every role of the CTA walks them.
@@ -146,8 +148,12 @@ struct SaMaps {
     CUtensorMap w;         // packed weights as bytes, rows of K/256 * 144 bytes, boxes of 144 bytes x 128 rows
 };
 
+// PEERS: the result tile goes to every GPU's buffer (SaPeers) instead of y. A template parameter, not a run-time
+// branch: these kernels are sensitive to their code size and layout (the peer stores as a branch inside the one-GPU kernel
+// cost it 14 to 37 %).
+template <bool PEERS>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
+gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p, const SaPeers<PEERS> pe) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (sbase - smem_u32(smem_raw));
@@ -430,22 +436,31 @@ gemm_q4k_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                     if (col < tr.nt) part[col * TW + wr] = v * __ldg(p.inv_s + tr.m0 + col);
                 }
             } else if (n < p.N) {
+                if constexpr (PEERS) {
+                    // one copy of the 64 unrolled stores, walked once per destination buffer
+#pragma unroll 1
+                    for (int r = 0; r < pe.n; ++r) {
+                        float* dst = pe.y[r] + pe.col0;
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const int col = half * 64 + c;
-                    if (col < tr.nt) {
-                        const int row = tr.m0 + col;
-                        int orow = p.out_row ? __ldg(p.out_row + row) : row;
-                        if (p.out_identity && orow >= 0) orow = row;
-                        const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-                        if (orow >= 0) {
-                            const float out = v * __ldg(p.inv_s + row);
-                            if (p.n_peers == 0) {
-                                p.y[static_cast<size_t>(orow) * p.N + n] = out;
-                            } else {
-                                const size_t at = static_cast<size_t>(orow) * p.peer_ld + p.peer_col0 + n;
-                                for (int r = 0; r < p.n_peers; ++r) p.peer_y[r][at] = out;
+                        for (int c = 0; c < 64; ++c) {
+                            const int col = half * 64 + c;
+                            if (col < tr.nt) {
+                                const int row = tr.m0 + col;
+                                const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                                dst[static_cast<size_t>(row) * pe.ld + n] = v * __ldg(p.inv_s + row);
                             }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const int col = half * 64 + c;
+                        if (col < tr.nt) {
+                            const int row = tr.m0 + col;
+                            int orow = p.out_row ? __ldg(p.out_row + row) : row;
+                            if (p.out_identity && orow >= 0) orow = row;
+                            const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                            if (orow >= 0) p.y[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
                         }
                     }
                 }
@@ -527,9 +542,9 @@ __device__ __forceinline__ const uint8_t* group_src(const SaParams& p, long long
     return src - mis;
 }
 
-template <uint32_t TYPE>
+template <uint32_t TYPE, bool PEERS>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
+gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p, const SaPeers<PEERS> pe) {
     using G = Geo<TYPE>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -851,22 +866,31 @@ gemm_w2_sa_kernel(const __grid_constant__ SaMaps maps, const SaParams p) {
                     if (col < tr.nt) part[col * TW + wr] = v * __ldg(p.inv_s + tr.m0 + col);
                 }
             } else if (n < p.N) {
+                if constexpr (PEERS) {
+                    // one copy of the 64 unrolled stores, walked once per destination buffer
+#pragma unroll 1
+                    for (int r = 0; r < pe.n; ++r) {
+                        float* dst = pe.y[r] + pe.col0;
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const int col = half * 64 + c;
-                    if (col < tr.nt) {
-                        const int row = tr.m0 + col;
-                        int orow = p.out_row ? __ldg(p.out_row + row) : row;
-                        if (p.out_identity && orow >= 0) orow = row;
-                        const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-                        if (orow >= 0) {
-                            const float out = v * __ldg(p.inv_s + row);
-                            if (p.n_peers == 0) {
-                                p.y[static_cast<size_t>(orow) * p.N + n] = out;
-                            } else {
-                                const size_t at = static_cast<size_t>(orow) * p.peer_ld + p.peer_col0 + n;
-                                for (int r = 0; r < p.n_peers; ++r) p.peer_y[r][at] = out;
+                        for (int c = 0; c < 64; ++c) {
+                            const int col = half * 64 + c;
+                            if (col < tr.nt) {
+                                const int row = tr.m0 + col;
+                                const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                                dst[static_cast<size_t>(row) * pe.ld + n] = v * __ldg(p.inv_s + row);
                             }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const int col = half * 64 + c;
+                        if (col < tr.nt) {
+                            const int row = tr.m0 + col;
+                            int orow = p.out_row ? __ldg(p.out_row + row) : row;
+                            if (p.out_identity && orow >= 0) orow = row;
+                            const float v = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                            if (orow >= 0) p.y[static_cast<size_t>(orow) * p.N + n] = v * __ldg(p.inv_s + row);
                         }
                     }
                 }
@@ -1007,9 +1031,9 @@ __global__ void __launch_bounds__(256) quantize_sa_norm_kernel(const float* __re
 
 // Adds up the pieces of every output tile that the balanced split cut, in k order, and writes the tile to y.
 // Block (t, j) handles 16 tokens of output tile t; a tile one CTA computed whole is already in y.
-struct FixupOut { float* y; float* peer_y[MAX_PEERS]; int n_peers, peer_ld, peer_col0; };
+template <bool PEERS>
 __global__ void __launch_bounds__(256) sk_fixup_kernel(const float* __restrict__ part, long long units, int grid, int nsb, int tiles_m,
-                                                       int M, int N, const FixupOut out) {
+                                                       int M, int N, float* __restrict__ y, const SaPeers<PEERS> pe) {
     const int t = blockIdx.x;
     const long long ua = static_cast<long long>(t) * nsb, ub = ua + nsb - 1;
     // the CTA that holds unit u is the largest c with sk_start(c) <= u
@@ -1042,11 +1066,11 @@ __global__ void __launch_bounds__(256) sk_fixup_kernel(const float* __restrict__
     for (int j = 0; j < 8; ++j) {
         const int col = col0 + 2 * j;
         if (col < nt) {
-            if (out.n_peers == 0) {
-                out.y[static_cast<size_t>(m0 + col) * N + n0 + wr] = a[j];
+            if constexpr (PEERS) {
+                const size_t at = static_cast<size_t>(m0 + col) * pe.ld + pe.col0 + n0 + wr;
+                for (int r = 0; r < pe.n; ++r) pe.y[r][at] = a[j];
             } else {
-                const size_t at = static_cast<size_t>(m0 + col) * out.peer_ld + out.peer_col0 + n0 + wr;
-                for (int r = 0; r < out.n_peers; ++r) out.peer_y[r][at] = a[j];
+                y[static_cast<size_t>(m0 + col) * N + n0 + wr] = a[j];
             }
         }
     }
@@ -1134,24 +1158,46 @@ int run_sa_kernel(const SaLaunch& L, cudaStream_t st) {
     p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n;
     p.tile_tab = L.tile_tab; p.n_tiles_dev = L.n_tiles_dev; p.out_row = L.out_row; p.out_identity = L.out_identity;
     p.sk_units = L.sk_units; p.y_part = L.y_part;
+    SaPeers<true> pe{};
     if (L.peers) {
-        for (int r = 0; r < L.peers->world; ++r) p.peer_y[r] = L.peers->y[r];
-        p.n_peers = L.peers->world; p.peer_ld = L.peers->ld; p.peer_col0 = L.peers->col0;
+        for (int r = 0; r < L.peers->world; ++r) pe.y[r] = L.peers->y[r];
+        pe.n = L.peers->world; pe.ld = L.peers->ld; pe.col0 = L.peers->col0;
     }
+    const SaPeers<false> none{};
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_sa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(w2::SMEM_BYTES));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(w2::SMEM_BYTES));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(w2::SMEM_BYTES));
+        const int q = static_cast<int>(SMEM_BYTES), w = static_cast<int>(w2::SMEM_BYTES);
+        const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        cudaError_t e = cudaFuncSetAttribute(gemm_q4k_sa_kernel<false>, at, q);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_q4k_sa_kernel<true>, at, q);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0, false>, at, w);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0, false>, at, w);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K, false>, at, w);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0, true>, at, w);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0, true>, at, w);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K, true>, at, w);
         if (e != cudaSuccess) return cuda_check(e, "cudaFuncSetAttribute gemm_sa");
         configured = true;
     }
+    if (L.peers && (L.out_row || L.tile_tab)) return fail(LAPLACE_ERR_STATE, "gemm_sa: the peer-store form takes a plain dense call");
+    const bool peers = L.peers != nullptr;
     switch (L.type) {
-        case LAPLACE_TYPE_Q4_K: gemm_q4k_sa_kernel<<<L.grid, THREADS, SMEM_BYTES, st>>>(maps, p); break;
-        case LAPLACE_TYPE_Q4_0: w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p); break;
-        case LAPLACE_TYPE_Q8_0: w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p); break;
-        case LAPLACE_TYPE_Q6_K: w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p); break;
+        case LAPLACE_TYPE_Q4_K:
+            if (peers) gemm_q4k_sa_kernel<true><<<L.grid, THREADS, SMEM_BYTES, st>>>(maps, p, pe);
+            else gemm_q4k_sa_kernel<false><<<L.grid, THREADS, SMEM_BYTES, st>>>(maps, p, none);
+            break;
+        case LAPLACE_TYPE_Q4_0:
+            if (peers) w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0, true><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p, pe);
+            else w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q4_0, false><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p, none);
+            break;
+        case LAPLACE_TYPE_Q8_0:
+            if (peers) w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0, true><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p, pe);
+            else w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q8_0, false><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p, none);
+            break;
+        case LAPLACE_TYPE_Q6_K:
+            if (peers) w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K, true><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p, pe);
+            else w2::gemm_w2_sa_kernel<LAPLACE_TYPE_Q6_K, false><<<L.grid, THREADS, w2::SMEM_BYTES, st>>>(maps, p, none);
+            break;
         default: return LAPLACE_UNSUPPORTED;
     }
     c.launches++;
@@ -1239,13 +1285,15 @@ int gemm_sa_on_scratch(uint8_t* scratch, const SaPlan& pl, const float* x, const
     L.grid = pl.sp.grid;
     if ((rc = run_sa_kernel(L, st))) return rc;
     if (pl.sp.units) {
-        FixupOut fo{};
-        fo.y = y;
+        const dim3 fg(pl.tiles_m * pl.tiles_n, TT / 16);
         if (peers) {
-            for (int r = 0; r < peers->world; ++r) fo.peer_y[r] = peers->y[r];
-            fo.n_peers = peers->world; fo.peer_ld = peers->ld; fo.peer_col0 = peers->col0;
+            SaPeers<true> pe{};
+            for (int r = 0; r < peers->world; ++r) pe.y[r] = peers->y[r];
+            pe.n = peers->world; pe.ld = peers->ld; pe.col0 = peers->col0;
+            sk_fixup_kernel<true><<<fg, 256, 0, st>>>(L.y_part, pl.sp.units, pl.sp.grid, K / 256, pl.tiles_m, M, N, nullptr, pe);
+        } else {
+            sk_fixup_kernel<false><<<fg, 256, 0, st>>>(L.y_part, pl.sp.units, pl.sp.grid, K / 256, pl.tiles_m, M, N, y, SaPeers<false>{});
         }
-        sk_fixup_kernel<<<dim3(pl.tiles_m * pl.tiles_n, TT / 16), 256, 0, st>>>(L.y_part, pl.sp.units, pl.sp.grid, K / 256, pl.tiles_m, M, N, fo);
         c.launches++;
         return cuda_check(cudaGetLastError(), "sk_fixup launch");
     }
@@ -1292,7 +1340,7 @@ int launch_gemm_sa_multi(const float* x, const float* norm_w, float eps, float* 
 }
 
 // The same call for a row-split matrix: this GPU's N columns of the result go to every GPU's [M][ld] buffer at column col0
-// (see SaParams::peer_y). The stores are complete when the launched kernels are; announcing them to the other GPUs is
+// (see SaPeers). The stores are complete when the launched kernels are; announcing them to the other GPUs is
 // the caller's next step (laplace_cuda_allgather_step_wait_dev).
 int launch_gemm_sa_peers(const float* x, const uint8_t* w, uint32_t type, const PeerOut& po, int M, int K, int N, cudaStream_t st) {
     int rc = check_args(x, w, type, M, K, N);
