@@ -7,12 +7,15 @@
 //   dequantize_kernel        every type, 16 values per thread, the reference's expressions with separate roundings
 //                            (d * sc * q - dmin * m and the like), so the result is bit-identical to dequantize()
 //   embed_rows_kernel        rows tokens[m] of the embedding table, times the model's embedding scale
-//   gemv_f32act_kernel       fp32 activations against on-the-fly dequantized rows: one warp per weight row, lanes
-//                            over groups of 16 values; HBM-bound, a few hundred GB/s to a few TB/s depending on the
-//                            type's bytes per value - these types carry embeddings, LM heads and the odd tensor of a
-//                            mixed-precision file, not the bulk of the weights
+//   gemv_f32act_kernel       fp32 activations against on-the-fly dequantized rows: one warp per weight row; plain
+//                            rows stream at 5 TB/s and more (an F16 LM head of 32,000 rows: 48 us), K-quant rows at
+//                            0.5-0.8 TB/s (bound by the per-value arithmetic) - these types carry embeddings, LM
+//                            heads and the odd tensor of a mixed-precision file, not the bulk of the weights
 //   softcap_kernel           logits = tanh(logits / cap) * cap (src/model.cpp:399-406)
+#include <type_traits>
+
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "lp_common.cuh"
 
@@ -23,7 +26,7 @@ constexpr uint32_t T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q5_0 = 6, T_Q8_0 = 8, T_Q
                    T_Q5_K = 13, T_Q6_K = 14, T_BF16 = 30;
 
 struct Geo { int elems, bytes; };       // per block; plain types are handled as "blocks" of 16 values
-__host__ __device__ inline Geo geo_of(uint32_t t) {
+__host__ __device__ constexpr Geo geo_of(uint32_t t) {
     switch (t) {
         case T_F32: return {16, 64};
         case T_F16: case T_BF16: return {16, 32};
@@ -207,35 +210,240 @@ __global__ void __launch_bounds__(256) embed_rows_kernel(const uint8_t* __restri
     }
 }
 
-// y[m][j] = sum_k x[m][k] * dequantized(w[j][k]) for M <= 8 activation rows: a warp per weight row.
-template <int M>
-__global__ void __launch_bounds__(256) gemv_f32act_kernel(const float* __restrict__ x, const uint8_t* __restrict__ w, uint32_t type,
+// ---- K-quant blocks read from shared memory -------------------------------------------------------------------
+// The fp32-activation GEMV stages each weight block at a 16-byte aligned shared address, so that a lane fetches
+// the 16 quants of its group (and their high bits) with one 16-byte read each instead of 16 single-byte loads from
+// global memory (which cost one L1 lookup per byte and held these types at 0.4-0.5 TB/s). Same expressions and
+// roundings as decode16 above.
+__device__ __forceinline__ uint4 lds_u4(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint32_t byte_of(const uint4& q, int l) {          // l is a compile-time constant after unrolling
+    const uint32_t w = l < 4 ? q.x : l < 8 ? q.y : l < 12 ? q.z : q.w;
+    return (w >> (8 * (l & 3))) & 0xFFu;
+}
+template <uint32_t TYPE>
+__device__ __forceinline__ void decode16_staged(const uint8_t* __restrict__ b, int g, float (&v)[16]) {
+    if constexpr (TYPE == T_Q5_K) {
+        const uint4 head = lds_u4(b);                    // d, dmin, scales[12]
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(head.x & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(head.x >> 16)));
+        const int jb = g >> 2, sub = (g >> 1) & 1, l0 = 16 * (g & 1), j = 2 * jb + sub;
+        auto sbyte = [&](int i) { return ((i < 4 ? head.y : i < 8 ? head.z : head.w) >> (8 * (i & 3))) & 0xFFu; };
+        int sc, mn;
+        if (j < 4) { sc = sbyte(j) & 63; mn = sbyte(j + 4) & 63; }
+        else { sc = (sbyte(j + 4) & 0xF) | ((sbyte(j - 4) >> 6) << 4); mn = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4); }
+        const float ds = __fmul_rn(d, static_cast<float>(sc)), mm = __fmul_rn(dmin, static_cast<float>(mn));
+        const uint4 qs = lds_u4(b + 48 + 32 * jb + l0), qh = lds_u4(b + 16 + l0);
+#pragma unroll
+        for (int l = 0; l < 16; ++l) {
+            const uint32_t byte = byte_of(qs, l);
+            int q = sub ? (byte >> 4) : (byte & 0xF);
+            q += 16 * ((byte_of(qh, l) >> j) & 1);
+            v[l] = __fsub_rn(__fmul_rn(ds, static_cast<float>(q)), mm);
+        }
+    } else if constexpr (TYPE == T_Q2_K) {
+        const uint32_t dd = *reinterpret_cast<const uint32_t*>(b + 80);
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(dd & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(dd >> 16)));
+        const int half = g >> 3, jj = g & 7, grp = jj >> 1, lo = jj & 1;
+        const uint32_t scb = b[g];
+        const float ds = __fmul_rn(d, static_cast<float>(scb & 0xF)), mm = __fmul_rn(dmin, static_cast<float>(scb >> 4));
+        const uint4 qs = lds_u4(b + 16 + half * 32 + lo * 16);
+#pragma unroll
+        for (int l = 0; l < 16; ++l) {
+            const int q = (byte_of(qs, l) >> (grp * 2)) & 3;
+            v[l] = __fsub_rn(__fmul_rn(ds, static_cast<float>(q)), mm);
+        }
+    } else {                                             // Q3_K
+        const uint4 tail = lds_u4(b + 96);               // scales[12], d
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(tail.w & 0xffffu)));
+        auto sbyte = [&](int i) { return ((i < 4 ? tail.x : i < 8 ? tail.y : tail.z) >> (8 * (i & 3))) & 0xFFu; };
+        const int lo4 = g < 8 ? (sbyte(g) & 0xF) : (sbyte(g - 8) >> 4);
+        const int hi2 = (sbyte(8 + (g & 3)) >> (2 * (g >> 2))) & 3;
+        const float ds = __fmul_rn(d, static_cast<float>((lo4 | (hi2 << 4)) - 32));
+        const int g32 = g >> 1, li0 = 16 * (g & 1);
+        const uint4 qs = lds_u4(b + 32 + (g32 >> 2) * 32 + li0), hm = lds_u4(b + li0);
+#pragma unroll
+        for (int l = 0; l < 16; ++l) {
+            const int low2 = (byte_of(qs, l) >> ((g32 & 3) * 2)) & 3;
+            const int hbit = (byte_of(hm, l) >> g32) & 1;
+            v[l] = __fmul_rn(ds, static_cast<float>(low2 - 4 + 4 * hbit));
+        }
+    }
+}
+
+// x in shared memory: 16-byte piece f of a row sits at piece (f & ~3) | ((f & 3) ^ ((f >> 3) & 3)). A lane that owns 16
+// consecutive values (4 pieces) reads piece i of every lane in one instruction; unswizzled, the lanes of a quarter warp
+// would hit two 16-byte bank groups four times each.
+__device__ __forceinline__ int x_piece(int f) { return (f & ~3) | ((f & 3) ^ ((f >> 3) & 3)); }
+
+// y[m][j] = sum_k x[m][k] * dequantized(w[j][k]) for M <= 8 activation rows: a warp per weight row. The type is a
+// template parameter (with it as a run-time argument the decoder's switch and the divisions by the groups per block sat
+// inside the loop).
+constexpr int F32ACT_WARPS = 8;
+template <uint32_t TYPE> struct Stage {                   // staging of K-quant blocks: two blocks (512 values) per warp step
+    static constexpr bool on = TYPE == T_Q2_K || TYPE == T_Q3_K || TYPE == T_Q5_K;
+    static constexpr int bytes = geo_of(TYPE).bytes;
+    static constexpr int pitch = (bytes + 15) & ~15;
+    static constexpr int unit = TYPE == T_Q5_K ? 16 : TYPE == T_Q2_K ? 4 : 2;      // load width the block size allows
+    static constexpr int units_per_block = bytes / unit;
+    static constexpr int per_lane = (2 * units_per_block + 31) / 32;
+    static constexpr int depth = 4;                                                // steps fetched back to back
+    static constexpr int warp_bytes = on ? depth * 2 * pitch : 0;
+};
+template <int M, uint32_t TYPE>
+__global__ void __launch_bounds__(256) gemv_f32act_kernel(const float* __restrict__ x, const uint8_t* __restrict__ w,
                                                           float* __restrict__ y, int K, int N, int x_in_smem) {
-    extern __shared__ float xs[];
-    const Geo geo = geo_of(type);
-    const int gpb = geo.elems / 16, groups = K / 16;
+    extern __shared__ __align__(16) uint8_t f32act_smem[];
+    using S = Stage<TYPE>;
+    uint8_t* stage_base = f32act_smem;
+    float* xs = reinterpret_cast<float*>(f32act_smem + F32ACT_WARPS * S::warp_bytes);
+    constexpr Geo geo = geo_of(TYPE);
+    constexpr int gpb = geo.elems / 16;
+    const int groups = K / 16;
     const size_t rb = static_cast<size_t>(K / geo.elems) * geo.bytes;
     if (x_in_smem) {
-        for (int i = threadIdx.x; i < M * K / 4; i += blockDim.x) reinterpret_cast<float4*>(xs)[i] = __ldg(reinterpret_cast<const float4*>(x) + i);
+        const int per_row = K / 4;
+        for (int i = threadIdx.x; i < M * per_row; i += blockDim.x) {
+            const int m = i / per_row, f = i - m * per_row;
+            reinterpret_cast<float4*>(xs)[m * per_row + x_piece(f)] = __ldg(reinterpret_cast<const float4*>(x) + i);
+        }
         __syncthreads();
     }
     const float* xa = x_in_smem ? xs : x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    const bool plain_fast = (TYPE == T_F32 || TYPE == T_F16 || TYPE == T_BF16) &&
+                            (reinterpret_cast<uintptr_t>(w) & (TYPE == T_F32 ? 15 : 7)) == 0;
+    // staged K-quant walk: needs block addresses that are multiples of the load width
+    const bool staged = S::on && (reinterpret_cast<uintptr_t>(w) & (S::unit - 1)) == 0;
+    // the fp32 activations of group gi, piece i (values 16 gi + 4 i .. + 3) of row m
+    auto x4 = [&](int m, int gi, int i) -> float4 {
+        const float4* base = reinterpret_cast<const float4*>(xa + static_cast<size_t>(m) * K);
+        return x_in_smem ? base[x_piece(4 * gi + i)] : __ldg(base + 4 * gi + i);
+    };
     for (int j = blockIdx.x * wpb + warp; j < N; j += gridDim.x * wpb) {
         const uint8_t* row = w + static_cast<size_t>(j) * rb;
         float acc[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m] = 0.f;
-        for (int gi = lane; gi < groups; gi += 32) {
+        if constexpr (TYPE == T_F32 || TYPE == T_F16 || TYPE == T_BF16) {
+            // Plain rows: lane l takes values 128 i + 4 l .. + 3, so that a warp reads 128 consecutive values of
+            // the row per step. Needs rows that start on an 8-byte (F32: 16-byte) boundary; row lengths are
+            // multiples of 32 bytes.
+            if (plain_fast) {
+                using Wv = typename std::conditional<TYPE == T_F32, float4, uint2>::type;
+                for (int k0 = lane * 4; k0 < K; k0 += 512) {
+                    Wv t[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)                  // four loads in flight before the first use
+                        if (k0 + 128 * u < K) t[u] = __ldg(reinterpret_cast<const Wv*>(row) + ((k0 + 128 * u) >> 2));
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int k = k0 + 128 * u;
+                        if (k < K) {
+                            float v0, v1, v2, v3;
+                            if constexpr (TYPE == T_F32) {
+                                v0 = t[u].x; v1 = t[u].y; v2 = t[u].z; v3 = t[u].w;
+                            } else if constexpr (TYPE == T_F16) {
+                                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t[u].x));
+                                const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t[u].y));
+                                v0 = a.x; v1 = a.y; v2 = b.x; v3 = b.y;
+                            } else {
+                                v0 = __uint_as_float(t[u].x << 16); v1 = __uint_as_float(t[u].x & 0xffff0000u);
+                                v2 = __uint_as_float(t[u].y << 16); v3 = __uint_as_float(t[u].y & 0xffff0000u);
+                            }
+#pragma unroll
+                            for (int m = 0; m < M; ++m) {
+                                const float4 xv = x4(m, k >> 4, (k >> 2) & 3);
+                                acc[m] = fmaf(xv.w, v3, fmaf(xv.z, v2, fmaf(xv.y, v1, fmaf(xv.x, v0, acc[m]))));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if constexpr (S::on) {
+            if (staged) {
+                // Two blocks (512 values, one group of 16 per lane) per step: the warp copies them with coalesced
+                // loads of the widest unit the block size allows into its staging area.
+                uint8_t* st = stage_base + warp * S::warp_bytes;
+                const int n_blocks = K / geo.elems, n_steps = (n_blocks + 1) / 2;
+                auto fetch = [&](int step, uint32_t (&r)[S::per_lane][S::unit == 16 ? 4 : 1]) {
+                    const int units = (n_blocks - 2 * step >= 2 ? 2 : 1) * S::units_per_block;
+                    const uint8_t* src = row + static_cast<size_t>(2 * step) * S::bytes;
+#pragma unroll
+                    for (int t = 0; t < S::per_lane; ++t) {
+                        const int u = lane + 32 * t;
+                        if (u < units) {
+                            if constexpr (S::unit == 16) {
+                                const uint4 q = __ldg(reinterpret_cast<const uint4*>(src) + u);
+                                r[t][0] = q.x; r[t][1] = q.y; r[t][2] = q.z; r[t][3] = q.w;
+                            } else if constexpr (S::unit == 4) {
+                                r[t][0] = __ldg(reinterpret_cast<const uint32_t*>(src) + u);
+                            } else {
+                                r[t][0] = __ldg(reinterpret_cast<const unsigned short*>(src) + u);
+                            }
+                        }
+                    }
+                };
+                auto put = [&](int slot, int step, const uint32_t (&r)[S::per_lane][S::unit == 16 ? 4 : 1]) {
+                    const int units = (n_blocks - 2 * step >= 2 ? 2 : 1) * S::units_per_block;
+                    uint8_t* dst = st + slot * 2 * S::pitch;
+#pragma unroll
+                    for (int t = 0; t < S::per_lane; ++t) {
+                        const int u = lane + 32 * t;
+                        if (u < units) {
+                            const int blk = u >= S::units_per_block ? 1 : 0;
+                            uint8_t* at = dst + blk * S::pitch + (u - blk * S::units_per_block) * S::unit;
+                            if constexpr (S::unit == 16) *reinterpret_cast<uint4*>(at) = make_uint4(r[t][0], r[t][1], r[t][2], r[t][3]);
+                            else if constexpr (S::unit == 4) *reinterpret_cast<uint32_t*>(at) = r[t][0];
+                            else *reinterpret_cast<unsigned short*>(at) = static_cast<unsigned short>(r[t][0]);
+                        }
+                    }
+                };
+                // DEPTH steps are fetched into registers back to back (loads in flight), staged, then decoded.
+                constexpr int DEPTH = S::depth;
+                for (int s0 = 0; s0 < n_steps; s0 += DEPTH) {
+                    uint32_t regs[DEPTH][S::per_lane][S::unit == 16 ? 4 : 1];
+#pragma unroll
+                    for (int d = 0; d < DEPTH; ++d)
+                        if (s0 + d < n_steps) fetch(s0 + d, regs[d]);
+                    __syncwarp();                               // every lane is done reading the previous batch
+#pragma unroll
+                    for (int d = 0; d < DEPTH; ++d)
+                        if (s0 + d < n_steps) put(d, s0 + d, regs[d]);
+                    __syncwarp();                               // the batch is in shared memory
+#pragma unroll
+                    for (int d = 0; d < DEPTH; ++d) {
+                        const int gi = 32 * (s0 + d) + lane;
+                        if (gi < groups) {
+                            float v[16];
+                            decode16_staged<TYPE>(st + d * 2 * S::pitch + (lane >> 4) * S::pitch, lane & 15, v);
+#pragma unroll
+                            for (int m = 0; m < M; ++m) {
+                                float sacc = 0.f;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float4 t = x4(m, gi, i);
+                                    sacc = fmaf(t.x, v[4 * i], sacc); sacc = fmaf(t.y, v[4 * i + 1], sacc);
+                                    sacc = fmaf(t.z, v[4 * i + 2], sacc); sacc = fmaf(t.w, v[4 * i + 3], sacc);
+                                }
+                                acc[m] += sacc;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll 2
+        for (int gi = lane; gi < ((plain_fast || staged) ? 0 : groups); gi += 32) {
             float v[16];
-            decode16(type, row + (gi / gpb) * geo.bytes, gi % gpb, v);
+            decode16(TYPE, row + (gi / gpb) * geo.bytes, gi % gpb, v);
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                const float4* xp = reinterpret_cast<const float4*>(xa + static_cast<size_t>(m) * K + gi * 16);
                 float s = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float4 t = x_in_smem ? xp[i] : __ldg(xp + i);
+                    const float4 t = x4(m, gi, i);
                     s = fmaf(t.x, v[4 * i], s); s = fmaf(t.y, v[4 * i + 1], s); s = fmaf(t.z, v[4 * i + 2], s); s = fmaf(t.w, v[4 * i + 3], s);
                 }
                 acc[m] += s;
@@ -256,22 +464,47 @@ __global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ y, lon
         y[i] = __fmul_rn(tanhf(__fmul_rn(y[i], inv_cap)), cap);
 }
 
-template <int M>
-cudaError_t launch_f32act(const float* x, const uint8_t* w, uint32_t type, float* y, int K, int N, cudaStream_t st) {
+template <int M, uint32_t TYPE>
+cudaError_t launch_f32act_typed(const float* x, const uint8_t* w, float* y, int K, int N, cudaStream_t st) {
     const size_t xbytes = static_cast<size_t>(M) * K * sizeof(float);
     const int in_smem = xbytes <= 96 * 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_f32act_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemv_f32act_kernel<M, TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 104 * 1024);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    const int wpb = 8;
+    const int wpb = F32ACT_WARPS;
     long long blocks = (static_cast<long long>(N) + wpb - 1) / wpb;
-    const long long cap = static_cast<long long>(ctx().sm_count) * (in_smem && xbytes > 48 * 1024 ? 2 : 8);
+    // One wave: as many CTAs as are resident at once (registers and the x copy in shared memory decide), each walking
+    // rows at the grid's stride. A grid of 8 CTAs per SM where 6 fit ran a second, one-third-full wave.
+    static size_t occ_for = ~size_t(0);
+    static int occ = 1;
+    const size_t dyn = (in_smem ? xbytes : 0) + static_cast<size_t>(F32ACT_WARPS) * Stage<TYPE>::warp_bytes;
+    if (occ_for != dyn) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_f32act_kernel<M, TYPE>, 256, dyn);
+        if (e != cudaSuccess) return e;
+        occ = n < 1 ? 1 : n;
+        occ_for = dyn;
+    }
+    const long long cap = static_cast<long long>(ctx().sm_count) * occ;
     if (blocks > cap) blocks = cap;
-    gemv_f32act_kernel<M><<<static_cast<int>(blocks), 256, in_smem ? xbytes : 0, st>>>(x, w, type, y, K, N, in_smem);
+    gemv_f32act_kernel<M, TYPE><<<static_cast<int>(blocks), 256, dyn, st>>>(x, w, y, K, N, in_smem);
     return cudaGetLastError();
+}
+
+template <int M>
+cudaError_t launch_f32act(const float* x, const uint8_t* w, uint32_t type, float* y, int K, int N, cudaStream_t st) {
+    switch (type) {
+        case T_F32:  return launch_f32act_typed<M, T_F32>(x, w, y, K, N, st);
+        case T_F16:  return launch_f32act_typed<M, T_F16>(x, w, y, K, N, st);
+        case T_BF16: return launch_f32act_typed<M, T_BF16>(x, w, y, K, N, st);
+        case T_Q2_K: return launch_f32act_typed<M, T_Q2_K>(x, w, y, K, N, st);
+        case T_Q3_K: return launch_f32act_typed<M, T_Q3_K>(x, w, y, K, N, st);
+        case T_Q5_K: return launch_f32act_typed<M, T_Q5_K>(x, w, y, K, N, st);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace
