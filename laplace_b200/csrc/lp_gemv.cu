@@ -52,6 +52,7 @@ struct KParams {
     int            n_seg;
     int            act_rows;        // rows of x quantized into shared memory
     int            per_seg_x;
+    int            act_regs;        // 32-value-block types, one activation row, K <= 4096: activations in registers
     uint32_t       rb;              // bytes per weight row
     int            rows_per_unit;   // whole rows per bulk copy (when n_slices == 1)
     int            n_slices;        // K-slices per row
@@ -222,29 +223,37 @@ template <> struct Traits<LAPLACE_TYPE_Q4_K> {
 };
 
 // Q4_0: item = one 18-byte block. The second term is d_w * 8 * sum_x.
+// (The 32-value-block types split an item into load_w, the weight side, and dot, one activation block against it, so
+// that the row loop can keep a lane's activation blocks in registers, see ACT_REGS in the kernel.)
 template <> struct Traits<LAPLACE_TYPE_Q4_0> {
     static constexpr int ITEMS_PER_BLOCK = 1;
+    struct W { float d; uint32_t q[4]; };
+    __device__ static __forceinline__ void load_w(uint32_t row, int i, W& w) {
+        const uint32_t blk = row + i * Q4_0_BYTES;
+        w.d = half_bits_to_float(lds16(blk));
+        lds16B_align2(blk + 2, w.q);
+    }
+    __device__ static __forceinline__ float dot(const W& w, const uint4& x0, const uint4& x1, float dx, float sx, float acc) {
+        const uint32_t xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
+        int ul = 0, uh = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            ul = dp4a_us(w.q[t] & 0x0f0f0f0fu, xl[t], ul);
+            uh = dp4a_us(w.q[t] & 0xf0f0f0f0u, xh[t], uh);
+        }
+        const int u = ul + (uh >> 4);
+        return fmaf(w.d * dx, static_cast<float>(u), acc) - w.d * 8.0f * sx;
+    }
     template <int M>
     __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
                                 float (&acc)[M]) {
-        const uint32_t blk = row + i * Q4_0_BYTES;
-        const float d = half_bits_to_float(lds16(blk));
-        uint32_t wq[4];
-        lds16B_align2(blk + 2, wq);
+        W w;
+        load_w(row, i, w);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const uint32_t q = act_q(act + m * astride, i), ds = act_d(act + m * astride, i);
             const uint4 x0 = lds128(q), x1 = lds128(q + 16);
-            const float dx = __uint_as_float(lds32(ds)), sx = __uint_as_float(lds32(ds + 16));
-            const uint32_t xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
-            int ul = 0, uh = 0;
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                ul = dp4a_us(wq[t] & 0x0f0f0f0fu, xl[t], ul);
-                uh = dp4a_us(wq[t] & 0xf0f0f0f0u, xh[t], uh);
-            }
-            const int u = ul + (uh >> 4);
-            acc[m] = fmaf(d * dx, static_cast<float>(u), acc[m]) - d * 8.0f * sx;
+            acc[m] = dot(w, x0, x1, __uint_as_float(lds32(ds)), __uint_as_float(lds32(ds + 16)), acc[m]);
         }
     }
 };
@@ -259,31 +268,37 @@ template <> struct Traits<LAPLACE_TYPE_Q5_0> {
     __device__ static __forceinline__ uint32_t sign_fill(uint32_t four_bits) {
         return (((four_bits * 0x00204081u) & 0x01010101u) ^ 0x01010101u) * 0xF0u;
     }
-    template <int M>
-    __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
-                                float (&acc)[M]) {
+    struct W { float d; uint32_t lo[4], hi[4]; };
+    __device__ static __forceinline__ void load_w(uint32_t row, int i, W& w) {
         const uint32_t blk = row + i * Q5_0_BYTES;
-        const float d = half_bits_to_float(lds16(blk));
+        w.d = half_bits_to_float(lds16(blk));
         const uint32_t qh = lds16(blk + 2) | (lds16(blk + 4) << 16);
         uint32_t wq[4];
         lds16B_align2(blk + 6, wq);
-        uint32_t wl[4], wh[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            wl[t] = (wq[t] & 0x0f0f0f0fu) | sign_fill((qh >> (4 * t)) & 15u);
-            wh[t] = ((wq[t] >> 4) & 0x0f0f0f0fu) | sign_fill((qh >> (16 + 4 * t)) & 15u);
+            w.lo[t] = (wq[t] & 0x0f0f0f0fu) | sign_fill((qh >> (4 * t)) & 15u);
+            w.hi[t] = ((wq[t] >> 4) & 0x0f0f0f0fu) | sign_fill((qh >> (16 + 4 * t)) & 15u);
         }
+    }
+    __device__ static __forceinline__ float dot(const W& w, const uint4& x0, const uint4& x1, float dx, float, float acc) {
+        int ua = 0, ub = 0;
+        ua = dp4a_ss(w.lo[0], x0.x, ua); ub = dp4a_ss(w.lo[1], x0.y, ub);
+        ua = dp4a_ss(w.lo[2], x0.z, ua); ub = dp4a_ss(w.lo[3], x0.w, ub);
+        ua = dp4a_ss(w.hi[0], x1.x, ua); ub = dp4a_ss(w.hi[1], x1.y, ub);
+        ua = dp4a_ss(w.hi[2], x1.z, ua); ub = dp4a_ss(w.hi[3], x1.w, ub);
+        return fmaf(w.d * dx, static_cast<float>(ua + ub), acc);
+    }
+    template <int M>
+    __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
+                                float (&acc)[M]) {
+        W w;
+        load_w(row, i, w);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const uint32_t q = act_q(act + m * astride, i);
             const uint4 x0 = lds128(q), x1 = lds128(q + 16);
-            const float dx = __uint_as_float(lds32(act_d(act + m * astride, i)));
-            int ua = 0, ub = 0;
-            ua = dp4a_ss(wl[0], x0.x, ua); ub = dp4a_ss(wl[1], x0.y, ub);
-            ua = dp4a_ss(wl[2], x0.z, ua); ub = dp4a_ss(wl[3], x0.w, ub);
-            ua = dp4a_ss(wh[0], x1.x, ua); ub = dp4a_ss(wh[1], x1.y, ub);
-            ua = dp4a_ss(wh[2], x1.z, ua); ub = dp4a_ss(wh[3], x1.w, ub);
-            acc[m] = fmaf(d * dx, static_cast<float>(ua + ub), acc[m]);
+            acc[m] = dot(w, x0, x1, __uint_as_float(lds32(act_d(act + m * astride, i))), 0.f, acc[m]);
         }
     }
 };
@@ -291,25 +306,31 @@ template <> struct Traits<LAPLACE_TYPE_Q5_0> {
 // Q8_0: item = one 34-byte block.
 template <> struct Traits<LAPLACE_TYPE_Q8_0> {
     static constexpr int ITEMS_PER_BLOCK = 1;
+    struct W { float d; uint32_t lo[4], hi[4]; };
+    __device__ static __forceinline__ void load_w(uint32_t row, int i, W& w) {
+        const uint32_t blk = row + i * Q8_0_BYTES;
+        w.d = half_bits_to_float(lds16(blk));
+        lds16B_align2(blk + 2, w.lo);
+        lds16B_align2(blk + 18, w.hi);
+    }
+    __device__ static __forceinline__ float dot(const W& w, const uint4& x0, const uint4& x1, float dx, float, float acc) {
+        int ua = 0, ub = 0;
+        ua = dp4a_ss(w.lo[0], x0.x, ua); ub = dp4a_ss(w.lo[1], x0.y, ub);
+        ua = dp4a_ss(w.lo[2], x0.z, ua); ub = dp4a_ss(w.lo[3], x0.w, ub);
+        ua = dp4a_ss(w.hi[0], x1.x, ua); ub = dp4a_ss(w.hi[1], x1.y, ub);
+        ua = dp4a_ss(w.hi[2], x1.z, ua); ub = dp4a_ss(w.hi[3], x1.w, ub);
+        return fmaf(w.d * dx, static_cast<float>(ua + ub), acc);
+    }
     template <int M>
     __device__ static void item(uint32_t row, int i, uint32_t act, uint32_t astride, uint32_t, uint32_t,
                                 float (&acc)[M]) {
-        const uint32_t blk = row + i * Q8_0_BYTES;
-        const float d = half_bits_to_float(lds16(blk));
-        uint32_t w0[4], w1[4];
-        lds16B_align2(blk + 2, w0);
-        lds16B_align2(blk + 18, w1);
+        W w;
+        load_w(row, i, w);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const uint32_t q = act_q(act + m * astride, i);
             const uint4 x0 = lds128(q), x1 = lds128(q + 16);
-            const float dx = __uint_as_float(lds32(act_d(act + m * astride, i)));
-            int ua = 0, ub = 0;
-            ua = dp4a_ss(w0[0], x0.x, ua); ub = dp4a_ss(w0[1], x0.y, ub);
-            ua = dp4a_ss(w0[2], x0.z, ua); ub = dp4a_ss(w0[3], x0.w, ub);
-            ua = dp4a_ss(w1[0], x1.x, ua); ub = dp4a_ss(w1[1], x1.y, ub);
-            ua = dp4a_ss(w1[2], x1.z, ua); ub = dp4a_ss(w1[3], x1.w, ub);
-            acc[m] = fmaf(d * dx, static_cast<float>(ua + ub), acc[m]);
+            acc[m] = dot(w, x0, x1, __uint_as_float(lds32(act_d(act + m * astride, i))), 0.f, acc[m]);
         }
     }
 };
@@ -438,6 +459,9 @@ __global__ void __launch_bounds__((WARPS + PW + (PEERS ? 1 : 0)) * 32, 1) gemv_s
     const int g0 = bx * p.rows_q + (bx < p.rows_r ? bx : p.rows_r);
     const int cta_rows = p.rows_q + (bx < p.rows_r ? 1 : 0);
     constexpr int RW = (RESIDENT && M > 1) ? 2 : 1;          // activation rows a warp keeps in registers
+    // register-held activations for the 32-value-block types (one activation row, 20 consumer warps: 89 registers a thread)
+    constexpr bool ACT_REGS = !RESIDENT && M == 1 && WARPS == 20 &&
+                              (TYPE == LAPLACE_TYPE_Q4_0 || TYPE == LAPLACE_TYPE_Q5_0 || TYPE == LAPLACE_TYPE_Q8_0);
     constexpr int G = RESIDENT ? (M + RW - 1) / RW : 1;       // warps per ring group
     constexpr int GROUPS = WARPS / G;
     static_assert(WARPS % G == 0, "consumer warps must split into whole groups");
@@ -791,6 +815,48 @@ __global__ void __launch_bounds__((WARPS + PW + (PEERS ? 1 : 0)) * 32, 1) gemv_s
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(grp, slot));                  // slot may be refilled
         }
+    } else if (ACT_REGS && p.act_regs) {
+        // One activation row, whole rows of at most 128 blocks of 32 values (K <= 4096): lane l keeps the activation
+        // blocks l, l + 32, l + 64, l + 96 in registers, so the row loop reads only weights from shared memory.
+        if constexpr (ACT_REGS) {
+            uint4 xa[4][2];
+            float xd[4], xs[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = lane + 32 * k;
+                if (i < n_items) {
+                    const uint32_t q = act_q(act0, i), ds = act_d(act0, i);
+                    xa[k][0] = lds128(q); xa[k][1] = lds128(q + 16);
+                    xd[k] = __uint_as_float(lds32(ds)); xs[k] = __uint_as_float(lds32(ds + 16));
+                } else {
+                    xa[k][0] = xa[k][1] = make_uint4(0u, 0u, 0u, 0u);
+                    xd[k] = xs[k] = 0.f;
+                }
+            }
+            for (; wk.template next<EXT>(p, un); ++u) {
+                const int slot = u % p.n_slots;
+                if (!mbar_wait_bounded(bar_full(grp, slot), (u / p.n_slots) & 1)) { ok = false; break; }
+                const uint32_t mis = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(un.src) & 15u);
+                for (int r = 0; r < un.nrows; ++r) {
+                    const uint32_t row = ring + slot * p.slot_bytes + mis + r * p.rb;
+                    float a = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int i = lane + 32 * k;
+                        if (i < n_items) {
+                            typename Traits<TYPE>::W w;
+                            Traits<TYPE>::load_w(row, i, w);
+                            a = Traits<TYPE>::dot(w, xa[k][0], xa[k][1], xd[k], xs[k], a);
+                        }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                    if (lane == 0) store_result<PEERS, EXT>(p, smem, g0, static_cast<size_t>(un.seg), un.j + r, a, un.mat);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty(grp, slot));
+            }
+        }
     } else {
         float acc[M];
 #pragma unroll
@@ -899,7 +965,11 @@ cudaError_t launch_typed(int M, bool resident, bool long_rows, const KParams& p,
                 if (resident) return (PE && p.peers.world) ? launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st)
                                                            : launch_one<TYPE, 1, 16, true, PRODUCER_WARPS, false, EXT>(p, grid, smem, st);
             }
+            if constexpr (TYPE == LAPLACE_TYPE_Q4_0 || TYPE == LAPLACE_TYPE_Q5_0 || TYPE == LAPLACE_TYPE_Q8_0) {
+                if (p.act_regs) return launch_one<TYPE, 1, 20, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+            }
             if (long_rows) return launch_one<TYPE, 1, 16, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
+            if constexpr (TYPE == LAPLACE_TYPE_Q6_K) return launch_one<TYPE, 1, 20, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
             return launch_one<TYPE, 1, 24, false, PRODUCER_WARPS, PE, EXT>(p, grid, smem, st);
 #define LP_RESIDENT_CASE(m) \
         if constexpr (TYPE == LAPLACE_TYPE_Q4_K) { if (resident) return launch_one<TYPE, m, RESIDENT_WARPS, true, RESIDENT_PRODUCER_WARPS, PE, EXT>(p, grid, smem, st); }
@@ -958,7 +1028,10 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
     // one activation row, rows of 8 KB and more (K = 14336): fewer consumer warps, so that a warp's ring slot
     // holds a K-slice of a few KB (small bulk copies are issue-bound)
     const bool long_rows = !resident && a.M == 1 && row_bytes(a.type, a.K) >= 8192;
-    const int cwarps = resident ? (a.M == 1 ? 16 : RESIDENT_WARPS) : (a.M <= 2 && !long_rows ? 24 : 16);
+    // one activation row against blocks of 32 values, at most four blocks per lane: activations in registers (16 warps)
+    const bool act_regs = a.M == 1 && !a.per_seg_x && !a.peers && a.K <= 4096 &&
+                          (a.type == LAPLACE_TYPE_Q4_0 || a.type == LAPLACE_TYPE_Q5_0 || a.type == LAPLACE_TYPE_Q8_0);
+    const int cwarps = resident ? (a.M == 1 ? 16 : RESIDENT_WARPS) : (act_regs || (a.type == LAPLACE_TYPE_Q6_K && a.M == 1 && !long_rows)) ? 20 : (a.M <= 2 && !long_rows ? 24 : 16);
     const int warps = (resident && a.M > 1) ? cwarps / ((a.M + 1) / 2) : cwarps;      // ring groups
     KParams p{};
     p.x = a.x; p.w = a.w; p.y = a.y; p.expert_idx = a.expert_idx; p.err = c.d_err;
@@ -967,6 +1040,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
         p.peers = *a.peers;
     }
     p.K = a.K; p.N = a.N; p.n_seg = a.n_seg; p.per_seg_x = a.per_seg_x;
+    p.act_regs = act_regs ? 1 : 0;
     p.n_mats = a.n_mats;
     for (int i = 0, end = 0; i < a.n_mats; ++i) {
         end += a.mat_n[i];
@@ -1037,6 +1111,7 @@ int launch_gemv_stream(const GemvArgs& a, cudaStream_t st) {
         p.n_slots = 3;
         p.slot_bytes = (p.slice_bytes + slack + 15u) & ~15u;
     }
+    if (p.n_slices != 1 && p.act_regs) return fail(LAPLACE_ERR_STATE, "gemv: internal planning error (register-held activations need whole rows)");
     // spare room: a deeper ring
     while (p.n_slots < MAX_SLOTS && static_cast<size_t>(p.n_slots + 1) * p.slot_bytes <= per_warp) p.n_slots++;
     size_t smem = p.off_ring + static_cast<size_t>(warps) * p.n_slots * p.slot_bytes;
