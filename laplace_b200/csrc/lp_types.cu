@@ -9,7 +9,7 @@
 //   embed_rows_kernel        rows tokens[m] of the embedding table, times the model's embedding scale
 //   gemv_f32act_kernel       fp32 activations against on-the-fly dequantized rows: one warp per weight row; plain
 //                            rows stream at 5 TB/s and more (an F16 LM head of 32,000 rows: 48 us), K-quant rows at
-//                            0.5-0.8 TB/s (bound by the per-value arithmetic) - these types carry embeddings, LM
+//                            0.7-1.2 TB/s (bound by instruction issue) - these types carry embeddings, LM
 //                            heads and the odd tensor of a mixed-precision file, not the bulk of the weights
 //   softcap_kernel           logits = tanh(logits / cap) * cap (src/model.cpp:399-406)
 #include <type_traits>
@@ -213,15 +213,20 @@ __global__ void __launch_bounds__(256) embed_rows_kernel(const uint8_t* __restri
 // ---- K-quant blocks read from shared memory -------------------------------------------------------------------
 // The fp32-activation GEMV stages each weight block at a 16-byte aligned shared address, so that a lane fetches
 // the 16 quants of its group (and their high bits) with one 16-byte read each instead of 16 single-byte loads from
-// global memory (which cost one L1 lookup per byte and held these types at 0.4-0.5 TB/s). Same expressions and
-// roundings as decode16 above.
+// global memory (which cost one L1 lookup per byte and held these types at 0.4-0.5 TB/s).
 __device__ __forceinline__ uint4 lds_u4(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ uint32_t byte_of(const uint4& q, int l) {          // l is a compile-time constant after unrolling
     const uint32_t w = l < 4 ? q.x : l < 8 ? q.y : l < 12 ? q.z : q.w;
     return (w >> (8 * (l & 3))) & 0xFFu;
 }
+// The 16 quants of group g as floats (unscaled integers) plus the two factors of the group:
+//   value_l = ds * q_l - mm        so        sum_l x_l * value_l = ds * (sum_l x_l q_l) - mm * (sum_l x_l).
+// Four quants are cut out of a 32-bit word at a time (byte-parallel shifts and masks); the per-value work is one
+// integer-to-float conversion and one FMA. Not the reference's rounding (it rounds ds * q - mm per value), which the
+// fp32-activation matmul is not held to: its bar is 1e-5 relative L2 against the reference's result.
 template <uint32_t TYPE>
-__device__ __forceinline__ void decode16_staged(const uint8_t* __restrict__ b, int g, float (&v)[16]) {
+__device__ __forceinline__ void quants16_staged(const uint8_t* __restrict__ b, int g, float (&qf)[16], float& ds, float& mm) {
+    uint32_t q4[4];
     if constexpr (TYPE == T_Q5_K) {
         const uint4 head = lds_u4(b);                    // d, dmin, scales[12]
         const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(head.x & 0xffffu)));
@@ -231,43 +236,47 @@ __device__ __forceinline__ void decode16_staged(const uint8_t* __restrict__ b, i
         int sc, mn;
         if (j < 4) { sc = sbyte(j) & 63; mn = sbyte(j + 4) & 63; }
         else { sc = (sbyte(j + 4) & 0xF) | ((sbyte(j - 4) >> 6) << 4); mn = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4); }
-        const float ds = __fmul_rn(d, static_cast<float>(sc)), mm = __fmul_rn(dmin, static_cast<float>(mn));
+        ds = __fmul_rn(d, static_cast<float>(sc));
+        mm = __fmul_rn(dmin, static_cast<float>(mn));
         const uint4 qs = lds_u4(b + 48 + 32 * jb + l0), qh = lds_u4(b + 16 + l0);
+        const uint32_t qsw[4] = {qs.x, qs.y, qs.z, qs.w}, qhw[4] = {qh.x, qh.y, qh.z, qh.w};
 #pragma unroll
-        for (int l = 0; l < 16; ++l) {
-            const uint32_t byte = byte_of(qs, l);
-            int q = sub ? (byte >> 4) : (byte & 0xF);
-            q += 16 * ((byte_of(qh, l) >> j) & 1);
-            v[l] = __fsub_rn(__fmul_rn(ds, static_cast<float>(q)), mm);
-        }
+        for (int w = 0; w < 4; ++w)
+            q4[w] = ((qsw[w] >> (4 * sub)) & 0x0f0f0f0fu) | (((qhw[w] >> j) & 0x01010101u) << 4);
     } else if constexpr (TYPE == T_Q2_K) {
         const uint32_t dd = *reinterpret_cast<const uint32_t*>(b + 80);
         const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(dd & 0xffffu)));
         const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(dd >> 16)));
         const int half = g >> 3, jj = g & 7, grp = jj >> 1, lo = jj & 1;
         const uint32_t scb = b[g];
-        const float ds = __fmul_rn(d, static_cast<float>(scb & 0xF)), mm = __fmul_rn(dmin, static_cast<float>(scb >> 4));
+        ds = __fmul_rn(d, static_cast<float>(scb & 0xF));
+        mm = __fmul_rn(dmin, static_cast<float>(scb >> 4));
         const uint4 qs = lds_u4(b + 16 + half * 32 + lo * 16);
+        const uint32_t qsw[4] = {qs.x, qs.y, qs.z, qs.w};
 #pragma unroll
-        for (int l = 0; l < 16; ++l) {
-            const int q = (byte_of(qs, l) >> (grp * 2)) & 3;
-            v[l] = __fsub_rn(__fmul_rn(ds, static_cast<float>(q)), mm);
-        }
-    } else {                                             // Q3_K
+        for (int w = 0; w < 4; ++w) q4[w] = (qsw[w] >> (grp * 2)) & 0x03030303u;
+    } else {                                             // Q3_K: value = ds * (low2 + 4 * hbit - 4)
         const uint4 tail = lds_u4(b + 96);               // scales[12], d
         const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(tail.w & 0xffffu)));
         auto sbyte = [&](int i) { return ((i < 4 ? tail.x : i < 8 ? tail.y : tail.z) >> (8 * (i & 3))) & 0xFFu; };
         const int lo4 = g < 8 ? (sbyte(g) & 0xF) : (sbyte(g - 8) >> 4);
         const int hi2 = (sbyte(8 + (g & 3)) >> (2 * (g >> 2))) & 3;
-        const float ds = __fmul_rn(d, static_cast<float>((lo4 | (hi2 << 4)) - 32));
+        ds = __fmul_rn(d, static_cast<float>((lo4 | (hi2 << 4)) - 32));
+        mm = __fmul_rn(ds, 4.0f);
         const int g32 = g >> 1, li0 = 16 * (g & 1);
         const uint4 qs = lds_u4(b + 32 + (g32 >> 2) * 32 + li0), hm = lds_u4(b + li0);
+        const uint32_t qsw[4] = {qs.x, qs.y, qs.z, qs.w}, hmw[4] = {hm.x, hm.y, hm.z, hm.w};
 #pragma unroll
-        for (int l = 0; l < 16; ++l) {
-            const int low2 = (byte_of(qs, l) >> ((g32 & 3) * 2)) & 3;
-            const int hbit = (byte_of(hm, l) >> g32) & 1;
-            v[l] = __fmul_rn(ds, static_cast<float>(low2 - 4 + 4 * hbit));
-        }
+        for (int w = 0; w < 4; ++w)
+            q4[w] = ((qsw[w] >> ((g32 & 3) * 2)) & 0x03030303u) | (((hmw[w] >> g32) & 0x01010101u) << 2);
+    }
+    // byte -> float without the conversion unit: 0x4B0000bb is the float 2^23 + bb
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        qf[4 * w]     = __uint_as_float(__byte_perm(q4[w], 0x4B000000u, 0x7440)) - 8388608.0f;
+        qf[4 * w + 1] = __uint_as_float(__byte_perm(q4[w], 0x4B000000u, 0x7441)) - 8388608.0f;
+        qf[4 * w + 2] = __uint_as_float(__byte_perm(q4[w], 0x4B000000u, 0x7442)) - 8388608.0f;
+        qf[4 * w + 3] = __uint_as_float(__byte_perm(q4[w], 0x4B000000u, 0x7443)) - 8388608.0f;
     }
 }
 
@@ -308,6 +317,22 @@ __global__ void __launch_bounds__(256) gemv_f32act_kernel(const float* __restric
             reinterpret_cast<float4*>(xs)[m * per_row + x_piece(f)] = __ldg(reinterpret_cast<const float4*>(x) + i);
         }
         __syncthreads();
+        if constexpr (S::on) {
+            // sum of x over every group of 16 values, once per CTA (the staged K-quant walk needs it per group and row)
+            float* xsum = xs + static_cast<size_t>(M) * K;
+            for (int i = threadIdx.x; i < M * groups; i += blockDim.x) {
+                const int m = i / groups, gi = i - m * groups;
+                const float4* base = reinterpret_cast<const float4*>(xs) + m * per_row;
+                float t = 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float4 v = base[x_piece(4 * gi + k)];
+                    t += (v.x + v.y) + (v.z + v.w);
+                }
+                xsum[i] = t;
+            }
+            __syncthreads();
+        }
     }
     const float* xa = x_in_smem ? xs : x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -416,18 +441,20 @@ __global__ void __launch_bounds__(256) gemv_f32act_kernel(const float* __restric
                     for (int d = 0; d < DEPTH; ++d) {
                         const int gi = 32 * (s0 + d) + lane;
                         if (gi < groups) {
-                            float v[16];
-                            decode16_staged<TYPE>(st + d * 2 * S::pitch + (lane >> 4) * S::pitch, lane & 15, v);
+                            float qf[16], ds, mm;
+                            quants16_staged<TYPE>(st + d * 2 * S::pitch + (lane >> 4) * S::pitch, lane & 15, qf, ds, mm);
 #pragma unroll
                             for (int m = 0; m < M; ++m) {
-                                float sacc = 0.f;
+                                float sq = 0.f, sx = 0.f;                 // sum x q and sum x over the group
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     const float4 t = x4(m, gi, i);
-                                    sacc = fmaf(t.x, v[4 * i], sacc); sacc = fmaf(t.y, v[4 * i + 1], sacc);
-                                    sacc = fmaf(t.z, v[4 * i + 2], sacc); sacc = fmaf(t.w, v[4 * i + 3], sacc);
+                                    sq = fmaf(t.x, qf[4 * i], sq); sq = fmaf(t.y, qf[4 * i + 1], sq);
+                                    sq = fmaf(t.z, qf[4 * i + 2], sq); sq = fmaf(t.w, qf[4 * i + 3], sq);
+                                    if (!x_in_smem) sx += (t.x + t.y) + (t.z + t.w);
                                 }
-                                acc[m] += sacc;
+                                if (x_in_smem) sx = xs[static_cast<size_t>(M) * K + m * groups + gi];
+                                acc[m] = fmaf(ds, sq, fmaf(-mm, sx, acc[m]));
                             }
                         }
                     }
@@ -470,7 +497,7 @@ cudaError_t launch_f32act_typed(const float* x, const uint8_t* w, float* y, int 
     const int in_smem = xbytes <= 96 * 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_f32act_kernel<M, TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 104 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemv_f32act_kernel<M, TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -480,7 +507,7 @@ cudaError_t launch_f32act_typed(const float* x, const uint8_t* w, float* y, int 
     // rows at the grid's stride. A grid of 8 CTAs per SM where 6 fit ran a second, one-third-full wave.
     static size_t occ_for = ~size_t(0);
     static int occ = 1;
-    const size_t dyn = (in_smem ? xbytes : 0) + static_cast<size_t>(F32ACT_WARPS) * Stage<TYPE>::warp_bytes;
+    const size_t dyn = (in_smem ? xbytes + (Stage<TYPE>::on ? xbytes / 16 : 0) : 0) + static_cast<size_t>(F32ACT_WARPS) * Stage<TYPE>::warp_bytes;
     if (occ_for != dyn) {
         int n = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_f32act_kernel<M, TYPE>, 256, dyn);
