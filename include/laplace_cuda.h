@@ -95,7 +95,11 @@ void laplace_cuda_nsplit(int N, int rank, int world, int* row_begin, int* row_en
 /* ---- the three back-end entry points (host pointers) -------------------- */
 
 /* Replaces kernels::gemm_fn (src/kernels.h:97), implemented in the reference
- * by gemm_simd (src/matmul_simd.cpp:480-496): y[m*N+j] = dot(x[m], row j). */
+ * by gemm_simd (src/matmul_simd.cpp:480-496): y[m*N+j] = dot(x[m], row j).
+ * Q4_0, Q5_0, Q8_0, Q4_K and Q6_K are computed as that back-end computes them (activations quantized to Q8 per 32
+ * values, integer block sums, fp32 scales); the three MoE entry points below take the same five types. More than 8
+ * rows run on the tensor cores for Q4_0 / Q8_0 / Q4_K / Q6_K when K % 256 == 0, otherwise (and for Q5_0) in passes
+ * of 8 rows through the streaming kernel. */
 int laplace_cuda_gemm(const float* x, const uint8_t* w, uint32_t type,
                       float* y, int M, int K, int N);
 
