@@ -21,7 +21,9 @@ def test_rmsnorm_restatement_matches_the_reference_build():
 @pytest.mark.parametrize("t,M,K,Ns", [(GGMLType.Q4_K, 1, 4096, (4096, 1024, 1024)), (GGMLType.Q4_K, 1, 4096, (14336, 14336)),
                                       (GGMLType.Q6_K, 2, 1024, (96, 40)), (GGMLType.Q8_0, 5, 512, (33, 64, 8)),
                                       (GGMLType.Q4_0, 8, 256, (24,)), (GGMLType.Q4_K, 4, 2048, (200, 136)),
-                                      (GGMLType.Q6_K, 1, 14336, (64, 32))])
+                                      (GGMLType.Q6_K, 1, 14336, (64, 32)),
+                                      # one row of a 32-value-block type: activations held in registers
+                                      (GGMLType.Q8_0, 1, 1024, (40, 24)), (GGMLType.Q4_0, 1, 4096, (33,)), (GGMLType.Q5_0, 1, 2048, (96, 40, 8))])
 @pytest.mark.parametrize("norm", [False, True])
 def test_multi_matrix_gemv(oracle, t, M, K, Ns, norm):
     import torch
