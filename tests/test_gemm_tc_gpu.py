@@ -179,7 +179,10 @@ def test_peer_store_form_on_one_gpu(oracle):
     from laplace_b200 import device
     from laplace_b200.shard import PeerGather, RowShards
     L = device.lib()
-    for t, M, K, N in ((GGMLType.Q4_K, 200, 1024, 1160), (GGMLType.Q6_K, 40, 2048, 136), (GGMLType.Q4_K, 512, 4096, 1024)):
+    # the last four: one GPU's slice of the k/v, q/o, gate/up and down projections when eight GPUs share a Llama-3-8B layer
+    for t, M, K, N in ((GGMLType.Q4_K, 200, 1024, 1160), (GGMLType.Q6_K, 40, 2048, 136), (GGMLType.Q4_K, 512, 4096, 1024),
+                       (GGMLType.Q4_K, 512, 4096, 128), (GGMLType.Q4_K, 512, 4096, 512), (GGMLType.Q4_K, 512, 4096, 1792),
+                       (GGMLType.Q6_K, 512, 14336, 512)):
         w = synth.weights(t, K, N, seed=2300 + M, how="random")
         x = synth.normal_f32(2301 + M, (M, K))
         pg = PeerGather(L, RowShards(L, N, 0, 1), M)
