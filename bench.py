@@ -576,6 +576,7 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
     orc = oracle_lib.Oracle()
     L = device.lib()
     out, total_ms, total_ops = {}, 0.0, 0.0
+    kept = {}
     xs_host = {K: synth.normal_f32(2004 + K, (M, K)) for K in (4096, 14336)}
     xs = {K: torch.from_numpy(xs_host[K]).cuda() for K in (4096, 14336)}
     for name, t, K, N in projs:
@@ -639,10 +640,45 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
                      "parity": {"rel_l2": par["rel_l2"], "maxabs_rms": par["maxabs_rms"]}}
         total_ms += ms
         total_ops += ops
+        if world == 1:
+            kept[name] = w
         del w
         if pg is not None:
             pg.close()
     device.sync()
+    # One GPU: the same seven matmuls in the layer's call order, with the matrices that share an input in one call each
+    # (q + k + v and gate + up, src/arch_llama.cpp:475-499): four quantizer launches instead of seven.
+    shared_ms = None
+    if world == 1:
+        x4, x14 = xs[4096], xs[14336]
+
+        def layer():
+            device.gemm_multi(x4, [kept["q"], kept["k"], kept["v"]], 12, M, 4096, [4096, 1024, 1024])
+            device.gemm(x4, kept["o"], 12, M, 4096, 4096)
+            device.gemm_multi(x4, [kept["gate"], kept["up"]], 12, M, 4096, [14336, 14336])
+            device.gemm(x14, kept["down"], 14, M, 14336, 4096)
+
+        for _ in range(2):
+            layer()
+        torch.cuda.synchronize()
+        g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                for _ in range(5):
+                    layer()
+        torch.cuda.current_stream().wait_stream(st)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        shared_ms = e0.elapsed_time(e1) / 5
+        del g
+        kept.clear()
+        device.sync()
     peak_bf16 = 1628.3
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -659,6 +695,9 @@ def prefill_leg(device, synth, torch, rank=0, world=1, dist=None):
     return {"workload": "Llama-3-8B decoder layer, 7 projections, M=512 tokens (223.34 Gop)" +
                         ("" if world == 1 else f", N-split over {world} GPUs, every GEMM storing its [512, N/{world}] slice into all GPUs' buffers (peer stores) + one closing wait kernel"),
             "ms_per_layer": total_ms,
+            **({"ms_per_layer_shared_inputs": shared_ms,
+                "shared_inputs": "the same seven matmuls in call order with q + k + v and gate + up as one call each (one quantizer launch per input)"}
+               if shared_ms is not None else {}),
             "tops": total_ops / total_ms / 1e9, "q4k_only_tops": q4k_ops / q4k_ms / 1e9,
             "roofline": {"bound": "tensor", "achieved": layer_tops / world, "peak": peak_i8.value, "unit": "Top/s (per GPU)",
                          "frac": layer_tops / world / peak_i8.value,
